@@ -1,0 +1,22 @@
+from .model_config import (  # noqa: F401
+    AttentionSpec,
+    ConfigError,
+    GatedMLPSpec,
+    LayerRun,
+    LayerSpec,
+    ModelConfig,
+    PartSpec,
+    RMSNormSpec,
+    RotarySpec,
+    normalise_dtype,
+    read_config_json,
+)
+from .registry import (  # noqa: F401
+    ARCHITECTURES,
+    Architecture,
+    TensorNames,
+    architecture_of,
+    load_config,
+    parse_config,
+    register_architecture,
+)

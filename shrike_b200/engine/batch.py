@@ -1,0 +1,165 @@
+"""A step's batch: entries in, one packed block of int32 metadata out.
+
+An entry is (a request's cache, its next tokens, the position of the first, the
+places whose logits are wanted).  Portions of prompts and single tokens lie side
+by side in one flat token batch, as in Azimml/shrike's ModelRunner.run
+(shrike/engine/model_runner.py:195-229): token ids, positions start..start+n-1,
+slot = page * page_size + position % page_size (:211-214), context length
+start + n (:215).  Unlike the reference, which treats rows with one token and
+longer rows through different metadata (:217-221), every row here is described the
+same way (query start, context length, block-table row, state slot), and all of
+it travels to the device as ONE copy from pinned memory.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+
+@dataclass
+class StepEntry:
+    cache: object  # cache.RequestCache
+    tokens: list[int]
+    start: int
+    want: list[int] = field(default_factory=list)
+
+
+@dataclass
+class GroupView:
+    slot_mapping: torch.Tensor  # int32 [N]: where each new token's key/value goes
+    block_table: torch.Tensor  # int32 [S, max_blocks], -1 where no page is held
+    max_blocks: int
+
+
+@dataclass
+class StepContext:
+    num_tokens: int
+    num_seqs: int
+    num_rows: int
+    token_ids: torch.Tensor  # int32 [N]
+    positions: torch.Tensor  # int32 [N]
+    seq_of_token: torch.Tensor  # int32 [N]
+    q_start: torch.Tensor  # int32 [S + 1]
+    ctx_len: torch.Tensor  # int32 [S], new tokens included
+    state_slot: torch.Tensor  # int32 [S]
+    out_rows: torch.Tensor  # int32 [R]
+    groups: list[GroupView]
+    storage: object  # cache.storage.CacheStorage
+    max_q_len: int
+    max_ctx_len: int
+    q_lens: list[int]
+    starts: list[int]
+
+
+class BatchBuilder:
+    """Packs entries into pinned host memory and copies them in one transfer."""
+
+    def __init__(self, page_size: int, num_groups: int, device, storage):
+        self.page_size = page_size
+        self.num_groups = num_groups
+        self.device = torch.device(device)
+        self.storage = storage
+        self._host: list[torch.Tensor] = []
+        self._events: list = []
+        self._turn = 0
+        self._dev = None
+
+    def _staging(self, count: int):
+        pinned = self.device.type == "cuda"
+        if not self._host or self._host[0].numel() < count:
+            capacity = max(4096, 2 * count)
+            self._host = [torch.empty(capacity, dtype=torch.int32, pin_memory=pinned) for _ in range(2)]
+            self._events = [None, None]
+            self._dev = torch.empty(capacity, dtype=torch.int32, device=self.device)
+        self._turn ^= 1
+        event = self._events[self._turn]
+        if event is not None:
+            event.synchronize()
+        return self._host[self._turn]
+
+    def build(self, entries: list[StepEntry]) -> StepContext:
+        page = self.page_size
+        q_lens = [len(e.tokens) for e in entries]
+        if not entries or min(q_lens) < 1:
+            raise ValueError("a step needs entries, each with at least one token")
+        n, s = sum(q_lens), len(entries)
+        r = sum(len(e.want) for e in entries)
+        starts = [e.start for e in entries]
+        ctx_lens = [st + q for st, q in zip(starts, q_lens)]
+        max_blocks = [1] * self.num_groups
+        for e, ctx in zip(entries, ctx_lens):
+            need = -(-ctx // page)
+            for g, table in enumerate(e.cache.tables):
+                if table.length < need:
+                    raise ValueError(
+                        f"entry holds {table.length} pages in group {g} but its context of {ctx} needs {need}"
+                    )
+                max_blocks[g] = max(max_blocks[g], need)
+
+        sizes = [n, n, n, s + 1, s, s, r]
+        for g in range(self.num_groups):
+            sizes += [n, s * max_blocks[g]]
+        offsets = np.concatenate([[0], np.cumsum(sizes)])
+        total = int(offsets[-1])
+        host = self._staging(total)
+        flat = host.numpy()
+        parts = [flat[offsets[i]: offsets[i + 1]] for i in range(len(sizes))]
+        ids, pos, seq_of, q_start, ctx_arr, slot_arr, out_rows = parts[:7]
+
+        cursor = 0
+        row = 0
+        q_start[0] = 0
+        for index, e in enumerate(entries):
+            q = q_lens[index]
+            ids[cursor: cursor + q] = e.tokens
+            pos[cursor: cursor + q] = np.arange(e.start, e.start + q, dtype=np.int32)
+            seq_of[cursor: cursor + q] = index
+            q_start[index + 1] = cursor + q
+            ctx_arr[index] = ctx_lens[index]
+            slot_arr[index] = e.cache.slot
+            for w in e.want:
+                if not 0 <= w < q:
+                    raise ValueError(f"wanted place {w} is outside the entry's {q} tokens")
+                out_rows[row] = cursor + w
+                row += 1
+            cursor += q
+
+        for g in range(self.num_groups):
+            slots = parts[7 + 2 * g]
+            table_flat = parts[8 + 2 * g]
+            table_flat[:] = -1
+            table2d = table_flat.reshape(s, max_blocks[g])
+            cursor = 0
+            for index, e in enumerate(entries):
+                q = q_lens[index]
+                pages = e.cache.tables[g].view()
+                held = min(len(pages), max_blocks[g])
+                table2d[index, :held] = pages[:held]
+                p = pos[cursor: cursor + q]
+                page_of = pages[p // page]
+                if (page_of < 0).any():
+                    raise ValueError(f"entry {index} writes into a page of group {g} it no longer holds")
+                slots[cursor: cursor + q] = page_of * page + p % page
+                cursor += q
+
+        dev = self._dev[:total]
+        dev.copy_(host[:total], non_blocking=True)
+        if self.device.type == "cuda":
+            event = torch.cuda.Event()
+            event.record()
+            self._events[self._turn] = event
+        views = [dev[int(offsets[i]): int(offsets[i + 1])] for i in range(len(sizes))]
+        groups = [
+            GroupView(views[7 + 2 * g], views[8 + 2 * g].view(s, max_blocks[g]), max_blocks[g])
+            for g in range(self.num_groups)
+        ]
+        return StepContext(
+            num_tokens=n, num_seqs=s, num_rows=r,
+            token_ids=views[0], positions=views[1], seq_of_token=views[2], q_start=views[3],
+            ctx_len=views[4], state_slot=views[5], out_rows=views[6], groups=groups,
+            storage=self.storage, max_q_len=max(q_lens), max_ctx_len=max(ctx_lens),
+            q_lens=q_lens, starts=starts,
+        )

@@ -1,0 +1,125 @@
+"""The model as data: parts built from the configuration, run in the listed order.
+
+Embedding, the layer runs, the final norm on the wanted rows only and the LM head
+(shrike/models/qwen.py:160-164,181-192).  Which class serves a part comes from the
+spec's `kind` through the part registries; which layer runs when, and on which
+cache, comes from `config.order`.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..config.model_config import ModelConfig
+from ..parts.base import part_class
+from ..weights.expected import LAYER_ROLES, tensor_names
+
+
+class Runtime:
+    """What parts share on the device: dtype, device and named scratch buffers.
+
+    A named buffer keeps its address while its capacity suffices, so captured
+    launch sequences stay valid; the same name is reused by every layer."""
+
+    def __init__(self, device, act_dtype: torch.dtype):
+        self.device = torch.device(device)
+        self.act_dtype = act_dtype
+        self._buffers: dict[str, torch.Tensor] = {}
+
+    def buffer(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        count = 1
+        for extent in shape:
+            count *= extent
+        held = self._buffers.get(name)
+        if held is None or held.dtype != dtype or held.numel() < count:
+            capacity = count if held is None or held.dtype != dtype else max(count, 2 * held.numel())
+            held = torch.empty(max(capacity, 1), dtype=dtype, device=self.device)
+            self._buffers[name] = held
+        return held[:count].view(shape)
+
+    def reserve(self, name: str, count: int, dtype: torch.dtype) -> None:
+        self.buffer(name, (count,), dtype)
+
+    def scratch_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self._buffers.values())
+
+
+def _take(tensors: dict, prefix: str, names) -> dict:
+    return {local: tensors[prefix + local] for local in names}
+
+
+class DecoderModel:
+    def __init__(self, config: ModelConfig, tensors: dict[str, torch.Tensor], ops, runtime: Runtime):
+        self.config = config
+        self.ops = ops
+        self.runtime = runtime
+        names = tensor_names(config)
+        self.embedding = tensors[names.embedding]
+        self.lm_head = tensors.get(names.lm_head)
+        if self.lm_head is None:
+            if not config.tie_word_embeddings:
+                raise KeyError(f"{names.lm_head} is absent and the configuration does not tie it to the embedding")
+            self.lm_head = self.embedding
+        self.blocks = []
+        for index, layer in enumerate(config.layers):
+            built = {}
+            for role, category in LAYER_ROLES:
+                spec = getattr(layer, role)
+                cls = part_class(category, spec.kind)
+                local = _take(tensors, names.layer_part(index, role), cls.parameters(spec))
+                built[role] = cls(spec, local, ops, runtime)
+            self.blocks.append(part_class("block", layer.block)(**built))
+        norm = config.final_norm
+        cls = part_class("norm", norm.kind)
+        self.final_norm = cls(norm, _take(tensors, names.final_norm_prefix, cls.parameters(norm)), ops, runtime)
+
+    def cache_needs(self):
+        """cache id -> KVNeed, and cache id -> StateNeed, over the run order."""
+        from ..parts.base import KVNeed, StateNeed
+
+        kv, state = {}, {}
+        for run in self.config.order:
+            spec = self.config.layers[run.layer].mixer
+            for need in part_class("mixer", spec.kind).cache_needs(spec):
+                table = kv if isinstance(need, KVNeed) else state
+                if run.cache in table and table[run.cache] != need:
+                    raise ValueError(f"cache {run.cache} is used by runs with different needs")
+                if isinstance(need, (KVNeed, StateNeed)):
+                    table[run.cache] = need
+        return kv, state
+
+    def weight_bytes(self) -> int:
+        seen, total = set(), 0
+
+        def visit(obj):
+            nonlocal total
+            for value in vars(obj).values():
+                if isinstance(value, torch.Tensor) and value.data_ptr() not in seen:
+                    seen.add(value.data_ptr())
+                    total += value.numel() * value.element_size()
+                elif hasattr(value, "__dict__") and not isinstance(value, (Runtime, type)) and value is not self.ops:
+                    if id(value) not in seen:
+                        seen.add(id(value))
+                        visit(value)
+
+        for block in self.blocks:
+            visit(block)
+        for tensor in (self.embedding, self.lm_head, self.final_norm.weight):
+            if tensor.data_ptr() not in seen:
+                seen.add(tensor.data_ptr())
+                total += tensor.numel() * tensor.element_size()
+        return total
+
+    def forward(self, ctx) -> torch.Tensor:
+        """float32 logits [R, vocab] at `ctx.out_rows`."""
+        rt, ops = self.runtime, self.ops
+        resid = rt.buffer("resid", (ctx.num_tokens, self.config.hidden_size), torch.float32)
+        ops.embed(ctx.token_ids, self.embedding, resid)
+        delta = None
+        for run in self.config.order:
+            resid, delta = self.blocks[run.layer].forward(resid, delta, ctx, run)
+        logits = rt.buffer("logits", (ctx.num_rows, self.config.vocab_size), torch.float32)
+        if ctx.num_rows:
+            hidden = self.final_norm.gather_norm(resid, delta, ctx.out_rows)
+            ops.linear(hidden, self.lm_head, logits)
+        return logits
