@@ -1,0 +1,262 @@
+// Embedding, residual-add + RMSNorm, SiLU-mul, bias + rotary + key/value store.
+//
+// All statistics, angles and sums are float32; a result is rounded once, when it
+// is stored in the activation type.  Formulas: shrike/models/qwen.py:64-74 (norm),
+// :77-101 (rotary), :136 (SiLU product), shrike/engine/model_runner.py:69-70 (store).
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+template <typename T>
+__global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                             float* __restrict__ out, int width, int vocab) {
+  const int row = blockIdx.x;
+  int id = ids[row];
+  const bool valid = id >= 0 && id < vocab;
+  if (!valid) id = 0;
+  const T* src = table + static_cast<size_t>(id) * width;
+  float* dst = out + static_cast<size_t>(row) * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = valid ? to_float(src[i]) : 0.f;
+}
+
+SHRIKE_API int shrike_embed(const int* ids, const void* table, int table_dtype, float* out, int n,
+                            int width, int vocab, cudaStream_t stream) {
+  if (n <= 0) return SHRIKE_OK;
+  if (width <= 0 || vocab <= 0) return SHRIKE_BAD_ARGUMENT;
+  const int threads = width >= 1024 ? 256 : 128;
+  if (table_dtype == SHRIKE_F32)
+    embed_kernel<float><<<n, threads, 0, stream>>>(ids, static_cast<const float*>(table), out, width, vocab);
+  else if (table_dtype == SHRIKE_BF16)
+    embed_kernel<__nv_bfloat16><<<n, threads, 0, stream>>>(ids, static_cast<const __nv_bfloat16*>(table), out, width, vocab);
+  else
+    return SHRIKE_BAD_ARGUMENT;
+  return shrike_launch_status();
+}
+
+// ------------------------------------------------- residual add + RMSNorm
+// One block per output row.  GATHER: the row comes from `rows`, the residual is
+// not written back (used for the final norm on the wanted rows only).
+template <typename TD, typename TO, bool HAS_DELTA, bool GATHER>
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
+                                   const int* __restrict__ rows, const float* __restrict__ weight,
+                                   float eps, TO* __restrict__ out, int width) {
+  __shared__ float scratch[33];
+  const int out_row = blockIdx.x;
+  const int row = GATHER ? rows[out_row] : out_row;
+  float* x = resid + static_cast<size_t>(row) * width;
+  const TD* d = HAS_DELTA ? delta + static_cast<size_t>(row) * width : nullptr;
+  TO* y = out + static_cast<size_t>(out_row) * width;
+
+  float sum_sq = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float v = x[i];
+    if (HAS_DELTA) {
+      v = __fadd_rn(v, to_float(d[i]));
+      if (!GATHER) x[i] = v;
+    }
+    sum_sq = fmaf(v, v, sum_sq);
+  }
+  const float total = block_sum(sum_sq, scratch);
+  const float inv = 1.0f / sqrtf(total / static_cast<float>(width) + eps);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float v = x[i];
+    if (HAS_DELTA && GATHER) v = __fadd_rn(v, to_float(d[i]));
+    y[i] = from_float<TO>(__fmul_rn(__fmul_rn(v, inv), weight[i]));
+  }
+}
+
+template <typename TD, typename TO, bool HAS_DELTA>
+static void launch_add_rmsnorm(float* resid, const void* delta, const int* rows, const float* weight,
+                               float eps, void* out, int n, int width, cudaStream_t stream) {
+  const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+  if (rows)
+    add_rmsnorm_kernel<TD, TO, HAS_DELTA, true><<<n, threads, 0, stream>>>(
+        resid, static_cast<const TD*>(delta), rows, weight, eps, static_cast<TO*>(out), width);
+  else
+    add_rmsnorm_kernel<TD, TO, HAS_DELTA, false><<<n, threads, 0, stream>>>(
+        resid, static_cast<const TD*>(delta), rows, weight, eps, static_cast<TO*>(out), width);
+}
+
+// resid [*, width] float32 (updated in place unless rows != null); delta may be null.
+SHRIKE_API int shrike_add_rmsnorm(float* resid, const void* delta, int delta_dtype, const int* rows,
+                                  const float* weight, float eps, void* out, int out_dtype, int n,
+                                  int width, cudaStream_t stream) {
+  if (n <= 0) return SHRIKE_OK;
+  if (width <= 0) return SHRIKE_BAD_ARGUMENT;
+  const bool has_delta = delta != nullptr;
+  if (has_delta && delta_dtype != SHRIKE_F32 && delta_dtype != SHRIKE_BF16) return SHRIKE_BAD_ARGUMENT;
+#define SHRIKE_NORM_CASE(TD, TO, HD) \
+  launch_add_rmsnorm<TD, TO, HD>(resid, delta, rows, weight, eps, out, n, width, stream)
+  if (out_dtype == SHRIKE_F32) {
+    if (!has_delta) SHRIKE_NORM_CASE(float, float, false);
+    else if (delta_dtype == SHRIKE_F32) SHRIKE_NORM_CASE(float, float, true);
+    else SHRIKE_NORM_CASE(__nv_bfloat16, float, true);
+  } else if (out_dtype == SHRIKE_BF16) {
+    if (!has_delta) SHRIKE_NORM_CASE(float, __nv_bfloat16, false);
+    else if (delta_dtype == SHRIKE_F32) SHRIKE_NORM_CASE(float, __nv_bfloat16, true);
+    else SHRIKE_NORM_CASE(__nv_bfloat16, __nv_bfloat16, true);
+  } else {
+    return SHRIKE_BAD_ARGUMENT;
+  }
+#undef SHRIKE_NORM_CASE
+  return shrike_launch_status();
+}
+
+// ------------------------------------------------------------- SiLU * up
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t row = i / inter;
+    const int col = static_cast<int>(i - row * inter);
+    const float g = to_float(gate_up[row * 2 * inter + col]);
+    const float u = to_float(gate_up[row * 2 * inter + inter + col]);
+    const float silu = g / (1.0f + expf(-g));
+    out[i] = from_float<T>(__fmul_rn(silu, u));
+  }
+}
+
+SHRIKE_API int shrike_silu_mul(const void* gate_up, void* out, int dtype, int n, int inter, cudaStream_t stream) {
+  if (n <= 0) return SHRIKE_OK;
+  if (inter <= 0) return SHRIKE_BAD_ARGUMENT;
+  const size_t total = static_cast<size_t>(n) * inter;
+  const int threads = 256;
+  const int blocks = static_cast<int>(min(static_cast<size_t>(148 * 16), (total + threads - 1) / threads));
+  if (dtype == SHRIKE_F32)
+    silu_mul_kernel<float><<<blocks, threads, 0, stream>>>(static_cast<const float*>(gate_up), static_cast<float*>(out), inter, total);
+  else if (dtype == SHRIKE_BF16)
+    silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), inter, total);
+  else
+    return SHRIKE_BAD_ARGUMENT;
+  return shrike_launch_status();
+}
+
+// --------------------------------------- bias + rotary + key/value store
+// One block per token.  qkv is the float32 result of the fused projection,
+// [n, (H + 2 Hkv) * D]: q heads, then k heads, then v heads.  The angle of pair j
+// is float(position) * inv_freq[j]; pair j rotates elements j and j + D/2.
+// Rotated q goes to q_out; rotated k and plain v go to the cache at slots[token]
+// (when caches are given) and to k_out / v_out (when given).
+template <typename T>
+__global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const float* __restrict__ bias,
+                                     const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                     T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                     const int* __restrict__ slots, T* __restrict__ k_out, T* __restrict__ v_out,
+                                     int num_heads, int num_kv_heads, int head_dim, long long num_slots) {
+  extern __shared__ float trig[];  // cos[half], sin[half]
+  const int token = blockIdx.x;
+  const int half = head_dim / 2;
+  const int q_width = num_heads * head_dim, kv_width = num_kv_heads * head_dim;
+  const float* row = qkv + static_cast<size_t>(token) * (q_width + 2 * kv_width);
+  const bool rotate = inv_freq != nullptr;
+  if (rotate) {
+    const float pos = static_cast<float>(positions[token]);
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+      float s, c;
+      sincosf(__fmul_rn(pos, inv_freq[j]), &s, &c);
+      trig[j] = c;
+      trig[half + j] = s;
+    }
+  }
+  __syncthreads();
+  long long slot = -1;
+  if (k_cache != nullptr) {
+    slot = slots[token];
+    if (slot < 0 || slot >= num_slots) slot = -1;  // never store outside the pool
+  }
+  // q and k heads: one thread per rotation pair
+  const int rot_pairs = (num_heads + num_kv_heads) * half;
+  for (int idx = threadIdx.x; idx < rot_pairs; idx += blockDim.x) {
+    const int head = idx / half, j = idx - head * half;
+    const int lo = head * head_dim + j, hi = lo + half;  // column within [q | k]
+    float a = row[lo], b = row[hi];
+    if (bias != nullptr) {
+      a = __fadd_rn(a, bias[lo]);
+      b = __fadd_rn(b, bias[hi]);
+    }
+    float ra = a, rb = b;
+    if (rotate) {
+      const float c = trig[j], s = trig[half + j];
+      ra = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
+      rb = __fadd_rn(__fmul_rn(b, c), __fmul_rn(a, s));
+    }
+    if (head < num_heads) {
+      T* dst = q_out + static_cast<size_t>(token) * q_width;
+      dst[lo] = from_float<T>(ra);
+      dst[hi] = from_float<T>(rb);
+    } else {
+      const int klo = lo - q_width, khi = hi - q_width;
+      if (slot >= 0) {
+        T* dst = k_cache + static_cast<size_t>(slot) * kv_width;
+        dst[klo] = from_float<T>(ra);
+        dst[khi] = from_float<T>(rb);
+      }
+      if (k_out != nullptr) {
+        T* dst = k_out + static_cast<size_t>(token) * kv_width;
+        dst[klo] = from_float<T>(ra);
+        dst[khi] = from_float<T>(rb);
+      }
+    }
+  }
+  // v heads: bias and store
+  for (int idx = threadIdx.x; idx < kv_width; idx += blockDim.x) {
+    const int col = q_width + kv_width + idx;
+    float v = row[col];
+    if (bias != nullptr) v = __fadd_rn(v, bias[col]);
+    if (slot >= 0) v_cache[static_cast<size_t>(slot) * kv_width + idx] = from_float<T>(v);
+    if (v_out != nullptr) v_out[static_cast<size_t>(token) * kv_width + idx] = from_float<T>(v);
+  }
+}
+
+SHRIKE_API int shrike_rope_kv_write(const float* qkv, const float* bias, const int* positions,
+                                    const float* inv_freq, void* q_out, void* k_cache, void* v_cache,
+                                    const int* slots, void* k_out, void* v_out, int dtype, int n,
+                                    int num_heads, int num_kv_heads, int head_dim, long long num_slots,
+                                    cudaStream_t stream) {
+  if (n <= 0) return SHRIKE_OK;
+  if (head_dim <= 0 || head_dim % 2 || num_heads <= 0 || num_kv_heads <= 0) return SHRIKE_BAD_ARGUMENT;
+  if ((k_cache == nullptr) != (v_cache == nullptr)) return SHRIKE_BAD_ARGUMENT;
+  if ((k_out == nullptr) != (v_out == nullptr)) return SHRIKE_BAD_ARGUMENT;
+  const int threads = 256;
+  const size_t smem = sizeof(float) * head_dim;
+#define SHRIKE_ROPE_CASE(T)                                                                         \
+  rope_kv_write_kernel<T><<<n, threads, smem, stream>>>(                                            \
+      qkv, bias, positions, inv_freq, static_cast<T*>(q_out), static_cast<T*>(k_cache),             \
+      static_cast<T*>(v_cache), slots, static_cast<T*>(k_out), static_cast<T*>(v_out), num_heads,   \
+      num_kv_heads, head_dim, num_slots)
+  if (dtype == SHRIKE_F32) SHRIKE_ROPE_CASE(float);
+  else if (dtype == SHRIKE_BF16) SHRIKE_ROPE_CASE(__nv_bfloat16);
+  else return SHRIKE_BAD_ARGUMENT;
+#undef SHRIKE_ROPE_CASE
+  return shrike_launch_status();
+}
+
+// ---------------------------------------------------- key/value store only
+template <typename T>
+__global__ void kv_write_kernel(const T* __restrict__ k_new, const T* __restrict__ v_new,
+                                T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                const int* __restrict__ slots, int kv_width, long long num_slots) {
+  const int token = blockIdx.x;
+  const long long slot = slots[token];
+  if (slot < 0 || slot >= num_slots) return;
+  for (int i = threadIdx.x; i < kv_width; i += blockDim.x) {
+    k_cache[static_cast<size_t>(slot) * kv_width + i] = k_new[static_cast<size_t>(token) * kv_width + i];
+    v_cache[static_cast<size_t>(slot) * kv_width + i] = v_new[static_cast<size_t>(token) * kv_width + i];
+  }
+}
+
+SHRIKE_API int shrike_kv_write(const void* k_new, const void* v_new, void* k_cache, void* v_cache,
+                               const int* slots, int dtype, int n, int kv_width, long long num_slots,
+                               cudaStream_t stream) {
+  if (n <= 0) return SHRIKE_OK;
+  if (kv_width <= 0) return SHRIKE_BAD_ARGUMENT;
+  if (dtype == SHRIKE_F32)
+    kv_write_kernel<float><<<n, 128, 0, stream>>>(static_cast<const float*>(k_new), static_cast<const float*>(v_new),
+                                                  static_cast<float*>(k_cache), static_cast<float*>(v_cache), slots, kv_width, num_slots);
+  else if (dtype == SHRIKE_BF16)
+    kv_write_kernel<__nv_bfloat16><<<n, 128, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(k_new), static_cast<const __nv_bfloat16*>(v_new),
+        static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), slots, kv_width, num_slots);
+  else
+    return SHRIKE_BAD_ARGUMENT;
+  return shrike_launch_status();
+}

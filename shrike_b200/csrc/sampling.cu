@@ -1,0 +1,138 @@
+// Sampling: one block per row of float32 logits.
+//
+// temperature == 0: the largest logit, lowest index on ties
+//   (shrike/engine/sampler.py:15-17).
+// otherwise: p = softmax(logits / temperature) in float32 (sampler.py:21-22);
+//   with top_p < 1 a token is kept while the probability mass strictly above it is
+//   below top_p (sampler.py:24-28: the most probable token is always kept); one
+//   token is then drawn from the kept ones in proportion to p.  The draw is the
+//   Gumbel-max form of a categorical sample, token = argmax(logit / T + g_i), with
+//   g_i = -log(-log(u_i)) and u_i a hash of (seed, i): the same seed gives the same
+//   token whatever else is in the batch (the reference's torch.multinomial on the
+//   global generator, sampler.py:29, does not have that property).
+#include "common.cuh"
+
+constexpr int SAMPLE_THREADS = 1024;
+
+__device__ __forceinline__ unsigned long long mix64(unsigned long long x) {
+  x ^= x >> 33;
+  x *= 0xFF51AFD7ED558CCDull;
+  x ^= x >> 33;
+  x *= 0xC4CEB9FE1A85EC53ull;
+  x ^= x >> 33;
+  return x;
+}
+__device__ __forceinline__ float gumbel(unsigned long long seed, int index) {
+  const unsigned long long word = mix64(seed + static_cast<unsigned long long>(index) * 0x9E3779B97F4A7C15ull);
+  const float u = (static_cast<float>(word >> 40) + 0.5f) * (1.0f / 16777216.0f);
+  return -logf(-logf(u));
+}
+
+struct Best {
+  float value;
+  int index;
+};
+__device__ __forceinline__ Best better(Best a, Best b) {
+  if (b.value > a.value || (b.value == a.value && b.index < a.index)) return b;
+  return a;
+}
+__device__ Best block_best(Best mine, Best* scratch /* 33 entries */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) {
+    Best other;
+    other.value = __shfl_xor_sync(0xffffffffu, mine.value, offset);
+    other.index = __shfl_xor_sync(0xffffffffu, mine.index, offset);
+    mine = better(mine, other);
+  }
+  __syncthreads();
+  if (lane == 0) scratch[warp] = mine;
+  __syncthreads();
+  if (warp == 0) {
+    const int warps = (blockDim.x + 31) >> 5;
+    Best w = lane < warps ? scratch[lane] : Best{-INFINITY, 0x7fffffff};
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+      Best other;
+      other.value = __shfl_xor_sync(0xffffffffu, w.value, offset);
+      other.index = __shfl_xor_sync(0xffffffffu, w.index, offset);
+      w = better(w, other);
+    }
+    if (lane == 0) scratch[32] = w;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+              const float* __restrict__ top_p, const long long* __restrict__ seeds, int* __restrict__ out,
+              int vocab) {
+  __shared__ float scratch[33];
+  __shared__ Best best_scratch[33];
+  const int row = blockIdx.x;
+  const float* x = logits + static_cast<size_t>(row) * vocab;
+  const float temp = temperature[row];
+
+  if (temp == 0.f) {
+    Best mine{-INFINITY, 0x7fffffff};
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) mine = better(mine, Best{x[i], i});
+    const Best top = block_best(mine, best_scratch);
+    if (threadIdx.x == 0) out[row] = top.index;
+    return;
+  }
+
+  const float inv_temp = 1.0f / temp;
+  float local_max = -INFINITY;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) local_max = fmaxf(local_max, x[i]);
+  const float row_max = block_max(local_max, scratch);
+  float threshold_bits_as_float = -1.f;  // keep p > threshold; -1 keeps everything
+  const float nucleus = top_p[row];
+  if (nucleus < 1.0f) {
+    float local_sum = 0.f;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) local_sum += expf((x[i] - row_max) * inv_temp);
+    const float total = block_sum(local_sum, scratch);
+    const float inv_total = 1.0f / total;
+    // Bisection on the bit pattern of a positive float: mass_above(lo) >= top_p and
+    // mass_above(hi) < top_p hold throughout; at the end no probability lies
+    // strictly between lo and hi, and the kept set is {p > lo}.
+    unsigned lo = 0u, hi = __float_as_uint(1.0f);  // mass_above(0) = 1 >= top_p; mass_above(1) = 0
+    while (hi - lo > 1u) {
+      const unsigned mid = lo + (hi - lo) / 2u;
+      const float cut = __uint_as_float(mid);
+      float above = 0.f;
+      for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float p = expf((x[i] - row_max) * inv_temp) * inv_total;
+        if (p > cut) above += p;
+      }
+      above = block_sum(above, scratch);
+      if (above < nucleus) hi = mid;
+      else lo = mid;
+    }
+    threshold_bits_as_float = __uint_as_float(lo);
+    if (lo == 0u) threshold_bits_as_float = -1.f;
+    Best mine{-INFINITY, 0x7fffffff};
+    const unsigned long long seed = static_cast<unsigned long long>(seeds[row]);
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+      const float p = expf((x[i] - row_max) * inv_temp) * inv_total;
+      if (p > threshold_bits_as_float) mine = better(mine, Best{x[i] * inv_temp + gumbel(seed, i), i});
+    }
+    const Best top = block_best(mine, best_scratch);
+    if (threadIdx.x == 0) out[row] = top.index;
+    return;
+  }
+  Best mine{-INFINITY, 0x7fffffff};
+  const unsigned long long seed = static_cast<unsigned long long>(seeds[row]);
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x)
+    mine = better(mine, Best{x[i] * inv_temp + gumbel(seed, i), i});
+  const Best top = block_best(mine, best_scratch);
+  if (threadIdx.x == 0) out[row] = top.index;
+}
+
+SHRIKE_API int shrike_sample(const float* logits, const float* temperature, const float* top_p,
+                             const long long* seeds, int* out, int rows, int vocab, cudaStream_t stream) {
+  if (rows <= 0) return SHRIKE_OK;
+  if (vocab <= 0) return SHRIKE_BAD_ARGUMENT;
+  sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, temperature, top_p, seeds, out, vocab);
+  return shrike_launch_status();
+}

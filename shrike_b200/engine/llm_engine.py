@@ -1,0 +1,232 @@
+"""LLMEngine: scheduler + step function + sampler in one loop.
+
+The public surface is Azimml/shrike's (shrike/engine/engine.py:41-203): the
+constructor's `block_size`, `gpu_mem_util`, `max_tokens_per_step`, `max_running`;
+`add_request(prompt, sampling, chat=True) -> req_id`, `has_work`,
+`step() -> [StepOutput(req_id, token_id, finished, finish_reason)]`,
+`generate(prompts, sampling) -> [[token ids]]`, `metrics()`, and the attributes
+`requests`, `scheduler`, `block_manager`, `tokenizer`, `stats`.  Added: `num_blocks`
+(an explicit pool size), `dtype` ("bfloat16" or "float32"), `seed`.  Left out:
+prefix caching and speculation.  step() = schedule -> one batched forward -> sample
+-> append / finish (engine.py:109-164); the sampled token of a request whose step
+reached the end of its known tokens comes from that entry's last row
+(shrike/engine/model_runner.py:222-228).
+"""
+
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from pathlib import Path
+
+import numpy as np
+import torch
+
+from .. import models as _models  # noqa: F401  (registers the architectures)
+from ..config.registry import load_config
+from ..sampling.rng import step_seed
+from ..weights.loader import load_weights
+from .batch import StepEntry
+from .request import Request, SamplingParams
+from .runner import TORCH_DTYPES, ModelRunner
+from .scheduler import Scheduler
+
+
+@dataclass
+class StepOutput:
+    req_id: int
+    token_id: int
+    finished: bool
+    finish_reason: str | None
+
+
+@dataclass
+class EngineStats:
+    steps: int = 0
+    tokens_generated: int = 0
+    started_at: float = field(default_factory=time.perf_counter)
+
+
+def make_ops(dtype: str, device):
+    from ..ops.cuda_ops import CudaOps
+
+    return CudaOps(TORCH_DTYPES[dtype], device)
+
+
+def _load_tokenizer(model_dir):
+    folder = Path(model_dir)
+    if not any((folder / name).is_file() for name in ("tokenizer.json", "tokenizer_config.json", "vocab.json")):
+        return None
+    from transformers import AutoTokenizer  # tokenizer only; no model code
+
+    return AutoTokenizer.from_pretrained(str(folder))
+
+
+class LLMEngine:
+    def __init__(
+        self,
+        model_dir: str | None,
+        block_size: int = 16,
+        gpu_mem_util: float = 0.85,
+        max_tokens_per_step: int = 512,
+        max_running: int = 256,
+        num_blocks: int | None = None,
+        dtype: str | None = None,
+        seed: int = 0,
+        device: str = "cuda",
+        config=None,
+        tensors=None,
+        ops=None,
+    ) -> None:
+        """`model_dir` holds config.json and *.safetensors; or pass `config` and
+        `tensors` (name -> tensor on `device`) to serve weights made in memory."""
+        if config is None:
+            config = load_config(model_dir)
+        self.config = config
+        self.dtype = dtype or config.dtype
+        if self.dtype not in TORCH_DTYPES:
+            raise ValueError(f"dtype {self.dtype!r}: choose bfloat16 or float32")
+        self.device = torch.device(device)
+        self.ops = ops if ops is not None else make_ops(self.dtype, self.device)
+        if tensors is None:
+            tensors = load_weights(model_dir, config, TORCH_DTYPES[self.dtype], self.device)
+        self.tokenizer = _load_tokenizer(model_dir) if model_dir is not None else None
+        self.runner = ModelRunner(
+            config, tensors, self.ops, self.device, self.dtype, page_size=block_size,
+            num_pages=num_blocks, gpu_mem_util=gpu_mem_util, max_slots=max_running,
+        )
+        self.block_manager = self.runner.cache
+        self.scheduler = Scheduler(self.block_manager, max_tokens_per_step, max_running)
+        self.eos_ids = set(config.eos_token_ids)
+        self.requests: dict[int, Request] = {}
+        self.stats = EngineStats()
+        self.seed = seed
+        self._arrivals = 0
+        self._request_seed: dict[int, int] = {}
+
+    # ---- requests -------------------------------------------------------------
+    def _tokenize(self, prompt: str, chat: bool) -> list[int]:
+        if self.tokenizer is None:
+            raise ValueError(
+                "the model folder has no tokenizer files: pass token ids (a list of int) instead of text"
+            )
+        if chat:
+            encoded = self.tokenizer.apply_chat_template(
+                [{"role": "user", "content": prompt}], add_generation_prompt=True
+            )
+            return list(encoded["input_ids"] if isinstance(encoded, dict) else encoded)
+        return list(self.tokenizer(prompt).input_ids)
+
+    def add_request(self, prompt, sampling: SamplingParams, chat: bool = True) -> int:
+        token_ids = self._tokenize(prompt, chat) if isinstance(prompt, str) else [int(t) for t in prompt]
+        if not token_ids:
+            raise ValueError("empty prompt: a request must have at least one token")
+        vocab = self.config.vocab_size
+        if min(token_ids) < 0 or max(token_ids) >= vocab:
+            raise ValueError(f"token ids must lie in [0, {vocab}); got {min(token_ids)}..{max(token_ids)}")
+        total = len(token_ids) + sampling.max_new_tokens
+        if total > self.config.max_position_embeddings:
+            raise ValueError(
+                f"{len(token_ids)} prompt + {sampling.max_new_tokens} generated tokens exceed "
+                f"max_position_embeddings={self.config.max_position_embeddings}"
+            )
+        worst = self.block_manager.worst_case_pages(total)
+        if any(w > have for w, have in zip(worst, self.block_manager.num_pages)):
+            raise ValueError(
+                f"request needs up to {max(worst)} KV blocks ({len(token_ids)} prompt + "
+                f"{sampling.max_new_tokens} generated tokens, block_size={self.block_manager.page_size}) "
+                f"but the pool has only {min(self.block_manager.num_pages)}; it could never be scheduled: "
+                "shorten the prompt, lower max_new_tokens, or raise gpu_mem_util / num_blocks"
+            )
+        request = Request(token_ids=token_ids, sampling=sampling)
+        self.requests[request.req_id] = request
+        base = sampling.seed if sampling.seed is not None else step_seed(self.seed, self._arrivals)
+        self._request_seed[request.req_id] = base
+        self._arrivals += 1
+        self.scheduler.add(request)
+        return request.req_id
+
+    def abort(self, req_id: int) -> None:
+        request = self.requests.pop(req_id, None)
+        if request is not None:
+            self.scheduler.abort(request)
+            self._request_seed.pop(req_id, None)
+
+    @property
+    def has_work(self) -> bool:
+        return self.scheduler.has_work
+
+    # ---- the loop ---------------------------------------------------------------
+    @torch.inference_mode()
+    def step(self) -> list[StepOutput]:
+        batch = self.scheduler.schedule()
+        if not batch:
+            return []
+        entries, sampled = [], []
+        for request, num_new in batch:
+            start = request.num_computed_tokens
+            reaches_end = start + num_new >= request.num_tokens
+            entries.append(StepEntry(request.cache, request.token_ids[start: start + num_new], start,
+                                     [num_new - 1] if reaches_end else []))
+            if reaches_end:
+                sampled.append(request)
+        logits = self.runner.step(entries)
+        tokens = self._sample(logits, sampled) if sampled else []
+        self.scheduler.postprocess(batch)
+
+        outputs: list[StepOutput] = []
+        for request, token in zip(sampled, tokens):
+            request.token_ids.append(token)
+            self.stats.tokens_generated += 1
+            finished, reason = False, None
+            if token in self.eos_ids and not request.sampling.ignore_eos:
+                finished, reason = True, "stop"
+            elif request.num_generated >= request.sampling.max_new_tokens:
+                finished, reason = True, "length"
+            outputs.append(StepOutput(request.req_id, token, finished, reason))
+            if finished:
+                self.scheduler.finish(request, reason)
+                del self.requests[request.req_id]
+                self._request_seed.pop(request.req_id, None)
+        self.stats.steps += 1
+        return outputs
+
+    def _sample(self, logits: torch.Tensor, requests: list[Request]) -> list[int]:
+        rows = len(requests)
+        pinned = self.device.type == "cuda"
+        floats = torch.empty(2 * rows, dtype=torch.float32, pin_memory=pinned)
+        seeds = torch.empty(rows, dtype=torch.int64, pin_memory=pinned)
+        f, s = floats.numpy(), seeds.numpy()
+        for row, request in enumerate(requests):
+            f[row] = request.sampling.temperature
+            f[rows + row] = request.sampling.top_p
+            s[row] = step_seed(self._request_seed[request.req_id], request.num_tokens)
+        floats_dev = floats.to(self.device, non_blocking=True)
+        seeds_dev = seeds.to(self.device, non_blocking=True)
+        out = self.runner.runtime.buffer("sampled", (rows,), torch.int32)
+        self.ops.sample(logits, floats_dev[:rows], floats_dev[rows:], seeds_dev, out)
+        return out.tolist()
+
+    def generate(self, prompts, sampling, chat: bool = True) -> list[list[int]]:
+        """Offline batch API (engine.py:166-183): generated token ids per prompt."""
+        if isinstance(sampling, SamplingParams):
+            sampling = [sampling] * len(prompts)
+        id_map = {self.add_request(p, s, chat): i for i, (p, s) in enumerate(zip(prompts, sampling, strict=True))}
+        results: list[list[int]] = [[] for _ in prompts]
+        while self.has_work:
+            for out in self.step():
+                results[id_map[out.req_id]].append(out.token_id)
+        return results
+
+    def metrics(self) -> dict:
+        elapsed = time.perf_counter() - self.stats.started_at
+        return {
+            "steps": self.stats.steps,
+            "tokens_generated": self.stats.tokens_generated,
+            "avg_tokens_per_sec": round(self.stats.tokens_generated / max(elapsed, 1e-9), 1),
+            "running": len(self.scheduler.running),
+            "waiting": len(self.scheduler.waiting),
+            "kv_blocks_total": min(self.block_manager.num_pages),
+            "kv_blocks_free": min(self.block_manager.num_free),
+            "preemptions": self.scheduler.num_preemptions,
+        }

@@ -1,0 +1,208 @@
+"""The kernels, as one object the parts call.
+
+Every method launches hand-written sm_100a code from `csrc/` through the C symbol
+of its launcher, on torch's current stream, with raw device pointers.  There is no
+CPU path and no library attention or model code: without a CUDA device, or when a
+kernel cannot be built, construction fails.  Matrix products in bfloat16 go to
+cuBLAS through `torch.mm` (Azimml/shrike's own GEMMs are cuBLAS calls through
+nn.Linear, shrike/models/qwen.py:111-136); in float32 they run on this package's own
+FFMA kernel, so the 32-bit path never touches a reduced-precision matrix mode.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import build
+
+_DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+_c = ctypes
+_P, _I, _F, _LL = _c.c_void_p, _c.c_int, _c.c_float, _c.c_longlong
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _ptr(tensor):
+    return None if tensor is None else tensor.data_ptr()
+
+
+def _check(code: int, what: str):
+    if code != 0:
+        reason = "bad argument" if code == -1 else f"CUDA error {code}"
+        raise KernelError(f"{what}: {reason}")
+
+
+def _dense(tensor, dtype, what):
+    if tensor.device.type != "cuda":
+        raise KernelError(f"{what} must be on the GPU, is on {tensor.device}")
+    if tensor.dtype != dtype:
+        raise KernelError(f"{what} must be {dtype}, is {tensor.dtype}")
+    if not tensor.is_contiguous():
+        raise KernelError(f"{what} must be contiguous")
+
+
+class CudaOps:
+    def __init__(self, dtype: torch.dtype, device="cuda"):
+        if dtype not in _DTYPE_CODE:
+            raise KernelError(f"no kernels for {dtype}; bfloat16 and float32 are served")
+        if not torch.cuda.is_available():
+            raise KernelError("shrike_b200 needs a CUDA device (B200, sm_100a); there is no CPU path")
+        self.dtype = dtype
+        self.code = _DTYPE_CODE[dtype]
+        self.device = torch.device(device)
+        self.core = build.core_library()
+        self._declare_core()
+        self._attention = {}
+        self.launches = 0
+        if dtype == torch.float32:
+            torch.backends.cuda.matmul.allow_tf32 = False
+
+    # ---- declarations -------------------------------------------------------
+    def _declare_core(self):
+        lib = self.core
+        lib.shrike_embed.argtypes = [_P, _P, _I, _P, _I, _I, _I, _P]
+        lib.shrike_add_rmsnorm.argtypes = [_P, _P, _I, _P, _P, _F, _P, _I, _I, _I, _P]
+        lib.shrike_silu_mul.argtypes = [_P, _P, _I, _I, _I, _P]
+        lib.shrike_rope_kv_write.argtypes = [_P] * 10 + [_I] * 5 + [_LL, _P]
+        lib.shrike_kv_write.argtypes = [_P] * 5 + [_I, _I, _I, _LL, _P]
+        lib.shrike_gemm_fp32.argtypes = [_P, _P, _P, _P, _I, _I, _I, _P]
+        lib.shrike_sample.argtypes = [_P, _P, _P, _P, _P, _I, _I, _P]
+        for name in ("shrike_embed", "shrike_add_rmsnorm", "shrike_silu_mul", "shrike_rope_kv_write",
+                     "shrike_kv_write", "shrike_gemm_fp32", "shrike_sample"):
+            getattr(lib, name).restype = _I
+
+    def _attention_lib(self, head_dim: int):
+        lib = self._attention.get(head_dim)
+        if lib is None:
+            self.check_head_dim(head_dim)
+            lib = build.attention_library(head_dim)
+            lib.shrike_paged_attention_generic.argtypes = (
+                [_P, _P, _P, _P, _I, _P, _P, _P] + [_I] * 6 + [_F, _I, _P, _P]
+            )
+            lib.shrike_paged_attention_generic.restype = _I
+            self._attention[head_dim] = lib
+        return lib
+
+    @staticmethod
+    def _stream():
+        return torch.cuda.current_stream().cuda_stream
+
+    def check_head_dim(self, head_dim: int):
+        if head_dim % 16 or not 16 <= head_dim <= 256:
+            raise KernelError(
+                f"head size {head_dim} is not served: the attention kernels take multiples of 16 from 16 to 256"
+            )
+
+    # ---- kernels ------------------------------------------------------------
+    def embed(self, ids, table, out):
+        _dense(ids, torch.int32, "token ids")
+        _dense(out, torch.float32, "residual")
+        n, width = out.shape
+        self.launches += 1
+        _check(self.core.shrike_embed(_ptr(ids), _ptr(table), _DTYPE_CODE[table.dtype], _ptr(out), n, width,
+                                      table.shape[0], self._stream()), "embed")
+
+    def add_rmsnorm(self, resid, delta, weight, eps, out):
+        _dense(resid, torch.float32, "residual")
+        _dense(weight, torch.float32, "norm weight")
+        n, width = resid.shape
+        code = -1 if delta is None else _DTYPE_CODE[delta.dtype]
+        self.launches += 1
+        _check(self.core.shrike_add_rmsnorm(_ptr(resid), _ptr(delta), code, None, _ptr(weight), eps, _ptr(out),
+                                            _DTYPE_CODE[out.dtype], n, width, self._stream()), "add_rmsnorm")
+
+    def gather_add_rmsnorm(self, resid, delta, rows, weight, eps, out):
+        _dense(resid, torch.float32, "residual")
+        _dense(rows, torch.int32, "rows")
+        width = resid.shape[1]
+        code = -1 if delta is None else _DTYPE_CODE[delta.dtype]
+        self.launches += 1
+        _check(self.core.shrike_add_rmsnorm(_ptr(resid), _ptr(delta), code, _ptr(rows), _ptr(weight), eps,
+                                            _ptr(out), _DTYPE_CODE[out.dtype], rows.shape[0], width,
+                                            self._stream()), "gather_add_rmsnorm")
+
+    def linear(self, x, w, out, bias=None):
+        """out[N, O] = x[N, K] @ w[O, K]^T (+ bias); out may be float32 or the activation type."""
+        n, k = x.shape
+        o = w.shape[0]
+        if w.shape[1] != k or tuple(out.shape) != (n, o):
+            raise KernelError(f"linear: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+        self.launches += 1
+        if self.dtype == torch.float32:
+            _dense(x, torch.float32, "linear input")
+            _dense(w, torch.float32, "linear weight")
+            _dense(out, torch.float32, "linear output")
+            _check(self.core.shrike_gemm_fp32(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), n, o, k, self._stream()),
+                   "gemm_fp32")
+            return
+        _dense(x, torch.bfloat16, "linear input")
+        _dense(w, torch.bfloat16, "linear weight")
+        if out.dtype == torch.float32:
+            torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+        else:
+            torch.mm(x, w.t(), out=out)
+        if bias is not None:
+            out.add_(bias)
+            self.launches += 1
+
+    def rope_kv_write(self, qkv, bias, positions, inv_freq, q_out, keys, values, slots,
+                      num_heads, num_kv_heads, head_dim, k_out=None, v_out=None):
+        _dense(qkv, torch.float32, "qkv")
+        _dense(q_out, self.dtype, "q")
+        n = qkv.shape[0]
+        num_slots = 0
+        if keys is not None:
+            _dense(keys, self.dtype, "key cache")
+            _dense(values, self.dtype, "value cache")
+            num_slots = keys.shape[0] * keys.shape[1]
+        self.launches += 1
+        _check(self.core.shrike_rope_kv_write(
+            _ptr(qkv), _ptr(bias), _ptr(positions), _ptr(inv_freq), _ptr(q_out), _ptr(keys), _ptr(values),
+            _ptr(slots), _ptr(k_out), _ptr(v_out), self.code, n, num_heads, num_kv_heads, head_dim,
+            num_slots, self._stream()), "rope_kv_write")
+
+    def kv_write(self, k_new, v_new, keys, values, slots):
+        _dense(keys, self.dtype, "key cache")
+        n, kv_width = k_new.shape
+        self.launches += 1
+        _check(self.core.shrike_kv_write(_ptr(k_new), _ptr(v_new), _ptr(keys), _ptr(values), _ptr(slots),
+                                         self.code, n, kv_width, keys.shape[0] * keys.shape[1],
+                                         self._stream()), "kv_write")
+
+    def paged_attention(self, q, keys, values, block_table, q_start, ctx_len, seq_of_token,
+                        num_heads, num_kv_heads, head_dim, scale, window, out,
+                        max_q_len=0, max_ctx_len=0):
+        _dense(q, self.dtype, "q")
+        _dense(keys, self.dtype, "key cache")
+        _dense(values, self.dtype, "value cache")
+        _dense(block_table, torch.int32, "block table")
+        if keys.shape[2] != num_kv_heads or keys.shape[3] != head_dim:
+            raise KernelError(f"key cache {tuple(keys.shape)} does not fit {num_kv_heads} heads of {head_dim}")
+        lib = self._attention_lib(head_dim)
+        self.launches += 1
+        _check(lib.shrike_paged_attention_generic(
+            _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), block_table.shape[1], _ptr(q_start),
+            _ptr(ctx_len), _ptr(seq_of_token), self.code, q.shape[0], num_heads, num_kv_heads,
+            keys.shape[1], keys.shape[0], scale, window or 0, _ptr(out), self._stream()), "paged_attention")
+
+    def silu_mul(self, gate_up, out):
+        _dense(gate_up, self.dtype, "gate_up")
+        _dense(out, self.dtype, "activation")
+        n, inter = out.shape
+        self.launches += 1
+        _check(self.core.shrike_silu_mul(_ptr(gate_up), _ptr(out), self.code, n, inter, self._stream()), "silu_mul")
+
+    def sample(self, logits, temperature, top_p, seeds, out):
+        _dense(logits, torch.float32, "logits")
+        _dense(temperature, torch.float32, "temperature")
+        _dense(top_p, torch.float32, "top_p")
+        _dense(seeds, torch.int64, "seeds")
+        _dense(out, torch.int32, "sampled tokens")
+        rows, vocab = logits.shape
+        self.launches += 1
+        _check(self.core.shrike_sample(_ptr(logits), _ptr(temperature), _ptr(top_p), _ptr(seeds), _ptr(out),
+                                       rows, vocab, self._stream()), "sample")

@@ -1,0 +1,111 @@
+"""The engine loop and the step function's metadata, driven on the CPU through a
+stand-in for the kernels (tests/emulated_ops.py).  This checks host logic only:
+block tables, slots, positions, wanted rows, preemption and recompute."""
+
+import numpy as np
+import pytest
+import torch
+
+import shrike_b200.models  # noqa: F401
+from shrike_b200 import SamplingParams
+from shrike_b200.config import parse_config
+from shrike_b200.engine.batch import StepEntry
+from shrike_b200.engine.llm_engine import LLMEngine
+from shrike_b200.engine.runner import ModelRunner
+from shrike_b200.weights import random_tensors
+from tests.emulated_ops import EmulatedOps
+from tests.helpers import random_tokens
+from tests.plain import plain_model as pm
+from tests.tiny_configs import PAGE_SIZES, SEEDS, TINY, windows_of
+
+
+def engine_for(key, **kw):
+    config = parse_config(TINY[key])
+    weights = random_tensors(config, SEEDS[key])
+    options = dict(block_size=PAGE_SIZES[key], dtype="float32", device="cpu", config=config,
+                   tensors=dict(weights), ops=EmulatedOps())
+    options.update(kw)
+    return LLMEngine(None, **options), weights
+
+
+@pytest.mark.parametrize("key", ["A", "C"])
+def test_step_function_matches_plain_under_cutting(key):
+    raw = TINY[key]
+    config = parse_config(raw)
+    weights = random_tensors(config, SEEDS[key])
+    ids = random_tokens(raw["vocab_size"], 70, 5)
+    want = pm.forward(raw, weights, ids, windows=windows_of(raw)).numpy()
+    runner = ModelRunner(config, dict(weights), EmulatedOps(), "cpu", "float32", page_size=16, num_pages=6, max_slots=2)
+    cache, pos, rows = runner.cache.open(), 0, []
+    for n in [7, 2, 5, 3, 2, 15, 16, 17, 1, 1, 1]:
+        runner.cache.append(cache, pos, n)
+        rows.append(runner.step([StepEntry(cache, ids[pos:pos + n], pos, list(range(n)))]).clone())
+        pos += n
+        runner.cache.advance(cache, pos)
+    np.testing.assert_allclose(torch.cat(rows).numpy(), want, atol=2e-5)
+    runner.cache.free(cache)
+    assert runner.cache.whole()
+
+
+def test_generate_equals_plain_greedy_with_preemption():
+    engine, weights = engine_for("B", max_tokens_per_step=24, max_running=4, num_blocks=20)
+    prompts = [random_tokens(384, n, 40 + n) for n in (1, 9, 40, 64, 70)]
+    outs = engine.generate(prompts, SamplingParams(max_new_tokens=12, ignore_eos=True))
+    assert engine.scheduler.num_preemptions >= 1, "the pool was meant to be too small"
+    assert engine.block_manager.whole() and not engine.requests
+    for prompt, out in zip(prompts, outs):
+        want, margins = pm.greedy_continue(TINY["B"], weights, prompt, 12)
+        assert min(margins) > 1e-5
+        assert out == want
+    metrics = engine.metrics()
+    assert metrics["tokens_generated"] == 60 and metrics["kv_blocks_free"] == metrics["kv_blocks_total"] == 20
+
+
+def test_eos_stops_and_ignore_eos_does_not():
+    engine, weights = engine_for("A", num_blocks=16)
+    prompt = random_tokens(256, 9, 1)
+    free_run = engine.generate([prompt], SamplingParams(max_new_tokens=6, ignore_eos=True))[0]
+    engine.eos_ids = {free_run[2]}
+    first = free_run.index(free_run[2])
+    outs = []
+    engine.add_request(prompt, SamplingParams(max_new_tokens=6))
+    while engine.has_work:
+        outs += engine.step()
+    assert [o.token_id for o in outs] == free_run[: first + 1]
+    assert outs[-1].finished and outs[-1].finish_reason == "stop"
+    again = engine.generate([prompt], SamplingParams(max_new_tokens=6, ignore_eos=True))[0]
+    assert again == free_run and engine.block_manager.whole()
+
+
+def test_requests_that_can_never_run_are_refused():
+    engine, _ = engine_for("A", num_blocks=4)
+    with pytest.raises(ValueError, match="empty prompt"):
+        engine.add_request([], SamplingParams())
+    with pytest.raises(ValueError, match="could never be scheduled"):
+        engine.add_request([1] * 60, SamplingParams(max_new_tokens=10))
+    with pytest.raises(ValueError, match="max_position_embeddings"):
+        engine.add_request([1, 2], SamplingParams(max_new_tokens=10_000_000))
+    with pytest.raises(ValueError, match="token ids"):
+        engine.add_request([1, 256], SamplingParams())
+    with pytest.raises(ValueError, match="tokenizer"):
+        engine.add_request("hello", SamplingParams())
+    assert not engine.has_work
+
+
+def test_sampling_does_not_depend_on_the_batch():
+    prompts = [random_tokens(384, n, 70 + n) for n in (3, 11, 26)]
+    params = [SamplingParams(max_new_tokens=8, temperature=0.8, ignore_eos=True, seed=100 + i) for i in range(3)]
+    together, _ = engine_for("B", num_blocks=32)
+    batched = together.generate(prompts, params)
+    for prompt, param, want in zip(prompts, params, batched):
+        alone, _ = engine_for("B", num_blocks=32, max_tokens_per_step=5)
+        assert alone.generate([prompt], param)[0] == want
+
+
+def test_abort_frees_pages():
+    engine, _ = engine_for("A", num_blocks=16)
+    rid = engine.add_request(random_tokens(256, 20, 2), SamplingParams(max_new_tokens=50))
+    engine.step()
+    engine.step()
+    engine.abort(rid)
+    assert not engine.has_work and engine.block_manager.whole()
