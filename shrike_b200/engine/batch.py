@@ -52,6 +52,7 @@ class StepContext:
     max_ctx_len: int
     q_lens: list[int]
     starts: list[int]
+    slots: list[int]  # host copy of state_slot
 
 
 class BatchBuilder:
@@ -161,5 +162,5 @@ class BatchBuilder:
             token_ids=views[0], positions=views[1], seq_of_token=views[2], q_start=views[3],
             ctx_len=views[4], state_slot=views[5], out_rows=views[6], groups=groups,
             storage=self.storage, max_q_len=max(q_lens), max_ctx_len=max(ctx_lens),
-            q_lens=q_lens, starts=starts,
+            q_lens=q_lens, starts=starts, slots=[e.cache.slot for e in entries],
         )

@@ -141,7 +141,7 @@ def attention_library(head_dim: int) -> ctypes.CDLL:
                         {"SHRIKE_HEAD_DIM": head_dim})
 
 
-def build_all(head_dims=(16, 32, 48, 64, 128)) -> list[Path]:
+def build_all(head_dims=(16, 32, 48, 64, 128, 256)) -> list[Path]:
     """Everything the package can load, for the usual head sizes."""
     built = [compile_library("shrike_core", CORE_SOURCES)]
     for head_dim in head_dims:

@@ -58,8 +58,10 @@ class CudaOps:
         self._declare_core()
         self._attention = {}
         self.launches = 0
-        if dtype == torch.float32:
-            torch.backends.cuda.matmul.allow_tf32 = False
+        # library matrix products keep float32 accumulation end to end: no TF32 for float32
+        # inputs, no bfloat16 partial sums when a bfloat16 product is split along K
+        torch.backends.cuda.matmul.allow_tf32 = False
+        torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 
     # ---- declarations -------------------------------------------------------
     def _declare_core(self):

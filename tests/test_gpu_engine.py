@@ -1,0 +1,59 @@
+"""Generation through the Python entry point on the GPU."""
+
+import pytest
+import torch
+
+from shrike_b200 import SamplingParams
+from shrike_b200.engine.llm_engine import LLMEngine
+from tests.helpers import make_model_folder, random_tokens, read_weights
+from tests.plain import plain_model as pm
+from tests.tiny_configs import PAGE_SIZES, TINY, windows_of
+
+pytestmark = pytest.mark.gpu
+
+
+def plain_greedy(key, weights, prompt, count, bf16):
+    raw = TINY[key]
+    if bf16:
+        weights = {k: (v.to(torch.bfloat16) if v.dim() >= 2 else v) for k, v in weights.items()}
+    return pm.greedy_continue(raw, weights, prompt, count, rounding=pm.ROUNDING_POINTS if bf16 else (),
+                              windows=windows_of(raw))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("key,lengths,new", [("A", (5, 17, 33), 8), ("C", (3, 40, 29), 8)])
+def test_greedy_generation_matches_plain(tmp_path, key, lengths, new, dtype):
+    folder = make_model_folder(tmp_path, key)
+    weights = read_weights(folder)
+    engine = LLMEngine(str(folder), block_size=PAGE_SIZES[key], num_blocks=24, dtype=dtype)
+    prompts = [random_tokens(TINY[key]["vocab_size"], n, 30 + n) for n in lengths]
+    outs = engine.generate(prompts, SamplingParams(max_new_tokens=new, ignore_eos=True))
+    assert engine.block_manager.whole()
+    for prompt, out in zip(prompts, outs):
+        want, margins = plain_greedy(key, weights, prompt, new, dtype == "bfloat16")
+        tie = 1e-4 if dtype == "float32" else 4e-2   # a top-2 gap below twice the logit tolerance is a tie
+        for position, (a, b, margin) in enumerate(zip(out, want, margins)):
+            if a != b:
+                assert margin < tie, f"token {position}: engine {a}, plain {b}, gap {margin}"
+                break  # after a tie went the other way the continuations differ
+
+
+def test_tiny_b_with_few_pages_chunking_and_temperature(tmp_path):
+    """Prompts 1/9/40/64/70, 12 tokens each at temperature 0.8, budget 24, page 8, 20
+    pages: preemption happens, and every request's tokens equal those it gets alone."""
+    folder = make_model_folder(tmp_path, "B")
+    prompts = [random_tokens(384, n, 40 + n) for n in (1, 9, 40, 64, 70)]
+    params = [SamplingParams(max_new_tokens=12, temperature=0.8, ignore_eos=True, seed=500 + i) for i in range(5)]
+    crowded = LLMEngine(str(folder), block_size=8, num_blocks=20, max_tokens_per_step=24, max_running=4, dtype="float32")
+    batched = crowded.generate(prompts, params)
+    assert crowded.scheduler.num_preemptions >= 1 and crowded.block_manager.whole()
+    roomy = LLMEngine(str(folder), block_size=8, num_blocks=64, dtype="float32")
+    for prompt, param, want in zip(prompts, params, batched):
+        assert roomy.generate([prompt], param)[0] == want
+    assert all(len(o) == 12 for o in batched)
+
+
+def test_engine_refuses_without_kernels_dtype(tmp_path):
+    folder = make_model_folder(tmp_path, "A")
+    with pytest.raises(ValueError, match="dtype"):
+        LLMEngine(str(folder), dtype="float16")

@@ -1,0 +1,296 @@
+"""Each kernel alone against a plain float64 reference of the same operation, at
+sizes other than the engine's tiny models: widths and vocabularies that are no
+power of two, head sizes 16..256, odd head counts and groups, context lengths
+around page edges."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from tests.gpu_common import cuda_ops
+from tests.plain import plain_model as pm
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def close(got, want, atol, rtol=0.0, what=""):
+    got, want = got.double().cpu(), want.double().cpu()
+    assert torch.isfinite(got).all(), what
+    bound = atol + rtol * want.abs()
+    worst = ((got - want).abs() - bound).max().item()
+    assert worst <= 0, f"{what}: exceeds tolerance by {worst:.3e}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed(dtype):
+    ops = cuda_ops(dtype)
+    table = rnd(331, 200, dtype=dtype)
+    ids = torch.tensor([0, 330, 7, 7, 129], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 200, device=DEV)
+    ops.embed(ids, table, out)
+    assert torch.equal(out, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width", [48, 200, 3584 + 16, 5000])
+def test_add_rmsnorm(dtype, width):
+    ops = cuda_ops(dtype)
+    n, eps = 7, 3e-6
+    resid, weight = rnd(n, width, seed=1, scale=3.0), 1 + 0.1 * rnd(width, seed=2)
+    for delta in (None, rnd(n, width, seed=3), rnd(n, width, seed=4, dtype=torch.bfloat16)):
+        x = resid.clone()
+        out = torch.empty(n, width, dtype=dtype, device=DEV)
+        ops.add_rmsnorm(x, delta, weight, eps, out)
+        summed = resid.double() + (0 if delta is None else delta.double())
+        close(x, summed, 1e-6, 1e-6, "residual sum")
+        want = pm.rms_norm(summed, weight.double(), eps)
+        tol = 1e-5 if dtype == torch.float32 else 0.0
+        close(out, want, tol, 0 if dtype == torch.float32 else 2 ** -8, f"norm width {width}")
+        rows = torch.tensor([5, 0, 5], dtype=torch.int32, device=DEV)
+        x2 = resid.clone()
+        picked = torch.empty(3, width, dtype=dtype, device=DEV)
+        ops.gather_add_rmsnorm(x2, delta, rows, weight, eps, picked)
+        assert torch.equal(x2, resid), "gather form must not write the residual"
+        assert torch.equal(picked, out[rows.long()])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_silu_mul(dtype):
+    ops = cuda_ops(dtype)
+    n, inter = 5, 176 + 3
+    gate_up = rnd(n, 2 * inter, dtype=dtype, scale=3.0)
+    out = torch.empty(n, inter, dtype=dtype, device=DEV)
+    ops.silu_mul(gate_up, out)
+    g, u = gate_up[:, :inter].double(), gate_up[:, inter:].double()
+    want = g * torch.sigmoid(g) * u
+    close(out, want, 1e-6 if dtype == torch.float32 else 0, 1e-6 if dtype == torch.float32 else 2 ** -8)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 7, 5), (33, 65, 17), (64, 64, 16), (70, 331, 240), (130, 96, 1000), (3, 500, 3)])
+def test_gemm_fp32_is_true_fp32(m, n, k):
+    ops = cuda_ops(torch.float32)
+    x, w, bias = rnd(m, k, seed=1), rnd(n, k, seed=2), rnd(n, seed=3)
+    out = torch.empty(m, n, device=DEV)
+    ops.linear(x, w, out, bias=bias)
+    want = x.double() @ w.double().T + bias.double()
+    # float32 summation of k terms: the probabilistic rounding bound is
+    # sqrt(k) * u * sum|a_i b_i| with u = 2^-24 (Higham & Mary 2019); products rounded to
+    # TF32 would be off by about 2^-11 * sqrt(sum (a_i b_i)^2), far above it
+    products = x.double().abs() @ w.double().abs().T + bias.double().abs()
+    bound = math.sqrt(k) * 2.0 ** -24 * products
+    excess = ((out.double() - want).abs() - bound).max().item()
+    assert excess <= 0, f"gemm {m}x{n}x{k}: exceeds the float32 bound by {excess:.3e}"
+    if k >= 64:
+        tf32_error = 2.0 ** -11 * math.sqrt(k) * float((x.double() ** 2).mean().sqrt() * (w.double() ** 2).mean().sqrt())
+        assert 5 * bound.mean().item() < tf32_error, "the bound would not tell float32 from TF32"
+    # a row's result does not depend on the rows beside it
+    alone = torch.empty(1, n, device=DEV)
+    ops.linear(x[m - 1:m].contiguous(), w, alone, bias=bias)
+    assert torch.equal(alone[0], out[m - 1])
+
+
+def test_linear_bf16():
+    ops = cuda_ops(torch.bfloat16)
+    x, w = rnd(9, 240, dtype=torch.bfloat16), rnd(331, 240, dtype=torch.bfloat16)
+    wide, narrow = torch.empty(9, 331, device=DEV), torch.empty(9, 331, dtype=torch.bfloat16, device=DEV)
+    ops.linear(x, w, wide)
+    ops.linear(x, w, narrow)
+    want = x.double() @ w.double().T
+    close(wide, want, 1e-3, 1e-4)
+    close(narrow, want, 1e-3, 2 ** -7)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,dim", [(5, 1, 48), (14, 2, 64), (3, 3, 16), (4, 2, 256)])
+def test_rope_kv_write(dtype, heads, kv_heads, dim):
+    ops = cuda_ops(dtype)
+    n, pages, page = 6, 5, 4
+    width = (heads + 2 * kv_heads) * dim
+    qkv, bias = rnd(n, width, seed=1), rnd(width, seed=2)
+    positions = torch.tensor([0, 1, 2, 17, 4000, 123456], dtype=torch.int32, device=DEV)
+    inv_freq = (1.0 / (1e6 ** (torch.arange(0, dim, 2).float() / dim))).to(DEV)
+    slots = torch.tensor([3, 0, 19, 7, 8, 12], dtype=torch.int32, device=DEV)
+    keys = torch.full((pages, page, kv_heads, dim), 9.0, dtype=dtype, device=DEV)
+    values = torch.full_like(keys, 9.0)
+    q = torch.empty(n, heads * dim, dtype=dtype, device=DEV)
+    ops.rope_kv_write(qkv, bias, positions, inv_freq, q, keys, values, slots, heads, kv_heads, dim)
+    x = (qkv.double() + bias.double()).cpu()
+    cos, sin = pm.rope_tables(positions.cpu(), dim, 1e6, torch.float64)
+    want_q = pm.apply_rope(x[:, : heads * dim].view(n, heads, dim), cos, sin)
+    want_k = pm.apply_rope(x[:, heads * dim: (heads + kv_heads) * dim].view(n, kv_heads, dim), cos, sin)
+    want_v = x[:, (heads + kv_heads) * dim:].view(n, kv_heads, dim)
+    # the angle is formed in float32 from a float32 table; at position 123456 one ulp of
+    # the angle is 8e-3 rad, which bounds how close any float32 implementation can be
+    atol = 2e-5 if dtype == torch.float32 else 4e-2
+    close(q.view(n, heads, dim)[:4], want_q[:4], atol, 0 if dtype == torch.float32 else 2 ** -8, "q")
+    flat_k, flat_v = keys.view(-1, kv_heads, dim), values.view(-1, kv_heads, dim)
+    close(flat_k[slots.long()][:4], want_k[:4], atol, 0 if dtype == torch.float32 else 2 ** -8, "k in cache")
+    close(flat_v[slots.long()], want_v, 1e-6 if dtype == torch.float32 else 0, 0 if dtype == torch.float32 else 2 ** -8, "v in cache")
+    # far positions: compare with the same float32 angle
+    angle = positions.float().cpu()[:, None] * inv_freq.cpu()[None, :]
+    cos32, sin32 = torch.cat([angle.cos(), angle.cos()], -1).double(), torch.cat([angle.sin(), angle.sin()], -1).double()
+    far_q = pm.apply_rope(x[:, : heads * dim].view(n, heads, dim), cos32, sin32)
+    close(q.view(n, heads, dim), far_q, 1e-4 if dtype == torch.float32 else 4e-2, 0 if dtype == torch.float32 else 2 ** -8, "q far")
+    untouched = torch.ones(pages * page, dtype=torch.bool)
+    untouched[slots.long().cpu()] = False
+    assert (flat_k[untouched.to(DEV)] == 9.0).all() and (flat_v[untouched.to(DEV)] == 9.0).all()
+    # without rotation and without a cache: bias only, into q / k_out / v_out
+    k_out = torch.empty(n, kv_heads * dim, dtype=dtype, device=DEV)
+    v_out = torch.empty_like(k_out)
+    ops.rope_kv_write(qkv, None, positions, None, q, None, None, slots, heads, kv_heads, dim, k_out=k_out, v_out=v_out)
+    close(q, qkv[:, : heads * dim], 0, 0 if dtype == torch.float32 else 2 ** -8, "plain q")
+    close(k_out, qkv[:, heads * dim: (heads + kv_heads) * dim], 0, 0 if dtype == torch.float32 else 2 ** -8, "plain k")
+    keys2, values2 = torch.zeros_like(keys), torch.zeros_like(values)
+    ops.kv_write(k_out, v_out, keys2, values2, slots)
+    assert torch.equal(keys2.view(-1, kv_heads * dim)[slots.long()], k_out)
+    assert torch.equal(values2.view(-1, kv_heads * dim)[slots.long()], v_out)
+
+
+def paged_case(dtype, heads, kv_heads, dim, page, ctx_lens, q_lens, seed=0):
+    """Random sequences scattered over distinct, shuffled pages."""
+    g = torch.Generator().manual_seed(seed)
+    total_pages = sum(-(-c // page) for c in ctx_lens) + 3
+    order = torch.randperm(total_pages, generator=g).tolist()
+    keys = torch.full((total_pages, page, kv_heads, dim), float("nan"), dtype=dtype)
+    values = torch.full_like(keys, float("nan"))
+    max_blocks = max(-(-c // page) for c in ctx_lens)
+    table = torch.full((len(ctx_lens), max_blocks), -1, dtype=torch.int32)
+    seqs, q_rows, seq_of, q_start = [], [], [], [0]
+    for s, (ctx, q_len) in enumerate(zip(ctx_lens, q_lens)):
+        k = torch.randn(ctx, kv_heads, dim, generator=g).to(dtype)
+        v = torch.randn(ctx, kv_heads, dim, generator=g).to(dtype)
+        q = torch.randn(ctx, heads, dim, generator=g).to(dtype)
+        for b in range(-(-ctx // page)):
+            pid = order.pop()
+            table[s, b] = pid
+            rows = slice(b * page, min(ctx, (b + 1) * page))
+            keys[pid, : rows.stop - rows.start] = k[rows]
+            values[pid, : rows.stop - rows.start] = v[rows]
+        seqs.append((q, k, v))
+        q_rows.append(q[ctx - q_len:])
+        seq_of += [s] * q_len
+        q_start.append(q_start[-1] + q_len)
+    return dict(
+        keys=keys.to(DEV), values=values.to(DEV), table=table.to(DEV), seqs=seqs,
+        q=torch.cat(q_rows).reshape(-1, heads * dim).contiguous().to(DEV),
+        q_start=torch.tensor(q_start, dtype=torch.int32, device=DEV),
+        ctx_len=torch.tensor(ctx_lens, dtype=torch.int32, device=DEV),
+        seq_of=torch.tensor(seq_of, dtype=torch.int32, device=DEV),
+    )
+
+
+def run_attention(ops, case, heads, kv_heads, dim, window, q_lens, ctx_lens):
+    out = torch.empty_like(case["q"])
+    ops.paged_attention(case["q"], case["keys"], case["values"], case["table"], case["q_start"], case["ctx_len"],
+                        case["seq_of"], heads, kv_heads, dim, dim ** -0.5, window, out,
+                        max_q_len=max(q_lens), max_ctx_len=max(ctx_lens))
+    want = []
+    for (q, k, v), q_len in zip(case["seqs"], q_lens):
+        full = pm.causal_attention(q.double(), k.double(), v.double(), window)
+        want.append(full[len(q) - q_len:])
+    return out, torch.cat(want).reshape(out.shape)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,dim,page", [(14, 2, 64, 16), (5, 1, 48, 16), (6, 3, 32, 8), (2, 2, 256, 16), (7, 7, 16, 4), (28, 4, 128, 16)])
+def test_paged_attention_single_tokens_around_page_edges(dtype, heads, kv_heads, dim, page):
+    ops = cuda_ops(dtype)
+    ctx_lens = [1, 15, 16, 17, 100, 333, 512, 7]   # shrike tests/test_triton_attention.py:35-37
+    q_lens = [1] * len(ctx_lens)
+    case = paged_case(dtype, heads, kv_heads, dim, page, ctx_lens, q_lens)
+    got, want = run_attention(ops, case, heads, kv_heads, dim, None, q_lens, ctx_lens)
+    close(got, want, 2e-5 if dtype == torch.float32 else 2e-2, 0, "decode attention")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [None, 1, 16, 50])
+def test_paged_attention_portions_mixed_with_single_tokens(dtype, window):
+    ops = cuda_ops(dtype)
+    heads, kv_heads, dim, page = 6, 2, 64, 16
+    ctx_lens = [40, 1, 130, 2, 16, 17, 300, 64, 33]
+    q_lens = [1, 1, 1, 2, 16, 3, 129, 64, 17]
+    case = paged_case(dtype, heads, kv_heads, dim, page, ctx_lens, q_lens, seed=4)
+    if window is not None:  # pages the window has passed are gone: the kernel must not touch them
+        for s, (ctx, q_len) in enumerate(zip(ctx_lens, q_lens)):
+            first_needed = max(0, ctx - q_len - window + 1)
+            for b in range(first_needed // page):
+                pid = int(case["table"][s, b])
+                case["keys"][pid] = float("nan")
+                case["table"][s, b] = -1
+    got, want = run_attention(ops, case, heads, kv_heads, dim, window, q_lens, ctx_lens)
+    close(got, want, 2e-5 if dtype == torch.float32 else 2e-2, 0, f"mixed attention window {window}")
+
+
+def test_head_sizes_outside_the_served_range_are_refused():
+    from shrike_b200.ops.cuda_ops import KernelError
+
+    ops = cuda_ops(torch.float32)
+    for bad in (8, 24, 272, 100):
+        with pytest.raises(KernelError, match="head size"):
+            ops.check_head_dim(bad)
+
+
+def test_sampling_greedy_takes_the_lowest_index_on_ties():
+    ops = cuda_ops(torch.float32)
+    vocab = 152064 + 5
+    logits = rnd(3, vocab, seed=1)
+    logits[0, 70000] = 50.0
+    logits[0, 9] = 50.0
+    logits[1, vocab - 1] = 60.0
+    logits[2] = -3.0   # all equal
+    out = torch.empty(3, dtype=torch.int32, device=DEV)
+    zeros = torch.zeros(3, device=DEV)
+    ops.sample(logits, zeros, torch.ones(3, device=DEV), torch.zeros(3, dtype=torch.int64, device=DEV), out)
+    assert out.tolist() == [9, vocab - 1, 0]
+
+
+def test_sampling_follows_the_distribution_and_top_p():
+    ops = cuda_ops(torch.float32)
+    vocab, draws = 331, 4000
+    g = torch.Generator().manual_seed(3)
+    row = torch.randn(vocab, generator=g) * 2.0
+    logits = row.to(DEV).repeat(draws, 1).contiguous()
+    seeds = torch.arange(draws, dtype=torch.int64, device=DEV) * 7919 + 13
+    out = torch.empty(draws, dtype=torch.int32, device=DEV)
+    temp = torch.full((draws,), 0.8, device=DEV)
+    ops.sample(logits, temp, torch.ones(draws, device=DEV), seeds, out)
+    probs = pm.softmax_with_temperature(row, 0.8)
+    counts = torch.bincount(out.long().cpu(), minlength=vocab).double()
+    top = probs.argsort(descending=True)[:10]
+    for token in top.tolist():   # binomial: five standard deviations
+        p = float(probs[token])
+        assert abs(counts[token] - draws * p) < 5 * math.sqrt(draws * p * (1 - p)) + 1, token
+    # same seeds, same tokens, whatever the row or the batch size
+    again = torch.empty(5, dtype=torch.int32, device=DEV)
+    ops.sample(logits[:5], temp[:5], torch.ones(5, device=DEV), seeds[[9, 3, 3, 0, 1]].contiguous(), again)
+    assert again.tolist() == [out[9].item(), out[3].item(), out[3].item(), out[0].item(), out[1].item()]
+    # top_p: nothing outside the nucleus is ever drawn, everything inside can be
+    for top_p in (0.3, 0.9):
+        keep = pm.top_p_keep(probs, top_p)
+        ops.sample(logits, temp, torch.full((draws,), top_p, device=DEV), seeds, out)
+        drawn = set(out.tolist())
+        kept = set(torch.nonzero(keep).flatten().tolist())
+        assert drawn <= kept, f"top_p {top_p}: drew {sorted(drawn - kept)} outside the nucleus"
+        likely = {t for t in kept if float(probs[t]) * draws > 30}
+        assert likely <= drawn
+    # a dominant token with a tiny top_p is always taken (shrike tests/test_sampler.py)
+    ops.sample(logits[:8], temp[:8], torch.full((8,), 1e-6, device=DEV), seeds[:8].contiguous(), out[:8])
+    assert set(out[:8].tolist()) == {int(probs.argmax())}
+
+
+def test_sampling_mixes_greedy_and_sampled_rows():
+    ops = cuda_ops(torch.float32)
+    logits = rnd(4, 1000, seed=5)
+    temp = torch.tensor([0.0, 1.0, 0.0, 0.7], device=DEV)
+    out = torch.empty(4, dtype=torch.int32, device=DEV)
+    ops.sample(logits, temp, torch.ones(4, device=DEV), torch.tensor([1, 2, 3, 4], dtype=torch.int64, device=DEV), out)
+    assert out[0].item() == int(logits[0].argmax()) and out[2].item() == int(logits[2].argmax())
+    assert 0 <= out[1].item() < 1000 and 0 <= out[3].item() < 1000
