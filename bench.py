@@ -1,0 +1,357 @@
+"""Decode and prefill throughput of the engine at Qwen2.5-7B shape on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+One JSON line is printed.  A "step" is one decode step of the whole batch (forward,
+sampling, the sampled tokens back on the host).  `value` is decoded tokens per second
+at batch 8 and a context of 1,024 tokens, timed with CUDA events around exactly K
+steps; `e2e` is the same measured through `LLMEngine.step()`, host token ids in and
+out; `prefill` is one 2,048-token prompt in one step; `roofline` relates the bytes a
+decode step must read (every weight once, the cache of the live requests) to its time;
+`points` holds decoding at batch 1 and 64.  Weights are random (seeded), token ids
+uniform random: no checkpoint and no dataset is read.  Peaks come from
+MEASURED_PEAKS.json beside this file when present, else from an earlier measurement
+on the same GPU pool.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+MODEL_7B = dict(
+    architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=3584, intermediate_size=18944,
+    num_hidden_layers=28, num_attention_heads=28, num_key_value_heads=4, head_dim=128, vocab_size=152064,
+    rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False, max_position_embeddings=32768,
+    eos_token_id=151643, torch_dtype="bfloat16",
+)
+CONTEXT = 1024
+PREFILL_TOKENS = 2048
+BLOCK_SIZE = 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def load_peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        try:
+            raw = json.loads(path.read_text())
+            flat = {}
+
+            def walk(node):
+                if isinstance(node, dict):
+                    for key, value in node.items():
+                        if isinstance(value, (int, float)) and key in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained"):
+                            flat.setdefault(key, float(value))
+                        else:
+                            walk(value)
+                elif isinstance(node, list):
+                    for item in node:
+                        walk(item)
+
+            walk(raw)
+            if "hbm_gbs" in flat and "bf16_tflops" in flat:
+                flat["source"] = "measured"
+                return flat
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples = []
+        self.process = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+
+        def read():
+            for line in self.process.stdout:
+                self.samples.append((time.perf_counter(), line.strip()))
+
+        self.thread = threading.Thread(target=read, daemon=True)
+        self.thread.start()
+
+    def stop(self):
+        if self.process is not None:
+            self.process.terminate()
+            try:
+                self.process.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.process.kill()
+
+    def summary(self, windows) -> dict:
+        clocks, max_clock, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for stamp, line in self.samples:
+            if not any(lo <= stamp <= hi for lo, hi in windows):
+                continue
+            fields = [f.strip() for f in line.split(",")]
+            if len(fields) < 6:
+                continue
+            try:
+                clocks.append(int(fields[0]))
+                max_clock = max(max_clock, int(fields[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, fields[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": int(statistics.median(clocks)) if clocks else None, "sm_max_mhz": max_clock or None,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def model_numbers(raw: dict, layers: int) -> dict:
+    h, inter, v = raw["hidden_size"], raw["intermediate_size"], raw["vocab_size"]
+    heads, kv, d = raw["num_attention_heads"], raw["num_key_value_heads"], raw["head_dim"]
+    matrices = h * (heads + 2 * kv) * d + heads * d * h + 3 * h * inter
+    vectors = (heads + 2 * kv) * d + 2 * h
+    return dict(
+        layer_matrix_params=matrices, layer_params=matrices + vectors, head_params=v * h,
+        kv_bytes_per_token=layers * 2 * kv * d * 2,
+        weight_bytes_per_step=2 * (layers * (matrices + vectors) + v * h + h),
+    )
+
+
+def decode_bytes(numbers: dict, batch: int, context: float) -> float:
+    return numbers["weight_bytes_per_step"] + batch * context * numbers["kv_bytes_per_token"]
+
+
+def prefill_flops(raw: dict, layers: int, tokens: int) -> float:
+    numbers = model_numbers(raw, layers)
+    heads, d = raw["num_attention_heads"], raw["head_dim"]
+    linear = 2.0 * tokens * layers * numbers["layer_matrix_params"]
+    attention = layers * 4.0 * heads * d * (tokens * (tokens + 1) / 2)
+    head = 2.0 * raw["vocab_size"] * raw["hidden_size"]
+    return linear + attention + head
+
+
+def run_ours(args) -> dict:
+    import numpy as np
+    import torch
+
+    import shrike_b200.models  # noqa: F401
+    from shrike_b200 import SamplingParams
+    from shrike_b200.config import parse_config
+    from shrike_b200.engine.batch import StepEntry
+    from shrike_b200.engine.llm_engine import LLMEngine
+    from shrike_b200.weights.random_init import random_tensors
+
+    torch.cuda.set_device(0)
+    device = torch.device("cuda:0")
+    raw = dict(MODEL_7B)
+    full_layers = raw["num_hidden_layers"]
+    raw["num_hidden_layers"] = args.layers or full_layers
+    layers = raw["num_hidden_layers"]
+    config = parse_config(raw)
+    tensors = random_tensors(config, seed=0, device=device, dtype=torch.bfloat16)
+    batches = sorted({args.batch, 1, 64})
+    pages = sum(b * (-(-(CONTEXT + args.steps + args.warmup + 8) // BLOCK_SIZE)) for b in batches[-1:]) + \
+        -(-PREFILL_TOKENS // BLOCK_SIZE) + 64
+    engine = LLMEngine(None, block_size=BLOCK_SIZE, num_blocks=pages, max_tokens_per_step=4096, max_running=64,
+                       dtype="bfloat16", config=config, tensors=tensors)
+    del tensors
+    runner, ops = engine.runner, engine.ops
+    rng = np.random.default_rng(0)
+    vocab = raw["vocab_size"]
+    numbers = model_numbers(raw, layers)
+    peaks = load_peaks()
+    sampler = ClockSampler()
+    sampler.start()
+    windows = []
+
+    def fill(batch: int):
+        """`batch` requests with CONTEXT - 1 tokens in the cache (untimed)."""
+        caches = []
+        for _ in range(batch):
+            cache = runner.cache.open()
+            ids = rng.integers(0, vocab, CONTEXT - 1).tolist()
+            runner.cache.append(cache, 0, len(ids))
+            runner.step([StepEntry(cache, ids, 0, [])])
+            caches.append(cache)
+        torch.cuda.synchronize()
+        return caches
+
+    greedy_t = torch.zeros(64, device=device)
+    greedy_p = torch.ones(64, device=device)
+    greedy_s = torch.zeros(64, dtype=torch.int64, device=device)
+
+    def decode_run(batch: int, steps: int, warmup: int):
+        """Device-timed decode through the step function and the sampling kernel."""
+        caches = fill(batch)
+        tokens = rng.integers(0, vocab, batch).tolist()
+        fed = CONTEXT - 1
+        out = torch.empty(batch, dtype=torch.int32, device=device)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+        def one_step(tokens, fed):
+            entries = []
+            for cache, token in zip(caches, tokens):
+                runner.cache.append(cache, fed, 1)
+                entries.append(StepEntry(cache, [token], fed, [0]))
+            logits = runner.step(entries)
+            ops.sample(logits, greedy_t[:batch], greedy_p[:batch], greedy_s[:batch], out)
+            return out.tolist()
+
+        for _ in range(warmup):
+            tokens = one_step(tokens, fed)
+            fed += 1
+        torch.cuda.synchronize()
+        launches_before = ops.launches
+        t0 = time.perf_counter()
+        start.record()
+        for _ in range(steps):
+            tokens = one_step(tokens, fed)
+            fed += 1
+        stop.record()
+        torch.cuda.synchronize()
+        windows.append((t0, time.perf_counter()))
+        ms = start.elapsed_time(stop) / steps
+        launches = ops.launches - launches_before
+        for cache in caches:
+            runner.cache.free(cache)
+        mean_context = CONTEXT + warmup + (steps - 1) / 2.0
+        return ms, launches, mean_context
+
+    # ---- decode at the headline batch, device-timed -------------------------
+    ms, launches, mean_context = decode_run(args.batch, args.steps, args.warmup)
+    value = args.batch * 1000.0 / ms
+    bytes_step = decode_bytes(numbers, args.batch, mean_context)
+    achieved = bytes_step / (ms * 1e-3) / 1e9
+
+    # ---- the same through the public entry point ------------------------------
+    def e2e_run(batch: int, steps: int, warmup: int):
+        prompts = [rng.integers(0, vocab, CONTEXT - 1).tolist() for _ in range(batch)]
+        params = SamplingParams(max_new_tokens=steps + warmup + 1, ignore_eos=True)
+        for prompt in prompts:
+            engine.add_request(prompt, params)
+        while any(not r.prefill_done for r in engine.requests.values()) or engine.scheduler.waiting:
+            engine.step()
+        for _ in range(warmup):
+            engine.step()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        start.record()
+        produced = 0
+        for _ in range(steps):
+            produced += len(engine.step())
+        stop.record()
+        torch.cuda.synchronize()
+        windows.append((t0, time.perf_counter()))
+        e2e_ms = start.elapsed_time(stop) / steps
+        for req_id in list(engine.requests):
+            engine.abort(req_id)
+        assert engine.block_manager.whole()
+        blocks = -(-(CONTEXT + warmup + steps) // BLOCK_SIZE)
+        h2d = 4 * (3 * batch + (batch + 1) + 2 * batch + batch + batch + batch * blocks) + 8 * batch + 8 * batch
+        return produced / steps * 1000.0 / e2e_ms, h2d, 4 * batch
+
+    e2e_value, h2d, d2h = e2e_run(args.batch, args.steps, args.warmup)
+
+    # ---- prefill of 2,048 tokens in one step ----------------------------------
+    def prefill_run(repeats: int, warmup: int):
+        times = []
+        for index in range(warmup + repeats):
+            cache = runner.cache.open()
+            ids = rng.integers(0, vocab, PREFILL_TOKENS).tolist()
+            runner.cache.append(cache, 0, PREFILL_TOKENS)
+            torch.cuda.synchronize()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0 = time.perf_counter()
+            start.record()
+            logits = runner.step([StepEntry(cache, ids, 0, [PREFILL_TOKENS - 1])])
+            stop.record()
+            torch.cuda.synchronize()
+            if index >= warmup:
+                times.append(start.elapsed_time(stop))
+                windows.append((t0, time.perf_counter()))
+            runner.cache.free(cache)
+        return statistics.median(times)
+
+    prefill_ms = prefill_run(5, 3)
+    flops = prefill_flops(raw, layers, PREFILL_TOKENS)
+    peak_flops = peaks["bf16_tflops"] * 1e12
+
+    points = {}
+    for batch in (1, 64):
+        point_ms, _, _ = decode_run(batch, max(10, args.steps // 2), 3)
+        points[f"decode_b{batch}"] = round(batch * 1000.0 / point_ms, 1)
+
+    sampler.stop()
+    clocks = sampler.summary(windows)
+    return {
+        "metric": "decode_tokens_per_second_qwen2.5-7b_b8_ctx1024",
+        "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded random weights and uniform random token ids",
+        "impl": "ours",
+        "config": {
+            "model": "Qwen2.5-7B shape", "layers": layers, "layers_full": full_layers, "hidden": raw["hidden_size"],
+            "heads": raw["num_attention_heads"], "kv_heads": raw["num_key_value_heads"], "head_dim": raw["head_dim"],
+            "intermediate": raw["intermediate_size"], "vocab": raw["vocab_size"], "global_batch": args.batch,
+            "seq_len": CONTEXT, "block_size": BLOCK_SIZE, "prefill_tokens": PREFILL_TOKENS,
+            "parallelism": "single_gpu", "l2": "inputs larger than L2 (weights read per step: 15 GB)",
+            "peaks": peaks["source"],
+        },
+        "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "prefill": {"value": round(PREFILL_TOKENS * 1000.0 / prefill_ms, 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(prefill_ms, 3), "frac": round(flops / (prefill_ms * 1e-3) / peak_flops, 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peaks["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clocks,
+    }
+
+
+def run_reference(args) -> dict:
+    reference = ROOT / "baseline" / "_ref"
+    if not (reference / "shrike").is_dir():
+        return {"impl": "reference", "unavailable": "the reference is not installed under baseline/_ref"}
+    from baseline.reference_arm import run  # the unmodified reference through its own LLMEngine
+
+    return run(args, MODEL_7B, CONTEXT)
+
+
+def main():
+    parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=50)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all)")
+    args = parser.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU: this engine runs on a single B200 (asked for {args.gpus})")
+        sys.exit(2)
+    args.warmup = max(3, args.warmup)
+    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    print(json.dumps(result))
+
+
+if __name__ == "__main__":
+    main()

@@ -57,7 +57,8 @@ class CudaOps:
         self.core = build.core_library()
         self._declare_core()
         self._attention = {}
-        self.launches = 0
+        self.launches = 0        # launches of this package's own kernels
+        self.library_calls = 0   # matrix products handed to cuBLAS
         # library matrix products keep float32 accumulation end to end: no TF32 for float32
         # inputs, no bfloat16 partial sums when a bfloat16 product is split along K
         torch.backends.cuda.matmul.allow_tf32 = False
@@ -133,8 +134,8 @@ class CudaOps:
         o = w.shape[0]
         if w.shape[1] != k or tuple(out.shape) != (n, o):
             raise KernelError(f"linear: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
-        self.launches += 1
         if self.dtype == torch.float32:
+            self.launches += 1
             _dense(x, torch.float32, "linear input")
             _dense(w, torch.float32, "linear weight")
             _dense(out, torch.float32, "linear output")
@@ -143,13 +144,13 @@ class CudaOps:
             return
         _dense(x, torch.bfloat16, "linear input")
         _dense(w, torch.bfloat16, "linear weight")
+        self.library_calls += 1
         if out.dtype == torch.float32:
             torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
         else:
             torch.mm(x, w.t(), out=out)
         if bias is not None:
             out.add_(bias)
-            self.launches += 1
 
     def rope_kv_write(self, qkv, bias, positions, inv_freq, q_out, keys, values, slots,
                       num_heads, num_kv_heads, head_dim, k_out=None, v_out=None):
