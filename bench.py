@@ -194,26 +194,20 @@ def run_ours(args) -> dict:
         torch.cuda.synchronize()
         return caches
 
-    greedy_t = torch.zeros(64, device=device)
-    greedy_p = torch.ones(64, device=device)
-    greedy_s = torch.zeros(64, dtype=torch.int64, device=device)
-
     def decode_run(batch: int, steps: int, warmup: int):
         """Device-timed decode through the step function and the sampling kernel."""
         caches = fill(batch)
         tokens = rng.integers(0, vocab, batch).tolist()
         fed = CONTEXT - 1
-        out = torch.empty(batch, dtype=torch.int32, device=device)
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
         def one_step(tokens, fed):
             entries = []
             for cache, token in zip(caches, tokens):
                 runner.cache.append(cache, fed, 1)
-                entries.append(StepEntry(cache, [token], fed, [0]))
-            logits = runner.step(entries)
-            ops.sample(logits, greedy_t[:batch], greedy_p[:batch], greedy_s[:batch], out)
-            return out.tolist()
+                entries.append(StepEntry(cache, [token], fed, [0], (0.0, 1.0, 0)))
+            _logits, drawn = runner.step(entries, sample=True)
+            return drawn.tolist()
 
         for _ in range(warmup):
             tokens = one_step(tokens, fed)

@@ -1,0 +1,492 @@
+// Paged grouped-query attention in bfloat16 on the tensor cores (mma.sync m16n8k16,
+// float32 accumulation), for the serving path.
+//
+// Two kernels share the tile code:
+//   * portions (q_len > 1): one CTA per (64 queries, query head, sequence); four warps
+//     own 16 query rows each and walk the keys 64 at a time (FlashAttention-2 order).
+//   * single tokens (q_len == 1): one CTA per (key split, kv head, sequence).  The G
+//     query heads that share a kv head are the rows of one 16-row tile, so keys and
+//     values are read once per kv head, not once per query head; the four warps take 16
+//     keys each of every 64-key tile; partial results of the splits are combined by a
+//     third, small kernel.  The split count is a launch parameter, the key ranges come
+//     from ctx_len on the device, so a captured launch sequence stays valid as contexts
+//     grow.
+// Keys and values are fetched through the block table with 16-byte cp.async copies into
+// padded shared-memory rows (double-buffered) and read with ldmatrix.  Scores, running
+// maximum, sum and the output accumulate in float32; probabilities are rounded to
+// bfloat16 for the PV product, as the values are.  Mask: a query at position p sees keys
+// [max(0, p - window + 1), p] (shrike/engine/model_runner.py:129-150).
+//
+// Built once per head size: -DSHRIKE_HEAD_DIM=<multiple of 16, at most 256>.
+#include "common.cuh"
+
+#ifndef SHRIKE_HEAD_DIM
+#error "compile with -DSHRIKE_HEAD_DIM=<head size>"
+#endif
+
+namespace bf16attn {
+
+constexpr int D = SHRIKE_HEAD_DIM;
+constexpr int BN = 64;              // keys per tile
+constexpr int BM = 64;              // query rows per CTA (portions)
+constexpr int THREADS = 128;
+constexpr int ROW = D + 8;          // padded row, in elements: 16 bytes of padding keep ldmatrix conflict-free
+constexpr int CHUNKS = D / 8;       // 16-byte chunks per row
+constexpr int KSTEPS = D / 16;
+constexpr int DTILES = D / 8;
+constexpr bool Q_IN_REGS = D <= 128;
+constexpr float LOG2E = 1.4426950408889634f;
+using bf16 = __nv_bfloat16;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+  const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(smem));
+  const int bytes = valid ? 16 : 0;  // 0: the 16 bytes are filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+  const unsigned addr = static_cast<unsigned>(__cvta_generic_to_shared(smem));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
+  const unsigned addr = static_cast<unsigned>(__cvta_generic_to_shared(smem));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const unsigned*>(&v);
+}
+
+struct Params {
+  const bf16* q;
+  const bf16* k_cache;
+  const bf16* v_cache;
+  const int* block_table;
+  const int* q_start;
+  const int* ctx_len;
+  bf16* out;
+  float* partial_out;   // [seq, head, split, D], single tokens only
+  float* partial_ml;    // [seq, head, split, 2]
+  int max_blocks, num_heads, num_kv_heads, page_size, num_pages, window, splits;
+  int skip_single;      // portions kernel: leave q_len == 1 to the single-token kernel
+  float scale_log2;     // scale * log2(e)
+};
+
+// Copies keys [tile_base, tile_base + BN) of one kv head into k_tile / v_tile.  Keys
+// outside [lo, hi] (or on a page the sequence does not hold) become zeros.
+__device__ __forceinline__ void load_kv_tile(bf16* k_tile, bf16* v_tile, const Params& p, const int* table,
+                                             int kv_head, int tile_base, int lo, int hi) {
+  const size_t row_stride = static_cast<size_t>(p.num_kv_heads) * D;
+  for (int c = threadIdx.x; c < BN * CHUNKS; c += THREADS) {
+    const int key = c / CHUNKS, chunk = c - key * CHUNKS;
+    const int j = tile_base + key;
+    bool valid = j >= lo && j <= hi;
+    size_t offset = 0;
+    if (valid) {
+      const int block = j / p.page_size;
+      const int page = block < p.max_blocks ? table[block] : -1;
+      if (page < 0 || page >= p.num_pages) valid = false;
+      else offset = (static_cast<size_t>(page) * p.page_size + (j - block * p.page_size)) * row_stride +
+                    static_cast<size_t>(kv_head) * D + chunk * 8;
+    }
+    cp_async16(k_tile + key * ROW + chunk * 8, p.k_cache + offset, valid);
+    cp_async16(v_tile + key * ROW + chunk * 8, p.v_cache + offset, valid);
+  }
+}
+
+// S[16 x (8 * NT)] += Q[16 x D] * K^T for keys [key0, key0 + 8 * NT) of the tile.
+template <int NT>
+__device__ __forceinline__ void scores(float (&s)[NT][4], const unsigned (&q_frag)[Q_IN_REGS ? KSTEPS : 1][4],
+                                       const bf16* q_rows, const bf16* k_tile, int key0, int lane) {
+#pragma unroll
+  for (int kk = 0; kk < KSTEPS; ++kk) {
+    unsigned a[4];
+    if (Q_IN_REGS) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = q_frag[Q_IN_REGS ? kk : 0][i];
+    } else {
+      ldmatrix_x4(a, q_rows + ((lane & 7) + 8 * ((lane >> 3) & 1)) * ROW + kk * 16 + 8 * (lane >> 4));
+    }
+#pragma unroll
+    for (int np = 0; np < NT / 2; ++np) {
+      unsigned b[4];
+      const int key = key0 + np * 16 + (lane & 7) + 8 * (lane >> 4);
+      ldmatrix_x4(b, k_tile + key * ROW + kk * 16 + 8 * ((lane >> 3) & 1));
+      mma_bf16(s[2 * np], a, b[0], b[1]);
+      mma_bf16(s[2 * np + 1], a, b[2], b[3]);
+    }
+  }
+}
+
+// O[16 x D] += P[16 x (8 * NT)] * V for keys [key0, key0 + 8 * NT) of the tile.
+template <int NT>
+__device__ __forceinline__ void accumulate(float (&o)[DTILES][4], const float (&s)[NT][4], const bf16* v_tile,
+                                           int key0, int lane) {
+#pragma unroll
+  for (int kk = 0; kk < NT / 2; ++kk) {
+    unsigned a[4];
+    a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+    a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+    a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+    a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+    for (int dp = 0; dp < DTILES / 2; ++dp) {
+      unsigned b[4];
+      const int key = key0 + kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
+      ldmatrix_x4_trans(b, v_tile + key * ROW + dp * 16 + 8 * (lane >> 4));
+      mma_bf16(o[2 * dp], a, b[0], b[1]);
+      mma_bf16(o[2 * dp + 1], a, b[2], b[3]);
+    }
+  }
+}
+
+// Masks, scales and folds one block of scores into the running softmax state of the two
+// rows this thread holds (row lane/4 and that + 8); leaves probabilities in s.
+template <int NT>
+__device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&o)[DTILES][4], float (&row_max)[2],
+                                               float (&row_sum)[2], const int (&first)[2], const int (&last)[2],
+                                               int key_base, float scale_log2, int lane) {
+  float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int j = 0; j < NT; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int key = key_base + j * 8 + (lane & 3) * 2 + (e & 1);
+      const int r = e >> 1;
+      const bool seen = key >= first[r] && key <= last[r];
+      s[j][e] = seen ? s[j][e] * scale_log2 : -INFINITY;
+      tile_max[r] = fmaxf(tile_max[r], s[j][e]);
+    }
+  float correction[2], base[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
+    tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
+    const float new_max = fmaxf(row_max[r], tile_max[r]);
+    base[r] = new_max == -INFINITY ? 0.f : new_max;   // a row that has seen no key yet
+    correction[r] = exp2f(row_max[r] - base[r]);      // exp2(-inf) = 0
+    row_max[r] = new_max;
+    row_sum[r] *= correction[r];
+  }
+#pragma unroll
+  for (int j = 0; j < NT; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float prob = exp2f(s[j][e] - base[e >> 1]);
+      s[j][e] = prob;
+      row_sum[e >> 1] += prob;
+    }
+#pragma unroll
+  for (int j = 0; j < DTILES; ++j) {
+    o[j][0] *= correction[0];
+    o[j][1] *= correction[0];
+    o[j][2] *= correction[1];
+    o[j][3] *= correction[1];
+  }
+}
+
+// ------------------------------------------------------------------ portions
+__global__ void __launch_bounds__(THREADS) portions_kernel(const Params p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);           // [BM][ROW]
+  bf16* k_tiles = q_tile + BM * ROW;                          // [2][BN][ROW]
+  bf16* v_tiles = k_tiles + 2 * BN * ROW;                     // [2][BN][ROW]
+  const int seq = blockIdx.z, head = blockIdx.y, tile_start = blockIdx.x * BM;
+  const int start = p.q_start[seq];
+  const int q_len = p.q_start[seq + 1] - start;
+  if (tile_start >= q_len || (q_len == 1 && p.skip_single)) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pos0 = p.ctx_len[seq] - q_len;                    // position of the first new token
+  const int kv_head = head / (p.num_heads / p.num_kv_heads);
+  const int* table = p.block_table + static_cast<size_t>(seq) * p.max_blocks;
+  const int rows_here = min(BM, q_len - tile_start);
+  const int lo = p.window > 0 ? max(0, pos0 + tile_start - p.window + 1) : 0;
+  const int hi = pos0 + tile_start + rows_here - 1;
+  const int tile_lo = lo / BN, tile_hi = hi / BN;
+
+  for (int c = threadIdx.x; c < BM * CHUNKS; c += THREADS) {
+    const int row = c / CHUNKS, chunk = c - row * CHUNKS;
+    const bool valid = row < rows_here;
+    const bf16* src = p.q + (static_cast<size_t>(start + tile_start + (valid ? row : 0)) * p.num_heads + head) * D + chunk * 8;
+    cp_async16(q_tile + row * ROW + chunk * 8, src, valid);
+  }
+  load_kv_tile(k_tiles, v_tiles, p, table, kv_head, tile_lo * BN, lo, hi);
+  cp_async_commit();
+
+  int first[2], last[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int t = tile_start + warp * 16 + (lane >> 2) + 8 * r;
+    last[r] = t < q_len ? pos0 + t : -1;
+    first[r] = p.window > 0 ? max(0, last[r] - p.window + 1) : 0;
+  }
+  float o[DTILES][4];
+#pragma unroll
+  for (int j = 0; j < DTILES; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
+  float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.f, 0.f};
+  unsigned q_frag[Q_IN_REGS ? KSTEPS : 1][4];
+  const bf16* q_rows = q_tile + warp * 16 * ROW;
+
+  for (int tile = tile_lo; tile <= tile_hi; ++tile) {
+    const int buffer = (tile - tile_lo) & 1;
+    if (tile < tile_hi) {
+      load_kv_tile(k_tiles + (buffer ^ 1) * BN * ROW, v_tiles + (buffer ^ 1) * BN * ROW, p, table, kv_head,
+                   (tile + 1) * BN, lo, hi);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    if (Q_IN_REGS && tile == tile_lo) {
+#pragma unroll
+      for (int kk = 0; kk < KSTEPS; ++kk)
+        ldmatrix_x4(q_frag[Q_IN_REGS ? kk : 0], q_rows + ((lane & 7) + 8 * ((lane >> 3) & 1)) * ROW + kk * 16 + 8 * (lane >> 4));
+    }
+    // a warp whose rows all end before this tile has nothing to add
+    const int warp_last = pos0 + min(q_len, tile_start + warp * 16 + 16) - 1;
+    const bool warp_active = tile_start + warp * 16 < q_len && tile * BN <= warp_last;
+    if (warp_active) {
+      float s[BN / 8][4];
+#pragma unroll
+      for (int j = 0; j < BN / 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+      const bf16* k_tile = k_tiles + buffer * BN * ROW;
+      const bf16* v_tile = v_tiles + buffer * BN * ROW;
+      scores<BN / 8>(s, q_frag, q_rows, k_tile, 0, lane);
+      softmax_update<BN / 8>(s, o, row_max, row_sum, first, last, tile * BN, p.scale_log2, lane);
+      accumulate<BN / 8>(o, s, v_tile, 0, lane);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 1);
+    row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 2);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int t = tile_start + warp * 16 + (lane >> 2) + 8 * r;
+    if (t >= q_len) continue;
+    const float inv = row_sum[r] > 0.f ? 1.0f / row_sum[r] : 0.f;
+    bf16* dst = p.out + (static_cast<size_t>(start + t) * p.num_heads + head) * D + (lane & 3) * 2;
+#pragma unroll
+    for (int j = 0; j < DTILES; ++j)
+      *reinterpret_cast<__nv_bfloat162*>(dst + j * 8) = __floats2bfloat162_rn(o[j][2 * r] * inv, o[j][2 * r + 1] * inv);
+  }
+}
+
+// ------------------------------------------------------------- single tokens
+__global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);           // [16][ROW]
+  bf16* k_tiles = q_tile + 16 * ROW;                          // [2][BN][ROW]
+  bf16* v_tiles = k_tiles + 2 * BN * ROW;
+  const int seq = blockIdx.z, split = blockIdx.x;
+  const int group = p.num_heads / p.num_kv_heads;
+  const int row_tiles = (group + 15) / 16;
+  const int kv_head = blockIdx.y / row_tiles, row_tile = blockIdx.y - kv_head * row_tiles;
+  const int start = p.q_start[seq];
+  if (p.q_start[seq + 1] - start != 1) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int last_key = p.ctx_len[seq] - 1;
+  const int first_key = p.window > 0 ? max(0, last_key - p.window + 1) : 0;
+  const int* table = p.block_table + static_cast<size_t>(seq) * p.max_blocks;
+  const int head0 = kv_head * group + row_tile * 16;
+  const int rows_here = min(16, group - row_tile * 16);
+  const int tile_lo = first_key / BN, tile_hi = last_key / BN;
+  const int per_split = (tile_hi - tile_lo + p.splits) / p.splits;
+  const int my_lo = tile_lo + split * per_split, my_hi = min(tile_hi, my_lo + per_split - 1);
+
+  float o[DTILES][4];
+#pragma unroll
+  for (int j = 0; j < DTILES; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
+  float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.f, 0.f};
+
+  if (my_lo <= my_hi) {
+    for (int c = threadIdx.x; c < 16 * CHUNKS; c += THREADS) {
+      const int row = c / CHUNKS, chunk = c - row * CHUNKS;
+      const bool valid = row < rows_here;
+      const bf16* src = p.q + (static_cast<size_t>(start) * p.num_heads + head0 + (valid ? row : 0)) * D + chunk * 8;
+      cp_async16(q_tile + row * ROW + chunk * 8, src, valid);
+    }
+    load_kv_tile(k_tiles, v_tiles, p, table, kv_head, my_lo * BN, first_key, last_key);
+    cp_async_commit();
+    int first[2] = {first_key, first_key}, last[2] = {last_key, last_key};
+    unsigned q_frag[Q_IN_REGS ? KSTEPS : 1][4];
+    for (int tile = my_lo; tile <= my_hi; ++tile) {
+      const int buffer = (tile - my_lo) & 1;
+      if (tile < my_hi) {
+        load_kv_tile(k_tiles + (buffer ^ 1) * BN * ROW, v_tiles + (buffer ^ 1) * BN * ROW, p, table, kv_head,
+                     (tile + 1) * BN, first_key, last_key);
+        cp_async_commit();
+        cp_async_wait<1>();
+      } else {
+        cp_async_wait<0>();
+      }
+      __syncthreads();
+      if (Q_IN_REGS && tile == my_lo) {
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk)
+          ldmatrix_x4(q_frag[Q_IN_REGS ? kk : 0], q_tile + ((lane & 7) + 8 * ((lane >> 3) & 1)) * ROW + kk * 16 + 8 * (lane >> 4));
+      }
+      const int key0 = warp * 16;
+      if (tile * BN + key0 <= last_key && tile * BN + key0 + 15 >= first_key) {
+        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        scores<2>(s, q_frag, q_tile, k_tiles + buffer * BN * ROW, key0, lane);
+        softmax_update<2>(s, o, row_max, row_sum, first, last, tile * BN + key0, p.scale_log2, lane);
+        accumulate<2>(o, s, v_tiles + buffer * BN * ROW, key0, lane);
+      }
+      __syncthreads();
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 1);
+    row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 2);
+  }
+  // combine the four warps' states through shared memory (the tiles are no longer needed)
+  __syncthreads();
+  float* warp_o = reinterpret_cast<float*>(smem_raw);         // [4][16][D]
+  float* warp_ml = warp_o + 4 * 16 * D;                       // [4][16][2]
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = (lane >> 2) + 8 * r;
+#pragma unroll
+    for (int j = 0; j < DTILES; ++j) {
+      float* dst = warp_o + (warp * 16 + row) * D + j * 8 + (lane & 3) * 2;
+      dst[0] = o[j][2 * r];
+      dst[1] = o[j][2 * r + 1];
+    }
+    if ((lane & 3) == 0) {
+      warp_ml[(warp * 16 + row) * 2] = row_max[r];
+      warp_ml[(warp * 16 + row) * 2 + 1] = row_sum[r];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < rows_here * D; idx += THREADS) {
+    const int row = idx / D, d = idx - row * D;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) m = fmaxf(m, warp_ml[(w * 16 + row) * 2]);
+    float total = 0.f, sum = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float wm = warp_ml[(w * 16 + row) * 2];
+      const float weight = wm == -INFINITY ? 0.f : exp2f(wm - m);
+      total += weight * warp_o[(w * 16 + row) * D + d];
+      sum += weight * warp_ml[(w * 16 + row) * 2 + 1];
+    }
+    const size_t slot = (static_cast<size_t>(seq) * p.num_heads + head0 + row) * p.splits + split;
+    p.partial_out[slot * D + d] = total;
+    if (d == 0) {
+      p.partial_ml[slot * 2] = m;
+      p.partial_ml[slot * 2 + 1] = sum;
+    }
+  }
+}
+
+__global__ void combine_splits_kernel(const Params p) {
+  const int seq = blockIdx.x / p.num_heads, head = blockIdx.x - seq * p.num_heads;
+  const int start = p.q_start[seq];
+  if (p.q_start[seq + 1] - start != 1) return;
+  const size_t slot0 = (static_cast<size_t>(seq) * p.num_heads + head) * p.splits;
+  float m = -INFINITY;
+  for (int s = 0; s < p.splits; ++s) m = fmaxf(m, p.partial_ml[(slot0 + s) * 2]);
+  float sum = 0.f;
+  for (int s = 0; s < p.splits; ++s) {
+    const float sm = p.partial_ml[(slot0 + s) * 2];
+    if (sm != -INFINITY) sum += exp2f(sm - m) * p.partial_ml[(slot0 + s) * 2 + 1];
+  }
+  const float inv = sum > 0.f ? 1.0f / sum : 0.f;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float total = 0.f;
+    for (int s = 0; s < p.splits; ++s) {
+      const float sm = p.partial_ml[(slot0 + s) * 2];
+      if (sm != -INFINITY) total += exp2f(sm - m) * p.partial_out[(slot0 + s) * D + d];
+    }
+    p.out[(static_cast<size_t>(start) * p.num_heads + head) * D + d] = __float2bfloat16_rn(total * inv);
+  }
+}
+
+constexpr size_t PORTIONS_SMEM = sizeof(bf16) * (BM * ROW + 4 * BN * ROW);
+constexpr size_t SINGLE_TILES_SMEM = sizeof(bf16) * (16 * ROW + 4 * BN * ROW);
+constexpr size_t SINGLE_MERGE_SMEM = sizeof(float) * (4 * 16 * D + 4 * 16 * 2);
+constexpr size_t SINGLE_SMEM = SINGLE_TILES_SMEM > SINGLE_MERGE_SMEM ? SINGLE_TILES_SMEM : SINGLE_MERGE_SMEM;
+
+}  // namespace bf16attn
+
+// Scratch the single-token path needs, in floats: partial outputs and (max, sum) pairs.
+SHRIKE_API long long shrike_attention_bf16_scratch_floats(int num_seqs, int num_heads, int splits) {
+  return static_cast<long long>(num_seqs) * num_heads * splits * (bf16attn::D + 2);
+}
+
+// has_single / has_portions: whether the batch holds rows with q_len == 1 / q_len > 1
+// (known on the host); max_q_len bounds the portions grid.  scratch holds
+// shrike_attention_bf16_scratch_floats(num_seqs, num_heads, splits) floats when has_single.
+SHRIKE_API int shrike_paged_attention_bf16(const void* q, const void* k_cache, const void* v_cache,
+                                           const int* block_table, int max_blocks, const int* q_start,
+                                           const int* ctx_len, int num_seqs, int num_heads, int num_kv_heads,
+                                           int page_size, int num_pages, float scale, int window, void* out,
+                                           int has_single, int has_portions, int max_q_len, int splits,
+                                           float* scratch, cudaStream_t stream) {
+  using namespace bf16attn;
+  if (num_seqs <= 0) return SHRIKE_OK;
+  if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || page_size <= 0 || max_blocks <= 0 ||
+      num_seqs > 65535 || num_heads > 65535)
+    return SHRIKE_BAD_ARGUMENT;
+  if (has_single && (splits < 1 || scratch == nullptr)) return SHRIKE_BAD_ARGUMENT;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e1 = cudaFuncSetAttribute(portions_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(PORTIONS_SMEM));
+    cudaError_t e2 = cudaFuncSetAttribute(single_token_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SINGLE_SMEM));
+    if (e1 != cudaSuccess || e2 != cudaSuccess) return static_cast<int>(e1 != cudaSuccess ? e1 : e2);
+    configured = true;
+  }
+  Params p;
+  p.q = static_cast<const bf16*>(q);
+  p.k_cache = static_cast<const bf16*>(k_cache);
+  p.v_cache = static_cast<const bf16*>(v_cache);
+  p.block_table = block_table;
+  p.q_start = q_start;
+  p.ctx_len = ctx_len;
+  p.out = static_cast<bf16*>(out);
+  p.max_blocks = max_blocks;
+  p.num_heads = num_heads;
+  p.num_kv_heads = num_kv_heads;
+  p.page_size = page_size;
+  p.num_pages = num_pages;
+  p.window = window;
+  p.splits = has_single ? splits : 1;
+  p.skip_single = has_single ? 1 : 0;
+  p.scale_log2 = scale * LOG2E;
+  p.partial_out = scratch;
+  p.partial_ml = scratch ? scratch + static_cast<size_t>(num_seqs) * num_heads * p.splits * D : nullptr;
+  if (has_single) {
+    const int group = num_heads / num_kv_heads;
+    const dim3 grid(p.splits, num_kv_heads * ((group + 15) / 16), num_seqs);
+    single_token_kernel<<<grid, THREADS, SINGLE_SMEM, stream>>>(p);
+    combine_splits_kernel<<<num_seqs * num_heads, D >= 128 ? 128 : 64, 0, stream>>>(p);
+  }
+  if (has_portions) {
+    const dim3 grid((max_q_len + BM - 1) / BM, num_heads, num_seqs);
+    portions_kernel<<<grid, THREADS, PORTIONS_SMEM, stream>>>(p);
+  }
+  return shrike_launch_status();
+}

@@ -25,6 +25,7 @@ class StepEntry:
     tokens: list[int]
     start: int
     want: list[int] = field(default_factory=list)
+    sampling: tuple | None = None  # (temperature, top_p, seed) for this entry's wanted rows
 
 
 @dataclass
@@ -49,10 +50,15 @@ class StepContext:
     groups: list[GroupView]
     storage: object  # cache.storage.CacheStorage
     max_q_len: int
+    min_q_len: int
     max_ctx_len: int
     q_lens: list[int]
     starts: list[int]
     slots: list[int]  # host copy of state_slot
+    all_single: bool = False  # every entry brings exactly one token
+    sample_temperature: torch.Tensor | None = None  # float32 [R], when every wanted row is sampled
+    sample_top_p: torch.Tensor | None = None  # float32 [R]
+    sample_seed: torch.Tensor | None = None  # int64 [R]
 
 
 class BatchBuilder:
@@ -67,6 +73,7 @@ class BatchBuilder:
         self._events: list = []
         self._turn = 0
         self._dev = None
+        self.generation = 0  # grows when the device buffer moves: captured launch sequences are stale then
 
     def _staging(self, count: int):
         pinned = self.device.type == "cuda"
@@ -75,6 +82,7 @@ class BatchBuilder:
             self._host = [torch.empty(capacity, dtype=torch.int32, pin_memory=pinned) for _ in range(2)]
             self._events = [None, None]
             self._dev = torch.empty(capacity, dtype=torch.int32, device=self.device)
+            self.generation += 1
         self._turn ^= 1
         event = self._events[self._turn]
         if event is not None:
@@ -99,8 +107,12 @@ class BatchBuilder:
                         f"entry holds {table.length} pages in group {g} but its context of {ctx} needs {need}"
                     )
                 max_blocks[g] = max(max_blocks[g], need)
+        # table widths grow in powers of two, so that the layout of a decode batch (and a
+        # launch sequence captured for it) stays the same while contexts grow
+        max_blocks = [max(8, 1 << (mb - 1).bit_length()) for mb in max_blocks]
+        sampled = r > 0 and all(e.sampling is not None for e in entries if e.want)
 
-        sizes = [n, n, n, s + 1, s, s, r]
+        sizes = [2 * r, r, r, n, n, n, s + 1, s, s, r]
         for g in range(self.num_groups):
             sizes += [n, s * max_blocks[g]]
         offsets = np.concatenate([[0], np.cumsum(sizes)])
@@ -108,7 +120,8 @@ class BatchBuilder:
         host = self._staging(total)
         flat = host.numpy()
         parts = [flat[offsets[i]: offsets[i + 1]] for i in range(len(sizes))]
-        ids, pos, seq_of, q_start, ctx_arr, slot_arr, out_rows = parts[:7]
+        seeds, temps, top_ps = parts[0].view(np.int64), parts[1].view(np.float32), parts[2].view(np.float32)
+        ids, pos, seq_of, q_start, ctx_arr, slot_arr, out_rows = parts[3:10]
 
         cursor = 0
         row = 0
@@ -125,12 +138,14 @@ class BatchBuilder:
                 if not 0 <= w < q:
                     raise ValueError(f"wanted place {w} is outside the entry's {q} tokens")
                 out_rows[row] = cursor + w
+                if sampled:
+                    temps[row], top_ps[row], seeds[row] = e.sampling
                 row += 1
             cursor += q
 
         for g in range(self.num_groups):
-            slots = parts[7 + 2 * g]
-            table_flat = parts[8 + 2 * g]
+            slots = parts[10 + 2 * g]
+            table_flat = parts[11 + 2 * g]
             table_flat[:] = -1
             table2d = table_flat.reshape(s, max_blocks[g])
             cursor = 0
@@ -154,13 +169,17 @@ class BatchBuilder:
             self._events[self._turn] = event
         views = [dev[int(offsets[i]): int(offsets[i + 1])] for i in range(len(sizes))]
         groups = [
-            GroupView(views[7 + 2 * g], views[8 + 2 * g].view(s, max_blocks[g]), max_blocks[g])
+            GroupView(views[10 + 2 * g], views[11 + 2 * g].view(s, max_blocks[g]), max_blocks[g])
             for g in range(self.num_groups)
         ]
         return StepContext(
             num_tokens=n, num_seqs=s, num_rows=r,
-            token_ids=views[0], positions=views[1], seq_of_token=views[2], q_start=views[3],
-            ctx_len=views[4], state_slot=views[5], out_rows=views[6], groups=groups,
-            storage=self.storage, max_q_len=max(q_lens), max_ctx_len=max(ctx_lens),
+            token_ids=views[3], positions=views[4], seq_of_token=views[5], q_start=views[6],
+            ctx_len=views[7], state_slot=views[8], out_rows=views[9], groups=groups,
+            storage=self.storage, max_q_len=max(q_lens), min_q_len=min(q_lens), max_ctx_len=max(ctx_lens),
             q_lens=q_lens, starts=starts, slots=[e.cache.slot for e in entries],
+            all_single=max(q_lens) == 1,
+            sample_temperature=views[1].view(torch.float32) if sampled else None,
+            sample_top_p=views[2].view(torch.float32) if sampled else None,
+            sample_seed=views[0].view(torch.int64) if sampled else None,
         )

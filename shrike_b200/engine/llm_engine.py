@@ -166,12 +166,20 @@ class LLMEngine:
         for request, num_new in batch:
             start = request.num_computed_tokens
             reaches_end = start + num_new >= request.num_tokens
-            entries.append(StepEntry(request.cache, request.token_ids[start: start + num_new], start,
-                                     [num_new - 1] if reaches_end else []))
+            sampling = None
             if reaches_end:
+                params = request.sampling
+                sampling = (params.temperature, params.top_p,
+                            step_seed(self._request_seed[request.req_id], request.num_tokens))
                 sampled.append(request)
-        logits = self.runner.step(entries)
-        tokens = self._sample(logits, sampled) if sampled else []
+            entries.append(StepEntry(request.cache, request.token_ids[start: start + num_new], start,
+                                     [num_new - 1] if reaches_end else [], sampling))
+        if sampled:
+            _logits, drawn = self.runner.step(entries, sample=True)
+            tokens = drawn.tolist()
+        else:
+            self.runner.step(entries)
+            tokens = []
         self.scheduler.postprocess(batch)
 
         outputs: list[StepOutput] = []
@@ -190,22 +198,6 @@ class LLMEngine:
                 self._request_seed.pop(request.req_id, None)
         self.stats.steps += 1
         return outputs
-
-    def _sample(self, logits: torch.Tensor, requests: list[Request]) -> list[int]:
-        rows = len(requests)
-        pinned = self.device.type == "cuda"
-        floats = torch.empty(2 * rows, dtype=torch.float32, pin_memory=pinned)
-        seeds = torch.empty(rows, dtype=torch.int64, pin_memory=pinned)
-        f, s = floats.numpy(), seeds.numpy()
-        for row, request in enumerate(requests):
-            f[row] = request.sampling.temperature
-            f[rows + row] = request.sampling.top_p
-            s[row] = step_seed(self._request_seed[request.req_id], request.num_tokens)
-        floats_dev = floats.to(self.device, non_blocking=True)
-        seeds_dev = seeds.to(self.device, non_blocking=True)
-        out = self.runner.runtime.buffer("sampled", (rows,), torch.int32)
-        self.ops.sample(logits, floats_dev[:rows], floats_dev[rows:], seeds_dev, out)
-        return out.tolist()
 
     def generate(self, prompts, sampling, chat: bool = True) -> list[list[int]]:
         """Offline batch API (engine.py:166-183): generated token ids per prompt."""

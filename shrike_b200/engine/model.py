@@ -25,6 +25,7 @@ class Runtime:
         self.device = torch.device(device)
         self.act_dtype = act_dtype
         self._buffers: dict[str, torch.Tensor] = {}
+        self.generation = 0  # grows when a buffer moves
 
     def buffer(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
         count = 1
@@ -35,6 +36,7 @@ class Runtime:
             capacity = count if held is None or held.dtype != dtype else max(count, 2 * held.numel())
             held = torch.empty(max(capacity, 1), dtype=dtype, device=self.device)
             self._buffers[name] = held
+            self.generation += 1
         return held[:count].view(shape)
 
     def reserve(self, name: str, count: int, dtype: torch.dtype) -> None:

@@ -56,8 +56,60 @@ class ModelRunner:
             self.groups, page_size, num_pages, state_needs, max_slots, self.dtype, self.device
         )
         self.builder = BatchBuilder(page_size, len(self.groups), self.device, self.storage)
+        self.use_graphs = True
+        self._graphs: dict = {}
+
+    # ---- the step ---------------------------------------------------------------
+    def _run(self, ctx, sample: bool):
+        logits = self.model.forward(ctx)
+        tokens = None
+        if sample:
+            tokens = self.runtime.buffer("sampled", (ctx.num_rows,), torch.int32)
+            self.ops.sample(logits, ctx.sample_temperature, ctx.sample_top_p, ctx.sample_seed, tokens)
+        return logits, tokens
+
+    def _generation(self):
+        return (self.runtime.generation, self.builder.generation, getattr(self.ops, "generation", 0))
 
     @torch.inference_mode()
-    def step(self, entries: list[StepEntry]) -> torch.Tensor:
+    def step(self, entries: list[StepEntry], sample: bool = False):
+        """Runs the entries' tokens as one batch.  Returns float32 logits [wanted, vocab];
+        with `sample=True` (every entry with wanted rows carries `sampling`) returns
+        (logits, int32 tokens [wanted]) instead, the tokens drawn by the sampling kernel.
+
+        A batch of single tokens that all want their logits is the steady state of
+        decoding; its launch sequence is captured once per (batch size, table width) as a
+        CUDA graph and replayed afterwards, because at small batch the step is bound by
+        launch latency otherwise (the remedy shrike's README names for its own per-layer
+        dispatch cost)."""
         ctx = self.builder.build(entries)
-        return self.model.forward(ctx)
+        if sample and ctx.sample_seed is None:
+            raise ValueError("sample=True needs `sampling` on every entry that wants logits")
+        graphable = (
+            self.use_graphs and self.device.type == "cuda" and ctx.all_single
+            and ctx.num_rows == ctx.num_seqs and all(e.want == [0] for e in entries)
+        )
+        if not graphable:
+            logits, tokens = self._run(ctx, sample)
+            return (logits, tokens) if sample else logits
+        key = (ctx.num_seqs, tuple(g.max_blocks for g in ctx.groups), sample)
+        held = self._graphs.get(key)
+        if held is not None and held[0] == self._generation():
+            held[1].replay()
+            self.ops.launches += held[4]
+            self.ops.library_calls += held[5]
+            return (held[2], held[3]) if sample else held[2]
+        # first time (or buffers moved): run eagerly for this step's result, then capture
+        logits, tokens = self._run(ctx, sample)
+        generation = self._generation()
+        before = (self.ops.launches, self.ops.library_calls)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            g_logits, g_tokens = self._run(ctx, sample)
+        counted = (self.ops.launches - before[0], self.ops.library_calls - before[1])
+        self.ops.launches, self.ops.library_calls = before
+        if generation == self._generation():
+            if len(self._graphs) >= 64:
+                self._graphs.pop(next(iter(self._graphs)))
+            self._graphs[key] = (generation, graph, g_logits, g_tokens, counted[0], counted[1])
+        return (logits, tokens) if sample else logits

@@ -130,6 +130,7 @@ def load_library(name: str, sources, defines=None, extra_flags=()) -> ctypes.CDL
 
 # The libraries of this package.
 CORE_SOURCES = ["elementwise.cu", "gemm_fp32.cu", "sampling.cu"]
+ATTENTION_SOURCES = ["attention_generic.cu", "attention_bf16.cu"]
 
 
 def core_library() -> ctypes.CDLL:
@@ -137,14 +138,13 @@ def core_library() -> ctypes.CDLL:
 
 
 def attention_library(head_dim: int) -> ctypes.CDLL:
-    return load_library(f"shrike_attention_d{head_dim}", ["attention_generic.cu"],
-                        {"SHRIKE_HEAD_DIM": head_dim})
+    return load_library(f"shrike_attention_d{head_dim}", ATTENTION_SOURCES, {"SHRIKE_HEAD_DIM": head_dim})
 
 
 def build_all(head_dims=(16, 32, 48, 64, 128, 256)) -> list[Path]:
     """Everything the package can load, for the usual head sizes."""
     built = [compile_library("shrike_core", CORE_SOURCES)]
     for head_dim in head_dims:
-        built.append(compile_library(f"shrike_attention_d{head_dim}", ["attention_generic.cu"],
+        built.append(compile_library(f"shrike_attention_d{head_dim}", ATTENTION_SOURCES,
                                      {"SHRIKE_HEAD_DIM": head_dim}))
     return built

@@ -57,6 +57,8 @@ class CudaOps:
         self.core = build.core_library()
         self._declare_core()
         self._attention = {}
+        self._scratch = None     # partial results of split single-token attention
+        self.generation = 0      # grows when the scratch moves
         self.launches = 0        # launches of this package's own kernels
         self.library_calls = 0   # matrix products handed to cuBLAS
         # library matrix products keep float32 accumulation end to end: no TF32 for float32
@@ -87,6 +89,10 @@ class CudaOps:
                 [_P, _P, _P, _P, _I, _P, _P, _P] + [_I] * 6 + [_F, _I, _P, _P]
             )
             lib.shrike_paged_attention_generic.restype = _I
+            lib.shrike_paged_attention_bf16.argtypes = (
+                [_P, _P, _P, _P, _I, _P, _P] + [_I] * 5 + [_F, _I, _P] + [_I] * 4 + [_P, _P]
+            )
+            lib.shrike_paged_attention_bf16.restype = _I
             self._attention[head_dim] = lib
         return lib
 
@@ -178,7 +184,9 @@ class CudaOps:
 
     def paged_attention(self, q, keys, values, block_table, q_start, ctx_len, seq_of_token,
                         num_heads, num_kv_heads, head_dim, scale, window, out,
-                        max_q_len=0, max_ctx_len=0):
+                        max_q_len=0, max_ctx_len=0, min_q_len=0):
+        """Attention of the batch's new tokens over the paged cache.  `max_q_len` and
+        `min_q_len` are the longest and shortest entry of the batch (0: not known)."""
         _dense(q, self.dtype, "q")
         _dense(keys, self.dtype, "key cache")
         _dense(values, self.dtype, "value cache")
@@ -186,11 +194,35 @@ class CudaOps:
         if keys.shape[2] != num_kv_heads or keys.shape[3] != head_dim:
             raise KernelError(f"key cache {tuple(keys.shape)} does not fit {num_kv_heads} heads of {head_dim}")
         lib = self._attention_lib(head_dim)
-        self.launches += 1
-        _check(lib.shrike_paged_attention_generic(
-            _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), block_table.shape[1], _ptr(q_start),
-            _ptr(ctx_len), _ptr(seq_of_token), self.code, q.shape[0], num_heads, num_kv_heads,
-            keys.shape[1], keys.shape[0], scale, window or 0, _ptr(out), self._stream()), "paged_attention")
+        num_seqs, max_blocks = block_table.shape
+        page_size, num_pages = keys.shape[1], keys.shape[0]
+        if self.dtype == torch.float32:
+            self.launches += 1
+            _check(lib.shrike_paged_attention_generic(
+                _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), max_blocks, _ptr(q_start),
+                _ptr(ctx_len), _ptr(seq_of_token), self.code, q.shape[0], num_heads, num_kv_heads,
+                page_size, num_pages, scale, window or 0, _ptr(out), self._stream()), "paged_attention")
+            return
+        if max_q_len < 1:
+            raise KernelError("paged_attention in bfloat16 needs max_q_len, the longest entry of the batch")
+        has_single = min_q_len <= 1
+        has_portions = max_q_len > 1
+        splits, scratch = 1, None
+        if has_single:
+            row_tiles = -(-(num_heads // num_kv_heads) // 16)
+            tiles = max(1, -(-(max_blocks * page_size) // 64))
+            splits = max(1, min(tiles, 32, 592 // max(1, num_seqs * num_kv_heads * row_tiles)))
+            need = num_seqs * num_heads * splits * (head_dim + 2)
+            if self._scratch is None or self._scratch.numel() < need:
+                self._scratch = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=self.device)
+                self.generation += 1
+            scratch = self._scratch
+        self.launches += (2 if has_single else 0) + (1 if has_portions else 0)
+        _check(lib.shrike_paged_attention_bf16(
+            _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), max_blocks, _ptr(q_start), _ptr(ctx_len),
+            num_seqs, num_heads, num_kv_heads, page_size, num_pages, scale, window or 0, _ptr(out),
+            int(has_single), int(has_portions), max_q_len, splits, _ptr(scratch), self._stream()),
+            "paged_attention_bf16")
 
     def silu_mul(self, gate_up, out):
         _dense(gate_up, self.dtype, "gate_up")
