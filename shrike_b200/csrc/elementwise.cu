@@ -34,8 +34,35 @@ SHRIKE_API int shrike_embed(const int* ids, const void* table, int table_dtype, 
 
 // ------------------------------------------------- residual add + RMSNorm
 // One block per output row.  GATHER: the row comes from `rows`, the residual is
-// not written back (used for the final norm on the wanted rows only).
-template <typename TD, typename TO, bool HAS_DELTA, bool GATHER>
+// not written back (used for the final norm on the wanted rows only).  Each thread
+// keeps its elements in registers between the sum of squares and the scaling, so a
+// row is read once; VEC = 4 uses 16-byte accesses (width a multiple of 4).
+constexpr int NORM_MAX_PER_THREAD = 8;  // elements (VEC = 1) or float4 groups (VEC = 4) a thread may hold
+
+template <typename TD> __device__ __forceinline__ void load4(const TD* p, float (&v)[4]);
+template <> __device__ __forceinline__ void load4<float>(const float* p, float (&v)[4]) {
+  const float4 t = *reinterpret_cast<const float4*>(p);
+  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+template <> __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 t = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&t.x);
+  const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
+  v[0] = __low2float(lo); v[1] = __high2float(lo); v[2] = __low2float(hi); v[3] = __high2float(hi);
+}
+template <typename TO> __device__ __forceinline__ void store4(TO* p, const float (&v)[4]);
+template <> __device__ __forceinline__ void store4<float>(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[4]) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 t;
+  t.x = *reinterpret_cast<const unsigned*>(&lo);
+  t.y = *reinterpret_cast<const unsigned*>(&hi);
+  *reinterpret_cast<uint2*>(p) = t;
+}
+
+template <typename TD, typename TO, bool HAS_DELTA, bool GATHER, int VEC>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
                                    const int* __restrict__ rows, const float* __restrict__ weight,
                                    float eps, TO* __restrict__ out, int width) {
@@ -45,35 +72,73 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
   float* x = resid + static_cast<size_t>(row) * width;
   const TD* d = HAS_DELTA ? delta + static_cast<size_t>(row) * width : nullptr;
   TO* y = out + static_cast<size_t>(out_row) * width;
+  const int groups = width / VEC;
 
+  float held[NORM_MAX_PER_THREAD][VEC];
   float sum_sq = 0.f;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    float v = x[i];
-    if (HAS_DELTA) {
-      v = __fadd_rn(v, to_float(d[i]));
-      if (!GATHER) x[i] = v;
+#pragma unroll
+  for (int it = 0; it < NORM_MAX_PER_THREAD; ++it) {
+    const int g = threadIdx.x + it * blockDim.x;
+    if (g < groups) {
+      if (VEC == 4) {
+        float v[4], dv[4];
+        load4<float>(x + g * 4, v);
+        if (HAS_DELTA) {
+          load4<TD>(d + g * 4, dv);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) v[i] = __fadd_rn(v[i], dv[i]);
+          if (!GATHER) store4<float>(x + g * 4, v);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          held[it][i % VEC] = v[i];
+          sum_sq = fmaf(v[i], v[i], sum_sq);
+        }
+      } else {
+        float v = x[g];
+        if (HAS_DELTA) {
+          v = __fadd_rn(v, to_float(d[g]));
+          if (!GATHER) x[g] = v;
+        }
+        held[it][0] = v;
+        sum_sq = fmaf(v, v, sum_sq);
+      }
     }
-    sum_sq = fmaf(v, v, sum_sq);
   }
   const float total = block_sum(sum_sq, scratch);
   const float inv = 1.0f / sqrtf(total / static_cast<float>(width) + eps);
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    float v = x[i];
-    if (HAS_DELTA && GATHER) v = __fadd_rn(v, to_float(d[i]));
-    y[i] = from_float<TO>(__fmul_rn(__fmul_rn(v, inv), weight[i]));
+#pragma unroll
+  for (int it = 0; it < NORM_MAX_PER_THREAD; ++it) {
+    const int g = threadIdx.x + it * blockDim.x;
+    if (g < groups) {
+      if (VEC == 4) {
+        float w[4], r[4];
+        load4<float>(weight + g * 4, w);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) r[i] = __fmul_rn(__fmul_rn(held[it][i % VEC], inv), w[i]);
+        store4<TO>(y + g * 4, r);
+      } else {
+        y[g] = from_float<TO>(__fmul_rn(__fmul_rn(held[it][0], inv), weight[g]));
+      }
+    }
   }
 }
 
 template <typename TD, typename TO, bool HAS_DELTA>
-static void launch_add_rmsnorm(float* resid, const void* delta, const int* rows, const float* weight,
-                               float eps, void* out, int n, int width, cudaStream_t stream) {
-  const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-  if (rows)
-    add_rmsnorm_kernel<TD, TO, HAS_DELTA, true><<<n, threads, 0, stream>>>(
-        resid, static_cast<const TD*>(delta), rows, weight, eps, static_cast<TO*>(out), width);
-  else
-    add_rmsnorm_kernel<TD, TO, HAS_DELTA, false><<<n, threads, 0, stream>>>(
-        resid, static_cast<const TD*>(delta), rows, weight, eps, static_cast<TO*>(out), width);
+static int launch_add_rmsnorm(float* resid, const void* delta, const int* rows, const float* weight,
+                              float eps, void* out, int n, int width, cudaStream_t stream) {
+  const bool vec = width % 4 == 0;
+  const int groups = vec ? width / 4 : width;
+  int threads = 128;
+  while (threads < 1024 && threads * 2 <= ((groups + 31) / 32) * 32) threads *= 2;
+  if (static_cast<long long>(threads) * NORM_MAX_PER_THREAD < groups) return SHRIKE_BAD_ARGUMENT;
+#define SHRIKE_NORM_LAUNCH(G, V)                                                                   \
+  add_rmsnorm_kernel<TD, TO, HAS_DELTA, G, V><<<n, threads, 0, stream>>>(                          \
+      resid, static_cast<const TD*>(delta), rows, weight, eps, static_cast<TO*>(out), width)
+  if (rows) { if (vec) SHRIKE_NORM_LAUNCH(true, 4); else SHRIKE_NORM_LAUNCH(true, 1); }
+  else { if (vec) SHRIKE_NORM_LAUNCH(false, 4); else SHRIKE_NORM_LAUNCH(false, 1); }
+#undef SHRIKE_NORM_LAUNCH
+  return SHRIKE_OK;
 }
 
 // resid [*, width] float32 (updated in place unless rows != null); delta may be null.
@@ -84,8 +149,9 @@ SHRIKE_API int shrike_add_rmsnorm(float* resid, const void* delta, int delta_dty
   if (width <= 0) return SHRIKE_BAD_ARGUMENT;
   const bool has_delta = delta != nullptr;
   if (has_delta && delta_dtype != SHRIKE_F32 && delta_dtype != SHRIKE_BF16) return SHRIKE_BAD_ARGUMENT;
+  int status = SHRIKE_OK;
 #define SHRIKE_NORM_CASE(TD, TO, HD) \
-  launch_add_rmsnorm<TD, TO, HD>(resid, delta, rows, weight, eps, out, n, width, stream)
+  status = launch_add_rmsnorm<TD, TO, HD>(resid, delta, rows, weight, eps, out, n, width, stream)
   if (out_dtype == SHRIKE_F32) {
     if (!has_delta) SHRIKE_NORM_CASE(float, float, false);
     else if (delta_dtype == SHRIKE_F32) SHRIKE_NORM_CASE(float, float, true);
@@ -98,6 +164,7 @@ SHRIKE_API int shrike_add_rmsnorm(float* resid, const void* delta, int delta_dty
     return SHRIKE_BAD_ARGUMENT;
   }
 #undef SHRIKE_NORM_CASE
+  if (status != SHRIKE_OK) return status;  // the width exceeds what one block can hold (32768 / 8192 odd)
   return shrike_launch_status();
 }
 
@@ -131,7 +198,8 @@ SHRIKE_API int shrike_silu_mul(const void* gate_up, void* out, int dtype, int n,
 }
 
 // --------------------------------------- bias + rotary + key/value store
-// One block per token.  qkv is the float32 result of the fused projection,
+// One block per (token, head) over the q, k and v heads; one thread per rotation
+// pair.  qkv is the float32 result of the fused projection,
 // [n, (H + 2 Hkv) * D]: q heads, then k heads, then v heads.  The angle of pair j
 // is float(position) * inv_freq[j]; pair j rotates elements j and j + D/2.
 // Rotated q goes to q_out; rotated k and plain v go to the cache at slots[token]
@@ -142,68 +210,51 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const float*
                                      T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
                                      const int* __restrict__ slots, T* __restrict__ k_out, T* __restrict__ v_out,
                                      int num_heads, int num_kv_heads, int head_dim, long long num_slots) {
-  extern __shared__ float trig[];  // cos[half], sin[half]
-  const int token = blockIdx.x;
+  const int token = blockIdx.x, head = blockIdx.y;
   const int half = head_dim / 2;
   const int q_width = num_heads * head_dim, kv_width = num_kv_heads * head_dim;
   const float* row = qkv + static_cast<size_t>(token) * (q_width + 2 * kv_width);
-  const bool rotate = inv_freq != nullptr;
-  if (rotate) {
-    const float pos = static_cast<float>(positions[token]);
-    for (int j = threadIdx.x; j < half; j += blockDim.x) {
-      float s, c;
-      sincosf(__fmul_rn(pos, inv_freq[j]), &s, &c);
-      trig[j] = c;
-      trig[half + j] = s;
-    }
-  }
-  __syncthreads();
+  const bool is_q = head < num_heads, is_k = !is_q && head < num_heads + num_kv_heads;
   long long slot = -1;
-  if (k_cache != nullptr) {
+  if (!is_q && k_cache != nullptr) {
     slot = slots[token];
     if (slot < 0 || slot >= num_slots) slot = -1;  // never store outside the pool
   }
-  // q and k heads: one thread per rotation pair
-  const int rot_pairs = (num_heads + num_kv_heads) * half;
-  for (int idx = threadIdx.x; idx < rot_pairs; idx += blockDim.x) {
-    const int head = idx / half, j = idx - head * half;
-    const int lo = head * head_dim + j, hi = lo + half;  // column within [q | k]
+  const float pos = static_cast<float>(positions[token]);
+  for (int j = threadIdx.x; j < half; j += blockDim.x) {
+    const int lo = head * head_dim + j, hi = lo + half;  // columns of the row
     float a = row[lo], b = row[hi];
     if (bias != nullptr) {
       a = __fadd_rn(a, bias[lo]);
       b = __fadd_rn(b, bias[hi]);
     }
     float ra = a, rb = b;
-    if (rotate) {
-      const float c = trig[j], s = trig[half + j];
+    if (inv_freq != nullptr && (is_q || is_k)) {
+      float s, c;
+      sincosf(__fmul_rn(pos, inv_freq[j]), &s, &c);
       ra = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
       rb = __fadd_rn(__fmul_rn(b, c), __fmul_rn(a, s));
     }
-    if (head < num_heads) {
+    if (is_q) {
       T* dst = q_out + static_cast<size_t>(token) * q_width;
       dst[lo] = from_float<T>(ra);
       dst[hi] = from_float<T>(rb);
     } else {
-      const int klo = lo - q_width, khi = hi - q_width;
+      const int base = is_k ? q_width : q_width + kv_width;
+      const int clo = lo - base, chi = hi - base;  // columns within the k (or v) heads
+      T* cache = is_k ? k_cache : v_cache;
+      T* extra = is_k ? k_out : v_out;
       if (slot >= 0) {
-        T* dst = k_cache + static_cast<size_t>(slot) * kv_width;
-        dst[klo] = from_float<T>(ra);
-        dst[khi] = from_float<T>(rb);
+        T* dst = cache + static_cast<size_t>(slot) * kv_width;
+        dst[clo] = from_float<T>(ra);
+        dst[chi] = from_float<T>(rb);
       }
-      if (k_out != nullptr) {
-        T* dst = k_out + static_cast<size_t>(token) * kv_width;
-        dst[klo] = from_float<T>(ra);
-        dst[khi] = from_float<T>(rb);
+      if (extra != nullptr) {
+        T* dst = extra + static_cast<size_t>(token) * kv_width;
+        dst[clo] = from_float<T>(ra);
+        dst[chi] = from_float<T>(rb);
       }
     }
-  }
-  // v heads: bias and store
-  for (int idx = threadIdx.x; idx < kv_width; idx += blockDim.x) {
-    const int col = q_width + kv_width + idx;
-    float v = row[col];
-    if (bias != nullptr) v = __fadd_rn(v, bias[col]);
-    if (slot >= 0) v_cache[static_cast<size_t>(slot) * kv_width + idx] = from_float<T>(v);
-    if (v_out != nullptr) v_out[static_cast<size_t>(token) * kv_width + idx] = from_float<T>(v);
   }
 }
 
@@ -216,10 +267,12 @@ SHRIKE_API int shrike_rope_kv_write(const float* qkv, const float* bias, const i
   if (head_dim <= 0 || head_dim % 2 || num_heads <= 0 || num_kv_heads <= 0) return SHRIKE_BAD_ARGUMENT;
   if ((k_cache == nullptr) != (v_cache == nullptr)) return SHRIKE_BAD_ARGUMENT;
   if ((k_out == nullptr) != (v_out == nullptr)) return SHRIKE_BAD_ARGUMENT;
-  const int threads = 256;
-  const size_t smem = sizeof(float) * head_dim;
+  if (num_heads + 2 * num_kv_heads > 65535) return SHRIKE_BAD_ARGUMENT;
+  const int half = head_dim / 2;
+  const int threads = half <= 32 ? 32 : (half <= 64 ? 64 : 128);
+  const dim3 grid(n, num_heads + 2 * num_kv_heads);
 #define SHRIKE_ROPE_CASE(T)                                                                         \
-  rope_kv_write_kernel<T><<<n, threads, smem, stream>>>(                                            \
+  rope_kv_write_kernel<T><<<grid, threads, 0, stream>>>(                                            \
       qkv, bias, positions, inv_freq, static_cast<T*>(q_out), static_cast<T*>(k_cache),             \
       static_cast<T*>(v_cache), slots, static_cast<T*>(k_out), static_cast<T*>(v_out), num_heads,   \
       num_kv_heads, head_dim, num_slots)

@@ -64,19 +64,57 @@ __device__ Best block_best(Best mine, Best* scratch /* 33 entries */) {
   return scratch[32];
 }
 
+// Stage 1: the vocabulary of every row is cut into `chunks` slices; each block finds the
+// best (score, index) of its slice, the score being the logit (greedy) or
+// logit / T + Gumbel noise (sampled without top_p).  Rows with top_p < 1 are left to
+// stage 2, which needs the whole row's probabilities.
+constexpr int SLICE_THREADS = 256;
+__global__ void __launch_bounds__(SLICE_THREADS)
+sample_slices_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+                     const float* __restrict__ top_p, const long long* __restrict__ seeds,
+                     float* __restrict__ partial_value, int* __restrict__ partial_index, int vocab, int chunks) {
+  __shared__ Best best_scratch[33];
+  const int row = blockIdx.y, chunk = blockIdx.x;
+  const float temp = temperature[row];
+  if (temp != 0.f && top_p[row] < 1.0f) return;
+  const int per = (vocab + chunks - 1) / chunks;
+  const int begin = chunk * per, end = min(vocab, begin + per);
+  const float* x = logits + static_cast<size_t>(row) * vocab;
+  Best mine{-INFINITY, 0x7fffffff};
+  if (temp == 0.f) {
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) mine = better(mine, Best{x[i], i});
+  } else {
+    const float inv_temp = 1.0f / temp;
+    const unsigned long long seed = static_cast<unsigned long long>(seeds[row]);
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x)
+      mine = better(mine, Best{x[i] * inv_temp + gumbel(seed, i), i});
+  }
+  const Best top = block_best(mine, best_scratch);
+  if (threadIdx.x == 0) {
+    partial_value[static_cast<size_t>(row) * chunks + chunk] = top.value;
+    partial_index[static_cast<size_t>(row) * chunks + chunk] = top.index;
+  }
+}
+
+// Stage 2: one block per row.  Rows handled by stage 1 only pick the best slice result;
+// rows with top_p < 1 run the whole nucleus procedure here.
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
               const float* __restrict__ top_p, const long long* __restrict__ seeds, int* __restrict__ out,
-              int vocab) {
+              const float* __restrict__ partial_value, const int* __restrict__ partial_index, int vocab,
+              int chunks) {
   __shared__ float scratch[33];
   __shared__ Best best_scratch[33];
   const int row = blockIdx.x;
   const float* x = logits + static_cast<size_t>(row) * vocab;
   const float temp = temperature[row];
+  const float nucleus = top_p[row];
 
-  if (temp == 0.f) {
+  if (temp == 0.f || nucleus >= 1.0f) {
     Best mine{-INFINITY, 0x7fffffff};
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) mine = better(mine, Best{x[i], i});
+    for (int i = threadIdx.x; i < chunks; i += blockDim.x)
+      mine = better(mine, Best{partial_value[static_cast<size_t>(row) * chunks + i],
+                               partial_index[static_cast<size_t>(row) * chunks + i]});
     const Best top = block_best(mine, best_scratch);
     if (threadIdx.x == 0) out[row] = top.index;
     return;
@@ -86,53 +124,52 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
   float local_max = -INFINITY;
   for (int i = threadIdx.x; i < vocab; i += blockDim.x) local_max = fmaxf(local_max, x[i]);
   const float row_max = block_max(local_max, scratch);
-  float threshold_bits_as_float = -1.f;  // keep p > threshold; -1 keeps everything
-  const float nucleus = top_p[row];
-  if (nucleus < 1.0f) {
-    float local_sum = 0.f;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) local_sum += expf((x[i] - row_max) * inv_temp);
-    const float total = block_sum(local_sum, scratch);
-    const float inv_total = 1.0f / total;
-    // Bisection on the bit pattern of a positive float: mass_above(lo) >= top_p and
-    // mass_above(hi) < top_p hold throughout; at the end no probability lies
-    // strictly between lo and hi, and the kept set is {p > lo}.
-    unsigned lo = 0u, hi = __float_as_uint(1.0f);  // mass_above(0) = 1 >= top_p; mass_above(1) = 0
-    while (hi - lo > 1u) {
-      const unsigned mid = lo + (hi - lo) / 2u;
-      const float cut = __uint_as_float(mid);
-      float above = 0.f;
-      for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float p = expf((x[i] - row_max) * inv_temp) * inv_total;
-        if (p > cut) above += p;
-      }
-      above = block_sum(above, scratch);
-      if (above < nucleus) hi = mid;
-      else lo = mid;
-    }
-    threshold_bits_as_float = __uint_as_float(lo);
-    if (lo == 0u) threshold_bits_as_float = -1.f;
-    Best mine{-INFINITY, 0x7fffffff};
-    const unsigned long long seed = static_cast<unsigned long long>(seeds[row]);
+  float local_sum = 0.f;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) local_sum += expf((x[i] - row_max) * inv_temp);
+  const float total = block_sum(local_sum, scratch);
+  const float inv_total = 1.0f / total;
+  // Bisection on the bit pattern of a positive float: mass_above(lo) >= top_p and
+  // mass_above(hi) < top_p hold throughout; at the end no probability lies
+  // strictly between lo and hi, and the kept set is {p > lo}.
+  unsigned lo = 0u, hi = __float_as_uint(1.0f);  // mass_above(0) = 1 >= top_p; mass_above(1) = 0
+  while (hi - lo > 1u) {
+    const unsigned mid = lo + (hi - lo) / 2u;
+    const float cut = __uint_as_float(mid);
+    float above = 0.f;
     for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
       const float p = expf((x[i] - row_max) * inv_temp) * inv_total;
-      if (p > threshold_bits_as_float) mine = better(mine, Best{x[i] * inv_temp + gumbel(seed, i), i});
+      if (p > cut) above += p;
     }
-    const Best top = block_best(mine, best_scratch);
-    if (threadIdx.x == 0) out[row] = top.index;
-    return;
+    above = block_sum(above, scratch);
+    if (above < nucleus) hi = mid;
+    else lo = mid;
   }
+  const float threshold = lo == 0u ? -1.f : __uint_as_float(lo);
   Best mine{-INFINITY, 0x7fffffff};
   const unsigned long long seed = static_cast<unsigned long long>(seeds[row]);
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x)
-    mine = better(mine, Best{x[i] * inv_temp + gumbel(seed, i), i});
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    const float p = expf((x[i] - row_max) * inv_temp) * inv_total;
+    if (p > threshold) mine = better(mine, Best{x[i] * inv_temp + gumbel(seed, i), i});
+  }
   const Best top = block_best(mine, best_scratch);
   if (threadIdx.x == 0) out[row] = top.index;
 }
 
+// How many slices stage 1 cuts a row into; scratch must hold rows * slices floats and ints.
+SHRIKE_API int shrike_sample_slices(int vocab) {
+  const int slices = (vocab + 2047) / 2048;
+  return slices < 1 ? 1 : (slices > 128 ? 128 : slices);
+}
+
 SHRIKE_API int shrike_sample(const float* logits, const float* temperature, const float* top_p,
-                             const long long* seeds, int* out, int rows, int vocab, cudaStream_t stream) {
+                             const long long* seeds, int* out, float* scratch_value, int* scratch_index,
+                             int rows, int vocab, cudaStream_t stream) {
   if (rows <= 0) return SHRIKE_OK;
-  if (vocab <= 0) return SHRIKE_BAD_ARGUMENT;
-  sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, temperature, top_p, seeds, out, vocab);
+  if (vocab <= 0 || rows > 65535 || scratch_value == nullptr || scratch_index == nullptr) return SHRIKE_BAD_ARGUMENT;
+  const int chunks = shrike_sample_slices(vocab);
+  sample_slices_kernel<<<dim3(chunks, rows), SLICE_THREADS, 0, stream>>>(logits, temperature, top_p, seeds,
+                                                                         scratch_value, scratch_index, vocab, chunks);
+  sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, temperature, top_p, seeds, out, scratch_value,
+                                                     scratch_index, vocab, chunks);
   return shrike_launch_status();
 }

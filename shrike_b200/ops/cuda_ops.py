@@ -58,6 +58,7 @@ class CudaOps:
         self._declare_core()
         self._attention = {}
         self._scratch = None     # partial results of split single-token attention
+        self._sample_scratch = None  # per-slice winners of the sampling kernel
         self.generation = 0      # grows when the scratch moves
         self.launches = 0        # launches of this package's own kernels
         self.library_calls = 0   # matrix products handed to cuBLAS
@@ -75,7 +76,9 @@ class CudaOps:
         lib.shrike_rope_kv_write.argtypes = [_P] * 10 + [_I] * 5 + [_LL, _P]
         lib.shrike_kv_write.argtypes = [_P] * 5 + [_I, _I, _I, _LL, _P]
         lib.shrike_gemm_fp32.argtypes = [_P, _P, _P, _P, _I, _I, _I, _P]
-        lib.shrike_sample.argtypes = [_P, _P, _P, _P, _P, _I, _I, _P]
+        lib.shrike_sample.argtypes = [_P, _P, _P, _P, _P, _P, _P, _I, _I, _P]
+        lib.shrike_sample_slices.argtypes = [_I]
+        lib.shrike_sample_slices.restype = _I
         for name in ("shrike_embed", "shrike_add_rmsnorm", "shrike_silu_mul", "shrike_rope_kv_write",
                      "shrike_kv_write", "shrike_gemm_fp32", "shrike_sample"):
             getattr(lib, name).restype = _I
@@ -238,6 +241,12 @@ class CudaOps:
         _dense(seeds, torch.int64, "seeds")
         _dense(out, torch.int32, "sampled tokens")
         rows, vocab = logits.shape
-        self.launches += 1
+        need = max(rows, 64) * self.core.shrike_sample_slices(vocab)
+        if self._sample_scratch is None or self._sample_scratch[0].numel() < need:
+            self._sample_scratch = (torch.empty(2 * need, dtype=torch.float32, device=self.device),
+                                    torch.empty(2 * need, dtype=torch.int32, device=self.device))
+            self.generation += 1
+        values, indices = self._sample_scratch
+        self.launches += 2
         _check(self.core.shrike_sample(_ptr(logits), _ptr(temperature), _ptr(top_p), _ptr(seeds), _ptr(out),
-                                       rows, vocab, self._stream()), "sample")
+                                       _ptr(values), _ptr(indices), rows, vocab, self._stream()), "sample")
