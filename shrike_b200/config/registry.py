@@ -45,7 +45,13 @@ def register_architecture(arch: Architecture) -> Architecture:
     return arch
 
 
+def _register_builtin() -> None:
+    """The package's own architectures register themselves on import."""
+    from .. import models  # noqa: F401
+
+
 def architecture_of(raw: dict) -> Architecture:
+    _register_builtin()
     names = raw.get("architectures")
     if not names or not isinstance(names, list):
         raise ConfigError(
