@@ -173,3 +173,64 @@ SHRIKE_API int shrike_sample(const float* logits, const float* temperature, cons
                                                      scratch_index, vocab, chunks);
   return shrike_launch_status();
 }
+
+// ------------------------------------------------------------------------------------
+// The same two kernels with their scratch in a fixed device array, for callers that
+// must not allocate (sampling_no_alloc.h says who they are and what the limits are).
+#include <mutex>
+
+#include "sampling_no_alloc.h"
+
+static __device__ __align__(256) unsigned char sample_no_alloc_scratch[SHRIKE_SAMPLE_NO_ALLOC_BYTES];
+
+namespace {
+constexpr int NO_ALLOC_MAX_DEVICES = 64;
+std::mutex no_alloc_mutex;
+void* no_alloc_address[NO_ALLOC_MAX_DEVICES] = {};
+
+// In host code `sample_no_alloc_scratch` is only a handle for the symbol, not an address a
+// kernel can use; the device address is asked for once per device, with that device current.
+int no_alloc_scratch(void** address) {
+  int device = -1;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return static_cast<int>(err);
+  if (device < 0 || device >= NO_ALLOC_MAX_DEVICES) return SHRIKE_BAD_ARGUMENT;
+  std::lock_guard<std::mutex> guard(no_alloc_mutex);
+  if (no_alloc_address[device] == nullptr) {
+    void* found = nullptr;
+    err = cudaGetSymbolAddress(&found, sample_no_alloc_scratch);
+    if (err != cudaSuccess) return static_cast<int>(err);
+    no_alloc_address[device] = found;
+  }
+  *address = no_alloc_address[device];
+  return SHRIKE_OK;
+}
+}  // namespace
+
+SHRIKE_API int shrike_sample_no_alloc(const float* logits, const float* temperature, const float* top_p,
+                                      const long long* seeds, int* out, int rows, int vocab,
+                                      cudaStream_t stream) {
+  if (rows <= 0) return SHRIKE_OK;
+  if (vocab <= 0) return SHRIKE_BAD_ARGUMENT;
+  if (rows > SHRIKE_SAMPLE_NO_ALLOC_MAX_ROWS) return SHRIKE_SAMPLE_NO_ALLOC_TOO_MANY_ROWS;
+  const int chunks = shrike_sample_slices(vocab);  // never more than SHRIKE_SAMPLE_NO_ALLOC_MAX_SLICES
+  void* base = nullptr;
+  const int status = no_alloc_scratch(&base);
+  if (status != SHRIKE_OK) return status;
+  float* values = static_cast<float*>(base);
+  int* indices = reinterpret_cast<int*>(static_cast<unsigned char*>(base) + SHRIKE_SAMPLE_NO_ALLOC_BYTES / 2);
+  sample_slices_kernel<<<dim3(chunks, rows), SLICE_THREADS, 0, stream>>>(logits, temperature, top_p, seeds,
+                                                                         values, indices, vocab, chunks);
+  sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, temperature, top_p, seeds, out, values, indices,
+                                                     vocab, chunks);
+  return shrike_launch_status();
+}
+
+SHRIKE_API const char* shrike_sample_no_alloc_message(int code) {
+  if (code == SHRIKE_OK) return "ok";
+  if (code == SHRIKE_SAMPLE_NO_ALLOC_TOO_MANY_ROWS)
+    return "shrike_sample_no_alloc: more than 256 rows in one call; the fixed scratch array holds 256 "
+           "(split the batch, or use shrike_sample with scratch of your own)";
+  if (code == SHRIKE_BAD_ARGUMENT) return "shrike_sample_no_alloc: bad argument (vocab must be positive)";
+  return cudaGetErrorString(static_cast<cudaError_t>(code));
+}
