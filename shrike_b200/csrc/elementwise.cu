@@ -62,10 +62,13 @@ template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16*
   *reinterpret_cast<uint2*>(p) = t;
 }
 
+// `delta` may be a stack of `partials` arrays (the slices of a K-split matrix product),
+// `partial_stride` elements apart; they are added in ascending order.
 template <typename TD, typename TO, bool HAS_DELTA, bool GATHER, int VEC>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
                                    const int* __restrict__ rows, const float* __restrict__ weight,
-                                   float eps, TO* __restrict__ out, int width) {
+                                   float eps, TO* __restrict__ out, int width, int partials,
+                                   long long partial_stride) {
   __shared__ float scratch[33];
   const int out_row = blockIdx.x;
   const int row = GATHER ? rows[out_row] : out_row;
@@ -85,6 +88,12 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
         load4<float>(x + g * 4, v);
         if (HAS_DELTA) {
           load4<TD>(d + g * 4, dv);
+          for (int p = 1; p < partials; ++p) {
+            float more[4];
+            load4<TD>(d + p * partial_stride + g * 4, more);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dv[i] = __fadd_rn(dv[i], more[i]);
+          }
 #pragma unroll
           for (int i = 0; i < 4; ++i) v[i] = __fadd_rn(v[i], dv[i]);
           if (!GATHER) store4<float>(x + g * 4, v);
@@ -97,7 +106,9 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
       } else {
         float v = x[g];
         if (HAS_DELTA) {
-          v = __fadd_rn(v, to_float(d[g]));
+          float dv = to_float(d[g]);
+          for (int p = 1; p < partials; ++p) dv = __fadd_rn(dv, to_float(d[p * partial_stride + g]));
+          v = __fadd_rn(v, dv);
           if (!GATHER) x[g] = v;
         }
         held[it][0] = v;
@@ -126,7 +137,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
 
 template <typename TD, typename TO, bool HAS_DELTA>
 static int launch_add_rmsnorm(float* resid, const void* delta, const int* rows, const float* weight,
-                              float eps, void* out, int n, int width, cudaStream_t stream) {
+                              float eps, void* out, int n, int width, int partials, long long partial_stride,
+                              cudaStream_t stream) {
   const bool vec = width % 4 == 0;
   const int groups = vec ? width / 4 : width;
   int threads = 128;
@@ -134,7 +146,8 @@ static int launch_add_rmsnorm(float* resid, const void* delta, const int* rows, 
   if (static_cast<long long>(threads) * NORM_MAX_PER_THREAD < groups) return SHRIKE_BAD_ARGUMENT;
 #define SHRIKE_NORM_LAUNCH(G, V)                                                                   \
   add_rmsnorm_kernel<TD, TO, HAS_DELTA, G, V><<<n, threads, 0, stream>>>(                          \
-      resid, static_cast<const TD*>(delta), rows, weight, eps, static_cast<TO*>(out), width)
+      resid, static_cast<const TD*>(delta), rows, weight, eps, static_cast<TO*>(out), width, partials,      \
+      partial_stride)
   if (rows) { if (vec) SHRIKE_NORM_LAUNCH(true, 4); else SHRIKE_NORM_LAUNCH(true, 1); }
   else { if (vec) SHRIKE_NORM_LAUNCH(false, 4); else SHRIKE_NORM_LAUNCH(false, 1); }
 #undef SHRIKE_NORM_LAUNCH
@@ -144,14 +157,14 @@ static int launch_add_rmsnorm(float* resid, const void* delta, const int* rows, 
 // resid [*, width] float32 (updated in place unless rows != null); delta may be null.
 SHRIKE_API int shrike_add_rmsnorm(float* resid, const void* delta, int delta_dtype, const int* rows,
                                   const float* weight, float eps, void* out, int out_dtype, int n,
-                                  int width, cudaStream_t stream) {
+                                  int width, int partials, long long partial_stride, cudaStream_t stream) {
   if (n <= 0) return SHRIKE_OK;
-  if (width <= 0) return SHRIKE_BAD_ARGUMENT;
+  if (width <= 0 || partials < 1) return SHRIKE_BAD_ARGUMENT;
   const bool has_delta = delta != nullptr;
   if (has_delta && delta_dtype != SHRIKE_F32 && delta_dtype != SHRIKE_BF16) return SHRIKE_BAD_ARGUMENT;
   int status = SHRIKE_OK;
 #define SHRIKE_NORM_CASE(TD, TO, HD) \
-  status = launch_add_rmsnorm<TD, TO, HD>(resid, delta, rows, weight, eps, out, n, width, stream)
+  status = launch_add_rmsnorm<TD, TO, HD>(resid, delta, rows, weight, eps, out, n, width, partials, partial_stride, stream)
   if (out_dtype == SHRIKE_F32) {
     if (!has_delta) SHRIKE_NORM_CASE(float, float, false);
     else if (delta_dtype == SHRIKE_F32) SHRIKE_NORM_CASE(float, float, true);
@@ -209,7 +222,8 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const float*
                                      const int* __restrict__ positions, const float* __restrict__ inv_freq,
                                      T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
                                      const int* __restrict__ slots, T* __restrict__ k_out, T* __restrict__ v_out,
-                                     int num_heads, int num_kv_heads, int head_dim, long long num_slots) {
+                                     int num_heads, int num_kv_heads, int head_dim, long long num_slots,
+                                     int partials, long long partial_stride) {
   const int token = blockIdx.x, head = blockIdx.y;
   const int half = head_dim / 2;
   const int q_width = num_heads * head_dim, kv_width = num_kv_heads * head_dim;
@@ -224,6 +238,10 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const float*
   for (int j = threadIdx.x; j < half; j += blockDim.x) {
     const int lo = head * head_dim + j, hi = lo + half;  // columns of the row
     float a = row[lo], b = row[hi];
+    for (int p = 1; p < partials; ++p) {   // slices of a K-split projection, added in order
+      a = __fadd_rn(a, row[p * partial_stride + lo]);
+      b = __fadd_rn(b, row[p * partial_stride + hi]);
+    }
     if (bias != nullptr) {
       a = __fadd_rn(a, bias[lo]);
       b = __fadd_rn(b, bias[hi]);
@@ -262,8 +280,9 @@ SHRIKE_API int shrike_rope_kv_write(const float* qkv, const float* bias, const i
                                     const float* inv_freq, void* q_out, void* k_cache, void* v_cache,
                                     const int* slots, void* k_out, void* v_out, int dtype, int n,
                                     int num_heads, int num_kv_heads, int head_dim, long long num_slots,
-                                    cudaStream_t stream) {
+                                    int partials, long long partial_stride, cudaStream_t stream) {
   if (n <= 0) return SHRIKE_OK;
+  if (partials < 1) return SHRIKE_BAD_ARGUMENT;
   if (head_dim <= 0 || head_dim % 2 || num_heads <= 0 || num_kv_heads <= 0) return SHRIKE_BAD_ARGUMENT;
   if ((k_cache == nullptr) != (v_cache == nullptr)) return SHRIKE_BAD_ARGUMENT;
   if ((k_out == nullptr) != (v_out == nullptr)) return SHRIKE_BAD_ARGUMENT;
@@ -275,7 +294,7 @@ SHRIKE_API int shrike_rope_kv_write(const float* qkv, const float* bias, const i
   rope_kv_write_kernel<T><<<grid, threads, 0, stream>>>(                                            \
       qkv, bias, positions, inv_freq, static_cast<T*>(q_out), static_cast<T*>(k_cache),             \
       static_cast<T*>(v_cache), slots, static_cast<T*>(k_out), static_cast<T*>(v_out), num_heads,   \
-      num_kv_heads, head_dim, num_slots)
+      num_kv_heads, head_dim, num_slots, partials, partial_stride)
   if (dtype == SHRIKE_F32) SHRIKE_ROPE_CASE(float);
   else if (dtype == SHRIKE_BF16) SHRIKE_ROPE_CASE(__nv_bfloat16);
   else return SHRIKE_BAD_ARGUMENT;

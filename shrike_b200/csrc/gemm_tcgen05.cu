@@ -1,0 +1,365 @@
+// out[T, N] = x[T, K] * w[N, K]^T (+ bias) in bfloat16 with float32 accumulation, on the
+// fifth-generation tensor cores: tcgen05.mma with the accumulator in tensor memory,
+// operands brought to shared memory by TMA.  Written for few tokens against a large
+// weight (decoding): the step is bound by reading w once from HBM, so the kernel is laid
+// out to keep every SM streaming weights.
+//
+// Orientation ("swap A and B"): the 128-row MMA dimension runs over WEIGHT rows, the
+// narrow dimension (16..256) over tokens.  One CTA owns 128 weight rows and, when K is
+// split, one slice of K; the accumulator D[weight row, token] sits in 128 TMEM lanes x
+// Tn columns.  Split K: CTA (tile, s) writes partial s of the result; the consumer kernel
+// (residual-add + norm, or bias + rotary) adds the partials in a fixed order, so the sum
+// is deterministic and costs no pass of its own.
+//
+// Roles (192 threads): warp 0 issues TMA loads (one elected lane), warp 1 allocates TMEM
+// and issues the MMAs (one elected lane), warps 2..5 read the accumulator back
+// (tcgen05.ld, each warp its quarter of the lanes) and store the result.  Stages are
+// handed over with mbarriers: full[s] (TMA bytes landed), empty[s] (tcgen05.commit: the
+// MMAs that read stage s are done), done (all MMAs of the tile are done).
+//
+// Shared-memory tiles are [rows][64 bf16] = 128-byte rows in the 128-byte swizzle that
+// both TMA (CU_TENSOR_MAP_SWIZZLE_128B) and the MMA descriptor (layout type 2, 1024-byte
+// stride between 8-row groups) understand; a k-step of 16 elements advances the
+// descriptor's start address by 32 bytes inside the swizzle atom.
+//
+// Every wait is bounded.  When a wait runs out, the waiting role records where in
+// `status` (a host-visible word), raises a CTA-wide abort flag that ends the other roles'
+// waits, the producer waits (bounded again) for its copies in flight, TMEM is freed and
+// the CTA returns.  No TMA load uses cluster multicast.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace tc {
+
+constexpr int BM = 128;        // weight rows per CTA = MMA M
+constexpr int BK = 64;         // k elements per stage: 128 bytes of bf16
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr int MAX_STAGES = 8;
+constexpr unsigned WAIT_HINT_NS = 20000;     // one try_wait may sleep this long
+constexpr unsigned WAIT_LIMIT = 100000;      // tries before giving up: about two seconds
+constexpr size_t A_BYTES = BM * BK * 2;
+
+enum : int { ERR_NONE = 0, ERR_PRODUCER = 1, ERR_MMA = 2, ERR_EPILOGUE = 3, ERR_DRAIN = 4 };
+
+struct Shared {
+  unsigned long long full[MAX_STAGES];
+  unsigned long long empty[MAX_STAGES];
+  unsigned long long done;
+  unsigned tmem_base;
+  volatile int abort;
+};
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(WAIT_HINT_NS) : "memory");
+  return ok != 0;
+}
+// Returns false when the wait ran out (and says so) or another role gave up.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, Shared* sh, int* status, int who) {
+  for (unsigned tries = 0; tries < WAIT_LIMIT; ++tries) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (sh->abort) return false;
+  }
+  sh->abort = 1;
+  if (status != nullptr && *status == 0) *status = who;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem, const CUtensorMap* map, unsigned long long* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem)), "l"(reinterpret_cast<unsigned long long>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ unsigned long long smem_descriptor(unsigned addr) {
+  // K-major operand, 128-byte swizzle: start address, leading offset 1 (unused with a
+  // swizzle), 1024 bytes between 8-row groups, descriptor version 1, layout type 2.
+  return static_cast<unsigned long long>((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (static_cast<unsigned long long>(1024 >> 4) << 32) |
+         (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ unsigned instruction_descriptor(int n) {
+  // kind::f16: D float32, A and B bfloat16, both K-major, M = 128, N = n.
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<unsigned>(n >> 3) << 17) | (static_cast<unsigned>(BM >> 4) << 24);
+}
+__device__ __forceinline__ void umma(unsigned tmem_d, unsigned long long a, unsigned long long b, unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_load16(unsigned taddr, unsigned (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+
+struct Args {
+  void* out;            // [splits][T][N] float32 when splits > 1, else [T][N] of out_dtype
+  const float* bias;    // [N] or null; added by split 0
+  int* status;          // host-visible; first failing role is recorded
+  int tokens, n, k, tn; // tn: token columns of the MMA (multiple of 16, at most 256)
+  int kblocks_per_split, stages, out_dtype;
+};
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_swap_ab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const Args args) {
+  extern __shared__ unsigned char smem_raw[];
+  // tiles want 1024-byte alignment (the swizzle pattern repeats every 1024 bytes)
+  unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const size_t b_bytes = static_cast<size_t>(args.tn) * BK * 2;
+  const size_t stage_bytes = A_BYTES + b_bytes;
+  Shared* sh = reinterpret_cast<Shared*>(tiles + stage_bytes * args.stages);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BM, split = blockIdx.y, t0 = blockIdx.z * args.tn;
+  const int total_kblocks = (args.k + BK - 1) / BK;
+  const int kb_begin = split * args.kblocks_per_split;
+  const int kb_end = min(total_kblocks, kb_begin + args.kblocks_per_split);
+  const int num_kb = max(0, kb_end - kb_begin);
+  unsigned tmem_cols = 32;
+  while (tmem_cols < static_cast<unsigned>(args.tn)) tmem_cols <<= 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < args.stages; ++s) {
+      mbar_init(&sh->full[s], 1);
+      mbar_init(&sh->empty[s], 1);
+    }
+    mbar_init(&sh->done, 1);
+    sh->abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(tmem_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const unsigned tmem_d = sh->tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int issued = 0;
+      for (int i = 0; i < num_kb; ++i) {
+        const int s = i % args.stages;
+        const unsigned phase = (i / args.stages) & 1;
+        if (!mbar_wait(&sh->empty[s], phase ^ 1, sh, args.status, ERR_PRODUCER)) break;
+        mbar_expect_tx(&sh->full[s], static_cast<unsigned>(stage_bytes));
+        unsigned char* a_tile = tiles + stage_bytes * s;
+        tma_load_2d(a_tile, &map_w, &sh->full[s], (kb_begin + i) * BK, n0);
+        tma_load_2d(a_tile + A_BYTES, &map_x, &sh->full[s], (kb_begin + i) * BK, t0);
+        issued = i + 1;
+      }
+      if (sh->abort) {
+        // copies may still be in flight: wait for the stages armed last before leaving
+        for (int i = max(0, issued - args.stages); i < issued; ++i) {
+          const int s = i % args.stages;
+          const unsigned phase = (i / args.stages) & 1;
+          bool landed = false;
+          for (unsigned tries = 0; tries < WAIT_LIMIT && !landed; ++tries) landed = mbar_try_wait(&sh->full[s], phase);
+          if (!landed && args.status != nullptr) *args.status = ERR_DRAIN;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const unsigned idesc = instruction_descriptor(args.tn);
+      bool ok = true;
+      for (int i = 0; i < num_kb && ok; ++i) {
+        const int s = i % args.stages;
+        const unsigned phase = (i / args.stages) & 1;
+        ok = mbar_wait(&sh->full[s], phase, sh, args.status, ERR_MMA);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const unsigned a_addr = smem_u32(tiles + stage_bytes * s);
+        const unsigned b_addr = a_addr + static_cast<unsigned>(A_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < BK / UMMA_K; ++kk)
+          umma(tmem_d, smem_descriptor(a_addr + kk * UMMA_K * 2), smem_descriptor(b_addr + kk * UMMA_K * 2), idesc,
+               (i > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&sh->empty[s]);   // frees the stage once these MMAs have read it
+      }
+      if (ok) umma_commit(&sh->done);
+    }
+  } else {
+    // epilogue: warp w may touch TMEM lanes 32 * (w % 4) .. + 31
+    const int quarter = warp & 3;
+    const int row = n0 + quarter * 32 + lane;   // weight row = output column
+    bool ok = true;
+    if (num_kb > 0) ok = mbar_wait(&sh->done, 0, sh, args.status, ERR_EPILOGUE);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+      const bool partial = gridDim.y > 1;
+      const float bias = (args.bias != nullptr && split == 0 && row < args.n) ? args.bias[row] : 0.f;
+      for (int c0 = 0; c0 < args.tn; c0 += 16) {
+        unsigned v[16];
+        if (num_kb > 0) {
+          tmem_load16(tmem_d + (static_cast<unsigned>(quarter * 32) << 16) + static_cast<unsigned>(c0), v);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = 0u;
+        }
+        if (row < args.n) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int t = t0 + c0 + j;
+            if (t >= args.tokens) break;
+            const float value = __uint_as_float(v[j]) + bias;
+            const size_t at = static_cast<size_t>(t) * args.n + row;
+            if (partial) static_cast<float*>(args.out)[static_cast<size_t>(split) * args.tokens * args.n + at] = value;
+            else if (args.out_dtype == SHRIKE_F32) static_cast<float*>(args.out)[at] = value;
+            else static_cast<__nv_bfloat16*>(args.out)[at] = __float2bfloat16_rn(value);
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(tmem_cols) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------- host side
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiled encode_tiled() {
+  static EncodeTiled fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiled>(ptr);
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* base;
+  int rows, cols, box_rows;
+  bool operator==(const MapKey& o) const { return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.base);
+    h = h * 1000003u ^ static_cast<size_t>(k.rows);
+    h = h * 1000003u ^ static_cast<size_t>(k.cols);
+    return h * 1000003u ^ static_cast<size_t>(k.box_rows);
+  }
+};
+
+// A row-major [rows, cols] bfloat16 matrix seen as boxes of box_rows x 64 elements.
+static int tensor_map(const void* base, int rows, int cols, int box_rows, CUtensorMap* out) {
+  static std::mutex mutex;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  const MapKey key{base, rows, cols, box_rows};
+  std::lock_guard<std::mutex> guard(mutex);
+  auto found = cache.find(key);
+  if (found != cache.end()) {
+    *out = found->second;
+    return SHRIKE_OK;
+  }
+  EncodeTiled encode = encode_tiled();
+  if (encode == nullptr) return SHRIKE_BAD_ARGUMENT;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+  const cuuint32_t box[2] = {BK, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t element_strides[2] = {1, 1};
+  CUtensorMap map;
+  const CUresult rc = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                             element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) return 1000 + static_cast<int>(rc);
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, map);
+  *out = map;
+  return SHRIKE_OK;
+}
+
+}  // namespace tc
+
+// How K is split for a product with `tokens` rows: enough CTAs to keep every SM
+// streaming, at least four k-blocks per CTA.  The same function sizes the partial stack.
+SHRIKE_API int shrike_gemm_tc_splits(int tokens, int n, int k) {
+  (void)tokens;
+  const int tiles = (n + tc::BM - 1) / tc::BM;
+  const int kblocks = (k + tc::BK - 1) / tc::BK;
+  int splits = 1;
+  while (tiles * splits < 148 && splits < 16 && kblocks / (splits * 2) >= 4) splits *= 2;
+  // round so that no split is empty
+  const int per = (kblocks + splits - 1) / splits;
+  return (kblocks + per - 1) / per;
+}
+
+// x [tokens, k] and w [n, k] bfloat16 row-major, k a multiple of 8 (TMA wants 16-byte row
+// strides) and both 16-byte aligned.  splits == 1: out is [tokens, n] of out_dtype.
+// splits > 1 (as shrike_gemm_tc_splits says): out is [splits, tokens, n] float32.
+SHRIKE_API int shrike_gemm_tc(const void* x, const void* w, const float* bias, void* out, int out_dtype, int tokens,
+                              int n, int k, int splits, int* status, cudaStream_t stream) {
+  using namespace tc;
+  if (tokens <= 0 || n <= 0) return SHRIKE_OK;
+  if (k <= 0 || k % 8 || splits < 1 || (out_dtype != SHRIKE_F32 && out_dtype != SHRIKE_BF16)) return SHRIKE_BAD_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return SHRIKE_BAD_ARGUMENT;
+  int tn = 16;
+  while (tn < tokens && tn < 256) tn *= 2;
+  const int token_tiles = (tokens + tn - 1) / tn;
+  const int kblocks = (k + BK - 1) / BK;
+  const int per_split = (kblocks + splits - 1) / splits;
+  if ((kblocks + per_split - 1) / per_split != splits) return SHRIKE_BAD_ARGUMENT;
+  const size_t stage_bytes = A_BYTES + static_cast<size_t>(tn) * BK * 2;
+  int stages = static_cast<int>((200 * 1024) / stage_bytes);
+  stages = stages > MAX_STAGES ? MAX_STAGES : stages;
+  if (stages > per_split) stages = per_split < 2 ? 2 : per_split;
+  const size_t smem = stage_bytes * stages + sizeof(Shared) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    const cudaError_t err = cudaFuncSetAttribute(gemm_swap_ab_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (err != cudaSuccess) return static_cast<int>(err);
+    configured = true;
+  }
+  CUtensorMap map_w, map_x;
+  int rc = tensor_map(w, n, k, BM, &map_w);
+  if (rc != SHRIKE_OK) return rc;
+  rc = tensor_map(x, tokens, k, tn, &map_x);
+  if (rc != SHRIKE_OK) return rc;
+  Args args;
+  args.out = out;
+  args.bias = bias;
+  args.status = status;
+  args.tokens = tokens;
+  args.n = n;
+  args.k = k;
+  args.tn = tn;
+  args.kblocks_per_split = per_split;
+  args.stages = stages;
+  args.out_dtype = out_dtype;
+  const dim3 grid((n + BM - 1) / BM, splits, token_tiles);
+  gemm_swap_ab_kernel<<<grid, THREADS, smem, stream>>>(map_w, map_x, args);
+  return shrike_launch_status();
+}

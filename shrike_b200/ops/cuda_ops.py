@@ -57,6 +57,17 @@ class CudaOps:
         self.core = build.core_library()
         self._declare_core()
         self._attention = {}
+        self.gemm_tc = None
+        self.tensor_core_gemm_max_tokens = 64   # above this the library product is used
+        self._partials = {}      # data_ptr of an output buffer -> its stack of K-split partial results
+        self.status = None
+        if dtype == torch.bfloat16:
+            self.gemm_tc = build.tensor_core_gemm_library()
+            self.gemm_tc.shrike_gemm_tc.argtypes = [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P]
+            self.gemm_tc.shrike_gemm_tc.restype = _I
+            self.gemm_tc.shrike_gemm_tc_splits.argtypes = [_I, _I, _I]
+            self.gemm_tc.shrike_gemm_tc_splits.restype = _I
+            self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._scratch = None     # partial results of split single-token attention
         self._sample_scratch = None  # per-slice winners of the sampling kernel
         self.generation = 0      # grows when the scratch moves
@@ -71,9 +82,9 @@ class CudaOps:
     def _declare_core(self):
         lib = self.core
         lib.shrike_embed.argtypes = [_P, _P, _I, _P, _I, _I, _I, _P]
-        lib.shrike_add_rmsnorm.argtypes = [_P, _P, _I, _P, _P, _F, _P, _I, _I, _I, _P]
+        lib.shrike_add_rmsnorm.argtypes = [_P, _P, _I, _P, _P, _F, _P, _I, _I, _I, _I, _LL, _P]
         lib.shrike_silu_mul.argtypes = [_P, _P, _I, _I, _I, _P]
-        lib.shrike_rope_kv_write.argtypes = [_P] * 10 + [_I] * 5 + [_LL, _P]
+        lib.shrike_rope_kv_write.argtypes = [_P] * 10 + [_I] * 5 + [_LL, _I, _LL, _P]
         lib.shrike_kv_write.argtypes = [_P] * 5 + [_I, _I, _I, _LL, _P]
         lib.shrike_gemm_fp32.argtypes = [_P, _P, _P, _P, _I, _I, _I, _P]
         lib.shrike_sample.argtypes = [_P, _P, _P, _P, _P, _P, _P, _I, _I, _P]
@@ -118,27 +129,42 @@ class CudaOps:
         _check(self.core.shrike_embed(_ptr(ids), _ptr(table), _DTYPE_CODE[table.dtype], _ptr(out), n, width,
                                       table.shape[0], self._stream()), "embed")
 
+    @staticmethod
+    def _stack(delta):
+        """(partials, stride in elements) of a [N, W] array or a [P, N, W] stack of partial sums."""
+        if delta is None or delta.dim() == 2:
+            return 1, 0
+        return delta.shape[0], delta.stride(0)
+
     def add_rmsnorm(self, resid, delta, weight, eps, out):
+        """resid += delta (a [N, W] array, or a [P, N, W] stack added in order); out = norm(resid) * weight."""
         _dense(resid, torch.float32, "residual")
         _dense(weight, torch.float32, "norm weight")
         n, width = resid.shape
         code = -1 if delta is None else _DTYPE_CODE[delta.dtype]
+        partials, stride = self._stack(delta)
         self.launches += 1
         _check(self.core.shrike_add_rmsnorm(_ptr(resid), _ptr(delta), code, None, _ptr(weight), eps, _ptr(out),
-                                            _DTYPE_CODE[out.dtype], n, width, self._stream()), "add_rmsnorm")
+                                            _DTYPE_CODE[out.dtype], n, width, partials, stride, self._stream()),
+               "add_rmsnorm")
 
     def gather_add_rmsnorm(self, resid, delta, rows, weight, eps, out):
         _dense(resid, torch.float32, "residual")
         _dense(rows, torch.int32, "rows")
         width = resid.shape[1]
         code = -1 if delta is None else _DTYPE_CODE[delta.dtype]
+        partials, stride = self._stack(delta)
         self.launches += 1
         _check(self.core.shrike_add_rmsnorm(_ptr(resid), _ptr(delta), code, _ptr(rows), _ptr(weight), eps,
-                                            _ptr(out), _DTYPE_CODE[out.dtype], rows.shape[0], width,
-                                            self._stream()), "gather_add_rmsnorm")
+                                            _ptr(out), _DTYPE_CODE[out.dtype], rows.shape[0], width, partials,
+                                            stride, self._stream()), "gather_add_rmsnorm")
 
-    def linear(self, x, w, out, bias=None):
-        """out[N, O] = x[N, K] @ w[O, K]^T (+ bias); out may be float32 or the activation type."""
+    def linear(self, x, w, out, bias=None, allow_partials=False):
+        """x[N, K] @ w[O, K]^T (+ bias) into `out` [N, O] (float32 or the activation type).
+
+        Returns the array to consume: `out`, or, when `allow_partials` and the product was
+        split along K, a float32 stack [P, N, O] whose sum over P is the result (the
+        norm and rotary kernels add such stacks themselves)."""
         n, k = x.shape
         o = w.shape[0]
         if w.shape[1] != k or tuple(out.shape) != (n, o):
@@ -150,9 +176,20 @@ class CudaOps:
             _dense(out, torch.float32, "linear output")
             _check(self.core.shrike_gemm_fp32(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), n, o, k, self._stream()),
                    "gemm_fp32")
-            return
+            return out
         _dense(x, torch.bfloat16, "linear input")
         _dense(w, torch.bfloat16, "linear weight")
+        if self.gemm_tc is not None and n <= self.tensor_core_gemm_max_tokens and k % 8 == 0:
+            _dense(out, out.dtype, "linear output")
+            splits, target = 1, out
+            if allow_partials and out.dtype == torch.float32:
+                splits = self.gemm_tc.shrike_gemm_tc_splits(n, o, k)
+                if splits > 1:
+                    target = self._partial_stack(out, splits)
+            self.launches += 1
+            _check(self.gemm_tc.shrike_gemm_tc(_ptr(x), _ptr(w), _ptr(bias), _ptr(target), _DTYPE_CODE[out.dtype],
+                                               n, o, k, splits, _ptr(self.status), self._stream()), "gemm_tcgen05")
+            return target
         self.library_calls += 1
         if out.dtype == torch.float32:
             torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
@@ -160,12 +197,37 @@ class CudaOps:
             torch.mm(x, w.t(), out=out)
         if bias is not None:
             out.add_(bias)
+        return out
+
+    def _partial_stack(self, out, splits):
+        """The float32 [splits, N, O] stack that belongs to the output buffer `out`."""
+        n, o = out.shape
+        key = out.data_ptr()
+        held = self._partials.get(key)
+        need = splits * n * o
+        if held is None or held.numel() < need:
+            capacity = max(need, 16 * self.tensor_core_gemm_max_tokens * o)
+            held = torch.empty(capacity, dtype=torch.float32, device=self.device)
+            self._partials[key] = held
+            self.generation += 1
+        return held[:need].view(splits, n, o)
+
+    def check_status(self):
+        """Raises when a tensor-core product gave up a bounded wait (reads one word from the device)."""
+        if self.status is None:
+            return
+        code = int(self.status[0].item())
+        if code:
+            self.status.zero_()
+            where = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue", 4: "draining copies"}.get(code, str(code))
+            raise KernelError(f"gemm_tcgen05: a wait ran out in {where}; the product of that step is not valid")
 
     def rope_kv_write(self, qkv, bias, positions, inv_freq, q_out, keys, values, slots,
                       num_heads, num_kv_heads, head_dim, k_out=None, v_out=None):
         _dense(qkv, torch.float32, "qkv")
         _dense(q_out, self.dtype, "q")
-        n = qkv.shape[0]
+        partials, stride = self._stack(qkv)
+        n = qkv.shape[-2]
         num_slots = 0
         if keys is not None:
             _dense(keys, self.dtype, "key cache")
@@ -175,7 +237,7 @@ class CudaOps:
         _check(self.core.shrike_rope_kv_write(
             _ptr(qkv), _ptr(bias), _ptr(positions), _ptr(inv_freq), _ptr(q_out), _ptr(keys), _ptr(values),
             _ptr(slots), _ptr(k_out), _ptr(v_out), self.code, n, num_heads, num_kv_heads, head_dim,
-            num_slots, self._stream()), "rope_kv_write")
+            num_slots, partials, stride, self._stream()), "rope_kv_write")
 
     def kv_write(self, k_new, v_new, keys, values, slots):
         _dense(keys, self.dtype, "key cache")

@@ -66,7 +66,7 @@ class PagedAttention:
         spec, rt, ops = self.spec, self.runtime, self.ops
         n = x.shape[0]
         qkv = rt.buffer("qkv", (n, self.qkv_width), torch.float32)
-        ops.linear(x, self.w_qkv, qkv)
+        qkv = ops.linear(x, self.w_qkv, qkv, allow_partials=True)
         group, keys, values = ctx.storage.keys_values(run.cache)
         view = ctx.groups[group]
         q = rt.buffer("q", (n, self.q_width), rt.act_dtype)
@@ -100,8 +100,7 @@ class PagedAttention:
             max_q_len=ctx.max_q_len, max_ctx_len=ctx.max_ctx_len, min_q_len=ctx.min_q_len,
         )
         delta = rt.buffer("mixer_delta", (n, spec.width), torch.float32)
-        ops.linear(attn, self.w_o, delta, bias=self.b_o)
-        return delta
+        return ops.linear(attn, self.w_o, delta, bias=self.b_o, allow_partials=True)
 
 
 register_part("mixer", "attention", PagedAttention)

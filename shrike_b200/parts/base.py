@@ -14,8 +14,10 @@ be checked and the cache sized before anything is put on the device):
       parameters(spec) -> {local name: ParamSpec}
       __init__(spec, tensors: {local name: Tensor}, ops, runtime)
   norm
-      add_norm(resid_f32[N,W], delta[N,W] | None, out | None) -> normed[N,W]
-          resid += delta (32-bit), then the normalised rows in the activation dtype
+      add_norm(resid_f32[N,W], delta | None) -> normed[N,W]
+          resid += delta (32-bit), then the normalised rows in the activation dtype;
+          delta is [N,W], or a stack [P,N,W] of partial sums that the kernel adds in order
+          (what `ops.linear(..., allow_partials=True)` may return)
       gather_norm(resid_f32, delta, rows_i32[R]) -> normed[R,W]   (only the wanted rows)
   position encoding
       rotary_table() -> float32 [D/2] inverse frequencies, when the mixer's fused

@@ -35,8 +35,7 @@ class GatedMLP:
         act = rt.buffer("ffn_act", (n, spec.intermediate), rt.act_dtype)
         ops.silu_mul(gate_up, act)
         delta = rt.buffer("ffn_delta", (n, spec.width), torch.float32)
-        ops.linear(act, self.w_down, delta)
-        return delta
+        return ops.linear(act, self.w_down, delta, allow_partials=True)
 
 
 register_part("feed_forward", "gated_mlp", GatedMLP)

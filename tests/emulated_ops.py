@@ -30,25 +30,32 @@ class EmulatedOps:
 
     def add_rmsnorm(self, resid, delta, weight, eps, out):
         if delta is not None:
-            resid.add_(delta.float())
+            resid.add_(delta.float().sum(0) if delta.dim() == 3 else delta.float())
         var = resid.pow(2).mean(-1, keepdim=True)
         out.copy_((resid * torch.rsqrt(var + eps) * weight).to(out.dtype))
 
     def gather_add_rmsnorm(self, resid, delta, rows, weight, eps, out):
         x = resid[rows.long()]
         if delta is not None:
-            x = x + delta[rows.long()].float()
+            summed = delta.float().sum(0) if delta.dim() == 3 else delta.float()
+            x = x + summed[rows.long()]
         var = x.pow(2).mean(-1, keepdim=True)
         out.copy_((x * torch.rsqrt(var + eps) * weight).to(out.dtype))
 
-    def linear(self, x, w, out, bias=None):
+    def linear(self, x, w, out, bias=None, allow_partials=False):
         y = x.float() @ w.float().T
         if bias is not None:
             y = y + bias
         out.copy_(y.to(out.dtype))
+        if allow_partials and out.dtype == torch.float32 and x.shape[0] <= 4:
+            # as the K-split tensor-core product does for few tokens: a stack whose sum is the result
+            return torch.stack([0.5 * out, 0.25 * out, 0.25 * out])
+        return out
 
     def rope_kv_write(self, qkv, bias, positions, inv_freq, q_out, keys, values, slots,
                       num_heads, num_kv_heads, head_dim, k_out=None, v_out=None):
+        if qkv.dim() == 3:
+            qkv = qkv.sum(0)
         n = qkv.shape[0]
         x = qkv.float()
         if bias is not None:

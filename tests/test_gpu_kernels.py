@@ -108,6 +108,44 @@ def test_linear_bf16():
     close(narrow, want, 1e-3, 2 ** -7)
 
 
+@pytest.mark.parametrize("tokens,n,k", [(1, 64, 64), (8, 384, 192), (3, 331, 240), (16, 130, 320), (17, 4608, 3584),
+                                        (33, 3584, 1000), (64, 256, 18944), (5, 1188, 136), (64, 37888, 3584)])
+def test_gemm_tcgen05(tokens, n, k):
+    """The tensor-core product for few tokens (TMA + tcgen05, accumulator in tensor memory):
+    float32 and bfloat16 outputs, bias, and the K-split stack of partial results."""
+    ops = cuda_ops(torch.bfloat16)
+    x, w, bias = rnd(tokens, k, dtype=torch.bfloat16, seed=1), rnd(n, k, dtype=torch.bfloat16, seed=2), rnd(n, seed=3)
+    want = x.double() @ w.double().T
+    products = x.double().abs() @ w.double().abs().T
+    bound = math.sqrt(k) * 2.0 ** -24 * products + 1e-30     # float32 accumulation of exact bf16 products
+
+    def check(got, reference, what, extra=0.0):
+        excess = ((got.double() - reference).abs() - bound - extra * reference.abs()).max().item()
+        assert excess <= 0, f"gemm_tcgen05 {tokens}x{n}x{k} {what}: exceeds the bound by {excess:.3e}"
+
+    wide = torch.full((tokens, n), float("nan"), device=DEV)
+    assert ops.linear(x, w, wide) is wide
+    check(wide, want, "float32")
+    biased = torch.full((tokens, n), float("nan"), device=DEV)
+    ops.linear(x, w, biased, bias=bias)
+    check(biased, want + bias.double(), "bias", extra=2.0 ** -23)
+    narrow = torch.full((tokens, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.linear(x, w, narrow)
+    check(narrow, want, "bfloat16", extra=2.0 ** -8)
+    stack = ops.linear(x, w, wide, bias=bias, allow_partials=True)
+    if stack.dim() == 3:
+        assert stack.dtype == torch.float32 and stack.shape[1:] == (tokens, n) and stack.shape[0] > 1
+        total = stack[0].clone()
+        for part in stack[1:]:
+            total += part
+        check(total, want + bias.double(), "partial stack", extra=2.0 ** -22)
+        resid = torch.zeros(tokens, n, device=DEV)
+        out = torch.empty(tokens, n, device=DEV)
+        ops.add_rmsnorm(resid, stack, torch.ones(n, device=DEV), 1e-6, out)
+        assert torch.equal(resid, total), "the norm kernel must add the partials in order"
+    ops.check_status()
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kv_heads,dim", [(5, 1, 48), (14, 2, 64), (3, 3, 16), (4, 2, 256)])
 def test_rope_kv_write(dtype, heads, kv_heads, dim):
