@@ -7,10 +7,11 @@
 //   * single tokens (q_len == 1): one CTA per (key split, kv head, sequence).  The G
 //     query heads that share a kv head are the rows of one 16-row tile, so keys and
 //     values are read once per kv head, not once per query head; the four warps take 16
-//     keys each of every 64-key tile; partial results of the splits are combined by a
-//     third, small kernel.  The split count is a launch parameter, the key ranges come
-//     from ctx_len on the device, so a captured launch sequence stays valid as contexts
-//     grow.
+//     keys each of every 64-key tile, tiles arrive through a three-deep cp.async pipeline;
+//     every split writes its partial result, and the split that finishes last (an atomic
+//     counter per kv head, which it resets) combines them.  The split count is a launch
+//     parameter, the key ranges come from ctx_len on the device, so a captured launch
+//     sequence stays valid as contexts grow.
 // Keys and values are fetched through the block table with 16-byte cp.async copies into
 // padded shared-memory rows (double-buffered) and read with ldmatrix.  Scores, running
 // maximum, sum and the output accumulate in float32; probabilities are rounded to
@@ -78,31 +79,51 @@ struct Params {
   bf16* out;
   float* partial_out;   // [seq, head, split, D], single tokens only
   float* partial_ml;    // [seq, head, split, 2]
+  int* arrivals;        // [seq, kv head * row tiles]: splits that have stored their partial; zero between launches
   int max_blocks, num_heads, num_kv_heads, page_size, num_pages, window, splits;
   int skip_single;      // portions kernel: leave q_len == 1 to the single-token kernel
   float scale_log2;     // scale * log2(e)
 };
 
-// Copies keys [tile_base, tile_base + BN) of one kv head into k_tile / v_tile.  Keys
-// outside [lo, hi] (or on a page the sequence does not hold) become zeros.
-__device__ __forceinline__ void load_kv_tile(bf16* k_tile, bf16* v_tile, const Params& p, const int* table,
-                                             int kv_head, int tile_base, int lo, int hi) {
-  const size_t row_stride = static_cast<size_t>(p.num_kv_heads) * D;
-  for (int c = threadIdx.x; c < BN * CHUNKS; c += THREADS) {
-    const int key = c / CHUNKS, chunk = c - key * CHUNKS;
-    const int j = tile_base + key;
-    bool valid = j >= lo && j <= hi;
-    size_t offset = 0;
-    if (valid) {
+// Where the keys [tile_base, tile_base + BN) of one kv head start in the cache, in
+// elements; -1 for keys outside [lo, hi] or on a page the sequence does not hold.  One
+// table lookup and one division per key, done by the first BN threads.
+__device__ __forceinline__ void locate_tile(long long* rows, const Params& p, const int* table, int kv_head,
+                                            int tile_base, int lo, int hi) {
+  if (threadIdx.x < BN) {
+    const int j = tile_base + threadIdx.x;
+    long long offset = -1;
+    if (j >= lo && j <= hi) {
       const int block = j / p.page_size;
       const int page = block < p.max_blocks ? table[block] : -1;
-      if (page < 0 || page >= p.num_pages) valid = false;
-      else offset = (static_cast<size_t>(page) * p.page_size + (j - block * p.page_size)) * row_stride +
-                    static_cast<size_t>(kv_head) * D + chunk * 8;
+      if (page >= 0 && page < p.num_pages)
+        offset = (static_cast<long long>(page) * p.page_size + (j - block * p.page_size)) * p.num_kv_heads * D +
+                 static_cast<long long>(kv_head) * D;
     }
+    rows[threadIdx.x] = offset;
+  }
+}
+
+// Copies the located keys and values into k_tile / v_tile; consecutive threads take
+// consecutive 16-byte chunks of a row, so a warp's copies cover whole 128-byte lines.
+// Keys without a row become zeros.
+__device__ __forceinline__ void copy_tile(bf16* k_tile, bf16* v_tile, const Params& p, const long long* rows) {
+  for (int c = threadIdx.x; c < BN * CHUNKS; c += THREADS) {
+    const int key = c / CHUNKS, chunk = c - key * CHUNKS;
+    const long long row = rows[key];
+    const bool valid = row >= 0;
+    const size_t offset = valid ? static_cast<size_t>(row) + chunk * 8 : 0;
     cp_async16(k_tile + key * ROW + chunk * 8, p.k_cache + offset, valid);
     cp_async16(v_tile + key * ROW + chunk * 8, p.v_cache + offset, valid);
   }
+}
+
+// Both steps at once, with a barrier between them (for code that loads one tile ahead).
+__device__ __forceinline__ void load_kv_tile(bf16* k_tile, bf16* v_tile, long long* rows, const Params& p,
+                                             const int* table, int kv_head, int tile_base, int lo, int hi) {
+  locate_tile(rows, p, table, kv_head, tile_base, lo, hi);
+  __syncthreads();
+  copy_tile(k_tile, v_tile, p, rows);
 }
 
 // S[16 x (8 * NT)] += Q[16 x D] * K^T for keys [key0, key0 + 8 * NT) of the tile.
@@ -202,6 +223,7 @@ __global__ void __launch_bounds__(THREADS) portions_kernel(const Params p) {
   bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);           // [BM][ROW]
   bf16* k_tiles = q_tile + BM * ROW;                          // [2][BN][ROW]
   bf16* v_tiles = k_tiles + 2 * BN * ROW;                     // [2][BN][ROW]
+  __shared__ long long tile_rows[2][BN];
   const int seq = blockIdx.z, head = blockIdx.y, tile_start = blockIdx.x * BM;
   const int start = p.q_start[seq];
   const int q_len = p.q_start[seq + 1] - start;
@@ -221,7 +243,7 @@ __global__ void __launch_bounds__(THREADS) portions_kernel(const Params p) {
     const bf16* src = p.q + (static_cast<size_t>(start + tile_start + (valid ? row : 0)) * p.num_heads + head) * D + chunk * 8;
     cp_async16(q_tile + row * ROW + chunk * 8, src, valid);
   }
-  load_kv_tile(k_tiles, v_tiles, p, table, kv_head, tile_lo * BN, lo, hi);
+  load_kv_tile(k_tiles, v_tiles, tile_rows[0], p, table, kv_head, tile_lo * BN, lo, hi);
   cp_async_commit();
 
   int first[2], last[2];
@@ -243,8 +265,8 @@ __global__ void __launch_bounds__(THREADS) portions_kernel(const Params p) {
   for (int tile = tile_lo; tile <= tile_hi; ++tile) {
     const int buffer = (tile - tile_lo) & 1;
     if (tile < tile_hi) {
-      load_kv_tile(k_tiles + (buffer ^ 1) * BN * ROW, v_tiles + (buffer ^ 1) * BN * ROW, p, table, kv_head,
-                   (tile + 1) * BN, lo, hi);
+      load_kv_tile(k_tiles + (buffer ^ 1) * BN * ROW, v_tiles + (buffer ^ 1) * BN * ROW, tile_rows[buffer ^ 1], p, table,
+                   kv_head, (tile + 1) * BN, lo, hi);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -291,11 +313,17 @@ __global__ void __launch_bounds__(THREADS) portions_kernel(const Params p) {
 }
 
 // ------------------------------------------------------------- single tokens
+constexpr int ST = 3;  // pipeline depth of the single-token kernel, in 64-key tiles
+constexpr int MAX_SPLITS = 32;
+
 __global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ int is_last;
+  __shared__ long long tile_rows[ST + 1][BN];
   bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);           // [16][ROW]
-  bf16* k_tiles = q_tile + 16 * ROW;                          // [2][BN][ROW]
-  bf16* v_tiles = k_tiles + 2 * BN * ROW;
+  bf16* k_tiles = q_tile + 16 * ROW;                          // [ST][BN][ROW]
+  bf16* v_tiles = k_tiles + ST * BN * ROW;
+  let_dependents_start();
   const int seq = blockIdx.z, split = blockIdx.x;
   const int group = p.num_heads / p.num_kv_heads;
   const int row_tiles = (group + 15) / 16;
@@ -326,20 +354,32 @@ __global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
       const bf16* src = p.q + (static_cast<size_t>(start) * p.num_heads + head0 + (valid ? row : 0)) * D + chunk * 8;
       cp_async16(q_tile + row * ROW + chunk * 8, src, valid);
     }
-    load_kv_tile(k_tiles, v_tiles, p, table, kv_head, my_lo * BN, first_key, last_key);
-    cp_async_commit();
+    // rows of the first ST tiles; tile t + ST is located while tile t is worked on
+#pragma unroll
+    for (int ahead = 0; ahead < ST; ++ahead)
+      if (my_lo + ahead <= my_hi)
+        locate_tile(tile_rows[ahead % (ST + 1)], p, table, kv_head, (my_lo + ahead) * BN, first_key, last_key);
+    __syncthreads();
+    // one commit group per tile, also when there is no tile left, so that the count is uniform
+#pragma unroll
+    for (int ahead = 0; ahead < ST - 1; ++ahead) {
+      if (my_lo + ahead <= my_hi)
+        copy_tile(k_tiles + ahead * BN * ROW, v_tiles + ahead * BN * ROW, p, tile_rows[ahead % (ST + 1)]);
+      cp_async_commit();
+    }
     int first[2] = {first_key, first_key}, last[2] = {last_key, last_key};
     unsigned q_frag[Q_IN_REGS ? KSTEPS : 1][4];
     for (int tile = my_lo; tile <= my_hi; ++tile) {
-      const int buffer = (tile - my_lo) & 1;
-      if (tile < my_hi) {
-        load_kv_tile(k_tiles + (buffer ^ 1) * BN * ROW, v_tiles + (buffer ^ 1) * BN * ROW, p, table, kv_head,
-                     (tile + 1) * BN, first_key, last_key);
-        cp_async_commit();
-        cp_async_wait<1>();
-      } else {
-        cp_async_wait<0>();
+      const int buffer = (tile - my_lo) % ST;
+      const int ahead = tile + ST - 1;
+      if (ahead <= my_hi) {
+        const int into = (ahead - my_lo) % ST;
+        copy_tile(k_tiles + into * BN * ROW, v_tiles + into * BN * ROW, p, tile_rows[(ahead - my_lo) % (ST + 1)]);
       }
+      cp_async_commit();
+      if (ahead + 1 <= my_hi)   // read in the next round, after this round's closing barrier
+        locate_tile(tile_rows[(ahead + 1 - my_lo) % (ST + 1)], p, table, kv_head, (ahead + 1) * BN, first_key, last_key);
+      cp_async_wait<ST - 1>();
       __syncthreads();
       if (Q_IN_REGS && tile == my_lo) {
 #pragma unroll
@@ -353,8 +393,9 @@ __global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
         softmax_update<2>(s, o, row_max, row_sum, first, last, tile * BN + key0, p.scale_log2, lane);
         accumulate<2>(o, s, v_tiles + buffer * BN * ROW, key0, lane);
       }
-      __syncthreads();
+      __syncthreads();   // the buffer is loaded into again by the next round
     }
+    cp_async_wait<0>();
   }
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
@@ -400,33 +441,63 @@ __global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
       p.partial_ml[slot * 2 + 1] = sum;
     }
   }
-}
-
-__global__ void combine_splits_kernel(const Params p) {
-  const int seq = blockIdx.x / p.num_heads, head = blockIdx.x - seq * p.num_heads;
-  const int start = p.q_start[seq];
-  if (p.q_start[seq + 1] - start != 1) return;
-  const size_t slot0 = (static_cast<size_t>(seq) * p.num_heads + head) * p.splits;
-  float m = -INFINITY;
-  for (int s = 0; s < p.splits; ++s) m = fmaxf(m, p.partial_ml[(slot0 + s) * 2]);
-  float sum = 0.f;
-  for (int s = 0; s < p.splits; ++s) {
-    const float sm = p.partial_ml[(slot0 + s) * 2];
-    if (sm != -INFINITY) sum += exp2f(sm - m) * p.partial_ml[(slot0 + s) * 2 + 1];
+  // the split that arrives last combines all of them; the order of the sum is by split
+  // index, whoever does it
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* counter = p.arrivals + static_cast<size_t>(seq) * gridDim.y + blockIdx.y;
+    const int before = atomicAdd(counter, 1);
+    is_last = before == p.splits - 1;
+    if (is_last) *counter = 0;   // ready for the next launch
   }
-  const float inv = sum > 0.f ? 1.0f / sum : 0.f;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float total = 0.f;
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  // weights of the splits: one (row, split) pair per thread, then a row-wise maximum and sum
+  float* weights = reinterpret_cast<float*>(smem_raw);        // [16][MAX_SPLITS], then [16] inverse sums
+  float* inverse = weights + 16 * MAX_SPLITS;
+  for (int idx = threadIdx.x; idx < rows_here * p.splits; idx += THREADS) {
+    const int row = idx / p.splits, s = idx - row * p.splits;
+    const size_t slot = (static_cast<size_t>(seq) * p.num_heads + head0 + row) * p.splits + s;
+    weights[row * MAX_SPLITS + s] = __ldcg(p.partial_ml + slot * 2);
+  }
+  __syncthreads();
+  if (threadIdx.x < rows_here) {
+    const int row = threadIdx.x;
+    const size_t slot0 = (static_cast<size_t>(seq) * p.num_heads + head0 + row) * p.splits;
+    float m = -INFINITY;
+    for (int s = 0; s < p.splits; ++s) m = fmaxf(m, weights[row * MAX_SPLITS + s]);
+    float sum = 0.f;
     for (int s = 0; s < p.splits; ++s) {
-      const float sm = p.partial_ml[(slot0 + s) * 2];
-      if (sm != -INFINITY) total += exp2f(sm - m) * p.partial_out[(slot0 + s) * D + d];
+      const float sm = weights[row * MAX_SPLITS + s];
+      const float weight = sm == -INFINITY ? 0.f : exp2f(sm - m);
+      weights[row * MAX_SPLITS + s] = weight;
+      sum += weight * __ldcg(p.partial_ml + (slot0 + s) * 2 + 1);
     }
-    p.out[(static_cast<size_t>(start) * p.num_heads + head) * D + d] = __float2bfloat16_rn(total * inv);
+    inverse[row] = sum > 0.f ? 1.0f / sum : 0.f;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < rows_here * D; idx += THREADS) {
+    const int row = idx / D, d = idx - row * D;
+    const float* src = p.partial_out + (static_cast<size_t>(seq) * p.num_heads + head0 + row) * p.splits * D + d;
+    float total = 0.f;
+    int s = 0;
+    for (; s + 4 <= p.splits; s += 4) {   // four independent loads in flight, summed in split order
+      const float v0 = __ldcg(src + (s + 0) * D), v1 = __ldcg(src + (s + 1) * D);
+      const float v2 = __ldcg(src + (s + 2) * D), v3 = __ldcg(src + (s + 3) * D);
+      total += weights[row * MAX_SPLITS + s] * v0;
+      total += weights[row * MAX_SPLITS + s + 1] * v1;
+      total += weights[row * MAX_SPLITS + s + 2] * v2;
+      total += weights[row * MAX_SPLITS + s + 3] * v3;
+    }
+    for (; s < p.splits; ++s) total += weights[row * MAX_SPLITS + s] * __ldcg(src + s * D);
+    p.out[(static_cast<size_t>(start) * p.num_heads + head0 + row) * D + d] = __float2bfloat16_rn(total * inverse[row]);
   }
 }
 
 constexpr size_t PORTIONS_SMEM = sizeof(bf16) * (BM * ROW + 4 * BN * ROW);
-constexpr size_t SINGLE_TILES_SMEM = sizeof(bf16) * (16 * ROW + 4 * BN * ROW);
+constexpr size_t SINGLE_TILES_SMEM = sizeof(bf16) * (16 * ROW + 2 * ST * BN * ROW);
 constexpr size_t SINGLE_MERGE_SMEM = sizeof(float) * (4 * 16 * D + 4 * 16 * 2);
 constexpr size_t SINGLE_SMEM = SINGLE_TILES_SMEM > SINGLE_MERGE_SMEM ? SINGLE_TILES_SMEM : SINGLE_MERGE_SMEM;
 
@@ -436,22 +507,31 @@ constexpr size_t SINGLE_SMEM = SINGLE_TILES_SMEM > SINGLE_MERGE_SMEM ? SINGLE_TI
 SHRIKE_API long long shrike_attention_bf16_scratch_floats(int num_seqs, int num_heads, int splits) {
   return static_cast<long long>(num_seqs) * num_heads * splits * (bf16attn::D + 2);
 }
+// How many single-token CTAs the GPU holds at once; the host picks
+// splits = min(tiles, this / (seqs * kv heads * row tiles)).
+SHRIKE_API int shrike_attention_bf16_resident_ctas() {
+  const size_t smem = bf16attn::SINGLE_SMEM + 1024;
+  const int per_sm = static_cast<int>((227 * 1024) / smem);
+  return 148 * (per_sm < 1 ? 1 : (per_sm > 4 ? 4 : per_sm));
+}
 
 // has_single / has_portions: whether the batch holds rows with q_len == 1 / q_len > 1
 // (known on the host); max_q_len bounds the portions grid.  scratch holds
-// shrike_attention_bf16_scratch_floats(num_seqs, num_heads, splits) floats when has_single.
+// shrike_attention_bf16_scratch_floats(num_seqs, num_heads, splits) floats when has_single, and
+// arrivals num_seqs * num_kv_heads * ceil(group / 16) ints that are zero before the first launch
+// (every launch leaves them zero again).
 SHRIKE_API int shrike_paged_attention_bf16(const void* q, const void* k_cache, const void* v_cache,
                                            const int* block_table, int max_blocks, const int* q_start,
                                            const int* ctx_len, int num_seqs, int num_heads, int num_kv_heads,
                                            int page_size, int num_pages, float scale, int window, void* out,
                                            int has_single, int has_portions, int max_q_len, int splits,
-                                           float* scratch, cudaStream_t stream) {
+                                           float* scratch, int* arrivals, cudaStream_t stream) {
   using namespace bf16attn;
   if (num_seqs <= 0) return SHRIKE_OK;
   if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || page_size <= 0 || max_blocks <= 0 ||
       num_seqs > 65535 || num_heads > 65535)
     return SHRIKE_BAD_ARGUMENT;
-  if (has_single && (splits < 1 || scratch == nullptr)) return SHRIKE_BAD_ARGUMENT;
+  if (has_single && (splits < 1 || splits > MAX_SPLITS || scratch == nullptr || arrivals == nullptr)) return SHRIKE_BAD_ARGUMENT;
   static bool configured = false;
   if (!configured) {
     cudaError_t e1 = cudaFuncSetAttribute(portions_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(PORTIONS_SMEM));
@@ -478,11 +558,11 @@ SHRIKE_API int shrike_paged_attention_bf16(const void* q, const void* k_cache, c
   p.scale_log2 = scale * LOG2E;
   p.partial_out = scratch;
   p.partial_ml = scratch ? scratch + static_cast<size_t>(num_seqs) * num_heads * p.splits * D : nullptr;
+  p.arrivals = arrivals;
   if (has_single) {
     const int group = num_heads / num_kv_heads;
     const dim3 grid(p.splits, num_kv_heads * ((group + 15) / 16), num_seqs);
     single_token_kernel<<<grid, THREADS, SINGLE_SMEM, stream>>>(p);
-    combine_splits_kernel<<<num_seqs * num_heads, D >= 128 ? 128 : 64, 0, stream>>>(p);
   }
   if (has_portions) {
     const dim3 grid((max_q_len + BM - 1) / BM, num_heads, num_seqs);

@@ -70,6 +70,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
                                    float eps, TO* __restrict__ out, int width, int partials,
                                    long long partial_stride) {
   __shared__ float scratch[33];
+  let_dependents_start();
   const int out_row = blockIdx.x;
   const int row = GATHER ? rows[out_row] : out_row;
   float* x = resid + static_cast<size_t>(row) * width;
@@ -184,6 +185,7 @@ SHRIKE_API int shrike_add_rmsnorm(float* resid, const void* delta, int delta_dty
 // ------------------------------------------------------------- SiLU * up
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
+  let_dependents_start();
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<size_t>(gridDim.x) * blockDim.x) {
     const size_t row = i / inter;

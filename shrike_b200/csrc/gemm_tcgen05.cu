@@ -22,6 +22,12 @@
 // stride between 8-row groups) understand; a k-step of 16 elements advances the
 // descriptor's start address by 32 bytes inside the swizzle atom.
 //
+// The kernel is launched as a programmatic dependent of the kernel before it: it may start
+// while that kernel is still running, sets up its barriers and tensor memory and already
+// streams the first weight tiles (weights are written by nobody), and only then waits
+// (griddepcontrol.wait) for the kernel before it to finish, before it touches the
+// activations or writes its output.
+//
 // Every wait is bounded.  When a wait runs out, the waiting role records where in
 // `status` (a host-visible word), raises a CTA-wide abort flag that ends the other roles'
 // waits, the producer waits (bounded again) for its copies in flight, TMEM is freed and
@@ -121,7 +127,7 @@ struct Args {
   int kblocks_per_split, stages, out_dtype;
 };
 
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, 3)
 gemm_swap_ab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const Args args) {
   extern __shared__ unsigned char smem_raw[];
   // tiles want 1024-byte alignment (the swizzle pattern repeats every 1024 bytes)
@@ -158,8 +164,17 @@ gemm_swap_ab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
   if (warp == 0) {
     if (lane == 0) {
-      int issued = 0;
-      for (int i = 0; i < num_kb; ++i) {
+      // weights first: they do not depend on the kernel before this one
+      const int early = min(num_kb, args.stages);
+      for (int i = 0; i < early; ++i) {
+        mbar_expect_tx(&sh->full[i], static_cast<unsigned>(stage_bytes));
+        tma_load_2d(tiles + stage_bytes * i, &map_w, &sh->full[i], (kb_begin + i) * BK, n0);
+      }
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      for (int i = 0; i < early; ++i)
+        tma_load_2d(tiles + stage_bytes * i + A_BYTES, &map_x, &sh->full[i], (kb_begin + i) * BK, t0);
+      int issued = early;
+      for (int i = early; i < num_kb; ++i) {
         const int s = i % args.stages;
         const unsigned phase = (i / args.stages) & 1;
         if (!mbar_wait(&sh->empty[s], phase ^ 1, sh, args.status, ERR_PRODUCER)) break;
@@ -204,6 +219,7 @@ gemm_swap_ab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     // epilogue: warp w may touch TMEM lanes 32 * (w % 4) .. + 31
     const int quarter = warp & 3;
     const int row = n0 + quarter * 32 + lane;   // weight row = output column
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // the output may still be read by the kernel before
     bool ok = true;
     if (num_kb > 0) ok = mbar_wait(&sh->done, 0, sh, args.status, ERR_EPILOGUE);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -304,6 +320,18 @@ static int tensor_map(const void* base, int rows, int cols, int box_rows, CUtens
 
 }  // namespace tc
 
+// Shared memory one CTA may take for its stages.  Half (or, for 16 token columns, a third
+// of) an SM's worth lets two or three CTAs live on an SM, so that one streams weights while
+// another starts up or stores its result.  0: choose by the token columns.
+static int g_smem_budget = 0;
+static int g_target_ctas = 148;
+static int g_dependent_launch = 1;
+SHRIKE_API void shrike_gemm_tc_dependent_launch(int enabled) { g_dependent_launch = enabled ? 1 : 0; }
+SHRIKE_API void shrike_gemm_tc_tune(int smem_budget_bytes, int target_ctas) {
+  if (smem_budget_bytes == 0 || (smem_budget_bytes >= 40 * 1024 && smem_budget_bytes <= 200 * 1024)) g_smem_budget = smem_budget_bytes;
+  if (target_ctas >= 1) g_target_ctas = target_ctas;
+}
+
 // How K is split for a product with `tokens` rows: enough CTAs to keep every SM
 // streaming, at least four k-blocks per CTA.  The same function sizes the partial stack.
 SHRIKE_API int shrike_gemm_tc_splits(int tokens, int n, int k) {
@@ -311,7 +339,7 @@ SHRIKE_API int shrike_gemm_tc_splits(int tokens, int n, int k) {
   const int tiles = (n + tc::BM - 1) / tc::BM;
   const int kblocks = (k + tc::BK - 1) / tc::BK;
   int splits = 1;
-  while (tiles * splits < 148 && splits < 16 && kblocks / (splits * 2) >= 4) splits *= 2;
+  while (tiles * splits < g_target_ctas && splits < 16 && kblocks / (splits * 2) >= 4) splits *= 2;
   // round so that no split is empty
   const int per = (kblocks + splits - 1) / splits;
   return (kblocks + per - 1) / per;
@@ -333,7 +361,9 @@ SHRIKE_API int shrike_gemm_tc(const void* x, const void* w, const float* bias, v
   const int per_split = (kblocks + splits - 1) / splits;
   if ((kblocks + per_split - 1) / per_split != splits) return SHRIKE_BAD_ARGUMENT;
   const size_t stage_bytes = A_BYTES + static_cast<size_t>(tn) * BK * 2;
-  int stages = static_cast<int>((200 * 1024) / stage_bytes);
+  const int budget = g_smem_budget ? g_smem_budget : (tn <= 16 ? 66 * 1024 : 100 * 1024);
+  int stages = static_cast<int>(budget / stage_bytes);
+  if (stages < 2) stages = 2;
   stages = stages > MAX_STAGES ? MAX_STAGES : stages;
   if (stages > per_split) stages = per_split < 2 ? 2 : per_split;
   const size_t smem = stage_bytes * stages + sizeof(Shared) + 1024;
@@ -359,7 +389,17 @@ SHRIKE_API int shrike_gemm_tc(const void* x, const void* w, const float* bias, v
   args.kblocks_per_split = per_split;
   args.stages = stages;
   args.out_dtype = out_dtype;
-  const dim3 grid((n + BM - 1) / BM, splits, token_tiles);
-  gemm_swap_ab_kernel<<<grid, THREADS, smem, stream>>>(map_w, map_x, args);
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3((n + BM - 1) / BM, splits, token_tiles);
+  config.blockDim = dim3(THREADS);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute;
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = g_dependent_launch;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  const cudaError_t err = cudaLaunchKernelEx(&config, gemm_swap_ab_kernel, map_w, map_x, args);
+  if (err != cudaSuccess) return static_cast<int>(err);
   return shrike_launch_status();
 }

@@ -70,6 +70,7 @@ class CudaOps:
             self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._scratch = None     # partial results of split single-token attention
         self._sample_scratch = None  # per-slice winners of the sampling kernel
+        self._arrivals = None    # per kv head: splits of single-token attention that have finished
         self.generation = 0      # grows when the scratch moves
         self.launches = 0        # launches of this package's own kernels
         self.library_calls = 0   # matrix products handed to cuBLAS
@@ -104,9 +105,10 @@ class CudaOps:
             )
             lib.shrike_paged_attention_generic.restype = _I
             lib.shrike_paged_attention_bf16.argtypes = (
-                [_P, _P, _P, _P, _I, _P, _P] + [_I] * 5 + [_F, _I, _P] + [_I] * 4 + [_P, _P]
+                [_P, _P, _P, _P, _I, _P, _P] + [_I] * 5 + [_F, _I, _P] + [_I] * 4 + [_P, _P, _P]
             )
             lib.shrike_paged_attention_bf16.restype = _I
+            lib.shrike_attention_bf16_resident_ctas.restype = _I
             self._attention[head_dim] = lib
         return lib
 
@@ -272,21 +274,26 @@ class CudaOps:
             raise KernelError("paged_attention in bfloat16 needs max_q_len, the longest entry of the batch")
         has_single = min_q_len <= 1
         has_portions = max_q_len > 1
-        splits, scratch = 1, None
+        splits, scratch, arrivals = 1, None, None
         if has_single:
             row_tiles = -(-(num_heads // num_kv_heads) // 16)
             tiles = max(1, -(-(max_blocks * page_size) // 64))
-            splits = max(1, min(tiles, 32, 592 // max(1, num_seqs * num_kv_heads * row_tiles)))
+            resident = lib.shrike_attention_bf16_resident_ctas()
+            splits = max(1, min(tiles, 16, resident // max(1, num_seqs * num_kv_heads * row_tiles)))
             need = num_seqs * num_heads * splits * (head_dim + 2)
             if self._scratch is None or self._scratch.numel() < need:
                 self._scratch = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=self.device)
                 self.generation += 1
-            scratch = self._scratch
-        self.launches += (2 if has_single else 0) + (1 if has_portions else 0)
+            groups = num_seqs * num_kv_heads * row_tiles
+            if self._arrivals is None or self._arrivals.numel() < groups:
+                self._arrivals = torch.zeros(max(groups, 4096), dtype=torch.int32, device=self.device)
+                self.generation += 1
+            scratch, arrivals = self._scratch, self._arrivals
+        self.launches += (1 if has_single else 0) + (1 if has_portions else 0)
         _check(lib.shrike_paged_attention_bf16(
             _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), max_blocks, _ptr(q_start), _ptr(ctx_len),
             num_seqs, num_heads, num_kv_heads, page_size, num_pages, scale, window or 0, _ptr(out),
-            int(has_single), int(has_portions), max_q_len, splits, _ptr(scratch), self._stream()),
+            int(has_single), int(has_portions), max_q_len, splits, _ptr(scratch), _ptr(arrivals), self._stream()),
             "paged_attention_bf16")
 
     def silu_mul(self, gate_up, out):
