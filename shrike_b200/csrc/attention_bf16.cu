@@ -224,6 +224,8 @@ __global__ void __launch_bounds__(THREADS) portions_kernel(const Params p) {
   bf16* k_tiles = q_tile + BM * ROW;                          // [2][BN][ROW]
   bf16* v_tiles = k_tiles + 2 * BN * ROW;                     // [2][BN][ROW]
   __shared__ long long tile_rows[2][BN];
+  let_dependents_start();
+  wait_for_previous();
   const int seq = blockIdx.z, head = blockIdx.y, tile_start = blockIdx.x * BM;
   const int start = p.q_start[seq];
   const int q_len = p.q_start[seq + 1] - start;
@@ -324,6 +326,7 @@ __global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
   bf16* k_tiles = q_tile + 16 * ROW;                          // [ST][BN][ROW]
   bf16* v_tiles = k_tiles + ST * BN * ROW;
   let_dependents_start();
+  wait_for_previous();
   const int seq = blockIdx.z, split = blockIdx.x;
   const int group = p.num_heads / p.num_kv_heads;
   const int row_tiles = (group + 15) / 16;
@@ -562,11 +565,11 @@ SHRIKE_API int shrike_paged_attention_bf16(const void* q, const void* k_cache, c
   if (has_single) {
     const int group = num_heads / num_kv_heads;
     const dim3 grid(p.splits, num_kv_heads * ((group + 15) / 16), num_seqs);
-    single_token_kernel<<<grid, THREADS, SINGLE_SMEM, stream>>>(p);
+    launch_dependent(single_token_kernel, grid, THREADS, SINGLE_SMEM, stream, p);
   }
   if (has_portions) {
     const dim3 grid((max_q_len + BM - 1) / BM, num_heads, num_seqs);
-    portions_kernel<<<grid, THREADS, PORTIONS_SMEM, stream>>>(p);
+    launch_dependent(portions_kernel, grid, THREADS, PORTIONS_SMEM, stream, p);
   }
   return shrike_launch_status();
 }

@@ -53,6 +53,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
                                int num_heads, int num_kv_heads, int page_size, int num_pages,
                                float scale, int window, T* __restrict__ out, int num_tokens) {
   __shared__ float q_shared[WARPS][D];
+  let_dependents_start();
+  wait_for_previous();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long work = static_cast<long long>(blockIdx.x) * WARPS + warp;
   if (work >= static_cast<long long>(num_tokens) * num_heads) return;

@@ -28,9 +28,33 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(f
   return __float2bfloat16_rn(v);
 }
 
-// Lets a kernel launched as a programmatic dependent of this one start now (it still waits
-// for this kernel to finish before it touches what this kernel writes).  No effect otherwise.
+// Programmatic dependent launch.  Every kernel of this package is launched so that it may
+// start while the kernel before it on the stream is still running (its launch latency and
+// set-up are hidden that way), and every kernel begins with
+//   let_dependents_start();   the kernel after this one may start now
+//   wait_for_previous();      block until the kernel before this one has finished and its
+//                             writes are visible
+// before it reads or writes any memory that another kernel touches.  Only work on memory
+// that no kernel writes (weights) may come before wait_for_previous().
 __device__ __forceinline__ void let_dependents_start() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void wait_for_previous() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Launches `kernel` as a programmatic dependent of the work before it on `stream`.
+template <typename... KernelArgs, typename... Args>
+static inline cudaError_t launch_dependent(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem,
+                                           cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute;
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+}
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

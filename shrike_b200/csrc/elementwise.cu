@@ -9,6 +9,8 @@
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                              float* __restrict__ out, int width, int vocab) {
+  let_dependents_start();
+  wait_for_previous();
   const int row = blockIdx.x;
   int id = ids[row];
   const bool valid = id >= 0 && id < vocab;
@@ -24,9 +26,9 @@ SHRIKE_API int shrike_embed(const int* ids, const void* table, int table_dtype, 
   if (width <= 0 || vocab <= 0) return SHRIKE_BAD_ARGUMENT;
   const int threads = width >= 1024 ? 256 : 128;
   if (table_dtype == SHRIKE_F32)
-    embed_kernel<float><<<n, threads, 0, stream>>>(ids, static_cast<const float*>(table), out, width, vocab);
+    launch_dependent(embed_kernel<float>, n, threads, 0, stream, ids, static_cast<const float*>(table), out, width, vocab);
   else if (table_dtype == SHRIKE_BF16)
-    embed_kernel<__nv_bfloat16><<<n, threads, 0, stream>>>(ids, static_cast<const __nv_bfloat16*>(table), out, width, vocab);
+    launch_dependent(embed_kernel<__nv_bfloat16>, n, threads, 0, stream, ids, static_cast<const __nv_bfloat16*>(table), out, width, vocab);
   else
     return SHRIKE_BAD_ARGUMENT;
   return shrike_launch_status();
@@ -71,6 +73,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
                                    long long partial_stride) {
   __shared__ float scratch[33];
   let_dependents_start();
+  wait_for_previous();
   const int out_row = blockIdx.x;
   const int row = GATHER ? rows[out_row] : out_row;
   float* x = resid + static_cast<size_t>(row) * width;
@@ -146,9 +149,9 @@ static int launch_add_rmsnorm(float* resid, const void* delta, const int* rows, 
   while (threads < 1024 && threads * 2 <= ((groups + 31) / 32) * 32) threads *= 2;
   if (static_cast<long long>(threads) * NORM_MAX_PER_THREAD < groups) return SHRIKE_BAD_ARGUMENT;
 #define SHRIKE_NORM_LAUNCH(G, V)                                                                   \
-  add_rmsnorm_kernel<TD, TO, HAS_DELTA, G, V><<<n, threads, 0, stream>>>(                          \
-      resid, static_cast<const TD*>(delta), rows, weight, eps, static_cast<TO*>(out), width, partials,      \
-      partial_stride)
+  launch_dependent(add_rmsnorm_kernel<TD, TO, HAS_DELTA, G, V>, n, threads, 0, stream, resid,      \
+                   static_cast<const TD*>(delta), rows, weight, eps, static_cast<TO*>(out), width, partials,  \
+                   partial_stride)
   if (rows) { if (vec) SHRIKE_NORM_LAUNCH(true, 4); else SHRIKE_NORM_LAUNCH(true, 1); }
   else { if (vec) SHRIKE_NORM_LAUNCH(false, 4); else SHRIKE_NORM_LAUNCH(false, 1); }
 #undef SHRIKE_NORM_LAUNCH
@@ -186,6 +189,7 @@ SHRIKE_API int shrike_add_rmsnorm(float* resid, const void* delta, int delta_dty
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
   let_dependents_start();
+  wait_for_previous();
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<size_t>(gridDim.x) * blockDim.x) {
     const size_t row = i / inter;
@@ -204,9 +208,9 @@ SHRIKE_API int shrike_silu_mul(const void* gate_up, void* out, int dtype, int n,
   const int threads = 256;
   const int blocks = static_cast<int>(min(static_cast<size_t>(148 * 16), (total + threads - 1) / threads));
   if (dtype == SHRIKE_F32)
-    silu_mul_kernel<float><<<blocks, threads, 0, stream>>>(static_cast<const float*>(gate_up), static_cast<float*>(out), inter, total);
+    launch_dependent(silu_mul_kernel<float>, blocks, threads, 0, stream, static_cast<const float*>(gate_up), static_cast<float*>(out), inter, total);
   else if (dtype == SHRIKE_BF16)
-    silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), inter, total);
+    launch_dependent(silu_mul_kernel<__nv_bfloat16>, blocks, threads, 0, stream, static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), inter, total);
   else
     return SHRIKE_BAD_ARGUMENT;
   return shrike_launch_status();
@@ -226,6 +230,8 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const float*
                                      const int* __restrict__ slots, T* __restrict__ k_out, T* __restrict__ v_out,
                                      int num_heads, int num_kv_heads, int head_dim, long long num_slots,
                                      int partials, long long partial_stride) {
+  let_dependents_start();
+  wait_for_previous();
   const int token = blockIdx.x, head = blockIdx.y;
   const int half = head_dim / 2;
   const int q_width = num_heads * head_dim, kv_width = num_kv_heads * head_dim;
@@ -293,7 +299,7 @@ SHRIKE_API int shrike_rope_kv_write(const float* qkv, const float* bias, const i
   const int threads = half <= 32 ? 32 : (half <= 64 ? 64 : 128);
   const dim3 grid(n, num_heads + 2 * num_kv_heads);
 #define SHRIKE_ROPE_CASE(T)                                                                         \
-  rope_kv_write_kernel<T><<<grid, threads, 0, stream>>>(                                            \
+  launch_dependent(rope_kv_write_kernel<T>, grid, threads, 0, stream,                               \
       qkv, bias, positions, inv_freq, static_cast<T*>(q_out), static_cast<T*>(k_cache),             \
       static_cast<T*>(v_cache), slots, static_cast<T*>(k_out), static_cast<T*>(v_out), num_heads,   \
       num_kv_heads, head_dim, num_slots, partials, partial_stride)
@@ -309,6 +315,8 @@ template <typename T>
 __global__ void kv_write_kernel(const T* __restrict__ k_new, const T* __restrict__ v_new,
                                 T* __restrict__ k_cache, T* __restrict__ v_cache,
                                 const int* __restrict__ slots, int kv_width, long long num_slots) {
+  let_dependents_start();
+  wait_for_previous();
   const int token = blockIdx.x;
   const long long slot = slots[token];
   if (slot < 0 || slot >= num_slots) return;

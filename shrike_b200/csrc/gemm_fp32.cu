@@ -12,6 +12,8 @@ gemm_fp32_kernel(const float* __restrict__ A, const float* __restrict__ W, const
                  float* __restrict__ C, int M, int N, int K, int vec_ok) {
   __shared__ __align__(16) float a_tile[BK][BM + 4];
   __shared__ __align__(16) float w_tile[BK][BN + 4];
+  let_dependents_start();
+  wait_for_previous();
   const int tid = threadIdx.x;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int load_row = tid >> 2, load_k = (tid & 3) * 4;

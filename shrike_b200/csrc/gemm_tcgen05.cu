@@ -135,6 +135,7 @@ gemm_swap_ab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   const size_t b_bytes = static_cast<size_t>(args.tn) * BK * 2;
   const size_t stage_bytes = A_BYTES + b_bytes;
   Shared* sh = reinterpret_cast<Shared*>(tiles + stage_bytes * args.stages);
+  let_dependents_start();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BM, split = blockIdx.y, t0 = blockIdx.z * args.tn;
   const int total_kblocks = (args.k + BK - 1) / BK;

@@ -74,6 +74,8 @@ sample_slices_kernel(const float* __restrict__ logits, const float* __restrict__
                      const float* __restrict__ top_p, const long long* __restrict__ seeds,
                      float* __restrict__ partial_value, int* __restrict__ partial_index, int vocab, int chunks) {
   __shared__ Best best_scratch[33];
+  let_dependents_start();
+  wait_for_previous();
   const int row = blockIdx.y, chunk = blockIdx.x;
   const float temp = temperature[row];
   if (temp != 0.f && top_p[row] < 1.0f) return;
@@ -105,6 +107,8 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
               int chunks) {
   __shared__ float scratch[33];
   __shared__ Best best_scratch[33];
+  let_dependents_start();
+  wait_for_previous();
   const int row = blockIdx.x;
   const float* x = logits + static_cast<size_t>(row) * vocab;
   const float temp = temperature[row];
@@ -167,10 +171,10 @@ SHRIKE_API int shrike_sample(const float* logits, const float* temperature, cons
   if (rows <= 0) return SHRIKE_OK;
   if (vocab <= 0 || rows > 65535 || scratch_value == nullptr || scratch_index == nullptr) return SHRIKE_BAD_ARGUMENT;
   const int chunks = shrike_sample_slices(vocab);
-  sample_slices_kernel<<<dim3(chunks, rows), SLICE_THREADS, 0, stream>>>(logits, temperature, top_p, seeds,
-                                                                         scratch_value, scratch_index, vocab, chunks);
-  sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, temperature, top_p, seeds, out, scratch_value,
-                                                     scratch_index, vocab, chunks);
+  launch_dependent(sample_slices_kernel, dim3(chunks, rows), SLICE_THREADS, 0, stream, logits, temperature, top_p, seeds,
+                   scratch_value, scratch_index, vocab, chunks);
+  launch_dependent(sample_kernel, rows, SAMPLE_THREADS, 0, stream, logits, temperature, top_p, seeds, out,
+                   static_cast<const float*>(scratch_value), static_cast<const int*>(scratch_index), vocab, chunks);
   return shrike_launch_status();
 }
 

@@ -112,6 +112,9 @@ def compile_library(name: str, sources, defines=None, extra_flags=(), verbose=Tr
                 scratch.unlink(missing_ok=True)
                 raise BuildError(f"nvcc failed for {name}:\n{' '.join(command)}\n{output}")
             os.replace(scratch, target)
+            for stale in target.parent.glob(f"{name}-*.so"):   # older builds of the same library
+                if stale != target and ".tmp" not in stale.name:
+                    stale.unlink(missing_ok=True)
             if verbose:
                 print(f"[shrike_b200] built {target.name} in {time.time() - started:.1f}s",
                       file=sys.stderr, flush=True)
