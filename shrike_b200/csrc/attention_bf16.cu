@@ -28,14 +28,15 @@
 namespace bf16attn {
 
 constexpr int D = SHRIKE_HEAD_DIM;
-constexpr int BN = 64;              // keys per tile
+constexpr int BN = 64;              // keys per tile, single tokens
+constexpr int PBN = 32;             // keys per tile, portions: small tiles and few registers, so that four CTAs fit an SM
 constexpr int BM = 64;              // query rows per CTA (portions)
 constexpr int THREADS = 128;
 constexpr int ROW = D + 8;          // padded row, in elements: 16 bytes of padding keep ldmatrix conflict-free
 constexpr int CHUNKS = D / 8;       // 16-byte chunks per row
 constexpr int KSTEPS = D / 16;
 constexpr int DTILES = D / 8;
-constexpr bool Q_IN_REGS = D <= 128;
+constexpr bool Q_IN_REGS = D <= 128;   // single tokens keep the query fragments in registers
 constexpr float LOG2E = 1.4426950408889634f;
 using bf16 = __nv_bfloat16;
 
@@ -88,9 +89,10 @@ struct Params {
 // Where the keys [tile_base, tile_base + BN) of one kv head start in the cache, in
 // elements; -1 for keys outside [lo, hi] or on a page the sequence does not hold.  One
 // table lookup and one division per key, done by the first BN threads.
+template <int KEYS>
 __device__ __forceinline__ void locate_tile(long long* rows, const Params& p, const int* table, int kv_head,
                                             int tile_base, int lo, int hi) {
-  if (threadIdx.x < BN) {
+  if (threadIdx.x < KEYS) {
     const int j = tile_base + threadIdx.x;
     long long offset = -1;
     if (j >= lo && j <= hi) {
@@ -107,8 +109,9 @@ __device__ __forceinline__ void locate_tile(long long* rows, const Params& p, co
 // Copies the located keys and values into k_tile / v_tile; consecutive threads take
 // consecutive 16-byte chunks of a row, so a warp's copies cover whole 128-byte lines.
 // Keys without a row become zeros.
+template <int KEYS>
 __device__ __forceinline__ void copy_tile(bf16* k_tile, bf16* v_tile, const Params& p, const long long* rows) {
-  for (int c = threadIdx.x; c < BN * CHUNKS; c += THREADS) {
+  for (int c = threadIdx.x; c < KEYS * CHUNKS; c += THREADS) {
     const int key = c / CHUNKS, chunk = c - key * CHUNKS;
     const long long row = rows[key];
     const bool valid = row >= 0;
@@ -119,23 +122,24 @@ __device__ __forceinline__ void copy_tile(bf16* k_tile, bf16* v_tile, const Para
 }
 
 // Both steps at once, with a barrier between them (for code that loads one tile ahead).
+template <int KEYS>
 __device__ __forceinline__ void load_kv_tile(bf16* k_tile, bf16* v_tile, long long* rows, const Params& p,
                                              const int* table, int kv_head, int tile_base, int lo, int hi) {
-  locate_tile(rows, p, table, kv_head, tile_base, lo, hi);
+  locate_tile<KEYS>(rows, p, table, kv_head, tile_base, lo, hi);
   __syncthreads();
-  copy_tile(k_tile, v_tile, p, rows);
+  copy_tile<KEYS>(k_tile, v_tile, p, rows);
 }
 
 // S[16 x (8 * NT)] += Q[16 x D] * K^T for keys [key0, key0 + 8 * NT) of the tile.
-template <int NT>
-__device__ __forceinline__ void scores(float (&s)[NT][4], const unsigned (&q_frag)[Q_IN_REGS ? KSTEPS : 1][4],
+template <int NT, bool IN_REGS>
+__device__ __forceinline__ void scores(float (&s)[NT][4], const unsigned (&q_frag)[IN_REGS ? KSTEPS : 1][4],
                                        const bf16* q_rows, const bf16* k_tile, int key0, int lane) {
 #pragma unroll
   for (int kk = 0; kk < KSTEPS; ++kk) {
     unsigned a[4];
-    if (Q_IN_REGS) {
+    if (IN_REGS) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) a[i] = q_frag[Q_IN_REGS ? kk : 0][i];
+      for (int i = 0; i < 4; ++i) a[i] = q_frag[IN_REGS ? kk : 0][i];
     } else {
       ldmatrix_x4(a, q_rows + ((lane & 7) + 8 * ((lane >> 3) & 1)) * ROW + kk * 16 + 8 * (lane >> 4));
     }
@@ -218,15 +222,16 @@ __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&o)[DTI
 }
 
 // ------------------------------------------------------------------ portions
-__global__ void __launch_bounds__(THREADS) portions_kernel(const Params p) {
+__global__ void __launch_bounds__(THREADS, D <= 128 ? 4 : 2) portions_kernel(const Params p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);           // [BM][ROW]
-  bf16* k_tiles = q_tile + BM * ROW;                          // [2][BN][ROW]
-  bf16* v_tiles = k_tiles + 2 * BN * ROW;                     // [2][BN][ROW]
-  __shared__ long long tile_rows[2][BN];
+  bf16* k_tiles = q_tile + BM * ROW;                          // [2][PBN][ROW]
+  bf16* v_tiles = k_tiles + 2 * PBN * ROW;                    // [2][PBN][ROW]
+  __shared__ long long tile_rows[2][PBN];
   let_dependents_start();
   wait_for_previous();
-  const int seq = blockIdx.z, head = blockIdx.y, tile_start = blockIdx.x * BM;
+  const int seq = blockIdx.z, head = blockIdx.y;
+  const int tile_start = (gridDim.x - 1 - blockIdx.x) * BM;   // long tiles are scheduled first
   const int start = p.q_start[seq];
   const int q_len = p.q_start[seq + 1] - start;
   if (tile_start >= q_len || (q_len == 1 && p.skip_single)) return;
@@ -237,7 +242,7 @@ __global__ void __launch_bounds__(THREADS) portions_kernel(const Params p) {
   const int rows_here = min(BM, q_len - tile_start);
   const int lo = p.window > 0 ? max(0, pos0 + tile_start - p.window + 1) : 0;
   const int hi = pos0 + tile_start + rows_here - 1;
-  const int tile_lo = lo / BN, tile_hi = hi / BN;
+  const int tile_lo = lo / PBN, tile_hi = hi / PBN;
 
   for (int c = threadIdx.x; c < BM * CHUNKS; c += THREADS) {
     const int row = c / CHUNKS, chunk = c - row * CHUNKS;
@@ -245,7 +250,7 @@ __global__ void __launch_bounds__(THREADS) portions_kernel(const Params p) {
     const bf16* src = p.q + (static_cast<size_t>(start + tile_start + (valid ? row : 0)) * p.num_heads + head) * D + chunk * 8;
     cp_async16(q_tile + row * ROW + chunk * 8, src, valid);
   }
-  load_kv_tile(k_tiles, v_tiles, tile_rows[0], p, table, kv_head, tile_lo * BN, lo, hi);
+  load_kv_tile<PBN>(k_tiles, v_tiles, tile_rows[0], p, table, kv_head, tile_lo * PBN, lo, hi);
   cp_async_commit();
 
   int first[2], last[2];
@@ -261,39 +266,34 @@ __global__ void __launch_bounds__(THREADS) portions_kernel(const Params p) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
   float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.f, 0.f};
-  unsigned q_frag[Q_IN_REGS ? KSTEPS : 1][4];
+  unsigned q_frag[1][4];   // query fragments are re-read from shared memory: registers are the scarcer resource here
   const bf16* q_rows = q_tile + warp * 16 * ROW;
 
   for (int tile = tile_lo; tile <= tile_hi; ++tile) {
     const int buffer = (tile - tile_lo) & 1;
     if (tile < tile_hi) {
-      load_kv_tile(k_tiles + (buffer ^ 1) * BN * ROW, v_tiles + (buffer ^ 1) * BN * ROW, tile_rows[buffer ^ 1], p, table,
-                   kv_head, (tile + 1) * BN, lo, hi);
+      load_kv_tile<PBN>(k_tiles + (buffer ^ 1) * PBN * ROW, v_tiles + (buffer ^ 1) * PBN * ROW, tile_rows[buffer ^ 1], p,
+                        table, kv_head, (tile + 1) * PBN, lo, hi);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
     }
     __syncthreads();
-    if (Q_IN_REGS && tile == tile_lo) {
-#pragma unroll
-      for (int kk = 0; kk < KSTEPS; ++kk)
-        ldmatrix_x4(q_frag[Q_IN_REGS ? kk : 0], q_rows + ((lane & 7) + 8 * ((lane >> 3) & 1)) * ROW + kk * 16 + 8 * (lane >> 4));
-    }
     // a warp whose rows all end before this tile has nothing to add
     const int warp_last = pos0 + min(q_len, tile_start + warp * 16 + 16) - 1;
-    const bool warp_active = tile_start + warp * 16 < q_len && tile * BN <= warp_last;
+    const bool warp_active = tile_start + warp * 16 < q_len && tile * PBN <= warp_last;
     if (warp_active) {
-      float s[BN / 8][4];
+      float s[PBN / 8][4];
 #pragma unroll
-      for (int j = 0; j < BN / 8; ++j)
+      for (int j = 0; j < PBN / 8; ++j)
 #pragma unroll
         for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
-      const bf16* k_tile = k_tiles + buffer * BN * ROW;
-      const bf16* v_tile = v_tiles + buffer * BN * ROW;
-      scores<BN / 8>(s, q_frag, q_rows, k_tile, 0, lane);
-      softmax_update<BN / 8>(s, o, row_max, row_sum, first, last, tile * BN, p.scale_log2, lane);
-      accumulate<BN / 8>(o, s, v_tile, 0, lane);
+      const bf16* k_tile = k_tiles + buffer * PBN * ROW;
+      const bf16* v_tile = v_tiles + buffer * PBN * ROW;
+      scores<PBN / 8, false>(s, q_frag, q_rows, k_tile, 0, lane);
+      softmax_update<PBN / 8>(s, o, row_max, row_sum, first, last, tile * PBN, p.scale_log2, lane);
+      accumulate<PBN / 8>(o, s, v_tile, 0, lane);
     }
     __syncthreads();
   }
@@ -361,13 +361,13 @@ __global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
 #pragma unroll
     for (int ahead = 0; ahead < ST; ++ahead)
       if (my_lo + ahead <= my_hi)
-        locate_tile(tile_rows[ahead % (ST + 1)], p, table, kv_head, (my_lo + ahead) * BN, first_key, last_key);
+        locate_tile<BN>(tile_rows[ahead % (ST + 1)], p, table, kv_head, (my_lo + ahead) * BN, first_key, last_key);
     __syncthreads();
     // one commit group per tile, also when there is no tile left, so that the count is uniform
 #pragma unroll
     for (int ahead = 0; ahead < ST - 1; ++ahead) {
       if (my_lo + ahead <= my_hi)
-        copy_tile(k_tiles + ahead * BN * ROW, v_tiles + ahead * BN * ROW, p, tile_rows[ahead % (ST + 1)]);
+        copy_tile<BN>(k_tiles + ahead * BN * ROW, v_tiles + ahead * BN * ROW, p, tile_rows[ahead % (ST + 1)]);
       cp_async_commit();
     }
     int first[2] = {first_key, first_key}, last[2] = {last_key, last_key};
@@ -377,11 +377,11 @@ __global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
       const int ahead = tile + ST - 1;
       if (ahead <= my_hi) {
         const int into = (ahead - my_lo) % ST;
-        copy_tile(k_tiles + into * BN * ROW, v_tiles + into * BN * ROW, p, tile_rows[(ahead - my_lo) % (ST + 1)]);
+        copy_tile<BN>(k_tiles + into * BN * ROW, v_tiles + into * BN * ROW, p, tile_rows[(ahead - my_lo) % (ST + 1)]);
       }
       cp_async_commit();
       if (ahead + 1 <= my_hi)   // read in the next round, after this round's closing barrier
-        locate_tile(tile_rows[(ahead + 1 - my_lo) % (ST + 1)], p, table, kv_head, (ahead + 1) * BN, first_key, last_key);
+        locate_tile<BN>(tile_rows[(ahead + 1 - my_lo) % (ST + 1)], p, table, kv_head, (ahead + 1) * BN, first_key, last_key);
       cp_async_wait<ST - 1>();
       __syncthreads();
       if (Q_IN_REGS && tile == my_lo) {
@@ -392,7 +392,7 @@ __global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
       const int key0 = warp * 16;
       if (tile * BN + key0 <= last_key && tile * BN + key0 + 15 >= first_key) {
         float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-        scores<2>(s, q_frag, q_tile, k_tiles + buffer * BN * ROW, key0, lane);
+        scores<2, Q_IN_REGS>(s, q_frag, q_tile, k_tiles + buffer * BN * ROW, key0, lane);
         softmax_update<2>(s, o, row_max, row_sum, first, last, tile * BN + key0, p.scale_log2, lane);
         accumulate<2>(o, s, v_tiles + buffer * BN * ROW, key0, lane);
       }
@@ -499,7 +499,7 @@ __global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
   }
 }
 
-constexpr size_t PORTIONS_SMEM = sizeof(bf16) * (BM * ROW + 4 * BN * ROW);
+constexpr size_t PORTIONS_SMEM = sizeof(bf16) * (BM * ROW + 4 * PBN * ROW);
 constexpr size_t SINGLE_TILES_SMEM = sizeof(bf16) * (16 * ROW + 2 * ST * BN * ROW);
 constexpr size_t SINGLE_MERGE_SMEM = sizeof(float) * (4 * 16 * D + 4 * 16 * 2);
 constexpr size_t SINGLE_SMEM = SINGLE_TILES_SMEM > SINGLE_MERGE_SMEM ? SINGLE_TILES_SMEM : SINGLE_MERGE_SMEM;

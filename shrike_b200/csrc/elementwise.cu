@@ -186,33 +186,61 @@ SHRIKE_API int shrike_add_rmsnorm(float* resid, const void* delta, int delta_dty
 }
 
 // ------------------------------------------------------------- SiLU * up
-template <typename T>
+// out[r, c] = silu(gate_up[r, c]) * gate_up[r, inter + c], silu(g) = g / (1 + exp(-g)),
+// in float32 with one rounding.  VEC elements per thread and access (16 bytes when the
+// row length allows, else one).
+template <typename T, int VEC>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
   let_dependents_start();
   wait_for_previous();
-  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+  const int groups_per_row = inter / VEC;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total / VEC;
        i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    const size_t row = i / inter;
-    const int col = static_cast<int>(i - row * inter);
-    const float g = to_float(gate_up[row * 2 * inter + col]);
-    const float u = to_float(gate_up[row * 2 * inter + inter + col]);
-    const float silu = g / (1.0f + expf(-g));
-    out[i] = from_float<T>(__fmul_rn(silu, u));
+    const size_t row = i / groups_per_row;
+    const int col = static_cast<int>(i - row * groups_per_row) * VEC;
+    const T* g_ptr = gate_up + row * 2 * inter + col;
+    const T* u_ptr = g_ptr + inter;
+    T* o_ptr = out + row * inter + col;
+    if (VEC == 1) {
+      const float g = to_float(*g_ptr), u = to_float(*u_ptr);
+      *o_ptr = from_float<T>(__fmul_rn(g / (1.0f + expf(-g)), u));
+    } else {
+      struct alignas(16) Pack { T v[VEC]; };
+      const Pack g = *reinterpret_cast<const Pack*>(g_ptr);
+      const Pack u = *reinterpret_cast<const Pack*>(u_ptr);
+      Pack r;
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) {
+        const float gv = to_float(g.v[j]);
+        r.v[j] = from_float<T>(__fmul_rn(gv / (1.0f + expf(-gv)), to_float(u.v[j])));
+      }
+      *reinterpret_cast<Pack*>(o_ptr) = r;
+    }
   }
+}
+
+template <typename T>
+static void launch_silu_mul(const void* gate_up, void* out, int n, int inter, cudaStream_t stream) {
+  constexpr int WIDE = 16 / sizeof(T);
+  const bool vec = inter % WIDE == 0 && (reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) % 16 == 0;
+  const size_t total = static_cast<size_t>(n) * inter;
+  const size_t work = vec ? total / WIDE : total;
+  const int threads = 256;
+  const int blocks = static_cast<int>(min(static_cast<size_t>(148 * 16), (work + threads - 1) / threads));
+  if (vec)
+    launch_dependent(silu_mul_kernel<T, WIDE>, blocks, threads, 0, stream, static_cast<const T*>(gate_up),
+                     static_cast<T*>(out), inter, total);
+  else
+    launch_dependent(silu_mul_kernel<T, 1>, blocks, threads, 0, stream, static_cast<const T*>(gate_up),
+                     static_cast<T*>(out), inter, total);
 }
 
 SHRIKE_API int shrike_silu_mul(const void* gate_up, void* out, int dtype, int n, int inter, cudaStream_t stream) {
   if (n <= 0) return SHRIKE_OK;
   if (inter <= 0) return SHRIKE_BAD_ARGUMENT;
-  const size_t total = static_cast<size_t>(n) * inter;
-  const int threads = 256;
-  const int blocks = static_cast<int>(min(static_cast<size_t>(148 * 16), (total + threads - 1) / threads));
-  if (dtype == SHRIKE_F32)
-    launch_dependent(silu_mul_kernel<float>, blocks, threads, 0, stream, static_cast<const float*>(gate_up), static_cast<float*>(out), inter, total);
-  else if (dtype == SHRIKE_BF16)
-    launch_dependent(silu_mul_kernel<__nv_bfloat16>, blocks, threads, 0, stream, static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), inter, total);
-  else
-    return SHRIKE_BAD_ARGUMENT;
+  if (dtype == SHRIKE_F32) launch_silu_mul<float>(gate_up, out, n, inter, stream);
+  else if (dtype == SHRIKE_BF16) launch_silu_mul<__nv_bfloat16>(gate_up, out, n, inter, stream);
+  else return SHRIKE_BAD_ARGUMENT;
   return shrike_launch_status();
 }
 
