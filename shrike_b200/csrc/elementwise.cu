@@ -245,8 +245,8 @@ SHRIKE_API int shrike_silu_mul(const void* gate_up, void* out, int dtype, int n,
 }
 
 // --------------------------------------- bias + rotary + key/value store
-// One block per (token, head) over the q, k and v heads; one thread per rotation
-// pair.  qkv is the float32 result of the fused projection,
+// One thread per rotation pair; blockIdx.x is the token, blockIdx.y a slice of the
+// (head, pair) space over the q, k and v heads (many slices for few tokens, one for many).  qkv is the float32 result of the fused projection,
 // [n, (H + 2 Hkv) * D]: q heads, then k heads, then v heads.  The angle of pair j
 // is float(position) * inv_freq[j]; pair j rotates elements j and j + D/2.
 // Rotated q goes to q_out; rotated k and plain v go to the cache at slots[token]
@@ -260,18 +260,20 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const float*
                                      int partials, long long partial_stride) {
   let_dependents_start();
   wait_for_previous();
-  const int token = blockIdx.x, head = blockIdx.y;
+  const int token = blockIdx.x;
   const int half = head_dim / 2;
   const int q_width = num_heads * head_dim, kv_width = num_kv_heads * head_dim;
   const float* row = qkv + static_cast<size_t>(token) * (q_width + 2 * kv_width);
-  const bool is_q = head < num_heads, is_k = !is_q && head < num_heads + num_kv_heads;
   long long slot = -1;
-  if (!is_q && k_cache != nullptr) {
+  if (k_cache != nullptr) {
     slot = slots[token];
     if (slot < 0 || slot >= num_slots) slot = -1;  // never store outside the pool
   }
   const float pos = static_cast<float>(positions[token]);
-  for (int j = threadIdx.x; j < half; j += blockDim.x) {
+  const int pairs = (num_heads + 2 * num_kv_heads) * half;
+  for (int idx = blockIdx.y * blockDim.x + threadIdx.x; idx < pairs; idx += gridDim.y * blockDim.x) {
+    const int head = idx / half, j = idx - head * half;
+    const bool is_q = head < num_heads, is_k = !is_q && head < num_heads + num_kv_heads;
     const int lo = head * head_dim + j, hi = lo + half;  // columns of the row
     float a = row[lo], b = row[hi];
     for (int p = 1; p < partials; ++p) {   // slices of a K-split projection, added in order
@@ -322,10 +324,11 @@ SHRIKE_API int shrike_rope_kv_write(const float* qkv, const float* bias, const i
   if (head_dim <= 0 || head_dim % 2 || num_heads <= 0 || num_kv_heads <= 0) return SHRIKE_BAD_ARGUMENT;
   if ((k_cache == nullptr) != (v_cache == nullptr)) return SHRIKE_BAD_ARGUMENT;
   if ((k_out == nullptr) != (v_out == nullptr)) return SHRIKE_BAD_ARGUMENT;
-  if (num_heads + 2 * num_kv_heads > 65535) return SHRIKE_BAD_ARGUMENT;
-  const int half = head_dim / 2;
-  const int threads = half <= 32 ? 32 : (half <= 64 ? 64 : 128);
-  const dim3 grid(n, num_heads + 2 * num_kv_heads);
+  const int pairs = (num_heads + 2 * num_kv_heads) * (head_dim / 2);
+  const int threads = n >= 256 ? 256 : 64;
+  const int slices = n >= 256 ? 1 : (pairs + threads - 1) / threads;
+  if (slices > 65535) return SHRIKE_BAD_ARGUMENT;
+  const dim3 grid(n, slices);
 #define SHRIKE_ROPE_CASE(T)                                                                         \
   launch_dependent(rope_kv_write_kernel<T>, grid, threads, 0, stream,                               \
       qkv, bias, positions, inv_freq, static_cast<T*>(q_out), static_cast<T*>(k_cache),             \

@@ -123,6 +123,69 @@ class BatchBuilder:
         seeds, temps, top_ps = parts[0].view(np.int64), parts[1].view(np.float32), parts[2].view(np.float32)
         ids, pos, seq_of, q_start, ctx_arr, slot_arr, out_rows = parts[3:10]
 
+        if max(q_lens) == 1:
+            # the steady state of decoding: one token per entry, filled without per-token work
+            ids[:] = [e.tokens[0] for e in entries]
+            pos[:] = starts
+            seq_of[:] = np.arange(s, dtype=np.int32)
+            q_start[:] = np.arange(s + 1, dtype=np.int32)
+            ctx_arr[:] = ctx_lens
+            slot_arr[:] = [e.cache.slot for e in entries]
+            row = 0
+            for index, e in enumerate(entries):
+                for w in e.want:
+                    if w != 0:
+                        raise ValueError(f"wanted place {w} is outside the entry's 1 tokens")
+                    out_rows[row] = index
+                    if sampled:
+                        temps[row], top_ps[row], seeds[row] = e.sampling
+                    row += 1
+            for g in range(self.num_groups):
+                slots = parts[10 + 2 * g]
+                table2d = parts[11 + 2 * g].reshape(s, max_blocks[g])
+                table2d[:] = -1
+                width = max_blocks[g]
+                for index, e in enumerate(entries):
+                    table = e.cache.tables[g]
+                    pages = table.pages
+                    held = table.length if table.length < width else width
+                    table2d[index, :held] = pages[:held]
+                    p = starts[index]
+                    page_of = int(pages[p // page])
+                    if page_of < 0:
+                        raise ValueError(f"entry {index} writes into a page of group {g} it no longer holds")
+                    slots[index] = page_of * page + p % page
+        else:
+            self._fill_general(entries, q_lens, parts, max_blocks, sampled, page, s)
+
+        dev = self._dev[:total]
+        dev.copy_(host[:total], non_blocking=True)
+        if self.device.type == "cuda":
+            event = torch.cuda.Event()
+            event.record()
+            self._events[self._turn] = event
+        views = [dev[int(offsets[i]): int(offsets[i + 1])] for i in range(len(sizes))]
+        groups = [
+            GroupView(views[10 + 2 * g], views[11 + 2 * g].view(s, max_blocks[g]), max_blocks[g])
+            for g in range(self.num_groups)
+        ]
+        return StepContext(
+            num_tokens=n, num_seqs=s, num_rows=r,
+            token_ids=views[3], positions=views[4], seq_of_token=views[5], q_start=views[6],
+            ctx_len=views[7], state_slot=views[8], out_rows=views[9], groups=groups,
+            storage=self.storage, max_q_len=max(q_lens), min_q_len=min(q_lens), max_ctx_len=max(ctx_lens),
+            q_lens=q_lens, starts=starts, slots=[e.cache.slot for e in entries],
+            all_single=max(q_lens) == 1,
+            sample_temperature=views[1].view(torch.float32) if sampled else None,
+            sample_top_p=views[2].view(torch.float32) if sampled else None,
+            sample_seed=views[0].view(torch.int64) if sampled else None,
+        )
+
+    def _fill_general(self, entries, q_lens, parts, max_blocks, sampled, page, s):
+        """Entries of any length: portions beside single tokens."""
+        seeds, temps, top_ps = parts[0].view(np.int64), parts[1].view(np.float32), parts[2].view(np.float32)
+        ids, pos, seq_of, q_start, ctx_arr, slot_arr, out_rows = parts[3:10]
+        ctx_lens = [e.start + q for e, q in zip(entries, q_lens)]
         cursor = 0
         row = 0
         q_start[0] = 0
@@ -161,25 +224,3 @@ class BatchBuilder:
                 slots[cursor: cursor + q] = page_of * page + p % page
                 cursor += q
 
-        dev = self._dev[:total]
-        dev.copy_(host[:total], non_blocking=True)
-        if self.device.type == "cuda":
-            event = torch.cuda.Event()
-            event.record()
-            self._events[self._turn] = event
-        views = [dev[int(offsets[i]): int(offsets[i + 1])] for i in range(len(sizes))]
-        groups = [
-            GroupView(views[10 + 2 * g], views[11 + 2 * g].view(s, max_blocks[g]), max_blocks[g])
-            for g in range(self.num_groups)
-        ]
-        return StepContext(
-            num_tokens=n, num_seqs=s, num_rows=r,
-            token_ids=views[3], positions=views[4], seq_of_token=views[5], q_start=views[6],
-            ctx_len=views[7], state_slot=views[8], out_rows=views[9], groups=groups,
-            storage=self.storage, max_q_len=max(q_lens), min_q_len=min(q_lens), max_ctx_len=max(ctx_lens),
-            q_lens=q_lens, starts=starts, slots=[e.cache.slot for e in entries],
-            all_single=max(q_lens) == 1,
-            sample_temperature=views[1].view(torch.float32) if sampled else None,
-            sample_top_p=views[2].view(torch.float32) if sampled else None,
-            sample_seed=views[0].view(torch.int64) if sampled else None,
-        )

@@ -38,8 +38,16 @@ def gumbel_noise_host(seed: int, count: int) -> np.ndarray:
     return -np.log(-np.log(u, dtype=np.float32), dtype=np.float32)
 
 
+def _mix64_int(x: int) -> int:
+    x &= _MASK
+    x ^= x >> 33
+    x = (x * 0xFF51AFD7ED558CCD) & _MASK
+    x ^= x >> 33
+    x = (x * 0xC4CEB9FE1A85EC53) & _MASK
+    x ^= x >> 33
+    return x
+
+
 def step_seed(request_seed: int, position: int) -> int:
     """The seed of the draw that picks the token at `position` of a request."""
-    with np.errstate(over="ignore"):
-        word = mix64(np.array([(request_seed * 0xD1342543DE82EF95 + position) & _MASK], dtype=np.uint64))
-    return int(word[0]) & 0x7FFFFFFFFFFFFFFF
+    return _mix64_int(request_seed * 0xD1342543DE82EF95 + position) & 0x7FFFFFFFFFFFFFFF
