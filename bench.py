@@ -321,6 +321,72 @@ def run_ours(args) -> dict:
     }
 
 
+def run_case(args) -> dict:
+    """A small, fixed workload around one kernel, a few launches long: what the ncu captures
+    under profiles/ are taken on.  Inputs are larger than L2 where the kernel streams."""
+    import torch
+
+    from shrike_b200.ops.cuda_ops import CudaOps
+
+    torch.cuda.set_device(0)
+    dev = "cuda"
+    ops = CudaOps(torch.bfloat16, dev)
+    raw = MODEL_7B
+    h, inter = raw["hidden_size"], raw["intermediate_size"]
+    heads, kv, d = raw["num_attention_heads"], raw["num_key_value_heads"], raw["head_dim"]
+    tokens = args.batch
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    times = []
+    if args.case.startswith("gemm_"):
+        shapes = {"gemm_gate_up": (2 * inter, h), "gemm_down": (h, inter), "gemm_qkv": ((heads + 2 * kv) * d, h)}
+        n, k = shapes[args.case]
+        weights = [torch.randn(n, k, device=dev, dtype=torch.bfloat16) for _ in range(3)]   # rotated: every call reads HBM
+        x = torch.randn(tokens, k, device=dev, dtype=torch.bfloat16)
+        out = torch.empty(tokens, n, device=dev, dtype=torch.bfloat16 if args.case == "gemm_gate_up" else torch.float32)
+        for i in range(6):
+            start.record()
+            ops.linear(x, weights[i % 3], out, allow_partials=args.case != "gemm_gate_up")
+            stop.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(stop) * 1e3)
+        work = {"bytes": n * k * 2}
+    elif args.case in ("attention_single", "attention_portions"):
+        single = args.case == "attention_single"
+        seqs = tokens if single else 1
+        ctx_len = CONTEXT if single else PREFILL_TOKENS
+        q_len = 1 if single else PREFILL_TOKENS
+        blocks = -(-ctx_len // BLOCK_SIZE)
+        pages = seqs * blocks + 8
+        keys = torch.randn(pages, BLOCK_SIZE, kv, d, device=dev, dtype=torch.bfloat16)
+        values = torch.randn_like(keys)
+        q = torch.randn(seqs * q_len, heads * d, device=dev, dtype=torch.bfloat16)
+        width = max(8, 1 << (blocks - 1).bit_length())
+        table = torch.full((seqs, width), -1, dtype=torch.int32, device=dev)
+        table[:, :blocks] = torch.arange(seqs * blocks, dtype=torch.int32, device=dev).view(seqs, blocks)
+        q_start = torch.arange(seqs + 1, dtype=torch.int32, device=dev) * q_len
+        ctx = torch.full((seqs,), ctx_len, dtype=torch.int32, device=dev)
+        seq_of = torch.arange(seqs, dtype=torch.int32, device=dev).repeat_interleave(q_len)
+        out = torch.empty_like(q)
+        for _ in range(6):
+            start.record()
+            ops.paged_attention(q, keys, values, table, q_start, ctx, seq_of, heads, kv, d, d ** -0.5, None, out,
+                                max_q_len=q_len, min_q_len=q_len)
+            stop.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(stop) * 1e3)
+        work = {"bytes": seqs * ctx_len * 2 * kv * d * 2} if single else {"flops": 4.0 * heads * d * q_len * (q_len + 1) / 2}
+    else:
+        raise SystemExit(f"unknown case {args.case!r}")
+    ops.check_status()
+    best = min(times[2:])
+    result = {"case": args.case, "tokens_or_sequences": tokens, "us": round(best, 2), "launch_times_us": [round(t, 1) for t in times]}
+    if "bytes" in work:
+        result["GBps"] = round(work["bytes"] / best / 1e3, 1)
+    else:
+        result["TFLOPs"] = round(work["flops"] / best / 1e6, 1)
+    return result
+
+
 def run_reference(args) -> dict:
     reference = ROOT / "baseline" / "_ref"
     if not (reference / "shrike").is_dir():
@@ -338,11 +404,17 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all)")
+    parser.add_argument("--case", default=None,
+                        help="run a small single-kernel workload instead (for profiling): gemm_gate_up, gemm_down, "
+                             "gemm_qkv, attention_single, attention_portions; --batch gives tokens / sequences")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU: this engine runs on a single B200 (asked for {args.gpus})")
         sys.exit(2)
     args.warmup = max(3, args.warmup)
+    if args.case:
+        print(json.dumps(run_case(args)))
+        return
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(result))
 
