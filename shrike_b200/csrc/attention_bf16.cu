@@ -89,13 +89,16 @@ struct Params {
 // Where the keys [tile_base, tile_base + BN) of one kv head start in the cache, in
 // elements; -1 for keys outside [lo, hi] or on a page the sequence does not hold.  One
 // table lookup and one division per key, done by the first BN threads.
+// `leave_out` (or -1): a key whose row is marked -2, which copy_tile does not touch at all.
 template <int KEYS>
 __device__ __forceinline__ void locate_tile(long long* rows, const Params& p, const int* table, int kv_head,
-                                            int tile_base, int lo, int hi) {
+                                            int tile_base, int lo, int hi, int leave_out = -1) {
   if (threadIdx.x < KEYS) {
     const int j = tile_base + threadIdx.x;
     long long offset = -1;
-    if (j >= lo && j <= hi) {
+    if (j == leave_out) {
+      offset = -2;
+    } else if (j >= lo && j <= hi) {
       const int block = j / p.page_size;
       const int page = block < p.max_blocks ? table[block] : -1;
       if (page >= 0 && page < p.num_pages)
@@ -114,6 +117,7 @@ __device__ __forceinline__ void copy_tile(bf16* k_tile, bf16* v_tile, const Para
   for (int c = threadIdx.x; c < KEYS * CHUNKS; c += THREADS) {
     const int key = c / CHUNKS, chunk = c - key * CHUNKS;
     const long long row = rows[key];
+    if (row == -2) continue;
     const bool valid = row >= 0;
     const size_t offset = valid ? static_cast<size_t>(row) + chunk * 8 : 0;
     cp_async16(k_tile + key * ROW + chunk * 8, p.k_cache + offset, valid);
@@ -326,13 +330,18 @@ __global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
   bf16* k_tiles = q_tile + 16 * ROW;                          // [ST][BN][ROW]
   bf16* v_tiles = k_tiles + ST * BN * ROW;
   let_dependents_start();
-  wait_for_previous();
+  // Before wait_for_previous() only what no kernel of this step writes is read: the batch's
+  // metadata and the keys and values of earlier positions.  The newest key (position
+  // ctx_len - 1) and the query are written by the kernel just before this one.
   const int seq = blockIdx.z, split = blockIdx.x;
   const int group = p.num_heads / p.num_kv_heads;
   const int row_tiles = (group + 15) / 16;
   const int kv_head = blockIdx.y / row_tiles, row_tile = blockIdx.y - kv_head * row_tiles;
   const int start = p.q_start[seq];
-  if (p.q_start[seq + 1] - start != 1) return;
+  if (p.q_start[seq + 1] - start != 1) {
+    wait_for_previous();
+    return;
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int last_key = p.ctx_len[seq] - 1;
   const int first_key = p.window > 0 ? max(0, last_key - p.window + 1) : 0;
@@ -351,25 +360,44 @@ __global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
   float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.f, 0.f};
 
   if (my_lo <= my_hi) {
+    // rows of the first ST - 1 tiles without the newest key, and their copies, ahead of the wait
+#pragma unroll
+    for (int ahead = 0; ahead < ST - 1; ++ahead)
+      if (my_lo + ahead <= my_hi)
+        locate_tile<BN>(tile_rows[ahead], p, table, kv_head, (my_lo + ahead) * BN, first_key, last_key, last_key);
+    __syncthreads();
+    // one commit group per tile, also when there is no tile left, so that the count is uniform
+#pragma unroll
+    for (int ahead = 0; ahead < ST - 1; ++ahead) {
+      if (my_lo + ahead <= my_hi) copy_tile<BN>(k_tiles + ahead * BN * ROW, v_tiles + ahead * BN * ROW, p, tile_rows[ahead]);
+      cp_async_commit();
+    }
+  }
+  wait_for_previous();
+  if (my_lo <= my_hi) {
     for (int c = threadIdx.x; c < 16 * CHUNKS; c += THREADS) {
       const int row = c / CHUNKS, chunk = c - row * CHUNKS;
       const bool valid = row < rows_here;
       const bf16* src = p.q + (static_cast<size_t>(start) * p.num_heads + head0 + (valid ? row : 0)) * D + chunk * 8;
       cp_async16(q_tile + row * ROW + chunk * 8, src, valid);
     }
-    // rows of the first ST tiles; tile t + ST is located while tile t is worked on
-#pragma unroll
-    for (int ahead = 0; ahead < ST; ++ahead)
-      if (my_lo + ahead <= my_hi)
-        locate_tile<BN>(tile_rows[ahead % (ST + 1)], p, table, kv_head, (my_lo + ahead) * BN, first_key, last_key);
-    __syncthreads();
-    // one commit group per tile, also when there is no tile left, so that the count is uniform
-#pragma unroll
-    for (int ahead = 0; ahead < ST - 1; ++ahead) {
-      if (my_lo + ahead <= my_hi)
-        copy_tile<BN>(k_tiles + ahead * BN * ROW, v_tiles + ahead * BN * ROW, p, tile_rows[ahead % (ST + 1)]);
-      cp_async_commit();
+    // the newest key, when its tile is one of those copied above
+    const int newest_tile = last_key / BN;
+    if (newest_tile >= my_lo && newest_tile - my_lo < ST - 1 && threadIdx.x < CHUNKS) {
+      const int block = last_key / p.page_size;
+      const int page = block < p.max_blocks ? table[block] : -1;
+      const bool valid = page >= 0 && page < p.num_pages;
+      const size_t offset = valid ? (static_cast<size_t>(page) * p.page_size + (last_key - block * p.page_size)) * p.num_kv_heads * D +
+                                        static_cast<size_t>(kv_head) * D + threadIdx.x * 8 : 0;
+      const int at = ((newest_tile - my_lo) * BN + (last_key - newest_tile * BN)) * ROW + threadIdx.x * 8;
+      cp_async16(k_tiles + at, p.k_cache + offset, valid);
+      cp_async16(v_tiles + at, p.v_cache + offset, valid);
     }
+    cp_async_commit();
+    if (my_lo + ST - 1 <= my_hi)   // copied by the first round of the loop
+      locate_tile<BN>(tile_rows[ST - 1], p, table, kv_head, (my_lo + ST - 1) * BN, first_key, last_key);
+    cp_async_wait<0>();
+    __syncthreads();
     int first[2] = {first_key, first_key}, last[2] = {last_key, last_key};
     unsigned q_frag[Q_IN_REGS ? KSTEPS : 1][4];
     for (int tile = my_lo; tile <= my_hi; ++tile) {
@@ -409,6 +437,7 @@ __global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
   __syncthreads();
   float* warp_o = reinterpret_cast<float*>(smem_raw);         // [4][16][D]
   float* warp_ml = warp_o + 4 * 16 * D;                       // [4][16][2]
+  float* row_weight = warp_ml + 4 * 16 * 2;                   // [16][4] weight of each warp, then [16] max, [16] sum
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     const int row = (lane >> 2) + 8 * r;
@@ -424,26 +453,43 @@ __global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
     }
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < rows_here * D; idx += THREADS) {
-    const int row = idx / D, d = idx - row * D;
+  if (threadIdx.x < rows_here) {   // per row: the four warps' weights, the common maximum and the sum
+    const int row = threadIdx.x;
     float m = -INFINITY;
 #pragma unroll
     for (int w = 0; w < 4; ++w) m = fmaxf(m, warp_ml[(w * 16 + row) * 2]);
-    float total = 0.f, sum = 0.f;
+    float sum = 0.f;
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
       const float wm = warp_ml[(w * 16 + row) * 2];
       const float weight = wm == -INFINITY ? 0.f : exp2f(wm - m);
-      total += weight * warp_o[(w * 16 + row) * D + d];
+      row_weight[row * 4 + w] = weight;
       sum += weight * warp_ml[(w * 16 + row) * 2 + 1];
     }
-    const size_t slot = (static_cast<size_t>(seq) * p.num_heads + head0 + row) * p.splits + split;
-    p.partial_out[slot * D + d] = total;
-    if (d == 0) {
-      p.partial_ml[slot * 2] = m;
-      p.partial_ml[slot * 2 + 1] = sum;
+    row_weight[64 + row] = m;
+    row_weight[80 + row] = sum;
+  }
+  __syncthreads();
+  const bool direct = p.splits == 1;   // nothing to combine: the result goes straight out
+  for (int idx = threadIdx.x; idx < rows_here * D; idx += THREADS) {
+    const int row = idx / D, d = idx - row * D;
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) total += row_weight[row * 4 + w] * warp_o[(w * 16 + row) * D + d];
+    if (direct) {
+      const float sum = row_weight[80 + row];
+      p.out[(static_cast<size_t>(start) * p.num_heads + head0 + row) * D + d] =
+          __float2bfloat16_rn(sum > 0.f ? total / sum : 0.f);
+    } else {
+      const size_t slot = (static_cast<size_t>(seq) * p.num_heads + head0 + row) * p.splits + split;
+      p.partial_out[slot * D + d] = total;
+      if (d == 0) {
+        p.partial_ml[slot * 2] = row_weight[64 + row];
+        p.partial_ml[slot * 2 + 1] = row_weight[80 + row];
+      }
     }
   }
+  if (direct) return;
   // the split that arrives last combines all of them; the order of the sum is by split
   // index, whoever does it
   __threadfence();
@@ -457,30 +503,33 @@ __global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  // weights of the splits: one (row, split) pair per thread, then a row-wise maximum and sum
-  float* weights = reinterpret_cast<float*>(smem_raw);        // [16][MAX_SPLITS], then [16] inverse sums
-  float* inverse = weights + 16 * MAX_SPLITS;
+  // (max, sum) of every (row, split): one pair per thread, all loads in flight at once
+  float* split_max = reinterpret_cast<float*>(smem_raw);      // [16][MAX_SPLITS], becomes the weights
+  float* split_sum = split_max + 16 * MAX_SPLITS;             // [16][MAX_SPLITS]
+  float* inverse = split_sum + 16 * MAX_SPLITS;               // [16]
   for (int idx = threadIdx.x; idx < rows_here * p.splits; idx += THREADS) {
     const int row = idx / p.splits, s = idx - row * p.splits;
     const size_t slot = (static_cast<size_t>(seq) * p.num_heads + head0 + row) * p.splits + s;
-    weights[row * MAX_SPLITS + s] = __ldcg(p.partial_ml + slot * 2);
+    const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.partial_ml + slot * 2));
+    split_max[row * MAX_SPLITS + s] = ml.x;
+    split_sum[row * MAX_SPLITS + s] = ml.y;
   }
   __syncthreads();
   if (threadIdx.x < rows_here) {
     const int row = threadIdx.x;
-    const size_t slot0 = (static_cast<size_t>(seq) * p.num_heads + head0 + row) * p.splits;
     float m = -INFINITY;
-    for (int s = 0; s < p.splits; ++s) m = fmaxf(m, weights[row * MAX_SPLITS + s]);
+    for (int s = 0; s < p.splits; ++s) m = fmaxf(m, split_max[row * MAX_SPLITS + s]);
     float sum = 0.f;
     for (int s = 0; s < p.splits; ++s) {
-      const float sm = weights[row * MAX_SPLITS + s];
+      const float sm = split_max[row * MAX_SPLITS + s];
       const float weight = sm == -INFINITY ? 0.f : exp2f(sm - m);
-      weights[row * MAX_SPLITS + s] = weight;
-      sum += weight * __ldcg(p.partial_ml + (slot0 + s) * 2 + 1);
+      split_max[row * MAX_SPLITS + s] = weight;
+      sum += weight * split_sum[row * MAX_SPLITS + s];
     }
     inverse[row] = sum > 0.f ? 1.0f / sum : 0.f;
   }
   __syncthreads();
+  const float* weights = split_max;
   for (int idx = threadIdx.x; idx < rows_here * D; idx += THREADS) {
     const int row = idx / D, d = idx - row * D;
     const float* src = p.partial_out + (static_cast<size_t>(seq) * p.num_heads + head0 + row) * p.splits * D + d;
@@ -501,7 +550,7 @@ __global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
 
 constexpr size_t PORTIONS_SMEM = sizeof(bf16) * (BM * ROW + 4 * PBN * ROW);
 constexpr size_t SINGLE_TILES_SMEM = sizeof(bf16) * (16 * ROW + 2 * ST * BN * ROW);
-constexpr size_t SINGLE_MERGE_SMEM = sizeof(float) * (4 * 16 * D + 4 * 16 * 2);
+constexpr size_t SINGLE_MERGE_SMEM = sizeof(float) * (4 * 16 * D + 4 * 16 * 2 + 96);
 constexpr size_t SINGLE_SMEM = SINGLE_TILES_SMEM > SINGLE_MERGE_SMEM ? SINGLE_TILES_SMEM : SINGLE_MERGE_SMEM;
 
 }  // namespace bf16attn
