@@ -35,6 +35,12 @@ MODEL_7B = dict(
     rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False, max_position_embeddings=32768,
     eos_token_id=151643, torch_dtype="bfloat16",
 )
+MODEL_1_5B = dict(
+    architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=1536, intermediate_size=8960,
+    num_hidden_layers=28, num_attention_heads=12, num_key_value_heads=2, head_dim=128, vocab_size=151936,
+    rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=True, max_position_embeddings=32768,
+    eos_token_id=151643, torch_dtype="bfloat16",
+)
 CONTEXT = 1024
 PREFILL_TOKENS = 2048
 BLOCK_SIZE = 16
@@ -321,6 +327,55 @@ def run_ours(args) -> dict:
     }
 
 
+def run_mixed(args) -> dict:
+    """The scheduler end to end at Qwen2.5-1.5B shape: 64 requests, random-id prompts of 32 to
+    2,048 tokens, 32 to 256 output tokens each (lengths drawn as shrike's bench/workload.py:15-22
+    does, `random.Random(20260718).randint`), greedy, fixed lengths, chunked-prefill budget 512,
+    through `LLMEngine.generate`.  Wall-clock, as shrike's bench/bench_engine.py:54-62 measures."""
+    import random
+
+    import torch
+
+    import shrike_b200.models  # noqa: F401
+    from shrike_b200 import SamplingParams
+    from shrike_b200.config import parse_config
+    from shrike_b200.engine.llm_engine import LLMEngine
+    from shrike_b200.weights.random_init import random_tensors
+
+    torch.cuda.set_device(0)
+    raw = dict(MODEL_1_5B)
+    if args.layers:
+        raw["num_hidden_layers"] = args.layers
+    config = parse_config(raw)
+    tensors = random_tensors(config, seed=0, device="cuda", dtype=torch.bfloat16)
+    engine = LLMEngine(None, block_size=BLOCK_SIZE, num_blocks=args.num_blocks or 12000, max_tokens_per_step=512,
+                       max_running=256, dtype="bfloat16", config=config, tensors=tensors)
+    del tensors
+    rng = random.Random(20260718)
+    outputs = [rng.randint(32, 256) for _ in range(64)]
+    prompts = [[rng.randrange(raw["vocab_size"]) for _ in range(rng.randint(32, 2048))] for _ in range(64)]
+    params = [SamplingParams(max_new_tokens=n, temperature=0.0, ignore_eos=True) for n in outputs]
+    engine.generate(prompts[:4], params[:4])   # warm-up: builds, graphs for small batches
+    torch.cuda.synchronize()
+    steps_before = engine.stats.steps
+    began = time.perf_counter()
+    results = engine.generate(prompts, params)
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - began
+    engine.ops.check_status()
+    generated = sum(len(r) for r in results)
+    assert [len(r) for r in results] == outputs and engine.block_manager.whole()
+    return {
+        "workload": "mixed", "model": "Qwen2.5-1.5B shape", "layers": raw["num_hidden_layers"], "requests": 64,
+        "prompt_tokens": sum(len(p) for p in prompts), "generated_tokens": generated, "seconds": round(seconds, 3),
+        "value": round(generated / seconds, 1), "unit": "generated tok/s",
+        "total_tokens_per_second": round((generated + sum(len(p) for p in prompts)) / seconds, 1),
+        "steps": engine.stats.steps - steps_before, "preemptions": engine.scheduler.num_preemptions,
+        "kv_blocks": min(engine.block_manager.num_pages), "budget": 512, "dtype": "bf16",
+        "data": "synthetic: seeded random weights and uniform random token ids",
+    }
+
+
 def run_case(args) -> dict:
     """A small, fixed workload around one kernel, a few launches long: what the ncu captures
     under profiles/ are taken on.  Inputs are larger than L2 where the kernel streams."""
@@ -404,6 +459,9 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all)")
+    parser.add_argument("--workload", default="decode", choices=["decode", "mixed"],
+                        help="decode: the headline line; mixed: 64 requests through the scheduler at 1.5B shape")
+    parser.add_argument("--num-blocks", type=int, default=0, help="cache pages for --workload mixed (few pages force preemption)")
     parser.add_argument("--case", default=None,
                         help="run a small single-kernel workload instead (for profiling): gemm_gate_up, gemm_down, "
                              "gemm_qkv, attention_single, attention_portions; --batch gives tokens / sequences")
@@ -414,6 +472,9 @@ def main():
     args.warmup = max(3, args.warmup)
     if args.case:
         print(json.dumps(run_case(args)))
+        return
+    if args.workload == "mixed":
+        print(json.dumps(run_mixed(args)))
         return
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(result))

@@ -30,9 +30,18 @@ def _ptr(tensor):
     return None if tensor is None else tensor.data_ptr()
 
 
+_LIMITS = {
+    "add_rmsnorm": "the row width must be at most 32768 (8192 when it is no multiple of 4)",
+    "gather_add_rmsnorm": "the row width must be at most 32768 (8192 when it is no multiple of 4)",
+    "gemm_tcgen05": "K must be a multiple of 8 and the operands 16-byte aligned",
+    "paged_attention_bf16": "at most 65535 sequences and heads, heads a multiple of kv heads, at most 32 splits",
+}
+
+
 def _check(code: int, what: str):
     if code != 0:
-        reason = "bad argument" if code == -1 else f"CUDA error {code}"
+        reason = f"bad argument ({_LIMITS[what]})" if code == -1 and what in _LIMITS else (
+            "bad argument" if code == -1 else f"CUDA error {code}")
         raise KernelError(f"{what}: {reason}")
 
 

@@ -238,7 +238,8 @@ def run_attention(ops, case, heads, kv_heads, dim, window, q_lens, ctx_lens):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,kv_heads,dim,page", [(14, 2, 64, 16), (5, 1, 48, 16), (6, 3, 32, 8), (2, 2, 256, 16), (7, 7, 16, 4), (28, 4, 128, 16)])
+@pytest.mark.parametrize("heads,kv_heads,dim,page", [(14, 2, 64, 16), (5, 1, 48, 16), (6, 3, 32, 8), (2, 2, 256, 16), (7, 7, 16, 4), (28, 4, 128, 16),
+                                                     (34, 2, 32, 16), (40, 1, 80, 3)])
 def test_paged_attention_single_tokens_around_page_edges(dtype, heads, kv_heads, dim, page):
     ops = cuda_ops(dtype)
     ctx_lens = [1, 15, 16, 17, 100, 333, 512, 7]   # shrike tests/test_triton_attention.py:35-37
@@ -250,9 +251,9 @@ def test_paged_attention_single_tokens_around_page_edges(dtype, heads, kv_heads,
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("window", [None, 1, 16, 50])
-def test_paged_attention_portions_mixed_with_single_tokens(dtype, window):
+@pytest.mark.parametrize("heads,kv_heads,dim,page", [(6, 2, 64, 16), (17, 1, 112, 5)])
+def test_paged_attention_portions_mixed_with_single_tokens(dtype, window, heads, kv_heads, dim, page):
     ops = cuda_ops(dtype)
-    heads, kv_heads, dim, page = 6, 2, 64, 16
     ctx_lens = [40, 1, 130, 2, 16, 17, 300, 64, 33]
     q_lens = [1, 1, 1, 2, 16, 3, 129, 64, 17]
     case = paged_case(dtype, heads, kv_heads, dim, page, ctx_lens, q_lens, seed=4)
@@ -265,6 +266,29 @@ def test_paged_attention_portions_mixed_with_single_tokens(dtype, window):
                 case["table"][s, b] = -1
     got, want = run_attention(ops, case, heads, kv_heads, dim, window, q_lens, ctx_lens)
     close(got, want, 2e-5 if dtype == torch.float32 else 2e-2, 0, f"mixed attention window {window}")
+
+
+def test_single_token_attention_twice_in_a_row_leaves_its_counters_clean():
+    """The split counters must be zero again after a launch: a second launch with other data
+    gives that data's result."""
+    ops = cuda_ops(torch.bfloat16)
+    heads, kv_heads, dim, page = 28, 4, 128, 16
+    for seed, ctx_lens in ((1, [700, 64, 65, 1023]), (2, [1, 300, 1024, 129, 17])):
+        q_lens = [1] * len(ctx_lens)
+        case = paged_case(torch.bfloat16, heads, kv_heads, dim, page, ctx_lens, q_lens, seed=seed)
+        got, want = run_attention(ops, case, heads, kv_heads, dim, None, q_lens, ctx_lens)
+        close(got, want, 2e-2, 0, f"launch with seed {seed}")
+    assert int(ops._arrivals.abs().sum()) == 0
+
+
+def test_widths_beyond_one_block_are_refused_not_miscomputed():
+    from shrike_b200.ops.cuda_ops import KernelError
+
+    ops = cuda_ops(torch.float32)
+    width = 32768 + 4
+    resid = torch.zeros(2, width, device=DEV)
+    with pytest.raises(KernelError, match="add_rmsnorm"):
+        ops.add_rmsnorm(resid, None, torch.ones(width, device=DEV), 1e-6, torch.empty(2, width, device=DEV))
 
 
 def test_head_sizes_outside_the_served_range_are_refused():
