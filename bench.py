@@ -300,6 +300,7 @@ def run_ours(args) -> dict:
         point_ms, _, _ = decode_run(batch, max(10, args.steps // 2), 3)
         points[f"decode_b{batch}"] = round(batch * 1000.0 / point_ms, 1)
 
+    kernels = dominant_kernels(ops, raw, args.batch, peaks) if not args.layers else {}
     sampler.stop()
     clocks = sampler.summary(windows)
     return {
@@ -323,8 +324,67 @@ def run_ours(args) -> dict:
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peaks["hbm_gbs"], 4)},
         "points": points,
+        "kernels": kernels,
         "clocks": clocks,
     }
+
+
+def dominant_kernels(ops, raw: dict, batch: int, peaks: dict) -> dict:
+    """Each dominant decode kernel alone, at the headline batch: microseconds per launch
+    (CUDA events around a captured graph of back-to-back launches over rotated operands, so
+    every launch reads HBM) and the fraction of the copy bandwidth its bytes ÷ time reaches."""
+    import torch
+
+    dev = "cuda"
+    h, inter, vocab = raw["hidden_size"], raw["intermediate_size"], raw["vocab_size"]
+    heads, kv, d = raw["num_attention_heads"], raw["num_key_value_heads"], raw["head_dim"]
+
+    def graph_us(fn, reps):
+        fn(0)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(reps):
+                fn(i)
+        graph.replay()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(5):
+            graph.replay()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) * 1e3 / (5 * reps)
+
+    out = {}
+    shapes = {"qkv": ((heads + 2 * kv) * d, h, 8), "o": (h, heads * d, 8), "gate_up": (2 * inter, h, 4),
+              "down": (h, inter, 4), "lm_head": (vocab, h, 2)}
+    for name, (n, k, copies) in shapes.items():
+        weights = [torch.randn(n, k, device=dev, dtype=torch.bfloat16) for _ in range(copies)]
+        x = torch.randn(batch, k, device=dev, dtype=torch.bfloat16)
+        result = torch.empty(batch, n, device=dev, dtype=torch.bfloat16 if name == "gate_up" else torch.float32)
+        partial = name in ("qkv", "o", "down")
+        us = graph_us(lambda i: ops.linear(x, weights[i % copies], result, allow_partials=partial), 2 * copies)
+        gbs = n * k * 2 / us / 1e3
+        out[name] = {"us": round(us, 1), "GBps": round(gbs, 0), "frac": round(gbs / peaks["hbm_gbs"], 3)}
+        del weights
+    blocks = -(-CONTEXT // BLOCK_SIZE)
+    sets = 4   # rotated key/value pools, so that a launch does not find its keys in L2
+    pools = [(torch.randn(batch * blocks, BLOCK_SIZE, kv, d, device=dev, dtype=torch.bfloat16),
+              torch.randn(batch * blocks, BLOCK_SIZE, kv, d, device=dev, dtype=torch.bfloat16)) for _ in range(sets)]
+    q = torch.randn(batch, heads * d, device=dev, dtype=torch.bfloat16)
+    width = max(8, 1 << (blocks - 1).bit_length())
+    table = torch.full((batch, width), -1, dtype=torch.int32, device=dev)
+    table[:, :blocks] = torch.arange(batch * blocks, dtype=torch.int32, device=dev).view(batch, blocks)
+    q_start = torch.arange(batch + 1, dtype=torch.int32, device=dev)
+    ctx = torch.full((batch,), CONTEXT, dtype=torch.int32, device=dev)
+    seq_of = torch.arange(batch, dtype=torch.int32, device=dev)
+    attn = torch.empty_like(q)
+    us = graph_us(lambda i: ops.paged_attention(q, pools[i % sets][0], pools[i % sets][1], table, q_start, ctx, seq_of,
+                                                heads, kv, d, d ** -0.5, None, attn, max_q_len=1, min_q_len=1), 2 * sets)
+    gbs = batch * CONTEXT * 2 * kv * d * 2 / us / 1e3
+    out["attention"] = {"us": round(us, 1), "GBps": round(gbs, 0), "frac": round(gbs / peaks["hbm_gbs"], 3)}
+    return out
 
 
 def run_mixed(args) -> dict:
