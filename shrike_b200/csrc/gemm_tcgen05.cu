@@ -135,7 +135,6 @@ gemm_swap_ab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   const size_t b_bytes = static_cast<size_t>(args.tn) * BK * 2;
   const size_t stage_bytes = A_BYTES + b_bytes;
   Shared* sh = reinterpret_cast<Shared*>(tiles + stage_bytes * args.stages);
-  let_dependents_start();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BM, split = blockIdx.y, t0 = blockIdx.z * args.tn;
   const int total_kblocks = (args.k + BK - 1) / BK;
@@ -161,6 +160,9 @@ gemm_swap_ab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  // dependents may start only now that this CTA holds its tensor memory: a dependent that also
+  // wants tensor memory must not be able to starve a CTA it is waiting for
+  let_dependents_start();
   const unsigned tmem_d = sh->tmem_base;
 
   if (warp == 0) {

@@ -133,7 +133,7 @@ def load_library(name: str, sources, defines=None, extra_flags=()) -> ctypes.CDL
 
 # The libraries of this package.
 CORE_SOURCES = ["elementwise.cu", "gemm_fp32.cu", "sampling.cu"]
-ATTENTION_SOURCES = ["attention_generic.cu", "attention_bf16.cu"]
+ATTENTION_SOURCES = ["attention_generic.cu", "attention_bf16.cu", "attention_tcgen05.cu"]
 
 
 def core_library() -> ctypes.CDLL:

@@ -67,6 +67,7 @@ class CudaOps:
         self._declare_core()
         self._attention = {}
         self.gemm_tc = None
+        self.tensor_core_attention = True   # tcgen05 kernel for portions where the head and page sizes allow
         self.tensor_core_gemm_max_tokens = 64   # above this the library product is used
         self._partials = {}      # data_ptr of an output buffer -> its stack of K-split partial results
         self.status = None
@@ -118,6 +119,11 @@ class CudaOps:
             )
             lib.shrike_paged_attention_bf16.restype = _I
             lib.shrike_attention_bf16_resident_ctas.restype = _I
+            lib.shrike_attention_tc_available.restype = _I
+            lib.shrike_paged_attention_tc_portions.argtypes = (
+                [_P, _P, _P, _P, _I, _P, _P] + [_I] * 6 + [_F, _I, _P, _I, _I, _P, _P]
+            )
+            lib.shrike_paged_attention_tc_portions.restype = _I
             self._attention[head_dim] = lib
         return lib
 
@@ -298,7 +304,19 @@ class CudaOps:
                 self._arrivals = torch.zeros(max(groups, 4096), dtype=torch.int32, device=self.device)
                 self.generation += 1
             scratch, arrivals = self._scratch, self._arrivals
+        tensor_core_portions = (has_portions and self.tensor_core_attention and lib.shrike_attention_tc_available()
+                                and page_size in (8, 16, 32, 64))
         self.launches += (1 if has_single else 0) + (1 if has_portions else 0)
+        if tensor_core_portions:
+            if self.status is None:
+                self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+            _check(lib.shrike_paged_attention_tc_portions(
+                _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), max_blocks, _ptr(q_start), _ptr(ctx_len),
+                q.shape[0], num_seqs, num_heads, num_kv_heads, page_size, num_pages, scale, window or 0, _ptr(out),
+                int(has_single), max_q_len, _ptr(self.status), self._stream()), "paged_attention_tc_portions")
+            has_portions = False
+            if not has_single:
+                return
         _check(lib.shrike_paged_attention_bf16(
             _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), max_blocks, _ptr(q_start), _ptr(ctx_len),
             num_seqs, num_heads, num_kv_heads, page_size, num_pages, scale, window or 0, _ptr(out),

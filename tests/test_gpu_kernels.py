@@ -251,7 +251,7 @@ def test_paged_attention_single_tokens_around_page_edges(dtype, heads, kv_heads,
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("window", [None, 1, 16, 50])
-@pytest.mark.parametrize("heads,kv_heads,dim,page", [(6, 2, 64, 16), (17, 1, 112, 5)])
+@pytest.mark.parametrize("heads,kv_heads,dim,page", [(6, 2, 64, 16), (17, 1, 112, 5), (8, 2, 128, 16), (6, 3, 64, 8), (4, 4, 128, 64)])
 def test_paged_attention_portions_mixed_with_single_tokens(dtype, window, heads, kv_heads, dim, page):
     ops = cuda_ops(dtype)
     ctx_lens = [40, 1, 130, 2, 16, 17, 300, 64, 33]
