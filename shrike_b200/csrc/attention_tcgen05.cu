@@ -9,9 +9,15 @@
 //                  tiles and is rescaled there (tcgen05.ld / st) when a row's maximum moved
 // Keys and values arrive by TMA, one box per page and 64-element half of the head (the
 // block table is read by the producer thread), double-buffered; the query tile by TMA once.
-// Roles: warp 0 TMA producer, warp 1 MMA issuer (one elected lane each), warps 2..5 softmax
-// and epilogue.  tcgen05.commit arrives on mbarriers: s_full after S, kv_free after PV;
-// MMAs execute in issue order, so "S of tile i+1 is ready" also says "PV of tile i is done".
+// Roles: warp 0 TMA producer, warp 1 MMA issuer (one elected lane), warps 2..5 softmax and
+// epilogue.  S has two buffers in tensor memory: the scores of tile i + 1 are computed while
+// the softmax warps work on tile i, and their exponentials while PV of tile i still runs;
+// only writing P (one buffer) and rescaling O wait for that PV (barrier pv_done).
+// Keys and values have stages and barriers of their own: a key stage is free again as soon
+// as its S is computed, long before the value stage of the same tile, so the keys of the tile
+// after next are already on their way while this tile's softmax runs.
+// tcgen05.commit arrives on mbarriers: s_full[b] and k_free after S into buffer b, v_free and
+// pv_done after PV.
 // Mask and window as everywhere: a query at position p sees keys [max(0, p - window + 1), p].
 // Rows of a page beyond the context may hold anything (a page is reused without clearing):
 // scores are masked by selection, and the value rows beyond the context are zeroed in shared
@@ -40,20 +46,27 @@ constexpr int THREADS = 192;
 constexpr int STAGES = 2;
 constexpr int Q_HALF = BM * 128, KV_HALF = BN * 128;          // bytes of one 64-element-wide sub-tile
 constexpr int Q_BYTES = HALVES * Q_HALF, KV_BYTES = HALVES * KV_HALF, P_BYTES = BM * BN * 2;
-constexpr unsigned TMEM_COLS = D == 128 ? 256 : 128;           // S: 64 columns, O: D columns
+constexpr unsigned TMEM_COLS = 256;                            // S: 2 x 64 columns, O: D columns from column 128
 constexpr float LOG2E = 1.4426950408889634f;
 
 enum : int { ERR_PRODUCER = 11, ERR_MMA = 12, ERR_SOFTMAX = 13, ERR_DRAIN = 14, ERR_ALIGNMENT = 15 };
 
 struct Shared {
-  unsigned long long q_full, s_full, p_full, o_done;
-  unsigned long long kv_full[STAGES], kv_free[STAGES];
+  unsigned long long q_full, s_full[2], p_full, pv_done;
+  unsigned long long k_full[STAGES], k_free[STAGES], v_full[STAGES], v_free[STAGES];
   unsigned tmem_base;
   volatile int abort;
 };
 // two CTAs must fit an SM (233,472 bytes, 1 KiB reserved per CTA): no slack for alignment is added; the
 // dynamic window starts 1 KiB-aligned (declared so below), and the kernel checks that it does.
 constexpr size_t SMEM_BYTES = Q_BYTES + STAGES * 2 * KV_BYTES + P_BYTES + sizeof(Shared);
+
+// 2^x on the special-function unit; -inf gives 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 struct Args {
   const int* block_table;
@@ -92,12 +105,15 @@ portions_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
   if (threadIdx.x == 0) {
     mbar_init(&sh->q_full, 1);
-    mbar_init(&sh->s_full, 1);
+    mbar_init(&sh->s_full[0], 1);
+    mbar_init(&sh->s_full[1], 1);
     mbar_init(&sh->p_full, 128);
-    mbar_init(&sh->o_done, 1);
+    mbar_init(&sh->pv_done, 1);
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&sh->kv_full[s], 1);
-      mbar_init(&sh->kv_free[s], 1);
+      mbar_init(&sh->k_full[s], 1);
+      mbar_init(&sh->k_free[s], 1);
+      mbar_init(&sh->v_full[s], 1);
+      mbar_init(&sh->v_free[s], 1);
     }
     sh->abort = 0;
     mbar_init_fence();
@@ -109,7 +125,7 @@ portions_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   let_dependents_start();
   wait_for_previous();   // the query and the newest keys come from the kernel before this one
 
-  const unsigned tmem_s = sh->tmem_base, tmem_o = sh->tmem_base + BN;
+  const unsigned tmem_s = sh->tmem_base, tmem_o = sh->tmem_base + 2 * BN;   // S buffer b at columns b * 64
   const int pos0 = args.ctx_len[seq] - q_len;                   // position of the first new token
   const int kv_head = head / (args.num_heads / args.num_kv_heads);
   const int rows_here = min(BM, q_len - tile_start);
@@ -119,73 +135,104 @@ portions_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   const int num_tiles = tile_hi - tile_lo + 1;
 
   if (warp == 0) {
+    // The whole warp runs the loop: lane 0 waits for the stage and arms its barrier, then lane
+    // pg looks up page pg of the tile and issues that page's four boxes (K and V, both halves).
+    const int* table = args.block_table + static_cast<size_t>(seq) * args.max_blocks;
+    const int pages_per_tile = BN / args.page_size;
+    const int nowhere = args.num_pages * args.page_size;      // a row coordinate outside the cache: reads zeros
     if (lane == 0) {
-      const int* table = args.block_table + static_cast<size_t>(seq) * args.max_blocks;
-      const int pages_per_tile = BN / args.page_size;
-      const int nowhere = args.num_pages * args.page_size;      // a row coordinate outside the cache: reads zeros
       mbar_expect_tx(&sh->q_full, Q_BYTES);
       for (int h = 0; h < HALVES; ++h) tma_load_2d(q_tile + h * Q_HALF, &map_q, &sh->q_full, head * D + h * 64, start + tile_start);
-      int issued = 0;
-      for (int i = 0; i < num_tiles; ++i) {
-        const int s = i % STAGES;
-        const unsigned phase = (i / STAGES) & 1;
-        if (!mbar_wait(&sh->kv_free[s], phase ^ 1, &sh->abort, args.status, ERR_PRODUCER)) break;
-        mbar_expect_tx(&sh->kv_full[s], 2 * KV_BYTES);
-        unsigned char* k_tile = kv_tiles + s * 2 * KV_BYTES;
-        unsigned char* v_tile = k_tile + KV_BYTES;
-        for (int pg = 0; pg < pages_per_tile; ++pg) {
-          const int key0 = (tile_lo + i) * BN + pg * args.page_size;
-          const int block = key0 / args.page_size;
-          int page = (key0 <= hi && block < args.max_blocks) ? table[block] : -1;
-          if (page < 0 || page >= args.num_pages) page = -1;
-          const int y = page < 0 ? nowhere : page * args.page_size;
-          const int at = pg * args.page_size * 128;
-          for (int h = 0; h < HALVES; ++h) {
-            tma_load_2d(k_tile + h * KV_HALF + at, &map_k, &sh->kv_full[s], kv_head * D + h * 64, y);
-            tma_load_2d(v_tile + h * KV_HALF + at, &map_v, &sh->kv_full[s], kv_head * D + h * 64, y);
-          }
-        }
-        issued = i + 1;
+    }
+    // page ids are looked up three tiles ahead of their use, so that the table's latency never
+    // sits between a stage becoming free and its copy being issued
+    auto look_up = [&](int i) -> int {
+      if (lane >= pages_per_tile || i >= num_tiles) return -1;
+      const int key0 = (tile_lo + i) * BN + lane * args.page_size;
+      const int block = key0 / args.page_size;
+      const int page = (key0 <= hi && block < args.max_blocks) ? table[block] : -1;
+      return page >= args.num_pages ? -1 : page;
+    };
+    int page = look_up(0), page_1 = look_up(1), page_2 = look_up(2);
+    int issued = 0;
+    for (int i = 0; i < num_tiles; ++i) {
+      const int s = i % STAGES;
+      const unsigned phase = (i / STAGES) & 1;
+      const int page_3 = look_up(i + 3);
+      unsigned char* k_tile = kv_tiles + s * 2 * KV_BYTES;
+      unsigned char* v_tile = k_tile + KV_BYTES;
+      const int y = page < 0 ? nowhere : page * args.page_size;
+      const int at = lane * args.page_size * 128;
+      int ok = 1;
+      if (lane == 0) {
+        ok = mbar_wait(&sh->k_free[s], phase ^ 1, &sh->abort, args.status, ERR_PRODUCER) ? 1 : 0;
+        if (ok) mbar_expect_tx(&sh->k_full[s], KV_BYTES);
       }
-      if (sh->abort) {   // copies may still be in flight: wait for the stages armed last
-        for (int i = max(0, issued - STAGES); i < issued; ++i) {
-          bool landed = false;
-          for (unsigned tries = 0; tries < WAIT_LIMIT && !landed; ++tries)
-            landed = mbar_try_wait(&sh->kv_full[i % STAGES], (i / STAGES) & 1);
-          if (!landed && args.status != nullptr) *args.status = ERR_DRAIN;
-        }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      if (lane < pages_per_tile)
+        for (int h = 0; h < HALVES; ++h) tma_load_2d(k_tile + h * KV_HALF + at, &map_k, &sh->k_full[s], kv_head * D + h * 64, y);
+      if (lane == 0) {
+        ok = mbar_wait(&sh->v_free[s], phase ^ 1, &sh->abort, args.status, ERR_PRODUCER) ? 1 : 0;
+        if (ok) mbar_expect_tx(&sh->v_full[s], KV_BYTES);
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      if (lane < pages_per_tile)
+        for (int h = 0; h < HALVES; ++h) tma_load_2d(v_tile + h * KV_HALF + at, &map_v, &sh->v_full[s], kv_head * D + h * 64, y);
+      issued = i + 1;
+      page = page_1;
+      page_1 = page_2;
+      page_2 = page_3;
+    }
+    if (lane == 0 && sh->abort) {   // copies may still be in flight: wait for the stages armed last
+      for (int i = max(0, issued - STAGES); i < issued; ++i) {
         bool landed = false;
-        for (unsigned tries = 0; tries < WAIT_LIMIT && !landed; ++tries) landed = mbar_try_wait(&sh->q_full, 0);
+        for (unsigned tries = 0; tries < WAIT_LIMIT && !landed; ++tries)
+          landed = mbar_try_wait(&sh->k_full[i % STAGES], (i / STAGES) & 1) && mbar_try_wait(&sh->v_full[i % STAGES], (i / STAGES) & 1);
+        if (!landed && args.status != nullptr) *args.status = ERR_DRAIN;
       }
+      bool landed = false;
+      for (unsigned tries = 0; tries < WAIT_LIMIT && !landed; ++tries) landed = mbar_try_wait(&sh->q_full, 0);
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const unsigned idesc_s = instruction_descriptor(BM, BN, false);
       const unsigned idesc_o = instruction_descriptor(BM, D, true);
       const unsigned q_addr = smem_u32(q_tile), p_addr = smem_u32(p_tile);
-      bool ok = mbar_wait(&sh->q_full, 0, &sh->abort, args.status, ERR_MMA);
-      for (int i = 0; i < num_tiles && ok; ++i) {
-        const int s = i % STAGES;
-        ok = mbar_wait(&sh->kv_full[s], (i / STAGES) & 1, &sh->abort, args.status, ERR_MMA);
-        if (!ok) break;
+      // S of tile i into buffer i mod 2; issued one tile ahead of the softmax
+      auto issue_scores = [&](int i) -> bool {
+        const int st = i % STAGES;
+        if (!mbar_wait(&sh->k_full[st], (i / STAGES) & 1, &sh->abort, args.status, ERR_MMA)) return false;
         fence_after_sync();
-        const unsigned k_addr = smem_u32(kv_tiles + s * 2 * KV_BYTES), v_addr = k_addr + KV_BYTES;
+        const unsigned k_addr = smem_u32(kv_tiles + st * 2 * KV_BYTES);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const unsigned off = (kk / 4) * Q_HALF + (kk % 4) * 32, koff = (kk / 4) * KV_HALF + (kk % 4) * 32;
-          umma(tmem_s, smem_descriptor(q_addr + off), smem_descriptor(k_addr + koff), idesc_s, kk > 0 ? 1u : 0u);
+          umma(tmem_s + (i & 1) * BN, smem_descriptor(q_addr + off), smem_descriptor(k_addr + koff), idesc_s, kk > 0 ? 1u : 0u);
         }
-        umma_commit(&sh->s_full);
-        ok = mbar_wait(&sh->p_full, i & 1, &sh->abort, args.status, ERR_MMA);
+        umma_commit(&sh->s_full[i & 1]);
+        umma_commit(&sh->k_free[st]);
+        return true;
+      };
+      bool ok = mbar_wait(&sh->q_full, 0, &sh->abort, args.status, ERR_MMA);
+      if (ok) ok = issue_scores(0);
+      for (int i = 0; i < num_tiles && ok; ++i) {
+        // buffer (i + 1) mod 2 was last read for tile i - 1, whose P has arrived: it is free
+        if (i + 1 < num_tiles) ok = issue_scores(i + 1);
+        if (!ok) break;
+        ok = mbar_wait(&sh->v_full[i % STAGES], (i / STAGES) & 1, &sh->abort, args.status, ERR_MMA) &&
+             mbar_wait(&sh->p_full, i & 1, &sh->abort, args.status, ERR_MMA);
         if (!ok) break;
         fence_after_sync();
+        const unsigned v_addr = smem_u32(kv_tiles + (i % STAGES) * 2 * KV_BYTES) + KV_BYTES;
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk)   // 16 keys a step: P advances 32 bytes in its rows, V 16 rows
           umma(tmem_o, smem_descriptor(p_addr + kk * 32), smem_descriptor(v_addr + kk * 16 * 128, KV_HALF, 1024), idesc_o,
                (i > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(&sh->kv_free[s]);
+        umma_commit(&sh->v_free[i % STAGES]);
+        umma_commit(&sh->pv_done);
       }
-      if (ok) umma_commit(&sh->o_done);
     }
   } else {
     const int quarter = warp & 3;
@@ -198,48 +245,67 @@ portions_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     bool ok = true;
     for (int i = 0; i < num_tiles && ok; ++i) {
       const int s = i % STAGES;
-      ok = mbar_wait(&sh->s_full, i & 1, &sh->abort, args.status, ERR_SOFTMAX);
+      ok = mbar_wait(&sh->s_full[i & 1], (i >> 1) & 1, &sh->abort, args.status, ERR_SOFTMAX);
       ok = __all_sync(0xffffffffu, ok);   // the warp stays together: the tensor-memory accesses below are warp-wide
       if (!ok) break;
       fence_after_sync();
       unsigned v0[32], v1[32];
-      tmem_load32(tmem_s + lane_base, v0);
-      tmem_load32(tmem_s + lane_base + 32, v1);
+      tmem_load32(tmem_s + (i & 1) * BN + lane_base, v0);
+      tmem_load32(tmem_s + (i & 1) * BN + lane_base + 32, v1);
       tmem_wait_load();
       const int key_base = (tile_lo + i) * BN;
+      // most tiles lie wholly inside the row's visible range: only the others pay for masking
+      if (key_base < first || key_base + BN - 1 > last) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int k0 = key_base + j, k1 = key_base + 32 + j;
+          if (k0 < first || k0 > last) v0[j] = 0xff800000u;   // -inf
+          if (k1 < first || k1 > last) v1[j] = 0xff800000u;
+        }
+      }
       float tile_max = -INFINITY;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const int k0 = key_base + j, k1 = key_base + 32 + j;
-        const float a = (k0 >= first && k0 <= last) ? __uint_as_float(v0[j]) * args.scale_log2 : -INFINITY;
-        const float b = (k1 >= first && k1 <= last) ? __uint_as_float(v1[j]) * args.scale_log2 : -INFINITY;
-        v0[j] = __float_as_uint(a);
-        v1[j] = __float_as_uint(b);
-        tile_max = fmaxf(tile_max, fmaxf(a, b));
+      for (int j = 0; j < 32; ++j) tile_max = fmaxf(tile_max, fmaxf(__uint_as_float(v0[j]), __uint_as_float(v1[j])));
+      tile_max *= args.scale_log2;   // the scale is positive: the maximum of the raw scores is the one to scale
+      // The base of the exponentials follows the running maximum lazily: it moves (and O is
+      // rescaled) only when the maximum has grown by more than 2^8; until then probabilities
+      // are at most 2^8, which float32 sums and bfloat16 products hold without loss.
+      float correction = 1.0f;
+      if (tile_max > row_max + 8.0f || row_max == -INFINITY) {
+        const float new_max = fmaxf(row_max, tile_max);
+        const float base = new_max == -INFINITY ? 0.f : new_max;   // a row that has seen no key yet
+        correction = row_max == -INFINITY ? 0.f : fast_exp2(row_max - base);
+        row_max = new_max;
       }
-      const float new_max = fmaxf(row_max, tile_max);
-      const float base = new_max == -INFINITY ? 0.f : new_max;   // a row that has seen no key yet
-      const float correction = exp2f(row_max - base);           // exp2(-inf) = 0
-      row_max = new_max;
+      const float base = row_max == -INFINITY ? 0.f : row_max;
       float sum = 0.f;
-      unsigned char* p_row = p_tile + row * 128;
+      unsigned packed[32];   // the row's 64 probabilities as bfloat16 pairs
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {   // eight 16-byte chunks of the row, chunk c at (c xor row mod 8)
-        unsigned packed[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int j = c * 8 + e * 2;
-          const float x0 = exp2f(__uint_as_float(j < 32 ? v0[j] : v1[j - 32]) - base);
-          const float x1 = exp2f(__uint_as_float(j + 1 < 32 ? v0[j + 1] : v1[j + 1 - 32]) - base);
-          sum += x0 + x1;
-          const __nv_bfloat162 pair = __floats2bfloat162_rn(x0, x1);
-          packed[e] = *reinterpret_cast<const unsigned*>(&pair);
-        }
-        *reinterpret_cast<uint4*>(p_row + ((c ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      for (int j = 0; j < 64; j += 2) {
+        const float x0 = fast_exp2(fmaf(__uint_as_float(j < 32 ? v0[j] : v1[j - 32]), args.scale_log2, -base));
+        const float x1 = fast_exp2(fmaf(__uint_as_float(j + 1 < 32 ? v0[j + 1] : v1[j + 1 - 32]), args.scale_log2, -base));
+        sum += x0 + x1;
+        const __nv_bfloat162 pair = __floats2bfloat162_rn(x0, x1);
+        packed[j / 2] = *reinterpret_cast<const unsigned*>(&pair);
       }
       row_sum = row_sum * correction + sum;
+      // P has one buffer and O one accumulator: both belong to PV of the tile before until it is done
+      if (i > 0) {
+        ok = mbar_wait(&sh->pv_done, (i - 1) & 1, &sh->abort, args.status, ERR_SOFTMAX);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        fence_after_sync();
+      }
+      unsigned char* p_row = p_tile + row * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c)   // eight 16-byte chunks of the row, chunk c at (c xor row mod 8)
+        *reinterpret_cast<uint4*>(p_row + ((c ^ (row & 7)) << 4)) =
+            make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
       // value rows beyond the context: zero them (only the tile that holds the last key has any)
       if (tile_lo + i == tile_hi && (hi + 1) % BN != 0) {
+        ok = mbar_wait(&sh->v_full[s], (i / STAGES) & 1, &sh->abort, args.status, ERR_SOFTMAX);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
         unsigned char* v_tile = kv_tiles + s * 2 * KV_BYTES + KV_BYTES;
         const int first_bad = hi + 1 - key_base;
         for (int idx = threadIdx.x - 64; idx < (BN - first_bad) * HALVES * 8; idx += 128) {
@@ -264,7 +330,7 @@ portions_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       fence_async_shared();
       mbar_arrive(&sh->p_full);
     }
-    if (ok) ok = mbar_wait(&sh->o_done, 0, &sh->abort, args.status, ERR_SOFTMAX);
+    if (ok) ok = mbar_wait(&sh->pv_done, (num_tiles - 1) & 1, &sh->abort, args.status, ERR_SOFTMAX);
     ok = __all_sync(0xffffffffu, ok);
     fence_after_sync();
     if (ok) {
