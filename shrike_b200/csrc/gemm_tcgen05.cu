@@ -32,22 +32,16 @@
 // `status` (a host-visible word), raises a CTA-wide abort flag that ends the other roles'
 // waits, the producer waits (bounded again) for its copies in flight, TMEM is freed and
 // the CTA returns.  No TMA load uses cluster multicast.
-#include <cuda.h>
-
-#include <mutex>
-#include <unordered_map>
-
-#include "common.cuh"
+#include "blackwell.cuh"
 
 namespace tc {
+using namespace bw;
 
 constexpr int BM = 128;        // weight rows per CTA = MMA M
 constexpr int BK = 64;         // k elements per stage: 128 bytes of bf16
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
 constexpr int MAX_STAGES = 8;
-constexpr unsigned WAIT_HINT_NS = 20000;     // one try_wait may sleep this long
-constexpr unsigned WAIT_LIMIT = 100000;      // tries before giving up: about two seconds
 constexpr size_t A_BYTES = BM * BK * 2;
 
 enum : int { ERR_NONE = 0, ERR_PRODUCER = 1, ERR_MMA = 2, ERR_EPILOGUE = 3, ERR_DRAIN = 4 };
@@ -60,57 +54,6 @@ struct Shared {
   volatile int abort;
 };
 
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
-__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
-  unsigned ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(WAIT_HINT_NS) : "memory");
-  return ok != 0;
-}
-// Returns false when the wait ran out (and says so) or another role gave up.
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, Shared* sh, int* status, int who) {
-  for (unsigned tries = 0; tries < WAIT_LIMIT; ++tries) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (sh->abort) return false;
-  }
-  sh->abort = 1;
-  if (status != nullptr && *status == 0) *status = who;
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* smem, const CUtensorMap* map, unsigned long long* bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(smem)), "l"(reinterpret_cast<unsigned long long>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
-      : "memory");
-}
-__device__ __forceinline__ unsigned long long smem_descriptor(unsigned addr) {
-  // K-major operand, 128-byte swizzle: start address, leading offset 1 (unused with a
-  // swizzle), 1024 bytes between 8-row groups, descriptor version 1, layout type 2.
-  return static_cast<unsigned long long>((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (static_cast<unsigned long long>(1024 >> 4) << 32) |
-         (1ull << 46) | (2ull << 61);
-}
-__device__ __forceinline__ unsigned instruction_descriptor(int n) {
-  // kind::f16: D float32, A and B bfloat16, both K-major, M = 128, N = n.
-  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<unsigned>(n >> 3) << 17) | (static_cast<unsigned>(BM >> 4) << 24);
-}
-__device__ __forceinline__ void umma(unsigned tmem_d, unsigned long long a, unsigned long long b, unsigned idesc, unsigned accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
 __device__ __forceinline__ void tmem_load16(unsigned taddr, unsigned (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
@@ -151,15 +94,14 @@ gemm_swap_ab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
     mbar_init(&sh->done, 1);
     sh->abort = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_init_fence();
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(tmem_cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tmem_alloc(&sh->tmem_base, tmem_cols);
   }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  fence_before_sync();
   __syncthreads();
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  fence_after_sync();
   // dependents may start only now that this CTA holds its tensor memory: a dependent that also
   // wants tensor memory must not be able to starve a CTA it is waiting for
   let_dependents_start();
@@ -173,14 +115,14 @@ gemm_swap_ab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         mbar_expect_tx(&sh->full[i], static_cast<unsigned>(stage_bytes));
         tma_load_2d(tiles + stage_bytes * i, &map_w, &sh->full[i], (kb_begin + i) * BK, n0);
       }
-      asm volatile("griddepcontrol.wait;" ::: "memory");
+      wait_for_previous();
       for (int i = 0; i < early; ++i)
         tma_load_2d(tiles + stage_bytes * i + A_BYTES, &map_x, &sh->full[i], (kb_begin + i) * BK, t0);
       int issued = early;
       for (int i = early; i < num_kb; ++i) {
         const int s = i % args.stages;
         const unsigned phase = (i / args.stages) & 1;
-        if (!mbar_wait(&sh->empty[s], phase ^ 1, sh, args.status, ERR_PRODUCER)) break;
+        if (!mbar_wait(&sh->empty[s], phase ^ 1, &sh->abort, args.status, ERR_PRODUCER)) break;
         mbar_expect_tx(&sh->full[s], static_cast<unsigned>(stage_bytes));
         unsigned char* a_tile = tiles + stage_bytes * s;
         tma_load_2d(a_tile, &map_w, &sh->full[s], (kb_begin + i) * BK, n0);
@@ -200,14 +142,14 @@ gemm_swap_ab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const unsigned idesc = instruction_descriptor(args.tn);
+      const unsigned idesc = instruction_descriptor(BM, args.tn, false);
       bool ok = true;
       for (int i = 0; i < num_kb && ok; ++i) {
         const int s = i % args.stages;
         const unsigned phase = (i / args.stages) & 1;
-        ok = mbar_wait(&sh->full[s], phase, sh, args.status, ERR_MMA);
+        ok = mbar_wait(&sh->full[s], phase, &sh->abort, args.status, ERR_MMA);
         if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        fence_after_sync();
         const unsigned a_addr = smem_u32(tiles + stage_bytes * s);
         const unsigned b_addr = a_addr + static_cast<unsigned>(A_BYTES);
 #pragma unroll
@@ -222,10 +164,10 @@ gemm_swap_ab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     // epilogue: warp w may touch TMEM lanes 32 * (w % 4) .. + 31
     const int quarter = warp & 3;
     const int row = n0 + quarter * 32 + lane;   // weight row = output column
-    asm volatile("griddepcontrol.wait;" ::: "memory");   // the output may still be read by the kernel before
+    wait_for_previous();   // the output may still be read by the kernel before
     bool ok = true;
-    if (num_kb > 0) ok = mbar_wait(&sh->done, 0, sh, args.status, ERR_EPILOGUE);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (num_kb > 0) ok = mbar_wait(&sh->done, 0, &sh->abort, args.status, ERR_EPILOGUE);
+    fence_after_sync();
     if (ok) {
       const bool partial = gridDim.y > 1;
       const float bias = (args.bias != nullptr && split == 0 && row < args.n) ? args.bias[row] : 0.f;
@@ -233,7 +175,7 @@ gemm_swap_ab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         unsigned v[16];
         if (num_kb > 0) {
           tmem_load16(tmem_d + (static_cast<unsigned>(quarter * 32) << 16) + static_cast<unsigned>(c0), v);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          tmem_wait_load();
         } else {
 #pragma unroll
           for (int j = 0; j < 16; ++j) v[j] = 0u;
@@ -253,72 +195,12 @@ gemm_swap_ab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       }
     }
   }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  fence_before_sync();
   __syncthreads();
   if (warp == 1) {
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(tmem_cols) : "memory");
+    fence_after_sync();
+    tmem_free(tmem_d, tmem_cols);
   }
-}
-
-// ---------------------------------------------------------------- host side
-using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiled encode_tiled() {
-  static EncodeTiled fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult result;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
-        result == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiled>(ptr);
-  });
-  return fn;
-}
-
-struct MapKey {
-  const void* base;
-  int rows, cols, box_rows;
-  bool operator==(const MapKey& o) const { return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
-};
-struct MapKeyHash {
-  size_t operator()(const MapKey& k) const {
-    size_t h = reinterpret_cast<size_t>(k.base);
-    h = h * 1000003u ^ static_cast<size_t>(k.rows);
-    h = h * 1000003u ^ static_cast<size_t>(k.cols);
-    return h * 1000003u ^ static_cast<size_t>(k.box_rows);
-  }
-};
-
-// A row-major [rows, cols] bfloat16 matrix seen as boxes of box_rows x 64 elements.
-static int tensor_map(const void* base, int rows, int cols, int box_rows, CUtensorMap* out) {
-  static std::mutex mutex;
-  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-  const MapKey key{base, rows, cols, box_rows};
-  std::lock_guard<std::mutex> guard(mutex);
-  auto found = cache.find(key);
-  if (found != cache.end()) {
-    *out = found->second;
-    return SHRIKE_OK;
-  }
-  EncodeTiled encode = encode_tiled();
-  if (encode == nullptr) return SHRIKE_BAD_ARGUMENT;
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
-  const cuuint32_t box[2] = {BK, static_cast<cuuint32_t>(box_rows)};
-  const cuuint32_t element_strides[2] = {1, 1};
-  CUtensorMap map;
-  const CUresult rc = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
-                             element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (rc != CUDA_SUCCESS) return 1000 + static_cast<int>(rc);
-  if (cache.size() > 4096) cache.clear();
-  cache.emplace(key, map);
-  *out = map;
-  return SHRIKE_OK;
 }
 
 }  // namespace tc
@@ -377,9 +259,9 @@ SHRIKE_API int shrike_gemm_tc(const void* x, const void* w, const float* bias, v
     configured = true;
   }
   CUtensorMap map_w, map_x;
-  int rc = tensor_map(w, n, k, BM, &map_w);
+  int rc = tensor_map_bf16(w, n, k, BM, &map_w);
   if (rc != SHRIKE_OK) return rc;
-  rc = tensor_map(x, tokens, k, tn, &map_x);
+  rc = tensor_map_bf16(x, tokens, k, tn, &map_x);
   if (rc != SHRIKE_OK) return rc;
   Args args;
   args.out = out;

@@ -197,7 +197,15 @@ class LLMEngine:
                 del self.requests[request.req_id]
                 self._request_seed.pop(request.req_id, None)
         self.stats.steps += 1
+        if self.stats.steps % 256 == 0:
+            self._check_kernels()
         return outputs
+
+    def _check_kernels(self) -> None:
+        """Raises if a kernel gave up a bounded wait since the last check (one word read from the device)."""
+        check = getattr(self.ops, "check_status", None)
+        if check is not None:
+            check()
 
     def generate(self, prompts, sampling, chat: bool = True) -> list[list[int]]:
         """Offline batch API (engine.py:166-183): generated token ids per prompt."""
@@ -208,6 +216,7 @@ class LLMEngine:
         while self.has_work:
             for out in self.step():
                 results[id_map[out.req_id]].append(out.token_id)
+        self._check_kernels()
         return results
 
     def metrics(self) -> dict:
