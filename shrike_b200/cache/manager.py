@@ -116,6 +116,7 @@ class CacheManager:
             raise ValueError("one page count per group")
         self.pools = [IdPool(count) for count in counts]
         self.slots = IdPool(max_slots)
+        self.has_windows = any(group.window is not None for group in self.groups)
 
     # ---- figures -----------------------------------------------------------
     @property
@@ -166,10 +167,21 @@ class CacheManager:
             for _ in range(count):
                 table.append(pool.take())
 
+    def has_room(self, cache: RequestCache, total_tokens: int) -> bool:
+        """True when the pages already held cover `total_tokens` in every group (nothing to take)."""
+        limit = total_tokens
+        size = self.page_size
+        for table in cache.tables:
+            if table.length * size < limit:
+                return False
+        return True
+
     def advance(self, cache: RequestCache, num_computed: int) -> int:
         """After a step: gives back the pages that every later query's window has
         passed.  The next query sits at position `num_computed` and sees keys from
         `num_computed - window + 1` on.  Returns how many pages were given back."""
+        if not self.has_windows:
+            return 0
         given = 0
         for table, pool, group in zip(cache.tables, self.pools, self.groups):
             if group.window is None:

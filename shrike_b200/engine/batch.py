@@ -61,6 +61,24 @@ class StepContext:
     sample_seed: torch.Tensor | None = None  # int64 [R]
 
 
+@dataclass
+class Staged:
+    """What `BatchBuilder.stage` copied: counts, the layout of the block, host-side lists."""
+
+    n: int
+    s: int
+    r: int
+    max_blocks: list
+    sizes: list
+    offsets: list
+    total: int
+    sampled: bool
+    q_lens: list
+    starts: list
+    ctx_lens: list
+    slots: list
+
+
 class BatchBuilder:
     """Packs entries into pinned host memory and copies them in one transfer."""
 
@@ -73,6 +91,7 @@ class BatchBuilder:
         self._events: list = []
         self._turn = 0
         self._dev = None
+        self._range = None
         self.generation = 0  # grows when the device buffer moves: captured launch sequences are stale then
 
     def _staging(self, count: int):
@@ -90,6 +109,13 @@ class BatchBuilder:
         return self._host[self._turn]
 
     def build(self, entries: list[StepEntry]) -> StepContext:
+        """Stages the entries and returns the device views of the step's metadata."""
+        return self.context(self.stage(entries))
+
+    def stage(self, entries: list[StepEntry]) -> "Staged":
+        """Fills the pinned buffer and starts its copy to the device.  The returned record holds
+        only host-side facts; `context` turns it into device views when a forward pass needs them
+        (a replayed launch sequence does not)."""
         page = self.page_size
         q_lens = [len(e.tokens) for e in entries]
         if not entries or min(q_lens) < 1:
@@ -98,15 +124,16 @@ class BatchBuilder:
         r = sum(len(e.want) for e in entries)
         starts = [e.start for e in entries]
         ctx_lens = [st + q for st, q in zip(starts, q_lens)]
+        need_max = -(-max(ctx_lens) // page)
         max_blocks = [1] * self.num_groups
-        for e, ctx in zip(entries, ctx_lens):
-            need = -(-ctx // page)
-            for g, table in enumerate(e.cache.tables):
-                if table.length < need:
-                    raise ValueError(
-                        f"entry holds {table.length} pages in group {g} but its context of {ctx} needs {need}"
-                    )
-                max_blocks[g] = max(max_blocks[g], need)
+        for g in range(self.num_groups):
+            short = min(e.cache.tables[g].length + (need_max - -(-c // page)) for e, c in zip(entries, ctx_lens))
+            if short < need_max:   # some entry holds fewer pages than its context needs: say which
+                for e, ctx in zip(entries, ctx_lens):
+                    if e.cache.tables[g].length < -(-ctx // page):
+                        raise ValueError(f"entry holds {e.cache.tables[g].length} pages in group {g} "
+                                         f"but its context of {ctx} needs {-(-ctx // page)}")
+            max_blocks[g] = need_max
         # table widths grow in powers of two, so that the layout of a decode batch (and a
         # launch sequence captured for it) stays the same while contexts grow
         max_blocks = [max(8, 1 << (mb - 1).bit_length()) for mb in max_blocks]
@@ -115,31 +142,41 @@ class BatchBuilder:
         sizes = [2 * r, r, r, n, n, n, s + 1, s, s, r]
         for g in range(self.num_groups):
             sizes += [n, s * max_blocks[g]]
-        offsets = np.concatenate([[0], np.cumsum(sizes)])
-        total = int(offsets[-1])
+        offsets = [0]
+        for size in sizes:
+            offsets.append(offsets[-1] + size)
+        total = offsets[-1]
         host = self._staging(total)
         flat = host.numpy()
         parts = [flat[offsets[i]: offsets[i + 1]] for i in range(len(sizes))]
         seeds, temps, top_ps = parts[0].view(np.int64), parts[1].view(np.float32), parts[2].view(np.float32)
         ids, pos, seq_of, q_start, ctx_arr, slot_arr, out_rows = parts[3:10]
+        slots_host = [e.cache.slot for e in entries]
 
         if max(q_lens) == 1:
             # the steady state of decoding: one token per entry, filled without per-token work
             ids[:] = [e.tokens[0] for e in entries]
             pos[:] = starts
-            seq_of[:] = np.arange(s, dtype=np.int32)
-            q_start[:] = np.arange(s + 1, dtype=np.int32)
+            seq_of[:] = self._arange(s)
+            q_start[:] = self._arange(s + 1)
             ctx_arr[:] = ctx_lens
-            slot_arr[:] = [e.cache.slot for e in entries]
-            row = 0
-            for index, e in enumerate(entries):
-                for w in e.want:
-                    if w != 0:
-                        raise ValueError(f"wanted place {w} is outside the entry's 1 tokens")
-                    out_rows[row] = index
-                    if sampled:
-                        temps[row], top_ps[row], seeds[row] = e.sampling
-                    row += 1
+            slot_arr[:] = slots_host
+            if r == s and all(e.want == [0] for e in entries):
+                out_rows[:] = self._arange(s)
+                if sampled:
+                    temps[:] = [e.sampling[0] for e in entries]
+                    top_ps[:] = [e.sampling[1] for e in entries]
+                    seeds[:] = [e.sampling[2] for e in entries]
+            else:
+                row = 0
+                for index, e in enumerate(entries):
+                    for w in e.want:
+                        if w != 0:
+                            raise ValueError(f"wanted place {w} is outside the entry's 1 tokens")
+                        out_rows[row] = index
+                        if sampled:
+                            temps[row], top_ps[row], seeds[row] = e.sampling
+                        row += 1
             for g in range(self.num_groups):
                 slots = parts[10 + 2 * g]
                 table2d = parts[11 + 2 * g].reshape(s, max_blocks[g])
@@ -158,24 +195,35 @@ class BatchBuilder:
         else:
             self._fill_general(entries, q_lens, parts, max_blocks, sampled, page, s)
 
-        dev = self._dev[:total]
-        dev.copy_(host[:total], non_blocking=True)
+        self._dev[:total].copy_(host[:total], non_blocking=True)
         if self.device.type == "cuda":
             event = torch.cuda.Event()
             event.record()
             self._events[self._turn] = event
-        views = [dev[int(offsets[i]): int(offsets[i + 1])] for i in range(len(sizes))]
+        return Staged(n, s, r, max_blocks, sizes, offsets, total, sampled, q_lens, starts, ctx_lens, slots_host)
+
+    def _arange(self, count: int) -> np.ndarray:
+        if self._range is None or len(self._range) < count:
+            self._range = np.arange(max(count, 1024), dtype=np.int32)
+        return self._range[:count]
+
+    def context(self, staged: "Staged") -> StepContext:
+        """Device views of what `stage` copied."""
+        n, s, r, max_blocks, sizes, offsets = staged.n, staged.s, staged.r, staged.max_blocks, staged.sizes, staged.offsets
+        dev = self._dev[: staged.total]
+        views = [dev[offsets[i]: offsets[i + 1]] for i in range(len(sizes))]
         groups = [
             GroupView(views[10 + 2 * g], views[11 + 2 * g].view(s, max_blocks[g]), max_blocks[g])
             for g in range(self.num_groups)
         ]
+        sampled = staged.sampled
         return StepContext(
             num_tokens=n, num_seqs=s, num_rows=r,
             token_ids=views[3], positions=views[4], seq_of_token=views[5], q_start=views[6],
             ctx_len=views[7], state_slot=views[8], out_rows=views[9], groups=groups,
-            storage=self.storage, max_q_len=max(q_lens), min_q_len=min(q_lens), max_ctx_len=max(ctx_lens),
-            q_lens=q_lens, starts=starts, slots=[e.cache.slot for e in entries],
-            all_single=max(q_lens) == 1,
+            storage=self.storage, max_q_len=max(staged.q_lens), min_q_len=min(staged.q_lens),
+            max_ctx_len=max(staged.ctx_lens), q_lens=staged.q_lens, starts=staged.starts, slots=staged.slots,
+            all_single=max(staged.q_lens) == 1,
             sample_temperature=views[1].view(torch.float32) if sampled else None,
             sample_top_p=views[2].view(torch.float32) if sampled else None,
             sample_seed=views[0].view(torch.int64) if sampled else None,

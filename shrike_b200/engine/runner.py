@@ -82,23 +82,24 @@ class ModelRunner:
         CUDA graph and replayed afterwards, because at small batch the step is bound by
         launch latency otherwise (the remedy shrike's README names for its own per-layer
         dispatch cost)."""
-        ctx = self.builder.build(entries)
-        if sample and ctx.sample_seed is None:
+        staged = self.builder.stage(entries)
+        if sample and not staged.sampled:
             raise ValueError("sample=True needs `sampling` on every entry that wants logits")
         graphable = (
-            self.use_graphs and self.device.type == "cuda" and ctx.all_single
-            and ctx.num_rows == ctx.num_seqs and all(e.want == [0] for e in entries)
+            self.use_graphs and self.device.type == "cuda" and max(staged.q_lens) == 1
+            and staged.r == staged.s and all(e.want == [0] for e in entries)
         )
         if not graphable:
-            logits, tokens = self._run(ctx, sample)
+            logits, tokens = self._run(self.builder.context(staged), sample)
             return (logits, tokens) if sample else logits
-        key = (ctx.num_seqs, tuple(g.max_blocks for g in ctx.groups), sample)
+        key = (staged.s, tuple(staged.max_blocks), sample)
         held = self._graphs.get(key)
         if held is not None and held[0] == self._generation():
-            held[1].replay()
+            held[1].replay()   # the metadata is already on its way; no views are needed
             self.ops.launches += held[4]
             self.ops.library_calls += held[5]
             return (held[2], held[3]) if sample else held[2]
+        ctx = self.builder.context(staged)
         # first time (or buffers moved): run eagerly for this step's result, then capture
         logits, tokens = self._run(ctx, sample)
         generation = self._generation()

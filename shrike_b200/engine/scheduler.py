@@ -72,13 +72,14 @@ class Scheduler:
                 num_new = 1
             else:
                 num_new = min(request.num_prompt_tokens - request.num_computed_tokens, budget)
-            while not self.cache.can_append(request.cache, request.num_computed_tokens, num_new):
-                if not self._preempt_newest(request):
-                    num_new = 0
-                    break
-            if num_new == 0:
-                continue
-            self.cache.append(request.cache, request.num_computed_tokens, num_new)
+            if not self.cache.has_room(request.cache, request.num_computed_tokens + num_new):
+                while not self.cache.can_append(request.cache, request.num_computed_tokens, num_new):
+                    if not self._preempt_newest(request):
+                        num_new = 0
+                        break
+                if num_new == 0:
+                    continue
+                self.cache.append(request.cache, request.num_computed_tokens, num_new)
             (singles if num_new == 1 else portions).append((request, num_new))
             budget -= num_new
 
