@@ -57,3 +57,36 @@ def test_engine_refuses_without_kernels_dtype(tmp_path):
     folder = make_model_folder(tmp_path, "A")
     with pytest.raises(ValueError, match="dtype"):
         LLMEngine(str(folder), dtype="float16")
+
+
+@pytest.mark.parametrize("block_size", [8, 32, 64])
+def test_pool_sized_from_free_memory_and_other_page_sizes(tmp_path, block_size):
+    """`gpu_mem_util` sizes the pool from free device memory (no explicit num_blocks), and
+    generation does not depend on the page size."""
+    folder = make_model_folder(tmp_path, "B")
+    weights = read_weights(folder)
+    engine = LLMEngine(str(folder), block_size=block_size, gpu_mem_util=0.002, dtype="float32")
+    assert min(engine.block_manager.num_pages) > 100
+    prompts = [random_tokens(384, n, 80 + n) for n in (7, 70, 33)]
+    outs = engine.generate(prompts, SamplingParams(max_new_tokens=6, ignore_eos=True))
+    assert engine.block_manager.whole()
+    for prompt, out in zip(prompts, outs):
+        want, margins = plain_greedy("B", weights, prompt, 6, False)
+        for a, b, margin in zip(out, want, margins):
+            if a != b:
+                assert margin < 1e-4
+                break
+
+
+def test_bfloat16_decode_steps_are_replayed_and_match_eager(tmp_path):
+    """The captured decode step gives the tokens the eager step gives."""
+    folder = make_model_folder(tmp_path, "A")
+    prompts = [random_tokens(256, n, 90 + n) for n in (5, 17, 33, 2)]
+    params = SamplingParams(max_new_tokens=40, ignore_eos=True)
+    captured = LLMEngine(str(folder), num_blocks=32, dtype="bfloat16")
+    a = captured.generate(prompts, params)
+    assert len(captured.runner._graphs) >= 1, "no decode step was captured"
+    eager = LLMEngine(str(folder), num_blocks=32, dtype="bfloat16")
+    eager.runner.use_graphs = False
+    b = eager.generate(prompts, params)
+    assert a == b
