@@ -56,6 +56,21 @@ static inline cudaError_t launch_dependent(void (*kernel)(KernelArgs...), dim3 g
   return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
 }
 
+// base[0] + base[stride] + ... over `partials` slices (the stack a K-split product leaves),
+// added in ascending order.  Up to 16 loads are issued together before the first addition,
+// so the sum costs one memory latency, not one per slice.
+__device__ __forceinline__ float sum_partials(const float* base, long long stride, int partials) {
+  float held[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) held[i] = (i == 0 || i < partials) ? base[i * stride] : 0.f;
+  float sum = held[0];
+#pragma unroll
+  for (int i = 1; i < 16; ++i)
+    if (i < partials) sum = __fadd_rn(sum, held[i]);
+  for (int i = 16; i < partials; ++i) sum = __fadd_rn(sum, base[i * stride]);
+  return sum;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int offset = 16; offset > 0; offset >>= 1) v += __shfl_xor_sync(0xffffffffu, v, offset);

@@ -66,8 +66,10 @@ template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16*
 
 // `delta` may be a stack of `partials` arrays (the slices of a K-split matrix product),
 // `partial_stride` elements apart; they are added in ascending order.
-template <typename TD, typename TO, bool HAS_DELTA, bool GATHER, int VEC>
-__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
+// MAX_THREADS 512 leaves registers to hold several slices' loads in flight; 1024 (wide rows) adds
+// slice by slice.
+template <typename TD, typename TO, bool HAS_DELTA, bool GATHER, int VEC, int MAX_THREADS>
+__global__ void __launch_bounds__(MAX_THREADS, 1024 / MAX_THREADS) add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
                                    const int* __restrict__ rows, const float* __restrict__ weight,
                                    float eps, TO* __restrict__ out, int width, int partials,
                                    long long partial_stride) {
@@ -92,11 +94,20 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
         load4<float>(x + g * 4, v);
         if (HAS_DELTA) {
           load4<TD>(d + g * 4, dv);
-          for (int p = 1; p < partials; ++p) {
-            float more[4];
-            load4<TD>(d + p * partial_stride + g * 4, more);
+          if (partials > 1) {   // AHEAD slices at a time: their loads are issued before the first addition
+            constexpr int AHEAD = MAX_THREADS <= 512 ? 2 : 1;
+            for (int first = 1; first < partials; first += AHEAD) {
+              float more[AHEAD][4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) dv[i] = __fadd_rn(dv[i], more[i]);
+              for (int q = 0; q < AHEAD; ++q)
+                if (first + q < partials) load4<TD>(d + (first + q) * partial_stride + g * 4, more[q]);
+#pragma unroll
+              for (int q = 0; q < AHEAD; ++q)
+                if (first + q < partials) {
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) dv[i] = __fadd_rn(dv[i], more[q][i]);
+                }
+            }
           }
 #pragma unroll
           for (int i = 0; i < 4; ++i) v[i] = __fadd_rn(v[i], dv[i]);
@@ -111,7 +122,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
         float v = x[g];
         if (HAS_DELTA) {
           float dv = to_float(d[g]);
-          for (int p = 1; p < partials; ++p) dv = __fadd_rn(dv, to_float(d[p * partial_stride + g]));
+          for (int p = 1; p < partials; ++p) dv = __fadd_rn(dv, to_float(d[p * partial_stride + g]));   // scalar path: widths no multiple of 4
           v = __fadd_rn(v, dv);
           if (!GATHER) x[g] = v;
         }
@@ -148,13 +159,16 @@ static int launch_add_rmsnorm(float* resid, const void* delta, const int* rows, 
   int threads = 128;
   while (threads < 1024 && threads * 2 <= ((groups + 31) / 32) * 32) threads *= 2;
   if (static_cast<long long>(threads) * NORM_MAX_PER_THREAD < groups) return SHRIKE_BAD_ARGUMENT;
-#define SHRIKE_NORM_LAUNCH(G, V)                                                                   \
-  launch_dependent(add_rmsnorm_kernel<TD, TO, HAS_DELTA, G, V>, n, threads, 0, stream, resid,      \
+#define SHRIKE_NORM_LAUNCH_T(G, V, T)                                                              \
+  launch_dependent(add_rmsnorm_kernel<TD, TO, HAS_DELTA, G, V, T>, n, threads, 0, stream, resid,   \
                    static_cast<const TD*>(delta), rows, weight, eps, static_cast<TO*>(out), width, partials,  \
                    partial_stride)
+#define SHRIKE_NORM_LAUNCH(G, V)                                                                   \
+  do { if (threads <= 512) SHRIKE_NORM_LAUNCH_T(G, V, 512); else SHRIKE_NORM_LAUNCH_T(G, V, 1024); } while (0)
   if (rows) { if (vec) SHRIKE_NORM_LAUNCH(true, 4); else SHRIKE_NORM_LAUNCH(true, 1); }
   else { if (vec) SHRIKE_NORM_LAUNCH(false, 4); else SHRIKE_NORM_LAUNCH(false, 1); }
 #undef SHRIKE_NORM_LAUNCH
+#undef SHRIKE_NORM_LAUNCH_T
   return SHRIKE_OK;
 }
 
@@ -275,11 +289,8 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const float*
     const int head = idx / half, j = idx - head * half;
     const bool is_q = head < num_heads, is_k = !is_q && head < num_heads + num_kv_heads;
     const int lo = head * head_dim + j, hi = lo + half;  // columns of the row
-    float a = row[lo], b = row[hi];
-    for (int p = 1; p < partials; ++p) {   // slices of a K-split projection, added in order
-      a = __fadd_rn(a, row[p * partial_stride + lo]);
-      b = __fadd_rn(b, row[p * partial_stride + hi]);
-    }
+    float a = sum_partials(row + lo, partial_stride, partials);   // slices of a K-split projection, added in order
+    float b = sum_partials(row + hi, partial_stride, partials);
     if (bias != nullptr) {
       a = __fadd_rn(a, bias[lo]);
       b = __fadd_rn(b, bias[hi]);
