@@ -8,10 +8,12 @@
 //     query heads that share a kv head are the rows of one 16-row tile, so keys and
 //     values are read once per kv head, not once per query head; the four warps take 16
 //     keys each of every 64-key tile, tiles arrive through a three-deep cp.async pipeline;
-//     every split writes its partial result, and the split that finishes last (an atomic
-//     counter per kv head, which it resets) combines them.  The split count is a launch
-//     parameter, the key ranges come from ctx_len on the device, so a captured launch
-//     sequence stays valid as contexts grow.
+//     the splits of one kv head form thread-block clusters of up to eight CTAs, which add
+//     their partial results up through distributed shared memory; where one cluster covers
+//     all splits the result goes straight out, otherwise each cluster writes one partial
+//     and the CTA that finishes last (an atomic counter per kv head, which it resets)
+//     combines them.  Split and cluster counts are launch parameters, the key ranges come
+//     from ctx_len on the device, so a captured launch sequence stays valid as contexts grow.
 // Keys and values are fetched through the block table with 16-byte cp.async copies into
 // padded shared-memory rows (double-buffered) and read with ldmatrix.  Scores, running
 // maximum, sum and the output accumulate in float32; probabilities are rounded to
@@ -19,6 +21,8 @@
 // [max(0, p - window + 1), p] (shrike/engine/model_runner.py:129-150).
 //
 // Built once per head size: -DSHRIKE_HEAD_DIM=<multiple of 16, at most 256>.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 #ifndef SHRIKE_HEAD_DIM
@@ -78,10 +82,11 @@ struct Params {
   const int* q_start;
   const int* ctx_len;
   bf16* out;
-  float* partial_out;   // [seq, head, split, D], single tokens only
-  float* partial_ml;    // [seq, head, split, 2]
-  int* arrivals;        // [seq, kv head * row tiles]: splits that have stored their partial; zero between launches
+  float* partial_out;   // [seq, head, splits / cluster, D], single tokens only
+  float* partial_ml;    // [seq, head, splits / cluster, 2]
+  int* arrivals;        // [seq, kv head * row tiles]: CTAs that have stored their share; zero between launches
   int max_blocks, num_heads, num_kv_heads, page_size, num_pages, window, splits;
+  int cluster;          // single tokens: consecutive splits that form one thread-block cluster
   int skip_single;      // portions kernel: leave q_len == 1 to the single-token kernel
   float scale_log2;     // scale * log2(e)
 };
@@ -349,8 +354,10 @@ __global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
   const int head0 = kv_head * group + row_tile * 16;
   const int rows_here = min(16, group - row_tile * 16);
   const int tile_lo = first_key / BN, tile_hi = last_key / BN;
-  const int per_split = (tile_hi - tile_lo + p.splits) / p.splits;
-  const int my_lo = tile_lo + split * per_split, my_hi = min(tile_hi, my_lo + per_split - 1);
+  // the tiles are dealt out as evenly as they go: no two splits differ by more than one
+  const int tiles = tile_hi - tile_lo + 1;
+  const int my_lo = tile_lo + static_cast<int>(static_cast<long long>(split) * tiles / p.splits);
+  const int my_hi = tile_lo + static_cast<int>(static_cast<long long>(split + 1) * tiles / p.splits) - 1;
 
   float o[DTILES][4];
 #pragma unroll
@@ -438,6 +445,8 @@ __global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
   float* warp_o = reinterpret_cast<float*>(smem_raw);         // [4][16][D]
   float* warp_ml = warp_o + 4 * 16 * D;                       // [4][16][2]
   float* row_weight = warp_ml + 4 * 16 * 2;                   // [16][4] weight of each warp, then [16] max, [16] sum
+  float* cta_o = row_weight + 96;                             // [16][D] this CTA's result, read by its cluster
+  float* cta_ml = cta_o + 16 * D;                             // [16][2]
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     const int row = (lane >> 2) + 8 * r;
@@ -471,12 +480,19 @@ __global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
   }
   __syncthreads();
   const bool direct = p.splits == 1;   // nothing to combine: the result goes straight out
+  const int partials = p.splits / p.cluster;   // what the clusters leave in global memory
   for (int idx = threadIdx.x; idx < rows_here * D; idx += THREADS) {
     const int row = idx / D, d = idx - row * D;
     float total = 0.f;
 #pragma unroll
     for (int w = 0; w < 4; ++w) total += row_weight[row * 4 + w] * warp_o[(w * 16 + row) * D + d];
-    if (direct) {
+    if (p.cluster > 1) {
+      cta_o[idx] = total;
+      if (d == 0) {
+        cta_ml[row * 2] = row_weight[64 + row];
+        cta_ml[row * 2 + 1] = row_weight[80 + row];
+      }
+    } else if (direct) {
       const float sum = row_weight[80 + row];
       p.out[(static_cast<size_t>(start) * p.num_heads + head0 + row) * D + d] =
           __float2bfloat16_rn(sum > 0.f ? total / sum : 0.f);
@@ -489,75 +505,151 @@ __global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
       }
     }
   }
-  if (direct) return;
-  // the split that arrives last combines all of them; the order of the sum is by split
+  if (p.cluster > 1) {
+    // The cluster's CTAs add their results up through distributed shared memory: each takes
+    // a slice of the (row, column) space and reads that slice from every CTA of the cluster,
+    // in rank order.  Nothing passes through global memory unless there are more clusters.
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    const int rank = static_cast<int>(cluster.block_rank());
+    const int outputs = rows_here * D;
+    const int share = (outputs + p.cluster - 1) / p.cluster;
+    const int stop = min(outputs, (rank + 1) * share);
+    for (int idx = rank * share + threadIdx.x; idx < stop; idx += THREADS) {
+      const int row = idx / D, d = idx - row * D;
+      float peer_max[8], peer_sum[8], peer_o[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        if (r < p.cluster) {
+          const float* ml = cluster.map_shared_rank(cta_ml, r);
+          peer_max[r] = ml[row * 2];
+          peer_sum[r] = ml[row * 2 + 1];
+          peer_o[r] = cluster.map_shared_rank(cta_o, r)[idx];
+        }
+      }
+      float m = -INFINITY;
+#pragma unroll
+      for (int r = 0; r < 8; ++r)
+        if (r < p.cluster) m = fmaxf(m, peer_max[r]);
+      float sum = 0.f, total = 0.f;
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        if (r < p.cluster) {
+          const float weight = peer_max[r] == -INFINITY ? 0.f : exp2f(peer_max[r] - m);
+          sum += weight * peer_sum[r];
+          total += weight * peer_o[r];
+        }
+      }
+      if (partials == 1) {
+        p.out[(static_cast<size_t>(start) * p.num_heads + head0 + row) * D + d] =
+            __float2bfloat16_rn(sum > 0.f ? total / sum : 0.f);
+      } else {
+        const size_t slot = (static_cast<size_t>(seq) * p.num_heads + head0 + row) * partials + split / p.cluster;
+        p.partial_out[slot * D + d] = total;
+        if (d == 0) {
+          p.partial_ml[slot * 2] = m;
+          p.partial_ml[slot * 2 + 1] = sum;
+        }
+      }
+    }
+    cluster.sync();   // no CTA leaves while its shared memory may still be read
+  }
+  if (direct || partials == 1) return;
+  // the CTA that arrives last combines all partials; the order of the sum is by partial
   // index, whoever does it
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) {
     int* counter = p.arrivals + static_cast<size_t>(seq) * gridDim.y + blockIdx.y;
     const int before = atomicAdd(counter, 1);
-    is_last = before == p.splits - 1;
+    is_last = before == p.splits - 1;   // every CTA counts, whatever the cluster size
     if (is_last) *counter = 0;   // ready for the next launch
   }
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  // (max, sum) of every (row, split): one pair per thread, all loads in flight at once
-  float* split_max = reinterpret_cast<float*>(smem_raw);      // [16][MAX_SPLITS], becomes the weights
-  float* split_sum = split_max + 16 * MAX_SPLITS;             // [16][MAX_SPLITS]
-  float* inverse = split_sum + 16 * MAX_SPLITS;               // [16]
-  for (int idx = threadIdx.x; idx < rows_here * p.splits; idx += THREADS) {
-    const int row = idx / p.splits, s = idx - row * p.splits;
-    const size_t slot = (static_cast<size_t>(seq) * p.num_heads + head0 + row) * p.splits + s;
-    const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.partial_ml + slot * 2));
-    split_max[row * MAX_SPLITS + s] = ml.x;
-    split_sum[row * MAX_SPLITS + s] = ml.y;
-  }
-  __syncthreads();
-  if (threadIdx.x < rows_here) {
-    const int row = threadIdx.x;
-    float m = -INFINITY;
-    for (int s = 0; s < p.splits; ++s) m = fmaxf(m, split_max[row * MAX_SPLITS + s]);
-    float sum = 0.f;
-    for (int s = 0; s < p.splits; ++s) {
-      const float sm = split_max[row * MAX_SPLITS + s];
-      const float weight = sm == -INFINITY ? 0.f : exp2f(sm - m);
-      split_max[row * MAX_SPLITS + s] = weight;
-      sum += weight * split_sum[row * MAX_SPLITS + s];
+  // Each thread takes four columns of one row, two such items at a time, and reads the
+  // (max, sum) pairs and the four columns of up to eight partials of both in one go: the
+  // combine costs one memory round trip per eight partials, not one per partial.  Chunks of
+  // eight are merged like attention tiles, in partial order.
+  constexpr int QUADS = D / 4;
+  const int items = rows_here * QUADS;
+  for (int first = threadIdx.x; first < items; first += 2 * THREADS) {
+    int row[2], quad[2];
+    bool live[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int item = first + k * THREADS;
+      live[k] = item < items;
+      row[k] = live[k] ? item / QUADS : 0;
+      quad[k] = live[k] ? item - row[k] * QUADS : 0;
     }
-    inverse[row] = sum > 0.f ? 1.0f / sum : 0.f;
-  }
-  __syncthreads();
-  const float* weights = split_max;
-  for (int idx = threadIdx.x; idx < rows_here * D; idx += THREADS) {
-    const int row = idx / D, d = idx - row * D;
-    const float* src = p.partial_out + (static_cast<size_t>(seq) * p.num_heads + head0 + row) * p.splits * D + d;
-    float total = 0.f;
-    int s = 0;
-    for (; s + 4 <= p.splits; s += 4) {   // four independent loads in flight, summed in split order
-      const float v0 = __ldcg(src + (s + 0) * D), v1 = __ldcg(src + (s + 1) * D);
-      const float v2 = __ldcg(src + (s + 2) * D), v3 = __ldcg(src + (s + 3) * D);
-      total += weights[row * MAX_SPLITS + s] * v0;
-      total += weights[row * MAX_SPLITS + s + 1] * v1;
-      total += weights[row * MAX_SPLITS + s + 2] * v2;
-      total += weights[row * MAX_SPLITS + s + 3] * v3;
+    float run_max[2] = {-INFINITY, -INFINITY}, run_sum[2] = {0.f, 0.f};
+    float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    for (int base = 0; base < partials; base += 8) {
+      float2 ml[2][8];
+      float4 o[2][8];
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (live[k] && base + j < partials) {
+            const size_t slot = (static_cast<size_t>(seq) * p.num_heads + head0 + row[k]) * partials + base + j;
+            ml[k][j] = __ldcg(reinterpret_cast<const float2*>(p.partial_ml + slot * 2));
+            o[k][j] = __ldcg(reinterpret_cast<const float4*>(p.partial_out + slot * D + quad[k] * 4));
+          }
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        if (!live[k]) continue;
+        float m = run_max[k];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (base + j < partials) m = fmaxf(m, ml[k][j].x);
+        const float rescale = run_max[k] == -INFINITY ? 0.f : exp2f(run_max[k] - m);
+        float sum = run_sum[k] * rescale;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[k][e] *= rescale;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (base + j < partials) {
+            const float weight = ml[k][j].x == -INFINITY ? 0.f : exp2f(ml[k][j].x - m);
+            sum += weight * ml[k][j].y;
+            acc[k][0] += weight * o[k][j].x;
+            acc[k][1] += weight * o[k][j].y;
+            acc[k][2] += weight * o[k][j].z;
+            acc[k][3] += weight * o[k][j].w;
+          }
+        }
+        run_max[k] = m;
+        run_sum[k] = sum;
+      }
     }
-    for (; s < p.splits; ++s) total += weights[row * MAX_SPLITS + s] * __ldcg(src + s * D);
-    p.out[(static_cast<size_t>(start) * p.num_heads + head0 + row) * D + d] = __float2bfloat16_rn(total * inverse[row]);
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      if (!live[k]) continue;
+      const float inv = run_sum[k] > 0.f ? 1.0f / run_sum[k] : 0.f;
+      uint2 packed;
+      packed.x = pack_bf16(acc[k][0] * inv, acc[k][1] * inv);
+      packed.y = pack_bf16(acc[k][2] * inv, acc[k][3] * inv);
+      *reinterpret_cast<uint2*>(p.out + (static_cast<size_t>(start) * p.num_heads + head0 + row[k]) * D + quad[k] * 4) = packed;
+    }
   }
 }
 
 constexpr size_t PORTIONS_SMEM = sizeof(bf16) * (BM * ROW + 4 * PBN * ROW);
 constexpr size_t SINGLE_TILES_SMEM = sizeof(bf16) * (16 * ROW + 2 * ST * BN * ROW);
-constexpr size_t SINGLE_MERGE_SMEM = sizeof(float) * (4 * 16 * D + 4 * 16 * 2 + 96);
+constexpr size_t SINGLE_MERGE_SMEM = sizeof(float) * (4 * 16 * D + 4 * 16 * 2 + 96 + 16 * D + 32);
 constexpr size_t SINGLE_SMEM = SINGLE_TILES_SMEM > SINGLE_MERGE_SMEM ? SINGLE_TILES_SMEM : SINGLE_MERGE_SMEM;
 
 }  // namespace bf16attn
 
-// Scratch the single-token path needs, in floats: partial outputs and (max, sum) pairs.
-SHRIKE_API long long shrike_attention_bf16_scratch_floats(int num_seqs, int num_heads, int splits) {
-  return static_cast<long long>(num_seqs) * num_heads * splits * (bf16attn::D + 2);
+// Scratch the single-token path needs, in floats: partial outputs and (max, sum) pairs,
+// one per cluster of splits.
+SHRIKE_API long long shrike_attention_bf16_scratch_floats(int num_seqs, int num_heads, int splits, int cluster) {
+  return static_cast<long long>(num_seqs) * num_heads * (splits / (cluster < 1 ? 1 : cluster)) * (bf16attn::D + 2);
 }
 // How many single-token CTAs the GPU holds at once; the host picks
 // splits = min(tiles, this / (seqs * kv heads * row tiles)).
@@ -568,8 +660,9 @@ SHRIKE_API int shrike_attention_bf16_resident_ctas() {
 }
 
 // has_single / has_portions: whether the batch holds rows with q_len == 1 / q_len > 1
-// (known on the host); max_q_len bounds the portions grid.  scratch holds
-// shrike_attention_bf16_scratch_floats(num_seqs, num_heads, splits) floats when has_single, and
+// (known on the host); max_q_len bounds the portions grid.  `cluster` (1, 2, 4 or 8, a
+// divisor of splits) consecutive splits add up on chip.  scratch holds
+// shrike_attention_bf16_scratch_floats(num_seqs, num_heads, splits, cluster) floats when has_single, and
 // arrivals num_seqs * num_kv_heads * ceil(group / 16) ints that are zero before the first launch
 // (every launch leaves them zero again).
 SHRIKE_API int shrike_paged_attention_bf16(const void* q, const void* k_cache, const void* v_cache,
@@ -577,13 +670,17 @@ SHRIKE_API int shrike_paged_attention_bf16(const void* q, const void* k_cache, c
                                            const int* ctx_len, int num_seqs, int num_heads, int num_kv_heads,
                                            int page_size, int num_pages, float scale, int window, void* out,
                                            int has_single, int has_portions, int max_q_len, int splits,
-                                           float* scratch, int* arrivals, cudaStream_t stream) {
+                                           int cluster, float* scratch, int* arrivals, cudaStream_t stream) {
   using namespace bf16attn;
   if (num_seqs <= 0) return SHRIKE_OK;
   if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || page_size <= 0 || max_blocks <= 0 ||
       num_seqs > 65535 || num_heads > 65535)
     return SHRIKE_BAD_ARGUMENT;
-  if (has_single && (splits < 1 || splits > MAX_SPLITS || scratch == nullptr || arrivals == nullptr)) return SHRIKE_BAD_ARGUMENT;
+  if (has_single) {
+    if (cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8) return SHRIKE_BAD_ARGUMENT;
+    if (splits < 1 || splits % cluster || splits / cluster > MAX_SPLITS || arrivals == nullptr) return SHRIKE_BAD_ARGUMENT;
+    if (splits > cluster && scratch == nullptr) return SHRIKE_BAD_ARGUMENT;
+  }
   static bool configured = false;
   if (!configured) {
     cudaError_t e1 = cudaFuncSetAttribute(portions_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(PORTIONS_SMEM));
@@ -606,15 +703,16 @@ SHRIKE_API int shrike_paged_attention_bf16(const void* q, const void* k_cache, c
   p.num_pages = num_pages;
   p.window = window;
   p.splits = has_single ? splits : 1;
+  p.cluster = has_single ? cluster : 1;
   p.skip_single = has_single ? 1 : 0;
   p.scale_log2 = scale * LOG2E;
   p.partial_out = scratch;
-  p.partial_ml = scratch ? scratch + static_cast<size_t>(num_seqs) * num_heads * p.splits * D : nullptr;
+  p.partial_ml = scratch ? scratch + static_cast<size_t>(num_seqs) * num_heads * (p.splits / p.cluster) * D : nullptr;
   p.arrivals = arrivals;
   if (has_single) {
     const int group = num_heads / num_kv_heads;
     const dim3 grid(p.splits, num_kv_heads * ((group + 15) / 16), num_seqs);
-    launch_dependent(single_token_kernel, grid, THREADS, SINGLE_SMEM, stream, p);
+    launch_dependent_clusters(single_token_kernel, grid, THREADS, SINGLE_SMEM, stream, p.cluster, p);
   }
   if (has_portions) {
     const dim3 grid((max_q_len + BM - 1) / BM, num_heads, num_seqs);

@@ -56,6 +56,27 @@ static inline cudaError_t launch_dependent(void (*kernel)(KernelArgs...), dim3 g
   return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
 }
 
+// The same for a kernel whose CTAs form clusters of `cluster_x` along x (gridDim.x a multiple of it).
+template <typename... KernelArgs, typename... Args>
+static inline cudaError_t launch_dependent_clusters(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem,
+                                                    cudaStream_t stream, unsigned cluster_x, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attributes[2];
+  attributes[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attributes[0].val.programmaticStreamSerializationAllowed = 1;
+  attributes[1].id = cudaLaunchAttributeClusterDimension;
+  attributes[1].val.clusterDim.x = cluster_x;
+  attributes[1].val.clusterDim.y = 1;
+  attributes[1].val.clusterDim.z = 1;
+  config.attrs = attributes;
+  config.numAttrs = 2;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+}
+
 // base[0] + base[stride] + ... over `partials` slices (the stack a K-split product leaves),
 // added in ascending order.  Up to 16 loads are issued together before the first addition,
 // so the sum costs one memory latency, not one per slice.

@@ -115,7 +115,7 @@ class CudaOps:
             )
             lib.shrike_paged_attention_generic.restype = _I
             lib.shrike_paged_attention_bf16.argtypes = (
-                [_P, _P, _P, _P, _I, _P, _P] + [_I] * 5 + [_F, _I, _P] + [_I] * 4 + [_P, _P, _P]
+                [_P, _P, _P, _P, _I, _P, _P] + [_I] * 5 + [_F, _I, _P] + [_I] * 5 + [_P, _P, _P]
             )
             lib.shrike_paged_attention_bf16.restype = _I
             lib.shrike_attention_bf16_resident_ctas.restype = _I
@@ -289,13 +289,13 @@ class CudaOps:
             raise KernelError("paged_attention in bfloat16 needs max_q_len, the longest entry of the batch")
         has_single = min_q_len <= 1
         has_portions = max_q_len > 1
-        splits, scratch, arrivals = 1, None, None
+        splits, cluster, scratch, arrivals = 1, 1, None, None
         if has_single:
             row_tiles = -(-(num_heads // num_kv_heads) // 16)
             tiles = max(1, -(-(max_blocks * page_size) // 64))
             resident = lib.shrike_attention_bf16_resident_ctas()
-            splits = max(1, min(tiles, 16, resident // max(1, num_seqs * num_kv_heads * row_tiles)))
-            need = num_seqs * num_heads * splits * (head_dim + 2)
+            splits, cluster = self.single_token_splits(tiles, num_seqs * num_kv_heads * row_tiles, resident)
+            need = num_seqs * num_heads * (splits // cluster) * (head_dim + 2)
             if self._scratch is None or self._scratch.numel() < need:
                 self._scratch = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=self.device)
                 self.generation += 1
@@ -320,8 +320,30 @@ class CudaOps:
         _check(lib.shrike_paged_attention_bf16(
             _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), max_blocks, _ptr(q_start), _ptr(ctx_len),
             num_seqs, num_heads, num_kv_heads, page_size, num_pages, scale, window or 0, _ptr(out),
-            int(has_single), int(has_portions), max_q_len, splits, _ptr(scratch), _ptr(arrivals), self._stream()),
+            int(has_single), int(has_portions), max_q_len, splits, cluster, _ptr(scratch), _ptr(arrivals),
+            self._stream()),
             "paged_attention_bf16")
+
+    @staticmethod
+    def single_token_splits(tiles: int, groups: int, resident: int):
+        """(splits, cluster) for single-token attention over `tiles` 64-key tiles of `groups`
+        (sequence, kv head) pairs when `resident` CTAs fit the GPU at once.
+
+        Up to eight splits may form a thread-block cluster and add up on chip.  That is the
+        quickest way while the clusters fill no more than two thirds of the GPU; a fuller grid
+        of clusters starts late (a cluster needs all its places free in one part of the chip
+        at once, while the kernel before it is still leaving), and the splits then meet in
+        global memory instead, eight partials to a round trip.  Long contexts take several
+        clusters per pair, whose partials meet in global memory too."""
+        want = max(1, min(tiles, resident // max(1, groups)))
+        cluster = 1
+        while cluster * 2 <= min(want, 8):
+            cluster *= 2
+        if cluster == 8 and groups * 8 * 3 > resident * 2:
+            return min(want, 32) // 8 * 8, 1
+        if tiles <= 4 * cluster or want < 2 * cluster:
+            return cluster, cluster
+        return min(want // cluster * cluster, 32 * cluster), cluster
 
     def silu_mul(self, gate_up, out):
         _dense(gate_up, self.dtype, "gate_up")

@@ -109,3 +109,21 @@ def test_abort_frees_pages():
     engine.step()
     engine.abort(rid)
     assert not engine.has_work and engine.block_manager.whole()
+
+
+def test_single_token_split_rule_keeps_its_bounds():
+    from shrike_b200.ops.cuda_ops import CudaOps
+
+    resident = 296
+    for tiles in (1, 2, 3, 7, 16, 17, 33, 64, 512, 4096):
+        for groups in (1, 2, 4, 8, 16, 32, 33, 64, 100, 256, 1000):
+            splits, cluster = CudaOps.single_token_splits(tiles, groups, resident)
+            assert cluster in (1, 2, 4, 8) and splits >= 1 and splits % cluster == 0
+            assert splits <= max(1, min(tiles, resident // groups)) and splits // cluster <= 32
+            if cluster == 8:   # clusters of eight only while they leave a third of the GPU free
+                assert groups * 8 * 3 <= resident * 2
+    assert CudaOps.single_token_splits(16, 4, resident) == (8, 8)       # one sequence of a 4-kv-head model
+    assert CudaOps.single_token_splits(16, 32, resident) == (8, 1)      # eight of them: too full for clusters
+    assert CudaOps.single_token_splits(16, 64, resident) == (4, 4)
+    assert CudaOps.single_token_splits(16, 256, resident) == (1, 1)
+    assert CudaOps.single_token_splits(512, 4, resident) == (72, 8)     # a long context: nine clusters

@@ -281,6 +281,22 @@ def test_single_token_attention_twice_in_a_row_leaves_its_counters_clean():
     assert int(ops._arrivals.abs().sum()) == 0
 
 
+@pytest.mark.parametrize("splits,cluster", [(1, 1), (3, 1), (2, 2), (4, 4), (8, 8), (6, 2), (16, 8), (24, 8), (12, 4)])
+@pytest.mark.parametrize("heads,kv_heads,dim,page", [(28, 4, 128, 16), (5, 1, 48, 16), (40, 2, 64, 8)])
+def test_single_token_attention_under_every_split_and_cluster_shape(splits, cluster, heads, kv_heads, dim, page, monkeypatch):
+    """Clusters add their splits up on chip, more clusters meet in global memory; the result
+    is the same attention whichever way the keys are cut, including splits with no keys."""
+    ops = cuda_ops(torch.bfloat16)
+    monkeypatch.setattr(ops, "single_token_splits", lambda tiles, groups, resident: (splits, cluster))
+    ctx_lens = [1, 64, 65, 700, 1500, 130]
+    q_lens = [1] * len(ctx_lens)
+    for seed in (5, 6):   # twice: the arrival counters are left clean
+        case = paged_case(torch.bfloat16, heads, kv_heads, dim, page, ctx_lens, q_lens, seed=seed)
+        got, want = run_attention(ops, case, heads, kv_heads, dim, None, q_lens, ctx_lens)
+        close(got, want, 2e-2, 0, f"splits {splits} cluster {cluster}")
+    assert int(ops._arrivals.abs().sum()) == 0
+
+
 def test_widths_beyond_one_block_are_refused_not_miscomputed():
     from shrike_b200.ops.cuda_ops import KernelError
 
