@@ -66,27 +66,45 @@ template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16*
 
 // `delta` may be a stack of `partials` arrays (the slices of a K-split matrix product),
 // `partial_stride` elements apart; they are added in ascending order.
-// MAX_THREADS 512 leaves registers to hold several slices' loads in flight; 1024 (wide rows) adds
-// slice by slice.
-template <typename TD, typename TO, bool HAS_DELTA, bool GATHER, int VEC, int MAX_THREADS>
-__global__ void __launch_bounds__(MAX_THREADS, 1024 / MAX_THREADS) add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
+// PER_THREAD 1 (rows of up to 1024 groups): a thread holds one group, reads the norm weight
+// before the wait and has the residual and up to eight slices in flight together, so the
+// row costs one memory round trip.  PER_THREAD 8 (wider rows) adds slice by slice.
+template <typename TD, typename TO, bool HAS_DELTA, bool GATHER, int VEC, int PER_THREAD>
+__global__ void __launch_bounds__(1024, 1) add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
                                    const int* __restrict__ rows, const float* __restrict__ weight,
                                    float eps, TO* __restrict__ out, int width, int partials,
                                    long long partial_stride) {
   __shared__ float scratch[33];
+  constexpr int AHEAD = PER_THREAD == 1 ? 7 : 1;   // the first slice and seven more: a stack of eight in one go
   let_dependents_start();
+  const int groups = width / VEC;
+  constexpr bool GAIN_AHEAD = PER_THREAD == 1;   // registers allow it only for the narrow form
+  float gain[GAIN_AHEAD ? PER_THREAD : 1][VEC];   // the norm weight: no kernel writes it, so it is read ahead of the wait
+#pragma unroll
+  for (int it = 0; it < (GAIN_AHEAD ? PER_THREAD : 0); ++it) {
+    const int g = threadIdx.x + it * blockDim.x;
+    if (g < groups) {
+      if (VEC == 4) {
+        float w[4];
+        load4<float>(weight + g * 4, w);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) gain[it][i % VEC] = w[i];
+      } else {
+        gain[it][0] = weight[g];
+      }
+    }
+  }
   wait_for_previous();
   const int out_row = blockIdx.x;
   const int row = GATHER ? rows[out_row] : out_row;
   float* x = resid + static_cast<size_t>(row) * width;
   const TD* d = HAS_DELTA ? delta + static_cast<size_t>(row) * width : nullptr;
   TO* y = out + static_cast<size_t>(out_row) * width;
-  const int groups = width / VEC;
 
-  float held[NORM_MAX_PER_THREAD][VEC];
+  float held[PER_THREAD][VEC];
   float sum_sq = 0.f;
 #pragma unroll
-  for (int it = 0; it < NORM_MAX_PER_THREAD; ++it) {
+  for (int it = 0; it < PER_THREAD; ++it) {
     const int g = threadIdx.x + it * blockDim.x;
     if (g < groups) {
       if (VEC == 4) {
@@ -95,7 +113,6 @@ __global__ void __launch_bounds__(MAX_THREADS, 1024 / MAX_THREADS) add_rmsnorm_k
         if (HAS_DELTA) {
           load4<TD>(d + g * 4, dv);
           if (partials > 1) {   // AHEAD slices at a time: their loads are issued before the first addition
-            constexpr int AHEAD = MAX_THREADS <= 512 ? 2 : 1;
             for (int first = 1; first < partials; first += AHEAD) {
               float more[AHEAD][4];
 #pragma unroll
@@ -134,17 +151,23 @@ __global__ void __launch_bounds__(MAX_THREADS, 1024 / MAX_THREADS) add_rmsnorm_k
   const float total = block_sum(sum_sq, scratch);
   const float inv = 1.0f / sqrtf(total / static_cast<float>(width) + eps);
 #pragma unroll
-  for (int it = 0; it < NORM_MAX_PER_THREAD; ++it) {
+  for (int it = 0; it < PER_THREAD; ++it) {
     const int g = threadIdx.x + it * blockDim.x;
     if (g < groups) {
       if (VEC == 4) {
         float w[4], r[4];
-        load4<float>(weight + g * 4, w);
+        if (GAIN_AHEAD) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) w[i] = gain[GAIN_AHEAD ? it : 0][i % VEC];
+        } else {
+          load4<float>(weight + g * 4, w);
+        }
 #pragma unroll
         for (int i = 0; i < 4; ++i) r[i] = __fmul_rn(__fmul_rn(held[it][i % VEC], inv), w[i]);
         store4<TO>(y + g * 4, r);
       } else {
-        y[g] = from_float<TO>(__fmul_rn(__fmul_rn(held[it][0], inv), weight[g]));
+        const float w = GAIN_AHEAD ? gain[GAIN_AHEAD ? it : 0][0] : weight[g];
+        y[g] = from_float<TO>(__fmul_rn(__fmul_rn(held[it][0], inv), w));
       }
     }
   }
@@ -156,15 +179,15 @@ static int launch_add_rmsnorm(float* resid, const void* delta, const int* rows, 
                               cudaStream_t stream) {
   const bool vec = width % 4 == 0;
   const int groups = vec ? width / 4 : width;
-  int threads = 128;
-  while (threads < 1024 && threads * 2 <= ((groups + 31) / 32) * 32) threads *= 2;
+  const bool narrow = groups <= 1024;
+  const int threads = narrow ? (groups + 31) / 32 * 32 : 1024;
   if (static_cast<long long>(threads) * NORM_MAX_PER_THREAD < groups) return SHRIKE_BAD_ARGUMENT;
 #define SHRIKE_NORM_LAUNCH_T(G, V, T)                                                              \
   launch_dependent(add_rmsnorm_kernel<TD, TO, HAS_DELTA, G, V, T>, n, threads, 0, stream, resid,   \
                    static_cast<const TD*>(delta), rows, weight, eps, static_cast<TO*>(out), width, partials,  \
                    partial_stride)
 #define SHRIKE_NORM_LAUNCH(G, V)                                                                   \
-  do { if (threads <= 512) SHRIKE_NORM_LAUNCH_T(G, V, 512); else SHRIKE_NORM_LAUNCH_T(G, V, 1024); } while (0)
+  do { if (narrow) SHRIKE_NORM_LAUNCH_T(G, V, 1); else SHRIKE_NORM_LAUNCH_T(G, V, NORM_MAX_PER_THREAD); } while (0)
   if (rows) { if (vec) SHRIKE_NORM_LAUNCH(true, 4); else SHRIKE_NORM_LAUNCH(true, 1); }
   else { if (vec) SHRIKE_NORM_LAUNCH(false, 4); else SHRIKE_NORM_LAUNCH(false, 1); }
 #undef SHRIKE_NORM_LAUNCH
