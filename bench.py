@@ -502,6 +502,81 @@ def run_case(args) -> dict:
     return result
 
 
+def run_timeline(args) -> dict:
+    """Where a captured decode step spends its time, kernel by kernel: start and end of every
+    kernel of one step from CUPTI activity records (torch.profiler), on a model of the
+    benchmark's widths with few layers.  Kernels overlap (each starts while the one before it
+    runs), so the figure per kernel is `end - end of the kernel before it`: what the step
+    would save if that kernel vanished from the chain.  Medians over the layers."""
+    import numpy as np
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    import shrike_b200.models  # noqa: F401
+    from shrike_b200.config import parse_config
+    from shrike_b200.engine.batch import StepEntry
+    from shrike_b200.engine.llm_engine import LLMEngine
+    from shrike_b200.weights.random_init import random_tensors
+
+    torch.cuda.set_device(0)
+    raw = dict(MODEL_7B)
+    raw["num_hidden_layers"] = layers = args.layers or 6
+    config = parse_config(raw)
+    tensors = random_tensors(config, seed=0, device=torch.device("cuda:0"), dtype=torch.bfloat16)
+    pages = args.batch * (-(-(CONTEXT + 64) // BLOCK_SIZE)) + 64
+    engine = LLMEngine(None, block_size=BLOCK_SIZE, num_blocks=pages, max_tokens_per_step=4096, max_running=64,
+                       dtype="bfloat16", config=config, tensors=tensors)
+    del tensors
+    runner = engine.runner
+    rng = np.random.default_rng(0)
+    caches = []
+    for _ in range(args.batch):
+        cache = runner.cache.open()
+        ids = rng.integers(0, raw["vocab_size"], CONTEXT - 1).tolist()
+        runner.cache.append(cache, 0, len(ids))
+        runner.step([StepEntry(cache, ids, 0, [])])
+        caches.append(cache)
+    fed = [CONTEXT - 1]
+
+    def one_step():
+        entries = []
+        for cache in caches:
+            runner.cache.append(cache, fed[0], 1)
+            entries.append(StepEntry(cache, [5], fed[0], [0], (0.0, 1.0, 0)))
+        _logits, drawn = runner.step(entries, sample=True)
+        fed[0] += 1
+        return drawn.tolist()
+
+    for _ in range(6):
+        one_step()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(3):
+            one_step()
+        torch.cuda.synchronize()
+    kernels = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA and "Memcpy" not in e.name),
+                     key=lambda e: e.time_range.start)
+    per_step = len(kernels) // 3
+    step = kernels[-per_step:]
+    rows, previous_end = [], step[0].time_range.start
+    for event in step:
+        rows.append((event.name.split("(")[0].split("<")[0].split("::")[-1], event.time_range.end - previous_end))
+        previous_end = event.time_range.end
+    first = next(i for i, (name, _) in enumerate(rows) if "add_rmsnorm" in name)
+    per_layer = 9   # norm, qkv, rotary, attention, o, norm, gate_up, SiLU product, down
+    labels = ["norm (mixer)", "qkv product", "rotary + cache store", "attention", "o product", "norm (feed-forward)",
+              "gate_up product", "SiLU product", "down product"]
+    table = []
+    for position in range(per_layer):
+        samples = [rows[first + layer * per_layer + position] for layer in range(1, layers)]   # the first layer follows the embedding
+        table.append({"kernel": labels[position], "name": samples[0][0], "in_situ_us": round(float(np.median([t for _, t in samples])), 2)})
+    layer_us = round(sum(row["in_situ_us"] for row in table), 2)
+    rest = rows[:first] + rows[first + layers * per_layer:]
+    return {"case": "timeline", "batch": args.batch, "layers": layers, "layer_us": layer_us, "per_layer": table,
+            "outside_layers": [{"name": name, "in_situ_us": round(t, 2)} for name, t in rest],
+            "step_us": round(step[-1].time_range.end - step[0].time_range.start, 1)}
+
+
 def run_reference(args) -> dict:
     reference = ROOT / "baseline" / "_ref"
     if not (reference / "shrike").is_dir():
@@ -524,12 +599,16 @@ def main():
     parser.add_argument("--num-blocks", type=int, default=0, help="cache pages for --workload mixed (few pages force preemption)")
     parser.add_argument("--case", default=None,
                         help="run a small single-kernel workload instead (for profiling): gemm_gate_up, gemm_down, "
-                             "gemm_qkv, attention_single, attention_portions; --batch gives tokens / sequences")
+                             "gemm_qkv, attention_single, attention_portions; --batch gives tokens / sequences.  timeline: per-kernel "
+                             "times inside one captured decode step (--layers, default 6)")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU: this engine runs on a single B200 (asked for {args.gpus})")
         sys.exit(2)
     args.warmup = max(3, args.warmup)
+    if args.case == "timeline":
+        print(json.dumps(run_timeline(args)))
+        return
     if args.case:
         print(json.dumps(run_case(args)))
         return

@@ -95,22 +95,25 @@ struct Params {
 // elements; -1 for keys outside [lo, hi] or on a page the sequence does not hold.  One
 // table lookup and one division per key, done by the first BN threads.
 // `leave_out` (or -1): a key whose row is marked -2, which copy_tile does not touch at all.
+// In two steps, so that a caller can issue the table lookup one round before it needs the
+// row: the page of key j (-1: none, -2: leave the row untouched), then the row's offset.
+__device__ __forceinline__ int lookup_page(const Params& p, const int* table, int j, int lo, int hi, int leave_out) {
+  if (j == leave_out) return -2;
+  if (j < lo || j > hi) return -1;
+  const int block = j / p.page_size;
+  return block < p.max_blocks ? table[block] : -1;
+}
+__device__ __forceinline__ long long row_of(const Params& p, int kv_head, int j, int page) {
+  if (page == -2) return -2;
+  if (page < 0 || page >= p.num_pages) return -1;
+  return (static_cast<long long>(page) * p.page_size + j % p.page_size) * p.num_kv_heads * D + static_cast<long long>(kv_head) * D;
+}
 template <int KEYS>
 __device__ __forceinline__ void locate_tile(long long* rows, const Params& p, const int* table, int kv_head,
                                             int tile_base, int lo, int hi, int leave_out = -1) {
   if (threadIdx.x < KEYS) {
     const int j = tile_base + threadIdx.x;
-    long long offset = -1;
-    if (j == leave_out) {
-      offset = -2;
-    } else if (j >= lo && j <= hi) {
-      const int block = j / p.page_size;
-      const int page = block < p.max_blocks ? table[block] : -1;
-      if (page >= 0 && page < p.num_pages)
-        offset = (static_cast<long long>(page) * p.page_size + (j - block * p.page_size)) * p.num_kv_heads * D +
-                 static_cast<long long>(kv_head) * D;
-    }
-    rows[threadIdx.x] = offset;
+    rows[threadIdx.x] = row_of(p, kv_head, j, lookup_page(p, table, j, lo, hi, leave_out));
   }
 }
 
@@ -407,6 +410,11 @@ __global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
     __syncthreads();
     int first[2] = {first_key, first_key}, last[2] = {last_key, last_key};
     unsigned q_frag[Q_IN_REGS ? KSTEPS : 1][4];
+    // The table lookup for a tile is issued one round before its rows are stored, which is
+    // one more round before they are copied: no round waits for a lookup of its own.
+    int pending_page = -1;
+    if (my_lo + ST <= my_hi && threadIdx.x < BN)
+      pending_page = lookup_page(p, table, (my_lo + ST) * BN + threadIdx.x, first_key, last_key, -1);
     for (int tile = my_lo; tile <= my_hi; ++tile) {
       const int buffer = (tile - my_lo) % ST;
       const int ahead = tile + ST - 1;
@@ -415,8 +423,12 @@ __global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
         copy_tile<BN>(k_tiles + into * BN * ROW, v_tiles + into * BN * ROW, p, tile_rows[(ahead - my_lo) % (ST + 1)]);
       }
       cp_async_commit();
-      if (ahead + 1 <= my_hi)   // read in the next round, after this round's closing barrier
-        locate_tile<BN>(tile_rows[(ahead + 1 - my_lo) % (ST + 1)], p, table, kv_head, (ahead + 1) * BN, first_key, last_key);
+      if (threadIdx.x < BN) {
+        if (ahead + 1 <= my_hi)   // read in the next round, after this round's closing barrier
+          tile_rows[(ahead + 1 - my_lo) % (ST + 1)][threadIdx.x] = row_of(p, kv_head, (ahead + 1) * BN + threadIdx.x, pending_page);
+        if (ahead + 2 <= my_hi)
+          pending_page = lookup_page(p, table, (ahead + 2) * BN + threadIdx.x, first_key, last_key, -1);
+      }
       cp_async_wait<ST - 1>();
       __syncthreads();
       if (Q_IN_REGS && tile == my_lo) {
