@@ -454,20 +454,19 @@ __global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
   }
   // combine the four warps' states through shared memory (the tiles are no longer needed)
   __syncthreads();
-  float* warp_o = reinterpret_cast<float*>(smem_raw);         // [4][16][D]
-  float* warp_ml = warp_o + 4 * 16 * D;                       // [4][16][2]
+  constexpr int WO = D + 8;   // padded row: the eight rows a warp stores at once fall into different banks
+  float* warp_o = reinterpret_cast<float*>(smem_raw);         // [4][16][WO]
+  float* warp_ml = warp_o + 4 * 16 * WO;                      // [4][16][2]
   float* row_weight = warp_ml + 4 * 16 * 2;                   // [16][4] weight of each warp, then [16] max, [16] sum
   float* cta_o = row_weight + 96;                             // [16][D] this CTA's result, read by its cluster
   float* cta_ml = cta_o + 16 * D;                             // [16][2]
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     const int row = (lane >> 2) + 8 * r;
+    if (row >= rows_here) continue;   // rows beyond the group's heads are never read
 #pragma unroll
-    for (int j = 0; j < DTILES; ++j) {
-      float* dst = warp_o + (warp * 16 + row) * D + j * 8 + (lane & 3) * 2;
-      dst[0] = o[j][2 * r];
-      dst[1] = o[j][2 * r + 1];
-    }
+    for (int j = 0; j < DTILES; ++j)
+      *reinterpret_cast<float2*>(warp_o + (warp * 16 + row) * WO + j * 8 + (lane & 3) * 2) = make_float2(o[j][2 * r], o[j][2 * r + 1]);
     if ((lane & 3) == 0) {
       warp_ml[(warp * 16 + row) * 2] = row_max[r];
       warp_ml[(warp * 16 + row) * 2 + 1] = row_sum[r];
@@ -497,7 +496,7 @@ __global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
     const int row = idx / D, d = idx - row * D;
     float total = 0.f;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) total += row_weight[row * 4 + w] * warp_o[(w * 16 + row) * D + d];
+    for (int w = 0; w < 4; ++w) total += row_weight[row * 4 + w] * warp_o[(w * 16 + row) * WO + d];
     if (p.cluster > 1) {
       cta_o[idx] = total;
       if (d == 0) {
@@ -653,7 +652,7 @@ __global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
 
 constexpr size_t PORTIONS_SMEM = sizeof(bf16) * (BM * ROW + 4 * PBN * ROW);
 constexpr size_t SINGLE_TILES_SMEM = sizeof(bf16) * (16 * ROW + 2 * ST * BN * ROW);
-constexpr size_t SINGLE_MERGE_SMEM = sizeof(float) * (4 * 16 * D + 4 * 16 * 2 + 96 + 16 * D + 32);
+constexpr size_t SINGLE_MERGE_SMEM = sizeof(float) * (4 * 16 * (D + 8) + 4 * 16 * 2 + 96 + 16 * D + 32);
 constexpr size_t SINGLE_SMEM = SINGLE_TILES_SMEM > SINGLE_MERGE_SMEM ? SINGLE_TILES_SMEM : SINGLE_MERGE_SMEM;
 
 }  // namespace bf16attn
