@@ -81,6 +81,7 @@ static inline cudaError_t launch_dependent_clusters(void (*kernel)(KernelArgs...
 // added in ascending order.  Up to 16 loads are issued together before the first addition,
 // so the sum costs one memory latency, not one per slice.
 __device__ __forceinline__ float sum_partials(const float* base, long long stride, int partials) {
+  if (partials == 1) return base[0];
   float held[16];
 #pragma unroll
   for (int i = 0; i < 16; ++i) held[i] = (i == 0 || i < partials) ? base[i * stride] : 0.f;

@@ -179,8 +179,14 @@ static int launch_add_rmsnorm(float* resid, const void* delta, const int* rows, 
                               cudaStream_t stream) {
   const bool vec = width % 4 == 0;
   const int groups = vec ? width / 4 : width;
-  const bool narrow = groups <= 1024;
-  const int threads = narrow ? (groups + 31) / 32 * 32 : 1024;
+  // Few rows (decode): latency counts, one group per thread.  Many rows (prompts): bandwidth
+  // counts, small blocks whose threads each keep up to eight groups in flight.
+  const bool narrow = groups <= 1024 && n <= 256;
+  int threads = (groups + 31) / 32 * 32;
+  if (!narrow) {
+    threads = ((groups + NORM_MAX_PER_THREAD - 1) / NORM_MAX_PER_THREAD + 31) / 32 * 32;
+    threads = threads < 128 ? 128 : (threads > 1024 ? 1024 : threads);
+  }
   if (static_cast<long long>(threads) * NORM_MAX_PER_THREAD < groups) return SHRIKE_BAD_ARGUMENT;
 #define SHRIKE_NORM_LAUNCH_T(G, V, T)                                                              \
   launch_dependent(add_rmsnorm_kernel<TD, TO, HAS_DELTA, G, V, T>, n, threads, 0, stream, resid,   \
@@ -226,32 +232,49 @@ SHRIKE_API int shrike_add_rmsnorm(float* resid, const void* delta, int delta_dty
 // out[r, c] = silu(gate_up[r, c]) * gate_up[r, inter + c], silu(g) = g / (1 + exp(-g)),
 // in float32 with one rounding.  VEC elements per thread and access (16 bytes when the
 // row length allows, else one).
+// bfloat16 results keep 8 bits of mantissa, so that path may use the hardware exponential and
+// reciprocal (relative error about 2^-22); the float32 path uses the exact functions.
+template <typename T> __device__ __forceinline__ float silu_times(float g, float u);
+template <> __device__ __forceinline__ float silu_times<float>(float g, float u) {
+  return __fmul_rn(g / (1.0f + expf(-g)), u);
+}
+template <> __device__ __forceinline__ float silu_times<__nv_bfloat16>(float g, float u) {
+  return __fmul_rn(__fdividef(g, 1.0f + __expf(-g)), u);
+}
+
 template <typename T, int VEC>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
   let_dependents_start();
   wait_for_previous();
   const int groups_per_row = inter / VEC;
-  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total / VEC;
-       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    const size_t row = i / groups_per_row;
-    const int col = static_cast<int>(i - row * groups_per_row) * VEC;
-    const T* g_ptr = gate_up + row * 2 * inter + col;
-    const T* u_ptr = g_ptr + inter;
-    T* o_ptr = out + row * inter + col;
-    if (VEC == 1) {
-      const float g = to_float(*g_ptr), u = to_float(*u_ptr);
-      *o_ptr = from_float<T>(__fmul_rn(g / (1.0f + expf(-g)), u));
-    } else {
-      struct alignas(16) Pack { T v[VEC]; };
-      const Pack g = *reinterpret_cast<const Pack*>(g_ptr);
-      const Pack u = *reinterpret_cast<const Pack*>(u_ptr);
+  const size_t groups = total / VEC;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  struct alignas(sizeof(T) * VEC) Pack { T v[VEC]; };
+  // two groups per round, so that four loads are in flight before the arithmetic starts
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < groups; i += 2 * stride) {
+    Pack g[2], u[2];
+    size_t at[2];
+    bool live[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const size_t index = i + k * stride;
+      live[k] = index < groups;
+      const size_t row = live[k] ? index / groups_per_row : 0;
+      const int col = live[k] ? static_cast<int>(index - row * groups_per_row) * VEC : 0;
+      at[k] = row * inter + col;
+      const T* g_ptr = gate_up + row * 2 * inter + col;
+      if (live[k]) {
+        g[k] = *reinterpret_cast<const Pack*>(g_ptr);
+        u[k] = *reinterpret_cast<const Pack*>(g_ptr + inter);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      if (!live[k]) continue;
       Pack r;
 #pragma unroll
-      for (int j = 0; j < VEC; ++j) {
-        const float gv = to_float(g.v[j]);
-        r.v[j] = from_float<T>(__fmul_rn(gv / (1.0f + expf(-gv)), to_float(u.v[j])));
-      }
-      *reinterpret_cast<Pack*>(o_ptr) = r;
+      for (int j = 0; j < VEC; ++j) r.v[j] = from_float<T>(silu_times<T>(to_float(g[k].v[j]), to_float(u[k].v[j])));
+      *reinterpret_cast<Pack*>(out + at[k]) = r;
     }
   }
 }
@@ -263,7 +286,7 @@ static void launch_silu_mul(const void* gate_up, void* out, int n, int inter, cu
   const size_t total = static_cast<size_t>(n) * inter;
   const size_t work = vec ? total / WIDE : total;
   const int threads = 256;
-  const int blocks = static_cast<int>(min(static_cast<size_t>(148 * 16), (work + threads - 1) / threads));
+  const int blocks = static_cast<int>(min(static_cast<size_t>(148 * 8), (work + 2 * threads - 1) / (2 * threads)));
   if (vec)
     launch_dependent(silu_mul_kernel<T, WIDE>, blocks, threads, 0, stream, static_cast<const T*>(gate_up),
                      static_cast<T*>(out), inter, total);
@@ -294,7 +317,7 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const float*
                                      T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
                                      const int* __restrict__ slots, T* __restrict__ k_out, T* __restrict__ v_out,
                                      int num_heads, int num_kv_heads, int head_dim, long long num_slots,
-                                     int partials, long long partial_stride) {
+                                     int partials, long long partial_stride, int wide) {
   let_dependents_start();
   wait_for_previous();
   const int token = blockIdx.x;
@@ -308,6 +331,69 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const float*
   }
   const float pos = static_cast<float>(positions[token]);
   const int pairs = (num_heads + 2 * num_kv_heads) * half;
+  // A block that walks all heads of its token computes the token's angles once, not once per head.
+  __shared__ float2 angle[128];
+  const bool shared_angles = gridDim.y == 1 && inv_freq != nullptr && half <= 128;
+  if (shared_angles) {
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+      float s, c;
+      sincosf(__fmul_rn(pos, inv_freq[j]), &s, &c);
+      angle[j] = make_float2(s, c);
+    }
+    __syncthreads();
+  }
+  if (wide && shared_angles) {
+    // whole rows (prompts): four pairs per thread with 16-byte loads and packed stores
+    for (int idx = threadIdx.x; idx < pairs / 4; idx += blockDim.x) {
+      const int head = idx / (half / 4), j = (idx - head * (half / 4)) * 4;
+      const bool is_q = head < num_heads, is_k = !is_q && head < num_heads + num_kv_heads;
+      const int lo = head * head_dim + j, hi = lo + half;
+      float a[4], b[4], ra[4], rb[4];
+      load4<float>(row + lo, a);
+      load4<float>(row + hi, b);
+      if (bias != nullptr) {
+        float ba[4], bb[4];
+        load4<float>(bias + lo, ba);
+        load4<float>(bias + hi, bb);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          a[e] = __fadd_rn(a[e], ba[e]);
+          b[e] = __fadd_rn(b[e], bb[e]);
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        ra[e] = a[e];
+        rb[e] = b[e];
+        if (is_q || is_k) {
+          const float s = angle[j + e].x, c = angle[j + e].y;
+          ra[e] = __fsub_rn(__fmul_rn(a[e], c), __fmul_rn(b[e], s));
+          rb[e] = __fadd_rn(__fmul_rn(b[e], c), __fmul_rn(a[e], s));
+        }
+      }
+      if (is_q) {
+        T* dst = q_out + static_cast<size_t>(token) * q_width;
+        store4<T>(dst + lo, ra);
+        store4<T>(dst + hi, rb);
+      } else {
+        const int base = is_k ? q_width : q_width + kv_width;
+        const int clo = lo - base, chi = hi - base;
+        T* cache = is_k ? k_cache : v_cache;
+        T* extra = is_k ? k_out : v_out;
+        if (slot >= 0) {
+          T* dst = cache + static_cast<size_t>(slot) * kv_width;
+          store4<T>(dst + clo, ra);
+          store4<T>(dst + chi, rb);
+        }
+        if (extra != nullptr) {
+          T* dst = extra + static_cast<size_t>(token) * kv_width;
+          store4<T>(dst + clo, ra);
+          store4<T>(dst + chi, rb);
+        }
+      }
+    }
+    return;
+  }
   for (int idx = blockIdx.y * blockDim.x + threadIdx.x; idx < pairs; idx += gridDim.y * blockDim.x) {
     const int head = idx / half, j = idx - head * half;
     const bool is_q = head < num_heads, is_k = !is_q && head < num_heads + num_kv_heads;
@@ -321,7 +407,12 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const float*
     float ra = a, rb = b;
     if (inv_freq != nullptr && (is_q || is_k)) {
       float s, c;
-      sincosf(__fmul_rn(pos, inv_freq[j]), &s, &c);
+      if (shared_angles) {
+        s = angle[j].x;
+        c = angle[j].y;
+      } else {
+        sincosf(__fmul_rn(pos, inv_freq[j]), &s, &c);
+      }
       ra = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
       rb = __fadd_rn(__fmul_rn(b, c), __fmul_rn(a, s));
     }
@@ -363,11 +454,17 @@ SHRIKE_API int shrike_rope_kv_write(const float* qkv, const float* bias, const i
   const int slices = n >= 256 ? 1 : (pairs + threads - 1) / threads;
   if (slices > 65535) return SHRIKE_BAD_ARGUMENT;
   const dim3 grid(n, slices);
+  // whole rows with 16-byte accesses: one slice, a single array, pairs in fours, every pointer aligned
+  const uintptr_t addresses = reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(bias) |
+                              reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_cache) |
+                              reinterpret_cast<uintptr_t>(v_cache) | reinterpret_cast<uintptr_t>(k_out) |
+                              reinterpret_cast<uintptr_t>(v_out);
+  const int wide = slices == 1 && partials == 1 && head_dim % 8 == 0 && addresses % 16 == 0 ? 1 : 0;
 #define SHRIKE_ROPE_CASE(T)                                                                         \
   launch_dependent(rope_kv_write_kernel<T>, grid, threads, 0, stream,                               \
       qkv, bias, positions, inv_freq, static_cast<T*>(q_out), static_cast<T*>(k_cache),             \
       static_cast<T*>(v_cache), slots, static_cast<T*>(k_out), static_cast<T*>(v_out), num_heads,   \
-      num_kv_heads, head_dim, num_slots, partials, partial_stride)
+      num_kv_heads, head_dim, num_slots, partials, partial_stride, wide)
   if (dtype == SHRIKE_F32) SHRIKE_ROPE_CASE(float);
   else if (dtype == SHRIKE_BF16) SHRIKE_ROPE_CASE(__nv_bfloat16);
   else return SHRIKE_BAD_ARGUMENT;

@@ -63,15 +63,16 @@ def test_add_rmsnorm(dtype, width):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_silu_mul(dtype):
+@pytest.mark.parametrize("n,inter", [(5, 176 + 3), (3, 176), (300, 320), (1, 18944)])   # odd rows: scalar path
+def test_silu_mul(dtype, n, inter):
     ops = cuda_ops(dtype)
-    n, inter = 5, 176 + 3
     gate_up = rnd(n, 2 * inter, dtype=dtype, scale=3.0)
     out = torch.empty(n, inter, dtype=dtype, device=DEV)
     ops.silu_mul(gate_up, out)
     g, u = gate_up[:, :inter].double(), gate_up[:, inter:].double()
     want = g * torch.sigmoid(g) * u
-    close(out, want, 1e-6 if dtype == torch.float32 else 0, 1e-6 if dtype == torch.float32 else 2 ** -8)
+    # bfloat16: one rounding to 8 bits (2^-8) of a float32 value that is itself good to about 2^-20
+    close(out, want, 1e-6 if dtype == torch.float32 else 0, 1e-6 if dtype == torch.float32 else 2 ** -8 + 2 ** -20)
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 7, 5), (33, 65, 17), (64, 64, 16), (70, 331, 240), (130, 96, 1000), (3, 500, 3)])
@@ -190,6 +191,41 @@ def test_rope_kv_write(dtype, heads, kv_heads, dim):
     ops.kv_write(k_out, v_out, keys2, values2, slots)
     assert torch.equal(keys2.view(-1, kv_heads * dim)[slots.long()], k_out)
     assert torch.equal(values2.view(-1, kv_heads * dim)[slots.long()], v_out)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,dim,with_bias", [(5, 1, 48, True), (28, 4, 128, True), (3, 3, 16, False), (4, 2, 256, True)])
+def test_rope_kv_write_whole_rows(dtype, heads, kv_heads, dim, with_bias):
+    """Many tokens take the form with one block per token, a shared angle table and 16-byte
+    accesses; its result is the one the few-token form gives, token by token, bit for bit."""
+    ops = cuda_ops(dtype)
+    n, page = 300, 16
+    pages = -(-n // page) + 2
+    width = (heads + 2 * kv_heads) * dim
+    qkv, bias = rnd(n, width, seed=5), (rnd(width, seed=6) if with_bias else None)
+    g = torch.Generator().manual_seed(7)
+    positions = torch.randint(0, 5000, (n,), generator=g, dtype=torch.int32).to(DEV)
+    slots = torch.randperm(pages * page, generator=g)[:n].to(torch.int32).to(DEV)
+    inv_freq = (1.0 / (1e4 ** (torch.arange(0, dim, 2).float() / dim))).to(DEV)
+
+    def run(rows):
+        keys = torch.full((pages, page, kv_heads, dim), 9.0, dtype=dtype, device=DEV)
+        values = torch.full_like(keys, 9.0)
+        q = torch.empty(n, heads * dim, dtype=dtype, device=DEV)
+        for lo in range(0, n, rows):
+            hi = min(n, lo + rows)
+            ops.rope_kv_write(qkv[lo:hi].contiguous(), bias, positions[lo:hi].contiguous(), inv_freq, q[lo:hi], keys, values,
+                              slots[lo:hi].contiguous(), heads, kv_heads, dim)
+        return q, keys, values
+
+    whole, few = run(n), run(7)
+    for got, want, what in zip(whole, few, ("q", "keys", "values")):
+        assert torch.equal(got, want), what
+    x = qkv.double().cpu() + (bias.double().cpu() if with_bias else 0)
+    angle = positions.float().cpu()[:, None] * inv_freq.cpu()[None, :]
+    cos32, sin32 = torch.cat([angle.cos(), angle.cos()], -1).double(), torch.cat([angle.sin(), angle.sin()], -1).double()
+    want_q = pm.apply_rope(x[:, : heads * dim].view(n, heads, dim), cos32, sin32)
+    close(whole[0].view(n, heads, dim), want_q, 1e-4 if dtype == torch.float32 else 4e-2, 0 if dtype == torch.float32 else 2 ** -8, "q")
 
 
 def paged_case(dtype, heads, kv_heads, dim, page, ctx_lens, q_lens, seed=0):
