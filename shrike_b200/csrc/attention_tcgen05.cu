@@ -82,8 +82,11 @@ __global__ void __launch_bounds__(THREADS, 2)
 portions_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const Args args) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  const int seq = blockIdx.z, head = blockIdx.y;
-  const int tile_start = (gridDim.x - 1 - blockIdx.x) * BM;    // long tiles are scheduled first
+  // CTAs are handed out x first: the longest query tiles of every head and sequence go first
+  // (a causal tile's work grows with its position), and the heads of a group, which read the
+  // same keys and values, run side by side.
+  const int head = blockIdx.x, seq = blockIdx.y;
+  const int tile_start = (gridDim.z - 1 - blockIdx.z) * BM;
   const int start = args.q_start[seq];                          // metadata: written before the step's kernels
   const int q_len = args.q_start[seq + 1] - start;
   if (tile_start >= q_len || (q_len == 1 && args.skip_single)) {
@@ -380,7 +383,7 @@ SHRIKE_API int shrike_paged_attention_tc_portions(const void* q, const void* k_c
   using namespace tcattn;
   if (num_seqs <= 0 || num_tokens <= 0) return SHRIKE_OK;
   if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || max_blocks <= 0 || max_q_len < 1 ||
-      num_seqs > 65535 || num_heads > 65535 || !(page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64))
+      num_seqs > 65535 || (max_q_len + BM - 1) / BM > 65535 || !(page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64))
     return SHRIKE_BAD_ARGUMENT;
   static bool configured = false;
   if (!configured) {
@@ -409,7 +412,7 @@ SHRIKE_API int shrike_paged_attention_tc_portions(const void* q, const void* k_c
   args.window = window;
   args.skip_single = skip_single;
   args.scale_log2 = scale * LOG2E;
-  const dim3 grid((max_q_len + BM - 1) / BM, num_heads, num_seqs);
+  const dim3 grid(num_heads, num_seqs, (max_q_len + BM - 1) / BM);
   const cudaError_t err = launch_dependent(portions_tc_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, map_q, map_k, map_v, args);
   if (err != cudaSuccess) return static_cast<int>(err);
   return shrike_launch_status();
