@@ -207,24 +207,30 @@ def run_ours(args) -> dict:
         fed = CONTEXT - 1
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
-        def one_step(tokens, fed):
+        def stage(fed, tokens=None):
+            """The host half of the step that feeds position `fed`; without tokens, ahead of them."""
             entries = []
-            for cache, token in zip(caches, tokens):
+            for index, cache in enumerate(caches):
                 runner.cache.append(cache, fed, 1)
-                entries.append(StepEntry(cache, [token], fed, [0], (0.0, 1.0, 0)))
-            _logits, drawn = runner.step(entries, sample=True)
-            return drawn.tolist()
+                entries.append(StepEntry(cache, [tokens[index] if tokens else 0], fed, [0], (0.0, 1.0, 0)))
+            return runner.prepare(entries, sample=True, ids_missing=tokens is None)
 
-        for _ in range(warmup):
-            tokens = one_step(tokens, fed)
-            fed += 1
+        def run(count, prepared, fed):
+            """`count` steps the way the engine runs them: while the device works on a step, the
+            host stages the next one; the drawn tokens come back and complete it."""
+            for _ in range(count):
+                _logits, drawn = runner.launch(prepared)
+                fed += 1
+                prepared = stage(fed)
+                runner.fill_ids(prepared, drawn.tolist())
+            return prepared, fed
+
+        prepared, fed = run(warmup, stage(fed, tokens), fed)
         torch.cuda.synchronize()
         launches_before = ops.launches
         t0 = time.perf_counter()
         start.record()
-        for _ in range(steps):
-            tokens = one_step(tokens, fed)
-            fed += 1
+        prepared, fed = run(steps, prepared, fed)
         stop.record()
         torch.cuda.synchronize()
         windows.append((t0, time.perf_counter()))
@@ -244,7 +250,8 @@ def run_ours(args) -> dict:
     # ---- the same through the public entry point ------------------------------
     def e2e_run(batch: int, steps: int, warmup: int):
         prompts = [rng.integers(0, vocab, CONTEXT - 1).tolist() for _ in range(batch)]
-        params = SamplingParams(max_new_tokens=steps + warmup + 1, ignore_eos=True)
+        # every request decodes through all timed steps (prompts finish their prefill a step or two apart)
+        params = SamplingParams(max_new_tokens=steps + warmup + 8, ignore_eos=True)
         for prompt in prompts:
             engine.add_request(prompt, params)
         while any(not r.prefill_done for r in engine.requests.values()) or engine.scheduler.waiting:

@@ -103,6 +103,8 @@ class LLMEngine:
         self.seed = seed
         self._arrivals = 0
         self._request_seed: dict[int, int] = {}
+        self.stage_ahead = True   # stage the next decode step while the device runs this one
+        self._ahead = None        # (batch, sampled requests, prepared step) staged that way
 
     # ---- requests -------------------------------------------------------------
     def _tokenize(self, prompt: str, chat: bool) -> list[int]:
@@ -143,11 +145,13 @@ class LLMEngine:
         base = sampling.seed if sampling.seed is not None else step_seed(self.seed, self._arrivals)
         self._request_seed[request.req_id] = base
         self._arrivals += 1
+        self._ahead = None   # the step staged ahead did not know of this request
         self.scheduler.add(request)
         return request.req_id
 
     def abort(self, req_id: int) -> None:
         request = self.requests.pop(req_id, None)
+        self._ahead = None
         if request is not None:
             self.scheduler.abort(request)
             self._request_seed.pop(req_id, None)
@@ -157,11 +161,7 @@ class LLMEngine:
         return self.scheduler.has_work
 
     # ---- the loop ---------------------------------------------------------------
-    @torch.inference_mode()
-    def step(self) -> list[StepOutput]:
-        batch = self.scheduler.schedule()
-        if not batch:
-            return []
+    def _entries(self, batch):
         entries, sampled = [], []
         for request, num_new in batch:
             start = request.num_computed_tokens
@@ -174,15 +174,60 @@ class LLMEngine:
                 sampled.append(request)
             entries.append(StepEntry(request.cache, request.token_ids[start: start + num_new], start,
                                      [num_new - 1] if reaches_end else [], sampling))
-        if sampled:
-            _logits, drawn = self.runner.step(entries, sample=True)
-            tokens = drawn.tolist()
+        return entries, sampled
+
+    def _stage_ahead(self, batch, sampled):
+        """While the device runs a decode step: schedules and stages the step after it, which is
+        certain but for the values of the tokens being drawn now.  Only in the steady state:
+        every running request decodes, nobody waits, nobody reaches its length limit with this
+        token.  Returns (batch, sampled requests, prepared step) or None.  If one of the requests
+        then ends on a stop token the staged step is dropped and the next step is scheduled
+        afresh: `Scheduler.schedule` keeps the pages it reserved, so scheduling twice does no harm."""
+        if not self.stage_ahead or len(sampled) != len(batch) or self.scheduler.waiting:
+            return None
+        if len(batch) != len(self.scheduler.running) or any(n != 1 for _, n in batch):
+            return None
+        if any(r.num_generated + 1 >= r.sampling.max_new_tokens for r in sampled):
+            return None
+        # only when the pages for everybody's next token are there: scheduling early must not
+        # preempt a request that a stop token, seen a moment later, would have spared
+        need = [0] * len(self.block_manager.num_free)
+        for request in sampled:
+            for group, pages in enumerate(self.block_manager.pages_needed(request.cache, request.num_computed_tokens, 1)):
+                need[group] += pages
+        if any(n > free for n, free in zip(need, self.block_manager.num_free)):
+            return None
+        preemptions = self.scheduler.num_preemptions
+        ahead = self.scheduler.schedule()
+        if (self.scheduler.num_preemptions != preemptions or len(ahead) != len(batch)
+                or any(n != 1 or not r.prefill_done for r, n in ahead)):
+            return None
+        entries = []
+        for request, _ in ahead:   # this step's token is not appended yet: it will sit at num_tokens
+            params = request.sampling
+            sampling = (params.temperature, params.top_p,
+                        step_seed(self._request_seed[request.req_id], request.num_tokens + 1))
+            entries.append(StepEntry(request.cache, [0], request.num_computed_tokens, [0], sampling))
+        return ahead, [r for r, _ in ahead], self.runner.prepare(entries, sample=True, ids_missing=True)
+
+    @torch.inference_mode()
+    def step(self) -> list[StepOutput]:
+        ahead, self._ahead = self._ahead, None
+        if ahead is not None:
+            batch, sampled, prepared = ahead
         else:
-            self.runner.step(entries)
-            tokens = []
+            batch = self.scheduler.schedule()
+            if not batch:
+                return []
+            entries, sampled = self._entries(batch)
+            prepared = self.runner.prepare(entries, sample=bool(sampled))
+        result = self.runner.launch(prepared)
         self.scheduler.postprocess(batch)
+        ahead = self._stage_ahead(batch, sampled)   # host work under the device's step
+        tokens = result[1].tolist() if sampled else []
 
         outputs: list[StepOutput] = []
+        ended = False
         for request, token in zip(sampled, tokens):
             request.token_ids.append(token)
             self.stats.tokens_generated += 1
@@ -193,9 +238,13 @@ class LLMEngine:
                 finished, reason = True, "length"
             outputs.append(StepOutput(request.req_id, token, finished, reason))
             if finished:
+                ended = True
                 self.scheduler.finish(request, reason)
                 del self.requests[request.req_id]
                 self._request_seed.pop(request.req_id, None)
+        if ahead is not None and not ended:
+            self.runner.fill_ids(ahead[2], [request.token_ids[-1] for request in ahead[1]])
+            self._ahead = ahead
         self.stats.steps += 1
         if self.stats.steps % 256 == 0:
             self._check_kernels()

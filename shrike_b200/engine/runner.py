@@ -21,6 +21,17 @@ from .model import DecoderModel, Runtime
 TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
 
+class Prepared:
+    """A step whose metadata is staged on the host: what `ModelRunner.launch` needs."""
+
+    __slots__ = ("staged", "sample", "graphable")
+
+    def __init__(self, staged, sample: bool, graphable: bool):
+        self.staged = staged
+        self.sample = sample
+        self.graphable = graphable
+
+
 class ModelRunner:
     def __init__(
         self,
@@ -71,9 +82,29 @@ class ModelRunner:
     def _generation(self):
         return (self.runtime.generation, self.builder.generation, getattr(self.ops, "generation", 0))
 
-    @torch.inference_mode()
     def step(self, entries: list[StepEntry], sample: bool = False):
-        """Runs the entries' tokens as one batch.  Returns float32 logits [wanted, vocab];
+        """Runs the entries' tokens as one batch: `launch(prepare(entries, sample))`."""
+        return self.launch(self.prepare(entries, sample))
+
+    def prepare(self, entries: list[StepEntry], sample: bool = False, ids_missing: bool = False) -> "Prepared":
+        """The host half of a step: the batch's metadata packed into pinned memory, nothing sent
+        yet.  It may run while the device still works on the step before; with `ids_missing=True`
+        the entries' (single) tokens are placeholders, supplied later by `fill_ids`."""
+        staged = self.builder.stage(entries, defer=True, ids_missing=ids_missing)
+        if sample and not staged.sampled:
+            raise ValueError("sample=True needs `sampling` on every entry that wants logits")
+        graphable = (
+            self.use_graphs and self.device.type == "cuda" and max(staged.q_lens) == 1
+            and staged.r == staged.s and all(e.want == [0] for e in entries)
+        )
+        return Prepared(staged, sample, graphable)
+
+    def fill_ids(self, prepared: "Prepared", tokens) -> None:
+        self.builder.fill_ids(prepared.staged, tokens)
+
+    @torch.inference_mode()
+    def launch(self, prepared: "Prepared"):
+        """The device half of a step.  Returns float32 logits [wanted, vocab];
         with `sample=True` (every entry with wanted rows carries `sampling`) returns
         (logits, int32 tokens [wanted]) instead, the tokens drawn by the sampling kernel.
 
@@ -82,13 +113,8 @@ class ModelRunner:
         CUDA graph and replayed afterwards, because at small batch the step is bound by
         launch latency otherwise (the remedy shrike's README names for its own per-layer
         dispatch cost)."""
-        staged = self.builder.stage(entries)
-        if sample and not staged.sampled:
-            raise ValueError("sample=True needs `sampling` on every entry that wants logits")
-        graphable = (
-            self.use_graphs and self.device.type == "cuda" and max(staged.q_lens) == 1
-            and staged.r == staged.s and all(e.want == [0] for e in entries)
-        )
+        staged, sample, graphable = prepared.staged, prepared.sample, prepared.graphable
+        self.builder.commit(staged)
         if not graphable:
             logits, tokens = self._run(self.builder.context(staged), sample)
             return (logits, tokens) if sample else logits

@@ -127,3 +127,43 @@ def test_single_token_split_rule_keeps_its_bounds():
     assert CudaOps.single_token_splits(16, 64, resident) == (4, 4)
     assert CudaOps.single_token_splits(16, 256, resident) == (1, 1)
     assert CudaOps.single_token_splits(512, 4, resident) == (72, 8)     # a long context: nine clusters
+
+
+def _run_script(stage_ahead: bool, pool: int):
+    """Requests that arrive, stop on a token, run out of length and are aborted at fixed steps."""
+    engine, _ = engine_for("B", max_tokens_per_step=32, max_running=4, num_blocks=pool)
+    engine.stage_ahead = stage_ahead
+    prompts = [random_tokens(384, n, 70 + n) for n in (5, 12, 30, 3, 17)]
+    first = engine.generate([prompts[0]], SamplingParams(max_new_tokens=8, ignore_eos=True))[0]
+    engine.eos_ids = {first[4]}   # the first request now stops at its fifth token (or earlier)
+    ids = [engine.add_request(prompts[0], SamplingParams(max_new_tokens=20)),
+           engine.add_request(prompts[1], SamplingParams(max_new_tokens=9, temperature=0.8, top_p=0.9, seed=3)),
+           engine.add_request(prompts[2], SamplingParams(max_new_tokens=25, ignore_eos=True))]
+    log, staged_steps, step = [], 0, 0
+    while engine.has_work:
+        staged_steps += engine._ahead is not None
+        for out in engine.step():
+            log.append((out.req_id - ids[0], out.token_id, out.finished, out.finish_reason))
+        step += 1
+        if step == 6:
+            ids.append(engine.add_request(prompts[3], SamplingParams(max_new_tokens=7, ignore_eos=True)))
+        if step == 9:
+            engine.abort(ids[2])
+        if step == 11:
+            ids.append(engine.add_request(prompts[4], SamplingParams(max_new_tokens=5, temperature=1.1, seed=9)))
+    assert engine.block_manager.whole() and not engine.requests and engine._ahead is None
+    return log, staged_steps, engine.scheduler.num_preemptions
+
+
+@pytest.mark.parametrize("pool", [40, 8])
+def test_staging_the_next_step_ahead_changes_no_token(pool):
+    """The engine stages a decode step while the one before it runs.  Arrivals, a stop token,
+    length limits, an abort and (with the small pool) preemption all fall between staged steps;
+    the tokens and the order of the outputs are those of the plain loop."""
+    plain, none_staged, _ = _run_script(False, pool)
+    ahead, staged, preemptions = _run_script(True, pool)
+    assert none_staged == 0 and staged >= 4
+    assert ahead == plain
+    assert any(reason == "stop" for *_, reason in plain) and any(reason == "length" for *_, reason in plain)
+    if pool == 8:
+        assert preemptions >= 1
