@@ -207,30 +207,35 @@ def run_ours(args) -> dict:
         fed = CONTEXT - 1
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
-        def stage(fed, tokens=None):
-            """The host half of the step that feeds position `fed`; without tokens, ahead of them."""
+        def launch(fed, tokens=None):
+            """Launches the step that feeds position `fed`.  Without tokens the step takes them on
+            the device from what the step before it draws (id -1 - row), as the engine does in
+            steady decoding: the host has not seen them yet."""
             entries = []
             for index, cache in enumerate(caches):
                 runner.cache.append(cache, fed, 1)
-                entries.append(StepEntry(cache, [tokens[index] if tokens else 0], fed, [0], (0.0, 1.0, 0)))
-            return runner.prepare(entries, sample=True, ids_missing=tokens is None)
+                entries.append(StepEntry(cache, [tokens[index] if tokens else -1 - index], fed, [0], (0.0, 1.0, 0)))
+            _logits, drawn = runner.step(entries, sample=True)
+            return runner.fetch(drawn)
 
-        def run(count, prepared, fed):
-            """`count` steps the way the engine runs them: while the device works on a step, the
-            host stages the next one; the drawn tokens come back and complete it."""
+        def run(count, in_flight, fed):
+            """`count` steps, one launched and one read back per round; the device never waits."""
             for _ in range(count):
-                _logits, drawn = runner.launch(prepared)
                 fed += 1
-                prepared = stage(fed)
-                runner.fill_ids(prepared, drawn.tolist())
-            return prepared, fed
+                following = launch(fed)
+                runner.wait(in_flight)          # this step's tokens reach the host
+                in_flight = following
+            return in_flight, fed
 
-        prepared, fed = run(warmup, stage(fed, tokens), fed)
+        in_flight, fed = run(warmup - 1, launch(fed, tokens), fed)
+        tokens = runner.wait(in_flight)
         torch.cuda.synchronize()
         launches_before = ops.launches
         t0 = time.perf_counter()
         start.record()
-        prepared, fed = run(steps, prepared, fed)
+        fed += 1
+        in_flight, fed = run(steps - 1, launch(fed, tokens), fed)   # `steps` launches ...
+        runner.wait(in_flight)                                       # ... and `steps` read-backs
         stop.record()
         torch.cuda.synchronize()
         windows.append((t0, time.perf_counter()))

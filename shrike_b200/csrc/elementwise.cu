@@ -6,13 +6,18 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------- embedding
+// A negative id -1 - r stands for "the token the step before drew in its row r": it is read
+// from `previous` on the device, so that a step can be launched before the host has seen the
+// tokens of the step before it.  Ids outside the vocabulary give a row of zeros.
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
-                             float* __restrict__ out, int width, int vocab) {
+                             float* __restrict__ out, int width, int vocab,
+                             const int* __restrict__ previous, int previous_rows) {
   let_dependents_start();
   wait_for_previous();
   const int row = blockIdx.x;
   int id = ids[row];
+  if (id < 0 && previous != nullptr && -1 - id < previous_rows) id = previous[-1 - id];
   const bool valid = id >= 0 && id < vocab;
   if (!valid) id = 0;
   const T* src = table + static_cast<size_t>(id) * width;
@@ -21,14 +26,16 @@ __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ 
 }
 
 SHRIKE_API int shrike_embed(const int* ids, const void* table, int table_dtype, float* out, int n,
-                            int width, int vocab, cudaStream_t stream) {
+                            int width, int vocab, const int* previous, int previous_rows, cudaStream_t stream) {
   if (n <= 0) return SHRIKE_OK;
   if (width <= 0 || vocab <= 0) return SHRIKE_BAD_ARGUMENT;
   const int threads = width >= 1024 ? 256 : 128;
   if (table_dtype == SHRIKE_F32)
-    launch_dependent(embed_kernel<float>, n, threads, 0, stream, ids, static_cast<const float*>(table), out, width, vocab);
+    launch_dependent(embed_kernel<float>, n, threads, 0, stream, ids, static_cast<const float*>(table), out, width, vocab,
+                     previous, previous_rows);
   else if (table_dtype == SHRIKE_BF16)
-    launch_dependent(embed_kernel<__nv_bfloat16>, n, threads, 0, stream, ids, static_cast<const __nv_bfloat16*>(table), out, width, vocab);
+    launch_dependent(embed_kernel<__nv_bfloat16>, n, threads, 0, stream, ids, static_cast<const __nv_bfloat16*>(table), out, width,
+                     vocab, previous, previous_rows);
   else
     return SHRIKE_BAD_ARGUMENT;
   return shrike_launch_status();

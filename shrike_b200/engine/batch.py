@@ -59,6 +59,7 @@ class StepContext:
     sample_temperature: torch.Tensor | None = None  # float32 [R], when every wanted row is sampled
     sample_top_p: torch.Tensor | None = None  # float32 [R]
     sample_seed: torch.Tensor | None = None  # int64 [R]
+    previous_tokens: torch.Tensor | None = None  # int32: what the step before drew; an id of -1 - r means its row r
 
 
 @dataclass

@@ -103,8 +103,8 @@ class LLMEngine:
         self.seed = seed
         self._arrivals = 0
         self._request_seed: dict[int, int] = {}
-        self.stage_ahead = True   # stage the next decode step while the device runs this one
-        self._ahead = None        # (batch, sampled requests, prepared step) staged that way
+        self.launch_ahead = True   # launch the next decode step before this one's tokens are read back
+        self._flight = None        # (batch, sampled requests, fetch handle) of a step launched that way
 
     # ---- requests -------------------------------------------------------------
     def _tokenize(self, prompt: str, chat: bool) -> list[int]:
@@ -145,13 +145,11 @@ class LLMEngine:
         base = sampling.seed if sampling.seed is not None else step_seed(self.seed, self._arrivals)
         self._request_seed[request.req_id] = base
         self._arrivals += 1
-        self._ahead = None   # the step staged ahead did not know of this request
         self.scheduler.add(request)
         return request.req_id
 
     def abort(self, req_id: int) -> None:
         request = self.requests.pop(req_id, None)
-        self._ahead = None
         if request is not None:
             self.scheduler.abort(request)
             self._request_seed.pop(req_id, None)
@@ -176,21 +174,23 @@ class LLMEngine:
                                      [num_new - 1] if reaches_end else [], sampling))
         return entries, sampled
 
-    def _stage_ahead(self, batch, sampled):
-        """While the device runs a decode step: schedules and stages the step after it, which is
-        certain but for the values of the tokens being drawn now.  Only in the steady state:
-        every running request decodes, nobody waits, nobody reaches its length limit with this
-        token.  Returns (batch, sampled requests, prepared step) or None.  If one of the requests
-        then ends on a stop token the staged step is dropped and the next step is scheduled
-        afresh: `Scheduler.schedule` keeps the pages it reserved, so scheduling twice does no harm."""
-        if not self.stage_ahead or len(sampled) != len(batch) or self.scheduler.waiting:
+    def _launch_ahead(self, batch, sampled):
+        """While the device runs a decode step: schedules, stages and launches the step after it,
+        whose input tokens the embedding kernel takes on the device from what this step draws.
+        Only in the steady state: every running request decodes, nobody waits, nobody reaches its
+        length limit with this token, and the pages for everybody's next token are there (so that
+        scheduling early preempts nobody whom a stop token, seen a moment later, would have
+        spared).  Returns the step in flight, or None.
+
+        A request that ends on a stop token while the next step is already in flight has one
+        token computed in vain; its row of that step's output is dropped.  Its pages go back at
+        once: whatever is given them later is launched later, and the device runs in order."""
+        if not self.launch_ahead or len(sampled) != len(batch) or self.scheduler.waiting:
             return None
         if len(batch) != len(self.scheduler.running) or any(n != 1 for _, n in batch):
             return None
         if any(r.num_generated + 1 >= r.sampling.max_new_tokens for r in sampled):
             return None
-        # only when the pages for everybody's next token are there: scheduling early must not
-        # preempt a request that a stop token, seen a moment later, would have spared
         need = [0] * len(self.block_manager.num_free)
         for request in sampled:
             for group, pages in enumerate(self.block_manager.pages_needed(request.cache, request.num_computed_tokens, 1)):
@@ -201,34 +201,40 @@ class LLMEngine:
         ahead = self.scheduler.schedule()
         if (self.scheduler.num_preemptions != preemptions or len(ahead) != len(batch)
                 or any(n != 1 or not r.prefill_done for r, n in ahead)):
-            return None
+            return None   # scheduling again at the next step does no harm: reserved pages are kept
+        row_of = {request.req_id: row for row, request in enumerate(sampled)}
         entries = []
         for request, _ in ahead:   # this step's token is not appended yet: it will sit at num_tokens
             params = request.sampling
             sampling = (params.temperature, params.top_p,
                         step_seed(self._request_seed[request.req_id], request.num_tokens + 1))
-            entries.append(StepEntry(request.cache, [0], request.num_computed_tokens, [0], sampling))
-        return ahead, [r for r, _ in ahead], self.runner.prepare(entries, sample=True, ids_missing=True)
+            entries.append(StepEntry(request.cache, [-1 - row_of[request.req_id]], request.num_computed_tokens, [0], sampling))
+        return self._launch(ahead, entries, [r for r, _ in ahead])
+
+    def _launch(self, batch, entries, sampled):
+        result = self.runner.step(entries, sample=bool(sampled))
+        self.scheduler.postprocess(batch)
+        return batch, sampled, self.runner.fetch(result[1]) if sampled else None
 
     @torch.inference_mode()
     def step(self) -> list[StepOutput]:
-        ahead, self._ahead = self._ahead, None
-        if ahead is not None:
-            batch, sampled, prepared = ahead
-        else:
+        """One step's outputs.  In the steady state of decoding the step after it is launched
+        before this step's tokens are read back, so the device does not wait for the host."""
+        flight, self._flight = self._flight, None
+        if flight is None:
             batch = self.scheduler.schedule()
             if not batch:
                 return []
             entries, sampled = self._entries(batch)
-            prepared = self.runner.prepare(entries, sample=bool(sampled))
-        result = self.runner.launch(prepared)
-        self.scheduler.postprocess(batch)
-        ahead = self._stage_ahead(batch, sampled)   # host work under the device's step
-        tokens = result[1].tolist() if sampled else []
+            flight = self._launch(batch, entries, sampled)
+        batch, sampled, fetched = flight
+        self._flight = self._launch_ahead(batch, sampled)
+        tokens = self.runner.wait(fetched) if sampled else []
 
         outputs: list[StepOutput] = []
-        ended = False
         for request, token in zip(sampled, tokens):
+            if self.requests.get(request.req_id) is not request:
+                continue   # ended (stop token, abort) while this step was in flight
             request.token_ids.append(token)
             self.stats.tokens_generated += 1
             finished, reason = False, None
@@ -238,13 +244,9 @@ class LLMEngine:
                 finished, reason = True, "length"
             outputs.append(StepOutput(request.req_id, token, finished, reason))
             if finished:
-                ended = True
                 self.scheduler.finish(request, reason)
                 del self.requests[request.req_id]
                 self._request_seed.pop(request.req_id, None)
-        if ahead is not None and not ended:
-            self.runner.fill_ids(ahead[2], [request.token_ids[-1] for request in ahead[1]])
-            self._ahead = ahead
         self.stats.steps += 1
         if self.stats.steps % 256 == 0:
             self._check_kernels()

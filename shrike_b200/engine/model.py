@@ -116,7 +116,7 @@ class DecoderModel:
         """float32 logits [R, vocab] at `ctx.out_rows`."""
         rt, ops = self.runtime, self.ops
         resid = rt.buffer("resid", (ctx.num_tokens, self.config.hidden_size), torch.float32)
-        ops.embed(ctx.token_ids, self.embedding, resid)
+        ops.embed(ctx.token_ids, self.embedding, resid, ctx.previous_tokens)
         delta = None
         for run in self.config.order:
             resid, delta = self.blocks[run.layer].forward(resid, delta, ctx, run)

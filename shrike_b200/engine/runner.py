@@ -69,18 +69,29 @@ class ModelRunner:
         self.builder = BatchBuilder(page_size, len(self.groups), self.device, self.storage)
         self.use_graphs = True
         self._graphs: dict = {}
+        self._drawn = torch.zeros(4096, dtype=torch.int32, device=self.device)   # the sampled tokens of a step
+        self._drawn_generation = 0
+        self._fetch_host = [None, None]
+        self._fetch_turn = 0
 
     # ---- the step ---------------------------------------------------------------
     def _run(self, ctx, sample: bool):
+        if ctx.num_rows > self._drawn.numel():   # rare: more sampled rows than any step before
+            self._drawn = torch.zeros(2 * ctx.num_rows, dtype=torch.int32, device=self.device)
+            self._drawn_generation += 1
+        # the tokens drawn by the step before are still in `_drawn` while the embedding runs;
+        # this step's sampling, at its very end, overwrites them
+        ctx.previous_tokens = self._drawn
         logits = self.model.forward(ctx)
         tokens = None
         if sample:
-            tokens = self.runtime.buffer("sampled", (ctx.num_rows,), torch.int32)
+            tokens = self._drawn[: ctx.num_rows]
             self.ops.sample(logits, ctx.sample_temperature, ctx.sample_top_p, ctx.sample_seed, tokens)
         return logits, tokens
 
     def _generation(self):
-        return (self.runtime.generation, self.builder.generation, getattr(self.ops, "generation", 0))
+        return (self.runtime.generation, self.builder.generation, getattr(self.ops, "generation", 0),
+                self._drawn_generation)
 
     def step(self, entries: list[StepEntry], sample: bool = False):
         """Runs the entries' tokens as one batch: `launch(prepare(entries, sample))`."""
@@ -101,6 +112,30 @@ class ModelRunner:
 
     def fill_ids(self, prepared: "Prepared", tokens) -> None:
         self.builder.fill_ids(prepared.staged, tokens)
+
+    def fetch(self, tokens: torch.Tensor):
+        """Starts the copy of a step's drawn tokens to pinned host memory and returns a handle for
+        `wait`.  The copy is ordered before whatever is launched next, so a later step may
+        overwrite the device buffer."""
+        count = tokens.numel()
+        if self.device.type != "cuda":
+            return tokens.tolist(), count, None
+        self._fetch_turn ^= 1
+        if self._fetch_host[self._fetch_turn] is None or self._fetch_host[self._fetch_turn].numel() < count:
+            self._fetch_host[self._fetch_turn] = torch.empty(max(256, 2 * count), dtype=torch.int32, pin_memory=True)
+        host = self._fetch_host[self._fetch_turn]
+        host[:count].copy_(tokens, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return host, count, event
+
+    @staticmethod
+    def wait(handle) -> list[int]:
+        host, count, event = handle
+        if event is None:
+            return host
+        event.synchronize()
+        return host[:count].tolist()
 
     @torch.inference_mode()
     def launch(self, prepared: "Prepared"):

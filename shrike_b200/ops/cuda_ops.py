@@ -92,7 +92,7 @@ class CudaOps:
     # ---- declarations -------------------------------------------------------
     def _declare_core(self):
         lib = self.core
-        lib.shrike_embed.argtypes = [_P, _P, _I, _P, _I, _I, _I, _P]
+        lib.shrike_embed.argtypes = [_P, _P, _I, _P, _I, _I, _I, _P, _I, _P]
         lib.shrike_add_rmsnorm.argtypes = [_P, _P, _I, _P, _P, _F, _P, _I, _I, _I, _I, _LL, _P]
         lib.shrike_silu_mul.argtypes = [_P, _P, _I, _I, _I, _P]
         lib.shrike_rope_kv_write.argtypes = [_P] * 10 + [_I] * 5 + [_LL, _I, _LL, _P]
@@ -138,13 +138,18 @@ class CudaOps:
             )
 
     # ---- kernels ------------------------------------------------------------
-    def embed(self, ids, table, out):
+    def embed(self, ids, table, out, previous=None):
+        """Rows of `table` into the float32 residual.  An id of -1 - r is replaced on the device
+        by `previous[r]` (int32: the tokens the step before drew)."""
         _dense(ids, torch.int32, "token ids")
         _dense(out, torch.float32, "residual")
         n, width = out.shape
+        if previous is not None:
+            _dense(previous, torch.int32, "previous tokens")
         self.launches += 1
         _check(self.core.shrike_embed(_ptr(ids), _ptr(table), _DTYPE_CODE[table.dtype], _ptr(out), n, width,
-                                      table.shape[0], self._stream()), "embed")
+                                      table.shape[0], _ptr(previous), 0 if previous is None else previous.numel(),
+                                      self._stream()), "embed")
 
     @staticmethod
     def _stack(delta):

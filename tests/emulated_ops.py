@@ -25,8 +25,11 @@ class EmulatedOps:
         if head_dim % 16 or not 16 <= head_dim <= 256:
             raise ValueError(f"head size {head_dim} is not served")
 
-    def embed(self, ids, table, out):
-        out.copy_(table[ids.long()].float())
+    def embed(self, ids, table, out, previous=None):
+        ids = ids.long()
+        if previous is not None and (ids < 0).any():
+            ids = torch.where(ids < 0, previous.long()[(-1 - ids).clamp(min=0, max=previous.numel() - 1)], ids)
+        out.copy_(table[ids].float())
 
     def add_rmsnorm(self, resid, delta, weight, eps, out):
         if delta is not None:

@@ -132,7 +132,7 @@ def test_single_token_split_rule_keeps_its_bounds():
 def _run_script(stage_ahead: bool, pool: int):
     """Requests that arrive, stop on a token, run out of length and are aborted at fixed steps."""
     engine, _ = engine_for("B", max_tokens_per_step=32, max_running=4, num_blocks=pool)
-    engine.stage_ahead = stage_ahead
+    engine.launch_ahead = stage_ahead
     prompts = [random_tokens(384, n, 70 + n) for n in (5, 12, 30, 3, 17)]
     first = engine.generate([prompts[0]], SamplingParams(max_new_tokens=8, ignore_eos=True))[0]
     engine.eos_ids = {first[4]}   # the first request now stops at its fifth token (or earlier)
@@ -141,7 +141,7 @@ def _run_script(stage_ahead: bool, pool: int):
            engine.add_request(prompts[2], SamplingParams(max_new_tokens=25, ignore_eos=True))]
     log, staged_steps, step = [], 0, 0
     while engine.has_work:
-        staged_steps += engine._ahead is not None
+        staged_steps += engine._flight is not None
         for out in engine.step():
             log.append((out.req_id - ids[0], out.token_id, out.finished, out.finish_reason))
         step += 1
@@ -151,19 +151,42 @@ def _run_script(stage_ahead: bool, pool: int):
             engine.abort(ids[2])
         if step == 11:
             ids.append(engine.add_request(prompts[4], SamplingParams(max_new_tokens=5, temperature=1.1, seed=9)))
-    assert engine.block_manager.whole() and not engine.requests and engine._ahead is None
+    assert engine.block_manager.whole() and not engine.requests 
     return log, staged_steps, engine.scheduler.num_preemptions
 
 
+def _by_request(log):
+    table = {}
+    for req, token, finished, reason in log:
+        table.setdefault(req, []).append((token, finished, reason))
+    return table
+
+
 @pytest.mark.parametrize("pool", [40, 8])
-def test_staging_the_next_step_ahead_changes_no_token(pool):
-    """The engine stages a decode step while the one before it runs.  Arrivals, a stop token,
-    length limits, an abort and (with the small pool) preemption all fall between staged steps;
-    the tokens and the order of the outputs are those of the plain loop."""
-    plain, none_staged, _ = _run_script(False, pool)
-    ahead, staged, preemptions = _run_script(True, pool)
-    assert none_staged == 0 and staged >= 4
-    assert ahead == plain
+def test_launching_the_next_step_ahead_changes_no_token(pool):
+    """In steady decoding the engine launches a step before the tokens of the step before it
+    are read back (the embedding takes them on the device).  Arrivals, a stop token, length
+    limits, an abort and (with the small pool) preemption all fall between such steps; every
+    request gets the tokens, the end and the reason of the plain loop.  Only the interleaving
+    may differ: a request that arrives while a step is in flight joins one step later."""
+    plain, none_ahead, _ = _run_script(False, pool)
+    ahead, launched_ahead, preemptions = _run_script(True, pool)
+    assert none_ahead == 0 and launched_ahead >= 4
+    assert _by_request(ahead) == _by_request(plain)
     assert any(reason == "stop" for *_, reason in plain) and any(reason == "length" for *_, reason in plain)
     if pool == 8:
         assert preemptions >= 1
+
+
+def test_a_stop_token_while_the_next_step_is_in_flight_drops_that_row_only():
+    engine, _ = engine_for("A", num_blocks=24, max_running=4)
+    prompts = [random_tokens(256, n, 11 + n) for n in (9, 4, 13)]
+    free_run = engine.generate(prompts, SamplingParams(max_new_tokens=10, ignore_eos=True))
+    stop = free_run[1][3]                      # the second request's fourth token becomes the stop token
+    engine.eos_ids = {stop}
+    cut = [run[: run.index(stop) + 1] if stop in run else run for run in free_run]
+    got = engine.generate(prompts, SamplingParams(max_new_tokens=10))
+    assert got == cut and len(cut[1]) <= 4
+    assert engine.block_manager.whole() and not engine.requests
+    # whatever was in flight when the last request ended is drained by the next call
+    assert engine.generate([prompts[0]], SamplingParams(max_new_tokens=3, ignore_eos=True))[0] == free_run[0][:3]
