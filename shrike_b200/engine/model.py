@@ -25,9 +25,14 @@ class Runtime:
         self.device = torch.device(device)
         self.act_dtype = act_dtype
         self._buffers: dict[str, torch.Tensor] = {}
+        self._views: dict = {}   # (name, shape, dtype) -> view, while the buffer has not moved
         self.generation = 0  # grows when a buffer moves
 
     def buffer(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        key = (name, tuple(shape), dtype)
+        view = self._views.get(key)
+        if view is not None:
+            return view
         count = 1
         for extent in shape:
             count *= extent
@@ -37,7 +42,12 @@ class Runtime:
             held = torch.empty(max(capacity, 1), dtype=dtype, device=self.device)
             self._buffers[name] = held
             self.generation += 1
-        return held[:count].view(shape)
+            self._views = {k: v for k, v in self._views.items() if k[0] != name}
+        if len(self._views) > 4096:
+            self._views.clear()
+        view = held[:count].view(shape)
+        self._views[key] = view
+        return view
 
     def reserve(self, name: str, count: int, dtype: torch.dtype) -> None:
         self.buffer(name, (count,), dtype)

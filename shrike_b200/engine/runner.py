@@ -82,11 +82,18 @@ class ModelRunner:
         # the tokens drawn by the step before are still in `_drawn` while the embedding runs;
         # this step's sampling, at its very end, overwrites them
         ctx.previous_tokens = self._drawn
-        logits = self.model.forward(ctx)
-        tokens = None
-        if sample:
-            tokens = self._drawn[: ctx.num_rows]
-            self.ops.sample(logits, ctx.sample_temperature, ctx.sample_top_p, ctx.sample_seed, tokens)
+        hold = getattr(self.ops, "hold_stream", None)
+        if hold is not None:
+            hold(True)
+        try:
+            logits = self.model.forward(ctx)
+            tokens = None
+            if sample:
+                tokens = self._drawn[: ctx.num_rows]
+                self.ops.sample(logits, ctx.sample_temperature, ctx.sample_top_p, ctx.sample_seed, tokens)
+        finally:
+            if hold is not None:
+                hold(False)
         return logits, tokens
 
     def _generation(self):

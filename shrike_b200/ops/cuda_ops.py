@@ -82,6 +82,7 @@ class CudaOps:
         self._sample_scratch = None  # per-slice winners of the sampling kernel
         self._arrivals = None    # per kv head: splits of single-token attention that have finished
         self.generation = 0      # grows when the scratch moves
+        self._held_stream = None
         self.launches = 0        # launches of this package's own kernels
         self.library_calls = 0   # matrix products handed to cuBLAS
         # library matrix products keep float32 accumulation end to end: no TF32 for float32
@@ -127,9 +128,14 @@ class CudaOps:
             self._attention[head_dim] = lib
         return lib
 
-    @staticmethod
-    def _stream():
-        return torch.cuda.current_stream().cuda_stream
+    def _stream(self):
+        return self._held_stream if self._held_stream is not None else torch.cuda.current_stream().cuda_stream
+
+    def hold_stream(self, hold: bool) -> None:
+        """Between `hold_stream(True)` and `hold_stream(False)` every launch goes to the stream
+        that was current at the first call, looked up once: asking torch for the current stream
+        costs more than a launch.  The step function brackets a forward pass with it."""
+        self._held_stream = torch.cuda.current_stream().cuda_stream if hold else None
 
     def check_head_dim(self, head_dim: int):
         if head_dim % 16 or not 16 <= head_dim <= 256:
