@@ -6,8 +6,10 @@
 //     own 16 query rows each and walk the keys 64 at a time (FlashAttention-2 order).
 //   * single tokens (q_len == 1): one CTA per (key split, kv head, sequence).  The G
 //     query heads that share a kv head are the rows of one 16-row tile, so keys and
-//     values are read once per kv head, not once per query head; the four warps take 16
-//     keys each of every 64-key tile, tiles arrive through a three-deep cp.async pipeline;
+//     values are read once per kv head, not once per query head; eight warps take 8 keys
+//     each of every 64-key tile for Q K^T and every eighth 16-column block of the output for
+//     P V (the probabilities pass through shared memory), tiles arrive through a three-deep
+//     cp.async pipeline;
 //     the splits of one kv head form thread-block clusters of up to eight CTAs, which add
 //     their partial results up through distributed shared memory; where one cluster covers
 //     all splits the result goes straight out, otherwise each cluster writes one partial
@@ -57,6 +59,10 @@ __device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) 
   const unsigned addr = static_cast<unsigned>(__cvta_generic_to_shared(smem));
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x2(unsigned (&r)[2], const void* smem) {
+  const unsigned addr = static_cast<unsigned>(__cvta_generic_to_shared(smem));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
 }
 __device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
   const unsigned addr = static_cast<unsigned>(__cvta_generic_to_shared(smem));
@@ -122,7 +128,7 @@ __device__ __forceinline__ void locate_tile(long long* rows, const Params& p, co
 // Keys without a row become zeros.
 template <int KEYS>
 __device__ __forceinline__ void copy_tile(bf16* k_tile, bf16* v_tile, const Params& p, const long long* rows) {
-  for (int c = threadIdx.x; c < KEYS * CHUNKS; c += THREADS) {
+  for (int c = threadIdx.x; c < KEYS * CHUNKS; c += blockDim.x) {
     const int key = c / CHUNKS, chunk = c - key * CHUNKS;
     const long long row = rows[key];
     if (row == -2) continue;
@@ -329,14 +335,33 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? 4 : 2) portions_kernel(con
 // ------------------------------------------------------------- single tokens
 constexpr int ST = 3;  // pipeline depth of the single-token kernel, in 64-key tiles
 constexpr int MAX_SPLITS = 32;
+constexpr int SW = 8;                      // warps: each takes BN / SW keys of a tile for the scores ...
+constexpr int STHREADS = SW * 32;
+constexpr int WARP_KEYS = BN / SW;         // ... (8: one MMA column block)
+constexpr int DPAIRS = D / 16;             // ... and every SW-th 16-column block of the output for PV
+constexpr int MY_PAIRS = (DPAIRS + SW - 1) / SW;
+constexpr int PROW = BN + 8;               // padded row of the probability tile, in elements
+constexpr size_t SINGLE_EXCHANGE_SMEM = sizeof(bf16) * 16 * PROW + sizeof(float) * 2 * SW * 16;
+// The probabilities and the warps' maxima and sums take the query tile's space once the query
+// sits in registers, where that space suffices (two CTAs of head size 128 fill an SM's shared
+// memory to the last kilobyte); otherwise they lie behind the key and value tiles.
+constexpr bool EXCHANGE_OVER_QUERY = Q_IN_REGS && SINGLE_EXCHANGE_SMEM <= sizeof(bf16) * 16 * ROW;
 
-__global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
+// The warps split a tile's keys for Q K^T and the head dimension for P V; the probabilities
+// pass through shared memory in between.  So each warp keeps only its columns of the output
+// (a few registers), twice as many warps fit as with a whole output row per warp, and nothing
+// is merged across warps when the keys run out.
+__global__ void __launch_bounds__(STHREADS, D <= 128 ? 2 : 1) single_token_kernel(const Params p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ int is_last;
   __shared__ long long tile_rows[ST + 1][BN];
   bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);           // [16][ROW]
   bf16* k_tiles = q_tile + 16 * ROW;                          // [ST][BN][ROW]
   bf16* v_tiles = k_tiles + ST * BN * ROW;
+  unsigned char* exchange = EXCHANGE_OVER_QUERY ? smem_raw : reinterpret_cast<unsigned char*>(v_tiles + ST * BN * ROW);
+  bf16* probs = reinterpret_cast<bf16*>(exchange);                                 // [16][PROW]
+  float* warp_max = reinterpret_cast<float*>(exchange + sizeof(bf16) * 16 * PROW); // [SW][16]
+  float* warp_sum = warp_max + SW * 16;                                            // [SW][16]
   let_dependents_start();
   // Before wait_for_previous() only what no kernel of this step writes is read: the batch's
   // metadata and the keys and values of earlier positions.  The newest key (position
@@ -362,12 +387,15 @@ __global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
   const int my_lo = tile_lo + static_cast<int>(static_cast<long long>(split) * tiles / p.splits);
   const int my_hi = tile_lo + static_cast<int>(static_cast<long long>(split + 1) * tiles / p.splits) - 1;
 
-  float o[DTILES][4];
+  float o[MY_PAIRS][2][4];   // rows lane/4 and lane/4 + 8 of this warp's 16-column blocks
 #pragma unroll
-  for (int j = 0; j < DTILES; ++j)
+  for (int i = 0; i < MY_PAIRS; ++i)
 #pragma unroll
-    for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
-  float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.f, 0.f};
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[i][j][e] = 0.f;
+  float row_max[2] = {-INFINITY, -INFINITY};   // the same in every warp
+  float row_sum[2] = {0.f, 0.f};               // this thread's share: its keys only
 
   if (my_lo <= my_hi) {
     // rows of the first ST - 1 tiles without the newest key, and their copies, ahead of the wait
@@ -385,7 +413,7 @@ __global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
   }
   wait_for_previous();
   if (my_lo <= my_hi) {
-    for (int c = threadIdx.x; c < 16 * CHUNKS; c += THREADS) {
+    for (int c = threadIdx.x; c < 16 * CHUNKS; c += STHREADS) {
       const int row = c / CHUNKS, chunk = c - row * CHUNKS;
       const bool valid = row < rows_here;
       const bf16* src = p.q + (static_cast<size_t>(start) * p.num_heads + head0 + (valid ? row : 0)) * D + chunk * 8;
@@ -406,113 +434,174 @@ __global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
     cp_async_commit();
     if (my_lo + ST - 1 <= my_hi)   // copied by the first round of the loop
       locate_tile<BN>(tile_rows[ST - 1], p, table, kv_head, (my_lo + ST - 1) * BN, first_key, last_key);
-    cp_async_wait<0>();
-    __syncthreads();
-    int first[2] = {first_key, first_key}, last[2] = {last_key, last_key};
-    unsigned q_frag[Q_IN_REGS ? KSTEPS : 1][4];
     // The table lookup for a tile is issued one round before its rows are stored, which is
     // one more round before they are copied: no round waits for a lookup of its own.
     int pending_page = -1;
     if (my_lo + ST <= my_hi && threadIdx.x < BN)
       pending_page = lookup_page(p, table, (my_lo + ST) * BN + threadIdx.x, first_key, last_key, -1);
+    cp_async_wait<0>();
+    __syncthreads();
+    unsigned q_frag[Q_IN_REGS ? KSTEPS : 1][4];
+    if (Q_IN_REGS) {
+#pragma unroll
+      for (int kk = 0; kk < KSTEPS; ++kk)
+        ldmatrix_x4(q_frag[Q_IN_REGS ? kk : 0], q_tile + ((lane & 7) + 8 * ((lane >> 3) & 1)) * ROW + kk * 16 + 8 * (lane >> 4));
+    }
     for (int tile = my_lo; tile <= my_hi; ++tile) {
       const int buffer = (tile - my_lo) % ST;
       const int ahead = tile + ST - 1;
+      // every warp is done with the tile before (its buffer is loaded into next), and, in the
+      // first round, with reading the query out of the space the probabilities take
+      cp_async_wait<ST - 2>();
+      __syncthreads();
       if (ahead <= my_hi) {
         const int into = (ahead - my_lo) % ST;
         copy_tile<BN>(k_tiles + into * BN * ROW, v_tiles + into * BN * ROW, p, tile_rows[(ahead - my_lo) % (ST + 1)]);
       }
       cp_async_commit();
       if (threadIdx.x < BN) {
-        if (ahead + 1 <= my_hi)   // read in the next round, after this round's closing barrier
+        if (ahead + 1 <= my_hi)   // read in the next round, after its opening barrier
           tile_rows[(ahead + 1 - my_lo) % (ST + 1)][threadIdx.x] = row_of(p, kv_head, (ahead + 1) * BN + threadIdx.x, pending_page);
         if (ahead + 2 <= my_hi)
           pending_page = lookup_page(p, table, (ahead + 2) * BN + threadIdx.x, first_key, last_key, -1);
       }
-      cp_async_wait<ST - 1>();
-      __syncthreads();
-      if (Q_IN_REGS && tile == my_lo) {
+      const bf16* k_tile = k_tiles + buffer * BN * ROW;
+      const bf16* v_tile = v_tiles + buffer * BN * ROW;
+      // scores of this warp's keys: S[16 x 8] = Q[16 x D] K^T
+      const int key0 = warp * WARP_KEYS;
+      float sc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int kk = 0; kk < KSTEPS; ++kk)
-          ldmatrix_x4(q_frag[Q_IN_REGS ? kk : 0], q_tile + ((lane & 7) + 8 * ((lane >> 3) & 1)) * ROW + kk * 16 + 8 * (lane >> 4));
+      for (int kk = 0; kk < KSTEPS; ++kk) {
+        unsigned a[4], b[2];
+        if (Q_IN_REGS) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) a[i] = q_frag[Q_IN_REGS ? kk : 0][i];
+        } else {
+          ldmatrix_x4(a, q_tile + ((lane & 7) + 8 * ((lane >> 3) & 1)) * ROW + kk * 16 + 8 * (lane >> 4));
+        }
+        ldmatrix_x2(b, k_tile + (key0 + (lane & 7)) * ROW + kk * 16 + 8 * ((lane >> 3) & 1));
+        mma_bf16(sc, a, b[0], b[1]);
       }
-      const int key0 = warp * 16;
-      if (tile * BN + key0 <= last_key && tile * BN + key0 + 15 >= first_key) {
-        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-        scores<2, Q_IN_REGS>(s, q_frag, q_tile, k_tiles + buffer * BN * ROW, key0, lane);
-        softmax_update<2>(s, o, row_max, row_sum, first, last, tile * BN + key0, p.scale_log2, lane);
-        accumulate<2>(o, s, v_tiles + buffer * BN * ROW, key0, lane);
+      // mask, scale, and this warp's maximum per row
+      float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = tile * BN + key0 + (lane & 3) * 2 + (e & 1);
+        const bool seen = key >= first_key && key <= last_key;
+        sc[e] = seen ? sc[e] * p.scale_log2 : -INFINITY;
+        tile_max[e >> 1] = fmaxf(tile_max[e >> 1], sc[e]);
       }
-      __syncthreads();   // the buffer is loaded into again by the next round
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
+        tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
+        if ((lane & 3) == 0) warp_max[warp * 16 + (lane >> 2) + 8 * r] = tile_max[r];
+      }
+      __syncthreads();
+      // the tile's maximum over all warps, the same sum order everywhere: every warp arrives
+      // at the same running maximum and the same correction
+      float correction[2], base[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        float m = row_max[r];
+#pragma unroll
+        for (int w = 0; w < SW; ++w) m = fmaxf(m, warp_max[w * 16 + (lane >> 2) + 8 * r]);
+        base[r] = m == -INFINITY ? 0.f : m;              // a row that has seen no key yet
+        correction[r] = exp2f(row_max[r] - base[r]);     // exp2(-inf) = 0
+        row_max[r] = m;
+        row_sum[r] *= correction[r];
+      }
+      float prob[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        prob[e] = exp2f(sc[e] - base[e >> 1]);
+        row_sum[e >> 1] += prob[e];
+      }
+      // probabilities as bfloat16 (as the values are) into the shared tile
+      *reinterpret_cast<unsigned*>(probs + (lane >> 2) * PROW + key0 + (lane & 3) * 2) = pack_bf16(prob[0], prob[1]);
+      *reinterpret_cast<unsigned*>(probs + ((lane >> 2) + 8) * PROW + key0 + (lane & 3) * 2) = pack_bf16(prob[2], prob[3]);
+#pragma unroll
+      for (int i = 0; i < MY_PAIRS; ++i)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          o[i][j][0] *= correction[0];
+          o[i][j][1] *= correction[0];
+          o[i][j][2] *= correction[1];
+          o[i][j][3] *= correction[1];
+        }
+      __syncthreads();
+      // O[16 x 16 columns] += P[16 x 64] V[64 x 16 columns] for each of this warp's column blocks
+#pragma unroll
+      for (int i = 0; i < MY_PAIRS; ++i) {
+        const int pair = warp + i * SW;
+        if (pair < DPAIRS) {
+#pragma unroll
+          for (int kk = 0; kk < BN / 16; ++kk) {
+            unsigned a[4], b[4];
+            ldmatrix_x4(a, probs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * PROW + kk * 16 + 8 * (lane >> 4));
+            ldmatrix_x4_trans(b, v_tile + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * ROW + pair * 16 + 8 * (lane >> 4));
+            mma_bf16(o[i][0], a, b[0], b[1]);
+            mma_bf16(o[i][1], a, b[2], b[3]);
+          }
+        }
+      }
     }
     cp_async_wait<0>();
   }
+  // every row's sum: the threads' shares over the quad, then over the warps
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 1);
     row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 2);
   }
-  // combine the four warps' states through shared memory (the tiles are no longer needed)
+  if ((lane & 3) == 0) {   // a space of its own: no barrier needed before it is written
+    warp_sum[warp * 16 + (lane >> 2)] = row_sum[0];
+    warp_sum[warp * 16 + (lane >> 2) + 8] = row_sum[1];
+  }
   __syncthreads();
-  constexpr int WO = D + 8;   // padded row: the eight rows a warp stores at once fall into different banks
-  float* warp_o = reinterpret_cast<float*>(smem_raw);         // [4][16][WO]
-  float* warp_ml = warp_o + 4 * 16 * WO;                      // [4][16][2]
-  float* row_weight = warp_ml + 4 * 16 * 2;                   // [16][4] weight of each warp, then [16] max, [16] sum
-  float* cta_o = row_weight + 96;                             // [16][D] this CTA's result, read by its cluster
+  float total_sum[2] = {0.f, 0.f};
+#pragma unroll
+  for (int r = 0; r < 2; ++r)
+#pragma unroll
+    for (int w = 0; w < SW; ++w) total_sum[r] += warp_sum[w * 16 + (lane >> 2) + 8 * r];
+  __syncthreads();   // the tiles and the exchange space are free from here on
+  // this CTA's result, unnormalised, with its maximum and sum: to the output, to the cluster
+  // (shared memory) or to global memory, straight from the registers
+  float* cta_o = reinterpret_cast<float*>(smem_raw);          // [16][D], read by the cluster
   float* cta_ml = cta_o + 16 * D;                             // [16][2]
+  const bool direct = p.splits == 1;   // nothing to combine: the result goes straight out
+  const int partials = p.splits / p.cluster;   // what the clusters leave in global memory
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     const int row = (lane >> 2) + 8 * r;
-    if (row >= rows_here) continue;   // rows beyond the group's heads are never read
+    if (row >= rows_here) continue;
+    const float inv = total_sum[r] > 0.f ? 1.0f / total_sum[r] : 0.f;
+    const size_t slot = (static_cast<size_t>(seq) * p.num_heads + head0 + row) * p.splits + split;
 #pragma unroll
-    for (int j = 0; j < DTILES; ++j)
-      *reinterpret_cast<float2*>(warp_o + (warp * 16 + row) * WO + j * 8 + (lane & 3) * 2) = make_float2(o[j][2 * r], o[j][2 * r + 1]);
-    if ((lane & 3) == 0) {
-      warp_ml[(warp * 16 + row) * 2] = row_max[r];
-      warp_ml[(warp * 16 + row) * 2 + 1] = row_sum[r];
-    }
-  }
-  __syncthreads();
-  if (threadIdx.x < rows_here) {   // per row: the four warps' weights, the common maximum and the sum
-    const int row = threadIdx.x;
-    float m = -INFINITY;
+    for (int i = 0; i < MY_PAIRS; ++i) {
+      const int pair = warp + i * SW;
+      if (pair >= DPAIRS) continue;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) m = fmaxf(m, warp_ml[(w * 16 + row) * 2]);
-    float sum = 0.f;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const float wm = warp_ml[(w * 16 + row) * 2];
-      const float weight = wm == -INFINITY ? 0.f : exp2f(wm - m);
-      row_weight[row * 4 + w] = weight;
-      sum += weight * warp_ml[(w * 16 + row) * 2 + 1];
-    }
-    row_weight[64 + row] = m;
-    row_weight[80 + row] = sum;
-  }
-  __syncthreads();
-  const bool direct = p.splits == 1;   // nothing to combine: the result goes straight out
-  const int partials = p.splits / p.cluster;   // what the clusters leave in global memory
-  for (int idx = threadIdx.x; idx < rows_here * D; idx += THREADS) {
-    const int row = idx / D, d = idx - row * D;
-    float total = 0.f;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) total += row_weight[row * 4 + w] * warp_o[(w * 16 + row) * WO + d];
-    if (p.cluster > 1) {
-      cta_o[idx] = total;
-      if (d == 0) {
-        cta_ml[row * 2] = row_weight[64 + row];
-        cta_ml[row * 2 + 1] = row_weight[80 + row];
+      for (int j = 0; j < 2; ++j) {
+        const int d = pair * 16 + j * 8 + (lane & 3) * 2;
+        const float x = o[i][j][2 * r], y = o[i][j][2 * r + 1];
+        if (p.cluster > 1) {
+          *reinterpret_cast<float2*>(cta_o + row * D + d) = make_float2(x, y);
+        } else if (direct) {
+          *reinterpret_cast<__nv_bfloat162*>(p.out + (static_cast<size_t>(start) * p.num_heads + head0 + row) * D + d) =
+              __floats2bfloat162_rn(x * inv, y * inv);
+        } else {
+          *reinterpret_cast<float2*>(p.partial_out + slot * D + d) = make_float2(x, y);
+        }
       }
-    } else if (direct) {
-      const float sum = row_weight[80 + row];
-      p.out[(static_cast<size_t>(start) * p.num_heads + head0 + row) * D + d] =
-          __float2bfloat16_rn(sum > 0.f ? total / sum : 0.f);
-    } else {
-      const size_t slot = (static_cast<size_t>(seq) * p.num_heads + head0 + row) * p.splits + split;
-      p.partial_out[slot * D + d] = total;
-      if (d == 0) {
-        p.partial_ml[slot * 2] = row_weight[64 + row];
-        p.partial_ml[slot * 2 + 1] = row_weight[80 + row];
+    }
+    if (warp == 0 && (lane & 3) == 0) {
+      if (p.cluster > 1) {
+        cta_ml[row * 2] = row_max[r];
+        cta_ml[row * 2 + 1] = total_sum[r];
+      } else if (!direct) {
+        p.partial_ml[slot * 2] = row_max[r];
+        p.partial_ml[slot * 2 + 1] = total_sum[r];
       }
     }
   }
@@ -527,7 +616,7 @@ __global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
     const int outputs = rows_here * D;
     const int share = (outputs + p.cluster - 1) / p.cluster;
     const int stop = min(outputs, (rank + 1) * share);
-    for (int idx = rank * share + threadIdx.x; idx < stop; idx += THREADS) {
+    for (int idx = rank * share + threadIdx.x; idx < stop; idx += STHREADS) {
       const int row = idx / D, d = idx - row * D;
       float peer_max[8], peer_sum[8], peer_o[8];
 #pragma unroll
@@ -580,79 +669,60 @@ __global__ void __launch_bounds__(THREADS) single_token_kernel(const Params p) {
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  // Each thread takes four columns of one row, two such items at a time, and reads the
-  // (max, sum) pairs and the four columns of up to eight partials of both in one go: the
-  // combine costs one memory round trip per eight partials, not one per partial.  Chunks of
-  // eight are merged like attention tiles, in partial order.
+  // Each thread takes four columns of one row and reads the (max, sum) pairs and the four
+  // columns of up to eight partials in one go: the combine costs one memory round trip per
+  // eight partials, not one per partial.  Chunks of eight are merged like attention tiles, in
+  // partial order.
   constexpr int QUADS = D / 4;
   const int items = rows_here * QUADS;
-  for (int first = threadIdx.x; first < items; first += 2 * THREADS) {
-    int row[2], quad[2];
-    bool live[2];
-#pragma unroll
-    for (int k = 0; k < 2; ++k) {
-      const int item = first + k * THREADS;
-      live[k] = item < items;
-      row[k] = live[k] ? item / QUADS : 0;
-      quad[k] = live[k] ? item - row[k] * QUADS : 0;
-    }
-    float run_max[2] = {-INFINITY, -INFINITY}, run_sum[2] = {0.f, 0.f};
-    float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+  for (int item = threadIdx.x; item < items; item += STHREADS) {
+    const int row = item / QUADS, quad = item - row * QUADS;
+    float run_max = -INFINITY, run_sum = 0.f;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
     for (int base = 0; base < partials; base += 8) {
-      float2 ml[2][8];
-      float4 o[2][8];
+      float2 ml[8];
+      float4 part[8];
 #pragma unroll
-      for (int k = 0; k < 2; ++k) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          if (live[k] && base + j < partials) {
-            const size_t slot = (static_cast<size_t>(seq) * p.num_heads + head0 + row[k]) * partials + base + j;
-            ml[k][j] = __ldcg(reinterpret_cast<const float2*>(p.partial_ml + slot * 2));
-            o[k][j] = __ldcg(reinterpret_cast<const float4*>(p.partial_out + slot * D + quad[k] * 4));
-          }
+      for (int j = 0; j < 8; ++j) {
+        if (base + j < partials) {
+          const size_t slot = (static_cast<size_t>(seq) * p.num_heads + head0 + row) * partials + base + j;
+          ml[j] = __ldcg(reinterpret_cast<const float2*>(p.partial_ml + slot * 2));
+          part[j] = __ldcg(reinterpret_cast<const float4*>(p.partial_out + slot * D + quad * 4));
         }
       }
+      float m = run_max;
 #pragma unroll
-      for (int k = 0; k < 2; ++k) {
-        if (!live[k]) continue;
-        float m = run_max[k];
+      for (int j = 0; j < 8; ++j)
+        if (base + j < partials) m = fmaxf(m, ml[j].x);
+      const float rescale = run_max == -INFINITY ? 0.f : exp2f(run_max - m);
+      float sum = run_sum * rescale;
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          if (base + j < partials) m = fmaxf(m, ml[k][j].x);
-        const float rescale = run_max[k] == -INFINITY ? 0.f : exp2f(run_max[k] - m);
-        float sum = run_sum[k] * rescale;
+      for (int e = 0; e < 4; ++e) acc[e] *= rescale;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) acc[k][e] *= rescale;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          if (base + j < partials) {
-            const float weight = ml[k][j].x == -INFINITY ? 0.f : exp2f(ml[k][j].x - m);
-            sum += weight * ml[k][j].y;
-            acc[k][0] += weight * o[k][j].x;
-            acc[k][1] += weight * o[k][j].y;
-            acc[k][2] += weight * o[k][j].z;
-            acc[k][3] += weight * o[k][j].w;
-          }
+      for (int j = 0; j < 8; ++j) {
+        if (base + j < partials) {
+          const float weight = ml[j].x == -INFINITY ? 0.f : exp2f(ml[j].x - m);
+          sum += weight * ml[j].y;
+          acc[0] += weight * part[j].x;
+          acc[1] += weight * part[j].y;
+          acc[2] += weight * part[j].z;
+          acc[3] += weight * part[j].w;
         }
-        run_max[k] = m;
-        run_sum[k] = sum;
       }
+      run_max = m;
+      run_sum = sum;
     }
-#pragma unroll
-    for (int k = 0; k < 2; ++k) {
-      if (!live[k]) continue;
-      const float inv = run_sum[k] > 0.f ? 1.0f / run_sum[k] : 0.f;
-      uint2 packed;
-      packed.x = pack_bf16(acc[k][0] * inv, acc[k][1] * inv);
-      packed.y = pack_bf16(acc[k][2] * inv, acc[k][3] * inv);
-      *reinterpret_cast<uint2*>(p.out + (static_cast<size_t>(start) * p.num_heads + head0 + row[k]) * D + quad[k] * 4) = packed;
-    }
+    const float inv = run_sum > 0.f ? 1.0f / run_sum : 0.f;
+    uint2 packed;
+    packed.x = pack_bf16(acc[0] * inv, acc[1] * inv);
+    packed.y = pack_bf16(acc[2] * inv, acc[3] * inv);
+    *reinterpret_cast<uint2*>(p.out + (static_cast<size_t>(start) * p.num_heads + head0 + row) * D + quad * 4) = packed;
   }
 }
 
 constexpr size_t PORTIONS_SMEM = sizeof(bf16) * (BM * ROW + 4 * PBN * ROW);
-constexpr size_t SINGLE_TILES_SMEM = sizeof(bf16) * (16 * ROW + 2 * ST * BN * ROW);
-constexpr size_t SINGLE_MERGE_SMEM = sizeof(float) * (4 * 16 * (D + 8) + 4 * 16 * 2 + 96 + 16 * D + 32);
+constexpr size_t SINGLE_TILES_SMEM = sizeof(bf16) * (16 * ROW + 2 * ST * BN * ROW) + (EXCHANGE_OVER_QUERY ? 0 : SINGLE_EXCHANGE_SMEM);
+constexpr size_t SINGLE_MERGE_SMEM = sizeof(float) * (16 * D + 32);
 constexpr size_t SINGLE_SMEM = SINGLE_TILES_SMEM > SINGLE_MERGE_SMEM ? SINGLE_TILES_SMEM : SINGLE_MERGE_SMEM;
 
 }  // namespace bf16attn
@@ -723,7 +793,7 @@ SHRIKE_API int shrike_paged_attention_bf16(const void* q, const void* k_cache, c
   if (has_single) {
     const int group = num_heads / num_kv_heads;
     const dim3 grid(p.splits, num_kv_heads * ((group + 15) / 16), num_seqs);
-    launch_dependent_clusters(single_token_kernel, grid, THREADS, SINGLE_SMEM, stream, p.cluster, p);
+    launch_dependent_clusters(single_token_kernel, grid, STHREADS, SINGLE_SMEM, stream, p.cluster, p);
   }
   if (has_portions) {
     const dim3 grid((max_q_len + BM - 1) / BM, num_heads, num_seqs);

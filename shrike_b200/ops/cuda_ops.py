@@ -315,12 +315,12 @@ class CudaOps:
                 self._arrivals = torch.zeros(max(groups, 4096), dtype=torch.int32, device=self.device)
                 self.generation += 1
             scratch, arrivals = self._scratch, self._arrivals
+        if self.status is None:
+            self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
         tensor_core_portions = (has_portions and self.tensor_core_attention and lib.shrike_attention_tc_available()
                                 and page_size in (8, 16, 32, 64))
         self.launches += (1 if has_single else 0) + (1 if has_portions else 0)
         if tensor_core_portions:
-            if self.status is None:
-                self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
             _check(lib.shrike_paged_attention_tc_portions(
                 _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), max_blocks, _ptr(q_start), _ptr(ctx_len),
                 q.shape[0], num_seqs, num_heads, num_kv_heads, page_size, num_pages, scale, window or 0, _ptr(out),
