@@ -574,10 +574,27 @@ def run_timeline(args) -> dict:
     for event in step:
         rows.append((event.name.split("(")[0].split("<")[0].split("::")[-1], event.time_range.end - previous_end))
         previous_end = event.time_range.end
-    first = next(i for i, (name, _) in enumerate(rows) if "add_rmsnorm" in name)
-    per_layer = 9   # norm, qkv, rotary, attention, o, norm, gate_up, SiLU product, down
-    labels = ["norm (mixer)", "qkv product", "rotary + cache store", "attention", "o product", "norm (feed-forward)",
-              "gate_up product", "SiLU product", "down product"]
+    norms = [i for i, (name, _) in enumerate(rows) if "add_rmsnorm" in name]
+    first, per_layer = norms[0], norms[2] - norms[0]   # two norms a layer
+    products = iter(["qkv product", "o product", "gate_up product", "down product"])
+    seen_norms = 0
+    labels = []
+    for name, _ in rows[first + per_layer: first + 2 * per_layer]:
+        if "add_rmsnorm" in name:
+            labels.append("norm (feed-forward)" if seen_norms else "norm (mixer)")
+            seen_norms += 1
+        elif "gemm" in name or "nvjet" in name or "cutlass" in name:
+            labels.append(next(products, "product"))
+        elif "rope" in name:
+            labels.append("rotary + cache store")
+        elif "single_token" in name or "portions" in name or "attention" in name:
+            labels.append("attention")
+        elif "silu" in name:
+            labels.append("SiLU product")
+        else:
+            labels.append(name)
+    if "SiLU product" not in labels:
+        labels = [label + " with SiLU" if label == "gate_up product" else label for label in labels]
     table = []
     for position in range(per_layer):
         samples = [rows[first + layer * per_layer + position] for layer in range(1, layers)]   # the first layer follows the embedding

@@ -77,6 +77,18 @@ static inline cudaError_t launch_dependent_clusters(void (*kernel)(KernelArgs...
   return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
 }
 
+// silu(g) * u, silu(g) = g / (1 + exp(-g)), with one rounding of the product.  bfloat16 results
+// keep 8 bits of mantissa, so that path may use the hardware exponential and reciprocal
+// (relative error about 2^-22); the float32 path uses the exact functions.  Shared by the
+// activation kernel and the tensor-core product's activation epilogue: both give the same bits.
+template <typename T> __device__ __forceinline__ float silu_times(float g, float u);
+template <> __device__ __forceinline__ float silu_times<float>(float g, float u) {
+  return __fmul_rn(g / (1.0f + expf(-g)), u);
+}
+template <> __device__ __forceinline__ float silu_times<__nv_bfloat16>(float g, float u) {
+  return __fmul_rn(__fdividef(g, 1.0f + __expf(-g)), u);
+}
+
 // base[0] + base[stride] + ... over `partials` slices (the stack a K-split product leaves),
 // added in ascending order.  Up to 16 loads are issued together before the first addition,
 // so the sum costs one memory latency, not one per slice.

@@ -239,18 +239,12 @@ SHRIKE_API int shrike_add_rmsnorm(float* resid, const void* delta, int delta_dty
 // out[r, c] = silu(gate_up[r, c]) * gate_up[r, inter + c], silu(g) = g / (1 + exp(-g)),
 // in float32 with one rounding.  VEC elements per thread and access (16 bytes when the
 // row length allows, else one).
-// bfloat16 results keep 8 bits of mantissa, so that path may use the hardware exponential and
-// reciprocal (relative error about 2^-22); the float32 path uses the exact functions.
-template <typename T> __device__ __forceinline__ float silu_times(float g, float u);
-template <> __device__ __forceinline__ float silu_times<float>(float g, float u) {
-  return __fmul_rn(g / (1.0f + expf(-g)), u);
-}
-template <> __device__ __forceinline__ float silu_times<__nv_bfloat16>(float g, float u) {
-  return __fmul_rn(__fdividef(g, 1.0f + __expf(-g)), u);
-}
-
+// `block`: how gate and up columns lie in a row of gate_up.  0: all gate columns, then all up
+// columns.  b > 0: runs of b gate columns followed by the b up columns of the same features
+// (the order in which a fused gate/up matrix keeps its rows for the tensor-core product's own
+// activation epilogue); b is a multiple of VEC.
 template <typename T, int VEC>
-__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total, int block) {
   let_dependents_start();
   wait_for_previous();
   const int groups_per_row = inter / VEC;
@@ -269,10 +263,10 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
       const size_t row = live[k] ? index / groups_per_row : 0;
       const int col = live[k] ? static_cast<int>(index - row * groups_per_row) * VEC : 0;
       at[k] = row * inter + col;
-      const T* g_ptr = gate_up + row * 2 * inter + col;
+      const T* g_ptr = gate_up + row * 2 * inter + (block > 0 ? (col / block) * 2 * block + col % block : col);
       if (live[k]) {
         g[k] = *reinterpret_cast<const Pack*>(g_ptr);
-        u[k] = *reinterpret_cast<const Pack*>(g_ptr + inter);
+        u[k] = *reinterpret_cast<const Pack*>(g_ptr + (block > 0 ? block : inter));
       }
     }
 #pragma unroll
@@ -287,26 +281,27 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
 }
 
 template <typename T>
-static void launch_silu_mul(const void* gate_up, void* out, int n, int inter, cudaStream_t stream) {
+static void launch_silu_mul(const void* gate_up, void* out, int n, int inter, int block, cudaStream_t stream) {
   constexpr int WIDE = 16 / sizeof(T);
-  const bool vec = inter % WIDE == 0 && (reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) % 16 == 0;
+  const bool vec = inter % WIDE == 0 && block % WIDE == 0 &&
+                   (reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) % 16 == 0;
   const size_t total = static_cast<size_t>(n) * inter;
   const size_t work = vec ? total / WIDE : total;
   const int threads = 256;
   const int blocks = static_cast<int>(min(static_cast<size_t>(148 * 8), (work + 2 * threads - 1) / (2 * threads)));
   if (vec)
     launch_dependent(silu_mul_kernel<T, WIDE>, blocks, threads, 0, stream, static_cast<const T*>(gate_up),
-                     static_cast<T*>(out), inter, total);
+                     static_cast<T*>(out), inter, total, block);
   else
     launch_dependent(silu_mul_kernel<T, 1>, blocks, threads, 0, stream, static_cast<const T*>(gate_up),
-                     static_cast<T*>(out), inter, total);
+                     static_cast<T*>(out), inter, total, block);
 }
 
-SHRIKE_API int shrike_silu_mul(const void* gate_up, void* out, int dtype, int n, int inter, cudaStream_t stream) {
+SHRIKE_API int shrike_silu_mul(const void* gate_up, void* out, int dtype, int n, int inter, int block, cudaStream_t stream) {
   if (n <= 0) return SHRIKE_OK;
-  if (inter <= 0) return SHRIKE_BAD_ARGUMENT;
-  if (dtype == SHRIKE_F32) launch_silu_mul<float>(gate_up, out, n, inter, stream);
-  else if (dtype == SHRIKE_BF16) launch_silu_mul<__nv_bfloat16>(gate_up, out, n, inter, stream);
+  if (inter <= 0 || block < 0 || (block > 0 && inter % block)) return SHRIKE_BAD_ARGUMENT;
+  if (dtype == SHRIKE_F32) launch_silu_mul<float>(gate_up, out, n, inter, block, stream);
+  else if (dtype == SHRIKE_BF16) launch_silu_mul<__nv_bfloat16>(gate_up, out, n, inter, block, stream);
   else return SHRIKE_BAD_ARGUMENT;
   return shrike_launch_status();
 }

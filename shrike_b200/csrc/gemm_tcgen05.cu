@@ -68,6 +68,8 @@ struct Args {
   int* status;          // host-visible; first failing role is recorded
   int tokens, n, k, tn; // tn: token columns of the MMA (multiple of 16, at most 256)
   int kblocks_per_split, stages, out_dtype;
+  int gated;            // the weight rows come in runs of 16 gate rows and the 16 up rows of the same
+                        // features; out is [T][N / 2] bfloat16 = silu(gate) * up
 };
 
 __global__ void __launch_bounds__(THREADS, 3)
@@ -168,7 +170,36 @@ gemm_swap_ab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     bool ok = true;
     if (num_kb > 0) ok = mbar_wait(&sh->done, 0, &sh->abort, args.status, ERR_EPILOGUE);
     fence_after_sync();
-    if (ok) {
+    if (ok && args.gated) {
+      // A warp's 32 rows are 16 gate rows and the 16 up rows of the same features.  Lanes below
+      // 16 finish tokens 0..7 of a block of 16, the others tokens 8..15; each half sends the
+      // other what it needs.  Gate and up are rounded to bfloat16 first, as the separate
+      // activation kernel finds them, so both ways give the same bits.
+      const int feature = (n0 >> 1) + quarter * 16 + (lane & 15);
+      const int half_n = args.n >> 1;
+      for (int c0 = 0; c0 < args.tn; c0 += 16) {
+        unsigned v[16];
+        if (num_kb > 0) {
+          tmem_load16(tmem_d + (static_cast<unsigned>(quarter * 32) << 16) + static_cast<unsigned>(c0), v);
+          tmem_wait_load();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = 0u;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const unsigned mine = lane < 16 ? v[j] : v[8 + j];
+          const unsigned sent = lane < 16 ? v[8 + j] : v[j];
+          const unsigned other = __shfl_xor_sync(0xffffffffu, sent, 16);
+          const float gate = __bfloat162float(__float2bfloat16_rn(__uint_as_float(lane < 16 ? mine : other)));
+          const float up = __bfloat162float(__float2bfloat16_rn(__uint_as_float(lane < 16 ? other : mine)));
+          const int t = t0 + c0 + j + (lane < 16 ? 0 : 8);
+          if (t < args.tokens && n0 + quarter * 32 + lane < args.n)
+            static_cast<__nv_bfloat16*>(args.out)[static_cast<size_t>(t) * half_n + feature] =
+                __float2bfloat16_rn(silu_times<__nv_bfloat16>(gate, up));
+        }
+      }
+    } else if (ok) {
       const bool partial = gridDim.y > 1;
       const float bias = (args.bias != nullptr && split == 0 && row < args.n) ? args.bias[row] : 0.f;
       for (int c0 = 0; c0 < args.tn; c0 += 16) {
@@ -235,8 +266,8 @@ SHRIKE_API int shrike_gemm_tc_splits(int tokens, int n, int k) {
 // x [tokens, k] and w [n, k] bfloat16 row-major, k a multiple of 8 (TMA wants 16-byte row
 // strides) and both 16-byte aligned.  splits == 1: out is [tokens, n] of out_dtype.
 // splits > 1 (as shrike_gemm_tc_splits says): out is [splits, tokens, n] float32.
-SHRIKE_API int shrike_gemm_tc(const void* x, const void* w, const float* bias, void* out, int out_dtype, int tokens,
-                              int n, int k, int splits, int* status, cudaStream_t stream) {
+static int launch_gemm_tc(const void* x, const void* w, const float* bias, void* out, int out_dtype, int tokens,
+                          int n, int k, int splits, int gated, int* status, cudaStream_t stream) {
   using namespace tc;
   if (tokens <= 0 || n <= 0) return SHRIKE_OK;
   if (k <= 0 || k % 8 || splits < 1 || (out_dtype != SHRIKE_F32 && out_dtype != SHRIKE_BF16)) return SHRIKE_BAD_ARGUMENT;
@@ -276,6 +307,7 @@ SHRIKE_API int shrike_gemm_tc(const void* x, const void* w, const float* bias, v
   args.tn = tn;
   args.kblocks_per_split = per_split;
   args.stages = stages;
+  args.gated = gated;
   args.out_dtype = out_dtype;
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3((n + BM - 1) / BM, splits, token_tiles);
@@ -290,4 +322,18 @@ SHRIKE_API int shrike_gemm_tc(const void* x, const void* w, const float* bias, v
   const cudaError_t err = cudaLaunchKernelEx(&config, gemm_swap_ab_kernel, map_w, map_x, args);
   if (err != cudaSuccess) return static_cast<int>(err);
   return shrike_launch_status();
+}
+
+SHRIKE_API int shrike_gemm_tc(const void* x, const void* w, const float* bias, void* out, int out_dtype, int tokens,
+                              int n, int k, int splits, int* status, cudaStream_t stream) {
+  return launch_gemm_tc(x, w, bias, out, out_dtype, tokens, n, k, splits, 0, status, stream);
+}
+
+// The gated feed-forward's first product with its activation: w [n, k] holds, in runs of 32 rows,
+// 16 gate rows and the 16 up rows of the same features (n a multiple of 32); out [tokens, n / 2]
+// bfloat16 = silu(x w_gate^T) * (x w_up^T), gate and up rounded to bfloat16 before the activation.
+SHRIKE_API int shrike_gemm_tc_gated(const void* x, const void* w, void* out, int tokens, int n, int k, int* status,
+                                    cudaStream_t stream) {
+  if (n % 32) return SHRIKE_BAD_ARGUMENT;
+  return launch_gemm_tc(x, w, nullptr, out, SHRIKE_BF16, tokens, n, k, 1, 1, status, stream);
 }

@@ -75,6 +75,8 @@ class CudaOps:
             self.gemm_tc = build.tensor_core_gemm_library()
             self.gemm_tc.shrike_gemm_tc.argtypes = [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P]
             self.gemm_tc.shrike_gemm_tc.restype = _I
+            self.gemm_tc.shrike_gemm_tc_gated.argtypes = [_P, _P, _P, _I, _I, _I, _P, _P]
+            self.gemm_tc.shrike_gemm_tc_gated.restype = _I
             self.gemm_tc.shrike_gemm_tc_splits.argtypes = [_I, _I, _I]
             self.gemm_tc.shrike_gemm_tc_splits.restype = _I
             self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
@@ -95,7 +97,7 @@ class CudaOps:
         lib = self.core
         lib.shrike_embed.argtypes = [_P, _P, _I, _P, _I, _I, _I, _P, _I, _P]
         lib.shrike_add_rmsnorm.argtypes = [_P, _P, _I, _P, _P, _F, _P, _I, _I, _I, _I, _LL, _P]
-        lib.shrike_silu_mul.argtypes = [_P, _P, _I, _I, _I, _P]
+        lib.shrike_silu_mul.argtypes = [_P, _P, _I, _I, _I, _I, _P]
         lib.shrike_rope_kv_write.argtypes = [_P] * 10 + [_I] * 5 + [_LL, _I, _LL, _P]
         lib.shrike_kv_write.argtypes = [_P] * 5 + [_I, _I, _I, _LL, _P]
         lib.shrike_gemm_fp32.argtypes = [_P, _P, _P, _P, _I, _I, _I, _P]
@@ -356,12 +358,38 @@ class CudaOps:
             return cluster, cluster
         return min(want // cluster * cluster, 32 * cluster), cluster
 
-    def silu_mul(self, gate_up, out):
+    def silu_mul(self, gate_up, out, block=0):
+        """out = silu(gate) * up.  `block` 0: a row of gate_up is all gate columns, then all up
+        columns; b > 0: runs of b gate columns, each followed by the b up columns of the same features."""
         _dense(gate_up, self.dtype, "gate_up")
         _dense(out, self.dtype, "activation")
         n, inter = out.shape
         self.launches += 1
-        _check(self.core.shrike_silu_mul(_ptr(gate_up), _ptr(out), self.code, n, inter, self._stream()), "silu_mul")
+        _check(self.core.shrike_silu_mul(_ptr(gate_up), _ptr(out), self.code, n, inter, block, self._stream()), "silu_mul")
+
+    @property
+    def gated_rows(self) -> int:
+        """How a gated feed-forward should interleave the rows of its fused gate/up matrix for
+        `linear_gated`: runs of this many gate rows, each followed by the up rows of the same
+        features.  0: keep gate rows, then up rows (no fused activation in this mode)."""
+        return 16 if self.dtype == torch.bfloat16 and self.gemm_tc is not None else 0
+
+    def linear_gated(self, x, w, out) -> bool:
+        """silu(x Wg^T) * (x Wu^T) into `out` [N, I] in one kernel, for `w` [2 I, K] interleaved as
+        `gated_rows` says.  Returns False when this shape is not served (many tokens: the caller
+        then runs the product and the activation kernel, the latter with block=gated_rows)."""
+        n, k = x.shape
+        rows = w.shape[0]
+        if (self.gated_rows == 0 or n > self.tensor_core_gemm_max_tokens or k % 8 or rows % 32
+                or tuple(out.shape) != (n, rows // 2) or w.shape[1] != k):
+            return False
+        _dense(x, torch.bfloat16, "linear input")
+        _dense(w, torch.bfloat16, "linear weight")
+        _dense(out, torch.bfloat16, "activation")
+        self.launches += 1
+        _check(self.gemm_tc.shrike_gemm_tc_gated(_ptr(x), _ptr(w), _ptr(out), n, rows, k, _ptr(self.status),
+                                                 self._stream()), "gemm_tcgen05")
+        return True
 
     def sample(self, logits, temperature, top_p, seeds, out):
         _dense(logits, torch.float32, "logits")

@@ -147,6 +147,58 @@ def test_gemm_tcgen05(tokens, n, k):
     ops.check_status()
 
 
+def interleave_rows(gate, up, run):
+    blocks = gate.shape[0] // run
+    return torch.stack([gate.view(blocks, run, -1), up.view(blocks, run, -1)], dim=1).reshape(2 * gate.shape[0], -1).contiguous()
+
+
+@pytest.mark.parametrize("tokens,inter,k", [(1, 64, 64), (8, 176, 192), (3, 320, 240), (17, 2368, 3584), (33, 1184, 1000),
+                                            (64, 128, 18944), (8, 18944, 3584), (64, 18944, 3584)])
+def test_gemm_tcgen05_with_the_activation_in_its_epilogue(tokens, inter, k):
+    """silu(x Wg^T) * (x Wu^T) in one kernel, over a gate/up matrix whose rows come in runs of 16
+    gate rows and their 16 up rows: bit for bit what the product followed by the activation
+    kernel gives (on the interleaved and on the plain layout), and close to the exact value."""
+    ops = cuda_ops(torch.bfloat16)
+    run = ops.gated_rows
+    assert run == 16
+    x = rnd(tokens, k, dtype=torch.bfloat16, seed=1)
+    gate, up = rnd(inter, k, dtype=torch.bfloat16, seed=2, scale=0.05), rnd(inter, k, dtype=torch.bfloat16, seed=3, scale=0.05)
+    mixed = interleave_rows(gate, up, run)
+    fused = torch.full((tokens, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
+    assert ops.linear_gated(x, mixed, fused)
+    # the product, then the activation kernel told about the interleaving
+    both = torch.empty(tokens, 2 * inter, dtype=torch.bfloat16, device=DEV)
+    ops.linear(x, mixed, both)
+    stepwise = torch.empty_like(fused)
+    ops.silu_mul(both, stepwise, block=run)
+    assert torch.equal(fused, stepwise), "fused epilogue and activation kernel must agree bit for bit"
+    # the plain layout: gate rows, then up rows
+    plain_both = torch.empty_like(both)
+    ops.linear(x, torch.cat([gate, up]).contiguous(), plain_both)
+    plain = torch.empty_like(fused)
+    ops.silu_mul(plain_both, plain)
+    assert torch.equal(fused, plain), "the interleaving must not change a bit"
+    # the arithmetic of the epilogue: from the product's own bfloat16 gate and up values (the product
+    # itself is checked in test_gemm_tcgen05), one rounding of a float32 value good to about 2^-20
+    g, u = plain_both[:, :inter].double(), plain_both[:, inter:].double()
+    want = g * torch.sigmoid(g) * u
+    assert ((fused.double() - want).abs() <= (2.0 ** -8 + 2.0 ** -20) * want.abs() + 1e-30).all()
+    ops.check_status()
+
+
+def test_activation_kernel_on_interleaved_columns():
+    for dtype in (torch.float32, torch.bfloat16):
+        ops = cuda_ops(dtype)
+        n, inter, run = 37, 320, 16
+        gate, up = rnd(n, inter, dtype=dtype, seed=4, scale=2.0), rnd(n, inter, dtype=dtype, seed=5)
+        plain = torch.empty(n, inter, dtype=dtype, device=DEV)
+        ops.silu_mul(torch.cat([gate, up], dim=1).contiguous(), plain)
+        mixed = torch.stack([gate.view(n, inter // run, run), up.view(n, inter // run, run)], dim=2).reshape(n, 2 * inter).contiguous()
+        got = torch.empty_like(plain)
+        ops.silu_mul(mixed, got, block=run)
+        assert torch.equal(got, plain)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kv_heads,dim", [(5, 1, 48), (14, 2, 64), (3, 3, 16), (4, 2, 256)])
 def test_rope_kv_write(dtype, heads, kv_heads, dim):
