@@ -92,6 +92,7 @@ struct Params {
   float* partial_ml;    // [seq, head, splits / cluster, 2]
   int* arrivals;        // [seq, kv head * row tiles]: CTAs that have stored their share; zero between launches
   int max_blocks, num_heads, num_kv_heads, page_size, num_pages, window, splits;
+  int page_shift;       // log2(page_size) when that is a power of two, else -1: shifts instead of divisions
   int cluster;          // single tokens: consecutive splits that form one thread-block cluster
   int skip_single;      // portions kernel: leave q_len == 1 to the single-token kernel
   float scale_log2;     // scale * log2(e)
@@ -106,13 +107,14 @@ struct Params {
 __device__ __forceinline__ int lookup_page(const Params& p, const int* table, int j, int lo, int hi, int leave_out) {
   if (j == leave_out) return -2;
   if (j < lo || j > hi) return -1;
-  const int block = j / p.page_size;
+  const int block = p.page_shift >= 0 ? j >> p.page_shift : j / p.page_size;
   return block < p.max_blocks ? table[block] : -1;
 }
 __device__ __forceinline__ long long row_of(const Params& p, int kv_head, int j, int page) {
   if (page == -2) return -2;
   if (page < 0 || page >= p.num_pages) return -1;
-  return (static_cast<long long>(page) * p.page_size + j % p.page_size) * p.num_kv_heads * D + static_cast<long long>(kv_head) * D;
+  const int within = p.page_shift >= 0 ? j & (p.page_size - 1) : j % p.page_size;
+  return (static_cast<long long>(page) * p.page_size + within) * p.num_kv_heads * D + static_cast<long long>(kv_head) * D;
 }
 template <int KEYS>
 __device__ __forceinline__ void locate_tile(long long* rows, const Params& p, const int* table, int kv_head,
@@ -781,6 +783,9 @@ SHRIKE_API int shrike_paged_attention_bf16(const void* q, const void* k_cache, c
   p.num_heads = num_heads;
   p.num_kv_heads = num_kv_heads;
   p.page_size = page_size;
+  p.page_shift = -1;
+  for (int shift = 0; shift < 31; ++shift)
+    if ((1 << shift) == page_size) p.page_shift = shift;
   p.num_pages = num_pages;
   p.window = window;
   p.splits = has_single ? splits : 1;
