@@ -128,14 +128,22 @@ __device__ __forceinline__ void locate_tile(long long* rows, const Params& p, co
 // Copies the located keys and values into k_tile / v_tile; consecutive threads take
 // consecutive 16-byte chunks of a row, so a warp's copies cover whole 128-byte lines.
 // Keys without a row become zeros.
-template <int KEYS>
+template <int KEYS, int NTHREADS>
 __device__ __forceinline__ void copy_tile(bf16* k_tile, bf16* v_tile, const Params& p, const long long* rows) {
-  for (int c = threadIdx.x; c < KEYS * CHUNKS; c += blockDim.x) {
+  constexpr int ROUNDS = (KEYS * CHUNKS + NTHREADS - 1) / NTHREADS;
+  long long row[ROUNDS];
+#pragma unroll
+  for (int i = 0; i < ROUNDS; ++i) {   // every row offset first: the copies then go out back to back
+    const int c = threadIdx.x + i * NTHREADS;
+    row[i] = c < KEYS * CHUNKS ? rows[c / CHUNKS] : -2;
+  }
+#pragma unroll
+  for (int i = 0; i < ROUNDS; ++i) {
+    const int c = threadIdx.x + i * NTHREADS;
     const int key = c / CHUNKS, chunk = c - key * CHUNKS;
-    const long long row = rows[key];
-    if (row == -2) continue;
-    const bool valid = row >= 0;
-    const size_t offset = valid ? static_cast<size_t>(row) + chunk * 8 : 0;
+    if (row[i] == -2) continue;
+    const bool valid = row[i] >= 0;
+    const size_t offset = valid ? static_cast<size_t>(row[i]) + chunk * 8 : 0;
     cp_async16(k_tile + key * ROW + chunk * 8, p.k_cache + offset, valid);
     cp_async16(v_tile + key * ROW + chunk * 8, p.v_cache + offset, valid);
   }
@@ -147,7 +155,7 @@ __device__ __forceinline__ void load_kv_tile(bf16* k_tile, bf16* v_tile, long lo
                                              const int* table, int kv_head, int tile_base, int lo, int hi) {
   locate_tile<KEYS>(rows, p, table, kv_head, tile_base, lo, hi);
   __syncthreads();
-  copy_tile<KEYS>(k_tile, v_tile, p, rows);
+  copy_tile<KEYS, THREADS>(k_tile, v_tile, p, rows);
 }
 
 // S[16 x (8 * NT)] += Q[16 x D] * K^T for keys [key0, key0 + 8 * NT) of the tile.
@@ -409,7 +417,7 @@ __global__ void __launch_bounds__(STHREADS, D <= 128 ? 2 : 1) single_token_kerne
     // one commit group per tile, also when there is no tile left, so that the count is uniform
 #pragma unroll
     for (int ahead = 0; ahead < ST - 1; ++ahead) {
-      if (my_lo + ahead <= my_hi) copy_tile<BN>(k_tiles + ahead * BN * ROW, v_tiles + ahead * BN * ROW, p, tile_rows[ahead]);
+      if (my_lo + ahead <= my_hi) copy_tile<BN, STHREADS>(k_tiles + ahead * BN * ROW, v_tiles + ahead * BN * ROW, p, tile_rows[ahead]);
       cp_async_commit();
     }
   }
@@ -458,7 +466,7 @@ __global__ void __launch_bounds__(STHREADS, D <= 128 ? 2 : 1) single_token_kerne
       __syncthreads();
       if (ahead <= my_hi) {
         const int into = (ahead - my_lo) % ST;
-        copy_tile<BN>(k_tiles + into * BN * ROW, v_tiles + into * BN * ROW, p, tile_rows[(ahead - my_lo) % (ST + 1)]);
+        copy_tile<BN, STHREADS>(k_tiles + into * BN * ROW, v_tiles + into * BN * ROW, p, tile_rows[(ahead - my_lo) % (ST + 1)]);
       }
       cp_async_commit();
       if (threadIdx.x < BN) {
@@ -471,7 +479,7 @@ __global__ void __launch_bounds__(STHREADS, D <= 128 ? 2 : 1) single_token_kerne
       const bf16* v_tile = v_tiles + buffer * BN * ROW;
       // scores of this warp's keys: S[16 x 8] = Q[16 x D] K^T
       const int key0 = warp * WARP_KEYS;
-      float sc[4] = {0.f, 0.f, 0.f, 0.f};
+      float sc[4] = {0.f, 0.f, 0.f, 0.f}, sc_odd[4] = {0.f, 0.f, 0.f, 0.f};   // two chains of dependent MMAs, not one
 #pragma unroll
       for (int kk = 0; kk < KSTEPS; ++kk) {
         unsigned a[4], b[2];
@@ -482,8 +490,11 @@ __global__ void __launch_bounds__(STHREADS, D <= 128 ? 2 : 1) single_token_kerne
           ldmatrix_x4(a, q_tile + ((lane & 7) + 8 * ((lane >> 3) & 1)) * ROW + kk * 16 + 8 * (lane >> 4));
         }
         ldmatrix_x2(b, k_tile + (key0 + (lane & 7)) * ROW + kk * 16 + 8 * ((lane >> 3) & 1));
-        mma_bf16(sc, a, b[0], b[1]);
+        if (kk & 1) mma_bf16(sc_odd, a, b[0], b[1]);
+        else mma_bf16(sc, a, b[0], b[1]);
       }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sc[e] += sc_odd[e];
       // mask, scale, and this warp's maximum per row
       float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
