@@ -25,6 +25,7 @@
 // Built once per head size: -DSHRIKE_HEAD_DIM=<multiple of 16, at most 256>.
 #include <cooperative_groups.h>
 
+#include "blackwell.cuh"
 #include "common.cuh"
 
 #ifndef SHRIKE_HEAD_DIM
@@ -94,6 +95,7 @@ struct Params {
   int max_blocks, num_heads, num_kv_heads, page_size, num_pages, window, splits;
   int page_shift;       // log2(page_size) when that is a power of two, else -1: shifts instead of divisions
   int cluster;          // single tokens: consecutive splits that form one thread-block cluster
+  int* status;          // host-visible; a wait that ran out leaves ERR_TILE_WAIT here
   int skip_single;      // portions kernel: leave q_len == 1 to the single-token kernel
   float scale_log2;     // scale * log2(e)
 };
@@ -251,7 +253,7 @@ __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&o)[DTI
 
 // ------------------------------------------------------------------ portions
 __global__ void __launch_bounds__(THREADS, D <= 128 ? 4 : 2) portions_kernel(const Params p) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
   bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);           // [BM][ROW]
   bf16* k_tiles = q_tile + BM * ROW;                          // [2][PBN][ROW]
   bf16* v_tiles = k_tiles + 2 * PBN * ROW;                    // [2][PBN][ROW]
@@ -356,19 +358,43 @@ constexpr size_t SINGLE_EXCHANGE_SMEM = sizeof(bf16) * 16 * PROW + sizeof(float)
 // sits in registers, where that space suffices (two CTAs of head size 128 fill an SM's shared
 // memory to the last kilobyte); otherwise they lie behind the key and value tiles.
 constexpr bool EXCHANGE_OVER_QUERY = Q_IN_REGS && SINGLE_EXCHANGE_SMEM <= sizeof(bf16) * 16 * ROW;
+// Two ways to bring a tile of keys and values in.  COPIES: sixteen-byte cp.async copies row by
+// row through the block table, into padded rows; any head size, any page size.  PAGES: one
+// tensor-map (TMA) load per page and 64-column half into dense, 128-byte-swizzled tiles, issued
+// by one thread: the other warps spend no instruction on moving data, which is what bounds the
+// COPIES form when a CTA walks many tiles (each tile is 2,048 copies through the load-store
+// unit).  PAGES wants head sizes that are multiples of 64 and pages of 8, 16, 32 or 64 tokens.
+constexpr bool CAN_PAGES = D % 64 == 0;
+constexpr int HALVES = D / 64;
+constexpr int ERR_TILE_WAIT = 21, ERR_TILE_ALIGNMENT = 22;
+
+// The 8-element chunk that holds element d (a multiple of 8) of key `key` in a tile.
+template <bool PAGES>
+__device__ __forceinline__ bf16* tile_chunk(bf16* tile, int key, int d) {
+  if (PAGES) return tile + ((d >> 6) * BN + key) * 64 + ((((d & 63) >> 3) ^ (key & 7)) << 3);
+  return tile + key * ROW + d;
+}
 
 // The warps split a tile's keys for Q K^T and the head dimension for P V; the probabilities
 // pass through shared memory in between.  So each warp keeps only its columns of the output
 // (a few registers), twice as many warps fit as with a whole output row per warp, and nothing
 // is merged across warps when the keys run out.
-__global__ void __launch_bounds__(STHREADS, D <= 128 ? 2 : 1) single_token_kernel(const Params p) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+template <bool PAGES>
+__global__ void __launch_bounds__(STHREADS, D <= 128 ? 2 : 1)
+single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const Params p) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ int is_last;
-  __shared__ long long tile_rows[ST + 1][BN];
-  bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);           // [16][ROW]
-  bf16* k_tiles = q_tile + 16 * ROW;                          // [ST][BN][ROW]
-  bf16* v_tiles = k_tiles + ST * BN * ROW;
-  unsigned char* exchange = EXCHANGE_OVER_QUERY ? smem_raw : reinterpret_cast<unsigned char*>(v_tiles + ST * BN * ROW);
+  __shared__ int give_up;
+  __shared__ long long tile_rows[PAGES ? 1 : ST + 1][PAGES ? 1 : BN];
+  __shared__ unsigned long long tile_full[ST];   // PAGES: a stage's pages have all arrived
+  constexpr int TILE = PAGES ? BN * D : BN * ROW;   // elements of one key (or value) tile
+  // COPIES: query tile, then the key and value stages.  PAGES: the stages first (the swizzle
+  // wants them on 1 KiB boundaries), then the query tile and the exchange space.
+  bf16* k_tiles = reinterpret_cast<bf16*>(smem_raw) + (PAGES ? 0 : 16 * ROW);   // [ST][TILE]
+  bf16* v_tiles = k_tiles + ST * TILE;
+  bf16* q_tile = PAGES ? v_tiles + ST * TILE : reinterpret_cast<bf16*>(smem_raw);   // [16][ROW]
+  unsigned char* exchange = PAGES ? reinterpret_cast<unsigned char*>(q_tile + 16 * ROW)
+                                  : (EXCHANGE_OVER_QUERY ? smem_raw : reinterpret_cast<unsigned char*>(v_tiles + ST * TILE));
   bf16* probs = reinterpret_cast<bf16*>(exchange);                                 // [16][PROW]
   float* warp_max = reinterpret_cast<float*>(exchange + sizeof(bf16) * 16 * PROW); // [SW][16]
   float* warp_sum = warp_max + SW * 16;                                            // [SW][16]
@@ -407,7 +433,58 @@ __global__ void __launch_bounds__(STHREADS, D <= 128 ? 2 : 1) single_token_kerne
   float row_max[2] = {-INFINITY, -INFINITY};   // the same in every warp
   float row_sum[2] = {0.f, 0.f};               // this thread's share: its keys only
 
-  if (my_lo <= my_hi) {
+  // PAGES: every warp brings in its share of a tile.  Lane j of each warp looks up page j of the
+  // tile in the block table (-1: no key of [first_key, last_key] lies there, or the sequence
+  // holds no such page); the tile's loads (page x 64-column half x key-or-value) are dealt out
+  // over the warps, a lane each.  The copy engine takes them in one after the other (about
+  // 50 ns apiece): issued by one warp they held that warp, and with it the CTA, for most of a
+  // microsecond per tile; spread out, each warp hands in its one or two and goes on.
+  const int pages_per_tile = PAGES ? BN >> p.page_shift : 1;
+  auto lookup_page_of_lane = [&](int tile) -> int {
+    if (lane >= pages_per_tile) return -1;
+    const int block = tile * pages_per_tile + lane;
+    const int lo = block << p.page_shift, hi = lo + p.page_size - 1;
+    if (hi < first_key || lo > last_key || block >= p.max_blocks) return -1;
+    return table[block];   // used (and checked) a round later: nothing here waits for the load
+  };
+  auto issue_pages = [&](int stage, int page_of_lane, bool after_stores) {   // every warp calls this, all lanes
+    if (page_of_lane >= p.num_pages) page_of_lane = -1;
+    const unsigned holders = __ballot_sync(0xffffffffu, page_of_lane >= 0);
+    // the copy engine is about to write where ordinary stores have been (value rows cleared in a
+    // sequence's first tile): those must be out of its way.  Reads alone need no such fence.
+    if (after_stores) bw::fence_async_shared();
+    if (warp == 0 && lane == 0) {   // the one arrival of the phase; loads of other warps may land before it
+      if (holders == 0) bw::mbar_arrive(&tile_full[stage]);
+      else bw::mbar_expect_tx(&tile_full[stage], static_cast<unsigned>(__popc(holders)) * p.page_size * D * 2u * sizeof(bf16));
+    }
+    __syncwarp();
+    const int loads = pages_per_tile * HALVES * 2, share = (loads + SW - 1) / SW;
+    for (int base = 0; base < share; base += 32) {
+      const int mine = base + lane, index = warp * share + mine;
+      const int j = min(index / (HALVES * 2), pages_per_tile - 1), rest = index % (HALVES * 2);
+      const int page = __shfl_sync(0xffffffffu, page_of_lane, j);
+      if (mine < share && index < loads && page >= 0) {
+        const int h = rest >> 1;
+        const int at = stage * TILE + (h * BN + j * p.page_size) * 64;
+        if (rest & 1) bw::tma_load_2d(v_tiles + at, &map_v, &tile_full[stage], kv_head * D + h * 64, page * p.page_size);
+        else bw::tma_load_2d(k_tiles + at, &map_k, &tile_full[stage], kv_head * D + h * 64, page * p.page_size);
+      }
+    }
+  };
+  if (PAGES) {
+    if (threadIdx.x == 0) {
+      for (int stage = 0; stage < ST; ++stage) bw::mbar_init(&tile_full[stage], 1);
+      give_up = 0;
+      bw::mbar_init_fence();
+      if ((bw::smem_u32(smem_raw) & 1023u) && p.status != nullptr) *p.status = ERR_TILE_ALIGNMENT;
+    }
+    __syncthreads();
+    // the first ST - 1 tiles ahead of the wait; the row of the newest key in them is stale and
+    // is copied again after the wait
+#pragma unroll
+    for (int ahead = 0; ahead < ST - 1; ++ahead)
+      if (my_lo + ahead <= my_hi) issue_pages(ahead, lookup_page_of_lane(my_lo + ahead), false);
+  } else if (my_lo <= my_hi) {
     // rows of the first ST - 1 tiles without the newest key, and their copies, ahead of the wait
 #pragma unroll
     for (int ahead = 0; ahead < ST - 1; ++ahead)
@@ -417,7 +494,7 @@ __global__ void __launch_bounds__(STHREADS, D <= 128 ? 2 : 1) single_token_kerne
     // one commit group per tile, also when there is no tile left, so that the count is uniform
 #pragma unroll
     for (int ahead = 0; ahead < ST - 1; ++ahead) {
-      if (my_lo + ahead <= my_hi) copy_tile<BN, STHREADS>(k_tiles + ahead * BN * ROW, v_tiles + ahead * BN * ROW, p, tile_rows[ahead]);
+      if (my_lo + ahead <= my_hi) copy_tile<BN, STHREADS>(k_tiles + ahead * TILE, v_tiles + ahead * TILE, p, tile_rows[ahead]);
       cp_async_commit();
     }
   }
@@ -431,24 +508,29 @@ __global__ void __launch_bounds__(STHREADS, D <= 128 ? 2 : 1) single_token_kerne
     }
     // the newest key, when its tile is one of those copied above
     const int newest_tile = last_key / BN;
-    if (newest_tile >= my_lo && newest_tile - my_lo < ST - 1 && threadIdx.x < CHUNKS) {
+    const bool newest_copied = newest_tile >= my_lo && newest_tile <= my_hi && newest_tile - my_lo < ST - 1;
+    if (PAGES && newest_copied)   // its page must have landed before the row is replaced
+      bw::mbar_wait(&tile_full[newest_tile - my_lo], 0, &give_up, p.status, ERR_TILE_WAIT);
+    if (newest_copied && threadIdx.x < CHUNKS) {
       const int block = last_key / p.page_size;
       const int page = block < p.max_blocks ? table[block] : -1;
       const bool valid = page >= 0 && page < p.num_pages;
       const size_t offset = valid ? (static_cast<size_t>(page) * p.page_size + (last_key - block * p.page_size)) * p.num_kv_heads * D +
                                         static_cast<size_t>(kv_head) * D + threadIdx.x * 8 : 0;
-      const int at = ((newest_tile - my_lo) * BN + (last_key - newest_tile * BN)) * ROW + threadIdx.x * 8;
-      cp_async16(k_tiles + at, p.k_cache + offset, valid);
-      cp_async16(v_tiles + at, p.v_cache + offset, valid);
+      const int stage = newest_tile - my_lo, key = last_key - newest_tile * BN;
+      cp_async16(tile_chunk<PAGES>(k_tiles + stage * TILE, key, threadIdx.x * 8), p.k_cache + offset, valid);
+      cp_async16(tile_chunk<PAGES>(v_tiles + stage * TILE, key, threadIdx.x * 8), p.v_cache + offset, valid);
     }
     cp_async_commit();
-    if (my_lo + ST - 1 <= my_hi)   // copied by the first round of the loop
+    if (!PAGES && my_lo + ST - 1 <= my_hi)   // copied by the first round of the loop
       locate_tile<BN>(tile_rows[ST - 1], p, table, kv_head, (my_lo + ST - 1) * BN, first_key, last_key);
     // The table lookup for a tile is issued one round before its rows are stored, which is
     // one more round before they are copied: no round waits for a lookup of its own.
     int pending_page = -1;
-    if (my_lo + ST <= my_hi && threadIdx.x < BN)
+    if (!PAGES && my_lo + ST <= my_hi && threadIdx.x < BN)
       pending_page = lookup_page(p, table, (my_lo + ST) * BN + threadIdx.x, first_key, last_key, -1);
+    int page_ahead = -1;   // PAGES: lane j's page of the tile that the next round loads
+    if (PAGES && my_lo + ST - 1 <= my_hi) page_ahead = lookup_page_of_lane(my_lo + ST - 1);
     cp_async_wait<0>();
     __syncthreads();
     unsigned q_frag[Q_IN_REGS ? KSTEPS : 1][4];
@@ -460,23 +542,42 @@ __global__ void __launch_bounds__(STHREADS, D <= 128 ? 2 : 1) single_token_kerne
     for (int tile = my_lo; tile <= my_hi; ++tile) {
       const int buffer = (tile - my_lo) % ST;
       const int ahead = tile + ST - 1;
-      // every warp is done with the tile before (its buffer is loaded into next), and, in the
-      // first round, with reading the query out of the space the probabilities take
-      cp_async_wait<ST - 2>();
+      // this tile has arrived; every warp is done with the tile before (its buffer is loaded into
+      // next), and, in the first round, with reading the query out of the space the probabilities take
+      if (PAGES) bw::mbar_wait(&tile_full[buffer], ((tile - my_lo) / ST) & 1, &give_up, p.status, ERR_TILE_WAIT);
+      else cp_async_wait<ST - 2>();
       __syncthreads();
-      if (ahead <= my_hi) {
+      if (PAGES && give_up) break;   // a load that never landed is reported, not waited for; all leave together
+      if (PAGES) {
+        if (ahead <= my_hi) {
+          issue_pages((ahead - my_lo) % ST, page_ahead, (ahead - ST) * BN < first_key);
+          page_ahead = ahead + 1 <= my_hi ? lookup_page_of_lane(ahead + 1) : -1;   // used one round from now
+        }
+        // Pages come whole: rows of keys outside [first_key, last_key] hold whatever the pool holds
+        // (or nothing was loaded for them).  Their probabilities are zero, but zero times a stray
+        // NaN is NaN, so those value rows are cleared.  Only a sequence's first and last tiles have any.
+        if (tile * BN < first_key || tile * BN + BN - 1 > last_key) {
+          for (int c = threadIdx.x; c < BN * CHUNKS; c += STHREADS) {
+            const int key = c / CHUNKS, chunk = c - key * CHUNKS;
+            const int position = tile * BN + key;
+            if (position < first_key || position > last_key)
+              *reinterpret_cast<uint4*>(tile_chunk<PAGES>(v_tiles + buffer * TILE, key, chunk * 8)) = make_uint4(0u, 0u, 0u, 0u);
+          }
+          __syncthreads();
+        }
+      } else if (ahead <= my_hi) {
         const int into = (ahead - my_lo) % ST;
-        copy_tile<BN, STHREADS>(k_tiles + into * BN * ROW, v_tiles + into * BN * ROW, p, tile_rows[(ahead - my_lo) % (ST + 1)]);
+        copy_tile<BN, STHREADS>(k_tiles + into * TILE, v_tiles + into * TILE, p, tile_rows[(ahead - my_lo) % (ST + 1)]);
       }
-      cp_async_commit();
-      if (threadIdx.x < BN) {
+      if (!PAGES) cp_async_commit();
+      if (!PAGES && threadIdx.x < BN) {
         if (ahead + 1 <= my_hi)   // read in the next round, after its opening barrier
           tile_rows[(ahead + 1 - my_lo) % (ST + 1)][threadIdx.x] = row_of(p, kv_head, (ahead + 1) * BN + threadIdx.x, pending_page);
         if (ahead + 2 <= my_hi)
           pending_page = lookup_page(p, table, (ahead + 2) * BN + threadIdx.x, first_key, last_key, -1);
       }
-      const bf16* k_tile = k_tiles + buffer * BN * ROW;
-      const bf16* v_tile = v_tiles + buffer * BN * ROW;
+      bf16* k_tile = k_tiles + buffer * TILE;
+      bf16* v_tile = v_tiles + buffer * TILE;
       // scores of this warp's keys: S[16 x 8] = Q[16 x D] K^T
       const int key0 = warp * WARP_KEYS;
       float sc[4] = {0.f, 0.f, 0.f, 0.f}, sc_odd[4] = {0.f, 0.f, 0.f, 0.f};   // two chains of dependent MMAs, not one
@@ -489,7 +590,7 @@ __global__ void __launch_bounds__(STHREADS, D <= 128 ? 2 : 1) single_token_kerne
         } else {
           ldmatrix_x4(a, q_tile + ((lane & 7) + 8 * ((lane >> 3) & 1)) * ROW + kk * 16 + 8 * (lane >> 4));
         }
-        ldmatrix_x2(b, k_tile + (key0 + (lane & 7)) * ROW + kk * 16 + 8 * ((lane >> 3) & 1));
+        ldmatrix_x2(b, tile_chunk<PAGES>(k_tile, key0 + (lane & 7), kk * 16 + 8 * ((lane >> 3) & 1)));
         if (kk & 1) mma_bf16(sc_odd, a, b[0], b[1]);
         else mma_bf16(sc, a, b[0], b[1]);
       }
@@ -552,14 +653,14 @@ __global__ void __launch_bounds__(STHREADS, D <= 128 ? 2 : 1) single_token_kerne
           for (int kk = 0; kk < BN / 16; ++kk) {
             unsigned a[4], b[4];
             ldmatrix_x4(a, probs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * PROW + kk * 16 + 8 * (lane >> 4));
-            ldmatrix_x4_trans(b, v_tile + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * ROW + pair * 16 + 8 * (lane >> 4));
+            ldmatrix_x4_trans(b, tile_chunk<PAGES>(v_tile, kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), pair * 16 + 8 * (lane >> 4)));
             mma_bf16(o[i][0], a, b[0], b[1]);
             mma_bf16(o[i][1], a, b[2], b[3]);
           }
         }
       }
     }
-    cp_async_wait<0>();
+    if (!PAGES) cp_async_wait<0>();
   }
   // every row's sum: the threads' shares over the quad, then over the warps
 #pragma unroll
@@ -737,8 +838,14 @@ constexpr size_t PORTIONS_SMEM = sizeof(bf16) * (BM * ROW + 4 * PBN * ROW);
 constexpr size_t SINGLE_TILES_SMEM = sizeof(bf16) * (16 * ROW + 2 * ST * BN * ROW) + (EXCHANGE_OVER_QUERY ? 0 : SINGLE_EXCHANGE_SMEM);
 constexpr size_t SINGLE_MERGE_SMEM = sizeof(float) * (16 * D + 32);
 constexpr size_t SINGLE_SMEM = SINGLE_TILES_SMEM > SINGLE_MERGE_SMEM ? SINGLE_TILES_SMEM : SINGLE_MERGE_SMEM;
+constexpr size_t SINGLE_PAGES_TILES_SMEM = sizeof(bf16) * (2 * ST * BN * D + 16 * ROW) + SINGLE_EXCHANGE_SMEM;
+constexpr size_t SINGLE_PAGES_SMEM = SINGLE_PAGES_TILES_SMEM > SINGLE_MERGE_SMEM ? SINGLE_PAGES_TILES_SMEM : SINGLE_MERGE_SMEM;
 
 }  // namespace bf16attn
+
+// Whether single tokens may take the PAGES form (tensor-map loads); off: always COPIES.
+static int g_single_token_pages = 1;
+SHRIKE_API void shrike_attention_single_token_pages(int enabled) { g_single_token_pages = enabled ? 1 : 0; }
 
 // Scratch the single-token path needs, in floats: partial outputs and (max, sum) pairs,
 // one per cluster of splits.
@@ -764,7 +871,7 @@ SHRIKE_API int shrike_paged_attention_bf16(const void* q, const void* k_cache, c
                                            const int* ctx_len, int num_seqs, int num_heads, int num_kv_heads,
                                            int page_size, int num_pages, float scale, int window, void* out,
                                            int has_single, int has_portions, int max_q_len, int splits,
-                                           int cluster, float* scratch, int* arrivals, cudaStream_t stream) {
+                                           int cluster, float* scratch, int* arrivals, int* status, cudaStream_t stream) {
   using namespace bf16attn;
   if (num_seqs <= 0) return SHRIKE_OK;
   if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || page_size <= 0 || max_blocks <= 0 ||
@@ -778,8 +885,12 @@ SHRIKE_API int shrike_paged_attention_bf16(const void* q, const void* k_cache, c
   static bool configured = false;
   if (!configured) {
     cudaError_t e1 = cudaFuncSetAttribute(portions_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(PORTIONS_SMEM));
-    cudaError_t e2 = cudaFuncSetAttribute(single_token_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SINGLE_SMEM));
+    cudaError_t e2 = cudaFuncSetAttribute(single_token_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SINGLE_SMEM));
     if (e1 != cudaSuccess || e2 != cudaSuccess) return static_cast<int>(e1 != cudaSuccess ? e1 : e2);
+    if (CAN_PAGES) {
+      cudaError_t e3 = cudaFuncSetAttribute(single_token_kernel<CAN_PAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SINGLE_PAGES_SMEM));
+      if (e3 != cudaSuccess) return static_cast<int>(e3);
+    }
     configured = true;
   }
   Params p;
@@ -806,10 +917,19 @@ SHRIKE_API int shrike_paged_attention_bf16(const void* q, const void* k_cache, c
   p.partial_out = scratch;
   p.partial_ml = scratch ? scratch + static_cast<size_t>(num_seqs) * num_heads * (p.splits / p.cluster) * D : nullptr;
   p.arrivals = arrivals;
+  p.status = status;
   if (has_single) {
     const int group = num_heads / num_kv_heads;
     const dim3 grid(p.splits, num_kv_heads * ((group + 15) / 16), num_seqs);
-    launch_dependent_clusters(single_token_kernel, grid, STHREADS, SINGLE_SMEM, stream, p.cluster, p);
+    CUtensorMap map_k = {}, map_v = {};
+    bool pages = CAN_PAGES && g_single_token_pages && p.page_shift >= 3 && p.page_shift <= 6;
+    if (pages) {   // one row of the map per cache slot, all kv heads side by side
+      const long long slots = static_cast<long long>(num_pages) * page_size;
+      pages = bw::tensor_map_bf16(k_cache, slots, num_kv_heads * D, page_size, &map_k) == SHRIKE_OK &&
+              bw::tensor_map_bf16(v_cache, slots, num_kv_heads * D, page_size, &map_v) == SHRIKE_OK;
+    }
+    if (pages) launch_dependent_clusters(single_token_kernel<CAN_PAGES>, grid, STHREADS, SINGLE_PAGES_SMEM, stream, p.cluster, map_k, map_v, p);
+    else launch_dependent_clusters(single_token_kernel<false>, grid, STHREADS, SINGLE_SMEM, stream, p.cluster, map_k, map_v, p);
   }
   if (has_portions) {
     const dim3 grid((max_q_len + BM - 1) / BM, num_heads, num_seqs);

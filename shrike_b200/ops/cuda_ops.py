@@ -118,9 +118,11 @@ class CudaOps:
             )
             lib.shrike_paged_attention_generic.restype = _I
             lib.shrike_paged_attention_bf16.argtypes = (
-                [_P, _P, _P, _P, _I, _P, _P] + [_I] * 5 + [_F, _I, _P] + [_I] * 5 + [_P, _P, _P]
+                [_P, _P, _P, _P, _I, _P, _P] + [_I] * 5 + [_F, _I, _P] + [_I] * 5 + [_P, _P, _P, _P]
             )
             lib.shrike_paged_attention_bf16.restype = _I
+            lib.shrike_attention_single_token_pages.argtypes = [_I]
+            lib.shrike_attention_single_token_pages.restype = None
             lib.shrike_attention_bf16_resident_ctas.restype = _I
             lib.shrike_attention_tc_available.restype = _I
             lib.shrike_paged_attention_tc_portions.argtypes = (
@@ -334,7 +336,7 @@ class CudaOps:
             _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), max_blocks, _ptr(q_start), _ptr(ctx_len),
             num_seqs, num_heads, num_kv_heads, page_size, num_pages, scale, window or 0, _ptr(out),
             int(has_single), int(has_portions), max_q_len, splits, cluster, _ptr(scratch), _ptr(arrivals),
-            self._stream()),
+            _ptr(self.status), self._stream()),
             "paged_attention_bf16")
 
     @staticmethod

@@ -385,6 +385,36 @@ def test_single_token_attention_under_every_split_and_cluster_shape(splits, clus
     assert int(ops._arrivals.abs().sum()) == 0
 
 
+@pytest.mark.parametrize("window", [None, 40])
+@pytest.mark.parametrize("heads,kv_heads,dim,page", [(28, 4, 128, 16), (40, 2, 64, 8), (4, 2, 256, 64), (8, 2, 128, 32), (6, 3, 64, 16)])
+def test_single_token_attention_by_pages_and_by_copies(heads, kv_heads, dim, page, window):
+    """Head sizes that are multiples of 64 with pages of 8 to 64 tokens load whole pages through
+    tensor maps; the same launch can be made to copy row by row.  Both give the attention of the
+    plain formula, on a pool whose unwritten slots hold NaN, with a window that has let pages go."""
+    ops = cuda_ops(torch.bfloat16)
+    lib = ops._attention_lib(dim)
+    ctx_lens = [1, 63, 64, 65, 129, 700, 1500, 2100]
+    q_lens = [1] * len(ctx_lens)
+    case = paged_case(torch.bfloat16, heads, kv_heads, dim, page, ctx_lens, q_lens, seed=9)
+    if window is not None:   # pages the window has passed are gone: the kernel must not touch them
+        for s, ctx in enumerate(ctx_lens):
+            for b in range(max(0, ctx - window) // page):
+                case["keys"][int(case["table"][s, b])] = float("nan")
+                case["values"][int(case["table"][s, b])] = float("nan")
+                case["table"][s, b] = -1
+    results = {}
+    try:
+        for form, enabled in (("pages", 1), ("copies", 0)):
+            lib.shrike_attention_single_token_pages(enabled)
+            got, want = run_attention(ops, case, heads, kv_heads, dim, window, q_lens, ctx_lens)
+            close(got, want, 2e-2, 0, f"single tokens by {form}")
+            results[form] = got.clone()
+    finally:
+        lib.shrike_attention_single_token_pages(1)
+    close(results["pages"], results["copies"].double(), 2e-2, 0, "the two forms")
+    ops.check_status()
+
+
 def test_widths_beyond_one_block_are_refused_not_miscomputed():
     from shrike_b200.ops.cuda_ops import KernelError
 
