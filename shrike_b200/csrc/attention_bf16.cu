@@ -379,8 +379,13 @@ __device__ __forceinline__ bf16* tile_chunk(bf16* tile, int key, int d) {
 // pass through shared memory in between.  So each warp keeps only its columns of the output
 // (a few registers), twice as many warps fit as with a whole output row per warp, and nothing
 // is merged across warps when the keys run out.
+// PAGES adds a ninth warp that does nothing but hand a tile's loads to the copy engine (each
+// takes the issuing warp a few hundred cycles), so the eight others never wait on that.
+constexpr int PAGES_THREADS = STHREADS + 32;
+__device__ __forceinline__ void math_warps_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(STHREADS) : "memory"); }
+
 template <bool PAGES>
-__global__ void __launch_bounds__(STHREADS, D <= 128 ? 2 : 1)
+__global__ void __launch_bounds__(PAGES ? PAGES_THREADS : STHREADS, D <= 128 ? 2 : 1)
 single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const Params p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ int is_last;
@@ -388,6 +393,7 @@ single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   __shared__ long long tile_rows[PAGES ? 1 : ST + 1][PAGES ? 1 : BN];
   __shared__ unsigned long long tile_full[ST];   // PAGES: a stage's pages have all arrived
   constexpr int TILE = PAGES ? BN * D : BN * ROW;   // elements of one key (or value) tile
+  constexpr int NT = PAGES ? PAGES_THREADS : STHREADS;
   // COPIES: query tile, then the key and value stages.  PAGES: the stages first (the swizzle
   // wants them on 1 KiB boundaries), then the query tile and the exchange space.
   bf16* k_tiles = reinterpret_cast<bf16*>(smem_raw) + (PAGES ? 0 : 16 * ROW);   // [ST][TILE]
@@ -433,12 +439,11 @@ single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   float row_max[2] = {-INFINITY, -INFINITY};   // the same in every warp
   float row_sum[2] = {0.f, 0.f};               // this thread's share: its keys only
 
-  // PAGES: every warp brings in its share of a tile.  Lane j of each warp looks up page j of the
-  // tile in the block table (-1: no key of [first_key, last_key] lies there, or the sequence
-  // holds no such page); the tile's loads (page x 64-column half x key-or-value) are dealt out
-  // over the warps, a lane each.  The copy engine takes them in one after the other (about
-  // 50 ns apiece): issued by one warp they held that warp, and with it the CTA, for most of a
-  // microsecond per tile; spread out, each warp hands in its one or two and goes on.
+  // PAGES: the ninth warp brings the tiles in.  Its lane j looks up page j of a tile in the block
+  // table (-1: no key of [first_key, last_key] lies there, or the sequence holds no such page);
+  // then each lane issues one of the tile's loads (page x 64-column half x key-or-value).  The
+  // copy engine takes them in one after the other (about 50 ns apiece), which holds the issuing
+  // warp for most of a microsecond per tile: hence a warp of its own.
   const int pages_per_tile = PAGES ? BN >> p.page_shift : 1;
   auto lookup_page_of_lane = [&](int tile) -> int {
     if (lane >= pages_per_tile) return -1;
@@ -447,23 +452,23 @@ single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     if (hi < first_key || lo > last_key || block >= p.max_blocks) return -1;
     return table[block];   // used (and checked) a round later: nothing here waits for the load
   };
-  auto issue_pages = [&](int stage, int page_of_lane, bool after_stores) {   // every warp calls this, all lanes
+  auto issue_pages = [&](int stage, int page_of_lane, bool after_stores) {   // the loading warp, all lanes
     if (page_of_lane >= p.num_pages) page_of_lane = -1;
     const unsigned holders = __ballot_sync(0xffffffffu, page_of_lane >= 0);
     // the copy engine is about to write where ordinary stores have been (value rows cleared in a
     // sequence's first tile): those must be out of its way.  Reads alone need no such fence.
     if (after_stores) bw::fence_async_shared();
-    if (warp == 0 && lane == 0) {   // the one arrival of the phase; loads of other warps may land before it
+    if (lane == 0) {   // the one arrival of the phase
       if (holders == 0) bw::mbar_arrive(&tile_full[stage]);
       else bw::mbar_expect_tx(&tile_full[stage], static_cast<unsigned>(__popc(holders)) * p.page_size * D * 2u * sizeof(bf16));
     }
     __syncwarp();
-    const int loads = pages_per_tile * HALVES * 2, share = (loads + SW - 1) / SW;
-    for (int base = 0; base < share; base += 32) {
-      const int mine = base + lane, index = warp * share + mine;
+    const int loads = pages_per_tile * HALVES * 2;
+    for (int base = 0; base < loads; base += 32) {
+      const int index = base + lane;
       const int j = min(index / (HALVES * 2), pages_per_tile - 1), rest = index % (HALVES * 2);
       const int page = __shfl_sync(0xffffffffu, page_of_lane, j);
-      if (mine < share && index < loads && page >= 0) {
+      if (index < loads && page >= 0) {
         const int h = rest >> 1;
         const int at = stage * TILE + (h * BN + j * p.page_size) * 64;
         if (rest & 1) bw::tma_load_2d(v_tiles + at, &map_v, &tile_full[stage], kv_head * D + h * 64, page * p.page_size);
@@ -481,9 +486,11 @@ single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     __syncthreads();
     // the first ST - 1 tiles ahead of the wait; the row of the newest key in them is stale and
     // is copied again after the wait
+    if (warp == SW) {
 #pragma unroll
-    for (int ahead = 0; ahead < ST - 1; ++ahead)
-      if (my_lo + ahead <= my_hi) issue_pages(ahead, lookup_page_of_lane(my_lo + ahead), false);
+      for (int ahead = 0; ahead < ST - 1; ++ahead)
+        if (my_lo + ahead <= my_hi) issue_pages(ahead, lookup_page_of_lane(my_lo + ahead), false);
+    }
   } else if (my_lo <= my_hi) {
     // rows of the first ST - 1 tiles without the newest key, and their copies, ahead of the wait
 #pragma unroll
@@ -500,7 +507,7 @@ single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   }
   wait_for_previous();
   if (my_lo <= my_hi) {
-    for (int c = threadIdx.x; c < 16 * CHUNKS; c += STHREADS) {
+    for (int c = threadIdx.x; c < 16 * CHUNKS; c += NT) {
       const int row = c / CHUNKS, chunk = c - row * CHUNKS;
       const bool valid = row < rows_here;
       const bf16* src = p.q + (static_cast<size_t>(start) * p.num_heads + head0 + (valid ? row : 0)) * D + chunk * 8;
@@ -529,12 +536,12 @@ single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     int pending_page = -1;
     if (!PAGES && my_lo + ST <= my_hi && threadIdx.x < BN)
       pending_page = lookup_page(p, table, (my_lo + ST) * BN + threadIdx.x, first_key, last_key, -1);
-    int page_ahead = -1;   // PAGES: lane j's page of the tile that the next round loads
-    if (PAGES && my_lo + ST - 1 <= my_hi) page_ahead = lookup_page_of_lane(my_lo + ST - 1);
+    int page_ahead = -1;   // PAGES, loading warp: lane j's page of the tile that the next round loads
+    if (PAGES && warp == SW && my_lo + ST - 1 <= my_hi) page_ahead = lookup_page_of_lane(my_lo + ST - 1);
     cp_async_wait<0>();
     __syncthreads();
     unsigned q_frag[Q_IN_REGS ? KSTEPS : 1][4];
-    if (Q_IN_REGS) {
+    if (Q_IN_REGS && warp < SW) {
 #pragma unroll
       for (int kk = 0; kk < KSTEPS; ++kk)
         ldmatrix_x4(q_frag[Q_IN_REGS ? kk : 0], q_tile + ((lane & 7) + 8 * ((lane >> 3) & 1)) * ROW + kk * 16 + 8 * (lane >> 4));
@@ -549,21 +556,24 @@ single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       __syncthreads();
       if (PAGES && give_up) break;   // a load that never landed is reported, not waited for; all leave together
       if (PAGES) {
-        if (ahead <= my_hi) {
-          issue_pages((ahead - my_lo) % ST, page_ahead, (ahead - ST) * BN < first_key);
-          page_ahead = ahead + 1 <= my_hi ? lookup_page_of_lane(ahead + 1) : -1;   // used one round from now
-        }
         // Pages come whole: rows of keys outside [first_key, last_key] hold whatever the pool holds
         // (or nothing was loaded for them).  Their probabilities are zero, but zero times a stray
         // NaN is NaN, so those value rows are cleared.  Only a sequence's first and last tiles have any.
         if (tile * BN < first_key || tile * BN + BN - 1 > last_key) {
-          for (int c = threadIdx.x; c < BN * CHUNKS; c += STHREADS) {
+          for (int c = threadIdx.x; c < BN * CHUNKS; c += NT) {
             const int key = c / CHUNKS, chunk = c - key * CHUNKS;
             const int position = tile * BN + key;
             if (position < first_key || position > last_key)
               *reinterpret_cast<uint4*>(tile_chunk<PAGES>(v_tiles + buffer * TILE, key, chunk * 8)) = make_uint4(0u, 0u, 0u, 0u);
           }
           __syncthreads();
+        }
+        if (warp == SW) {   // the loading warp: the next tile's loads, then on to the next round's barrier
+          if (ahead <= my_hi) {
+            issue_pages((ahead - my_lo) % ST, page_ahead, (ahead - ST) * BN < first_key);
+            page_ahead = ahead + 1 <= my_hi ? lookup_page_of_lane(ahead + 1) : -1;   // used one round from now
+          }
+          continue;
         }
       } else if (ahead <= my_hi) {
         const int into = (ahead - my_lo) % ST;
@@ -611,7 +621,8 @@ single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
         if ((lane & 3) == 0) warp_max[warp * 16 + (lane >> 2) + 8 * r] = tile_max[r];
       }
-      __syncthreads();
+      if (PAGES) math_warps_barrier();
+      else __syncthreads();
       // the tile's maximum over all warps, the same sum order everywhere: every warp arrives
       // at the same running maximum and the same correction
       float correction[2], base[2];
@@ -643,7 +654,8 @@ single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
           o[i][j][2] *= correction[1];
           o[i][j][3] *= correction[1];
         }
-      __syncthreads();
+      if (PAGES) math_warps_barrier();
+      else __syncthreads();
       // O[16 x 16 columns] += P[16 x 64] V[64 x 16 columns] for each of this warp's column blocks
 #pragma unroll
       for (int i = 0; i < MY_PAIRS; ++i) {
@@ -668,7 +680,7 @@ single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 1);
     row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 2);
   }
-  if ((lane & 3) == 0) {   // a space of its own: no barrier needed before it is written
+  if ((lane & 3) == 0 && warp < SW) {   // a space of its own: no barrier needed before it is written
     warp_sum[warp * 16 + (lane >> 2)] = row_sum[0];
     warp_sum[warp * 16 + (lane >> 2) + 8] = row_sum[1];
   }
@@ -688,7 +700,7 @@ single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     const int row = (lane >> 2) + 8 * r;
-    if (row >= rows_here) continue;
+    if (row >= rows_here || warp >= SW) continue;
     const float inv = total_sum[r] > 0.f ? 1.0f / total_sum[r] : 0.f;
     const size_t slot = (static_cast<size_t>(seq) * p.num_heads + head0 + row) * p.splits + split;
 #pragma unroll
@@ -730,7 +742,7 @@ single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     const int outputs = rows_here * D;
     const int share = (outputs + p.cluster - 1) / p.cluster;
     const int stop = min(outputs, (rank + 1) * share);
-    for (int idx = rank * share + threadIdx.x; idx < stop; idx += STHREADS) {
+    for (int idx = rank * share + threadIdx.x; idx < stop; idx += NT) {
       const int row = idx / D, d = idx - row * D;
       float peer_max[8], peer_sum[8], peer_o[8];
 #pragma unroll
@@ -789,7 +801,7 @@ single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   // partial order.
   constexpr int QUADS = D / 4;
   const int items = rows_here * QUADS;
-  for (int item = threadIdx.x; item < items; item += STHREADS) {
+  for (int item = threadIdx.x; item < items; item += NT) {
     const int row = item / QUADS, quad = item - row * QUADS;
     float run_max = -INFINITY, run_sum = 0.f;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -928,7 +940,7 @@ SHRIKE_API int shrike_paged_attention_bf16(const void* q, const void* k_cache, c
       pages = bw::tensor_map_bf16(k_cache, slots, num_kv_heads * D, page_size, &map_k) == SHRIKE_OK &&
               bw::tensor_map_bf16(v_cache, slots, num_kv_heads * D, page_size, &map_v) == SHRIKE_OK;
     }
-    if (pages) launch_dependent_clusters(single_token_kernel<CAN_PAGES>, grid, STHREADS, SINGLE_PAGES_SMEM, stream, p.cluster, map_k, map_v, p);
+    if (pages) launch_dependent_clusters(single_token_kernel<CAN_PAGES>, grid, PAGES_THREADS, SINGLE_PAGES_SMEM, stream, p.cluster, map_k, map_v, p);
     else launch_dependent_clusters(single_token_kernel<false>, grid, STHREADS, SINGLE_SMEM, stream, p.cluster, map_k, map_v, p);
   }
   if (has_portions) {
