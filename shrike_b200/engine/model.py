@@ -81,6 +81,8 @@ class DecoderModel:
                 local = _take(tensors, names.layer_part(index, role), cls.parameters(spec))
                 built[role] = cls(spec, local, ops, runtime)
             self.blocks.append(part_class("block", layer.block)(**built))
+            self.capture_safe = getattr(self, "capture_safe", True) and all(
+                getattr(part, "capture_safe", False) for part in (*built.values(), self.blocks[-1]))
         norm = config.final_norm
         cls = part_class("norm", norm.kind)
         self.final_norm = cls(norm, _take(tensors, names.final_norm_prefix, cls.parameters(norm)), ops, runtime)

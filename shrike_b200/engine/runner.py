@@ -24,12 +24,14 @@ TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 class Prepared:
     """A step whose metadata is staged on the host: what `ModelRunner.launch` needs."""
 
-    __slots__ = ("staged", "sample", "graphable")
+    __slots__ = ("staged", "sample", "graphable", "key", "decode")
 
-    def __init__(self, staged, sample: bool, graphable: bool):
+    def __init__(self, staged, sample: bool, graphable: bool, key=None, decode: bool = False):
         self.staged = staged
         self.sample = sample
         self.graphable = graphable
+        self.key = key
+        self.decode = decode
 
 
 class ModelRunner:
@@ -68,7 +70,12 @@ class ModelRunner:
         )
         self.builder = BatchBuilder(page_size, len(self.groups), self.device, self.storage)
         self.use_graphs = True
+        # also capture batches with portions, once their shape repeats: only if every part says that
+        # its forward() depends on the batch's shape alone (`capture_safe`; parts that do not say so,
+        # such as one that branches on a request's position, keep such batches uncaptured)
+        self.capture_portions = bool(getattr(self.model, "capture_safe", False))
         self._graphs: dict = {}
+        self._seen: set = set()
         self._drawn = torch.zeros(4096, dtype=torch.int32, device=self.device)   # the sampled tokens of a step
         self._drawn_generation = 0
         self._fetch_host = [None, None]
@@ -111,11 +118,12 @@ class ModelRunner:
         staged = self.builder.stage(entries, defer=True, ids_missing=ids_missing)
         if sample and not staged.sampled:
             raise ValueError("sample=True needs `sampling` on every entry that wants logits")
-        graphable = (
-            self.use_graphs and self.device.type == "cuda" and max(staged.q_lens) == 1
-            and staged.r == staged.s and all(e.want == [0] for e in entries)
-        )
-        return Prepared(staged, sample, graphable)
+        decode = max(staged.q_lens) == 1 and staged.r == staged.s and all(e.want == [0] for e in entries)
+        graphable = self.use_graphs and self.device.type == "cuda" and (decode or self.capture_portions)
+        # what a captured launch sequence has baked in: the number of entries, every entry's
+        # length (grids and shapes follow from them), the number of wanted rows, the table widths
+        key = (staged.s if decode else tuple(staged.q_lens), staged.r, tuple(staged.max_blocks), sample)
+        return Prepared(staged, sample, graphable, key, decode)
 
     def fill_ids(self, prepared: "Prepared", tokens) -> None:
         self.builder.fill_ids(prepared.staged, tokens)
@@ -154,13 +162,23 @@ class ModelRunner:
         decoding; its launch sequence is captured once per (batch size, table width) as a
         CUDA graph and replayed afterwards, because at small batch the step is bound by
         launch latency otherwise (the remedy shrike's README names for its own per-layer
-        dispatch cost)."""
+        dispatch cost).  Other batches are captured when their exact shape (every entry's
+        length, the wanted rows, the table widths) is seen a second time.  A captured sequence
+        bakes in what the parts computed on the host from the shape; parts must not branch on
+        other host-side values of the step (positions, slots) if they are to be captured."""
         staged, sample, graphable = prepared.staged, prepared.sample, prepared.graphable
         self.builder.commit(staged)
+        key = prepared.key
+        if graphable and not prepared.decode and key not in self._graphs and key not in self._seen:
+            # a batch with portions: captured only when the same shape comes a second time (a long
+            # prompt cut into equal portions, a benchmark's repeats); most mixed batches never repeat
+            if len(self._seen) >= 256:
+                self._seen.clear()
+            self._seen.add(key)
+            graphable = False
         if not graphable:
             logits, tokens = self._run(self.builder.context(staged), sample)
             return (logits, tokens) if sample else logits
-        key = (staged.s, tuple(staged.max_blocks), sample)
         held = self._graphs.get(key)
         if held is not None and held[0] == self._generation():
             held[1].replay()   # the metadata is already on its way; no views are needed

@@ -19,6 +19,8 @@ from .base import KVNeed, ParamSpec, part_class, register_part
 
 
 class PagedAttention:
+    capture_safe = True   # forward() launches the same kernels for the same batch shape, whatever the positions
+
     @staticmethod
     def parameters(spec) -> dict[str, ParamSpec]:
         q_out = spec.num_heads * spec.head_dim

@@ -8,6 +8,8 @@ from .base import register_part
 
 
 class PreNormBlock:
+    capture_safe = True   # forward() launches the same kernels for the same batch shape, whatever the positions
+
     def __init__(self, mixer, mixer_norm, feed_forward, feed_forward_norm):
         self.mixer = mixer
         self.mixer_norm = mixer_norm

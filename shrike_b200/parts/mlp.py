@@ -12,6 +12,8 @@ from .base import ParamSpec, register_part
 
 
 class GatedMLP:
+    capture_safe = True   # forward() launches the same kernels for the same batch shape, whatever the positions
+
     @staticmethod
     def parameters(spec) -> dict[str, ParamSpec]:
         return {

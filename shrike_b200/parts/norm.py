@@ -15,6 +15,8 @@ from .base import ParamSpec, register_part
 
 
 class RMSNorm:
+    capture_safe = True   # forward() launches the same kernels for the same batch shape, whatever the positions
+
     @staticmethod
     def parameters(spec) -> dict[str, ParamSpec]:
         return {"weight": ParamSpec((spec.width,), "norm")}

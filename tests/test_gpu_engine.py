@@ -90,3 +90,47 @@ def test_bfloat16_decode_steps_are_replayed_and_match_eager(tmp_path):
     eager.runner.use_graphs = False
     b = eager.generate(prompts, params)
     assert a == b
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_batches_with_portions_are_captured_when_their_shape_repeats(tmp_path, dtype):
+    """A long prompt cut into equal portions beside a decoding request: from the third such step
+    on the launch sequence is replayed, at other positions and pages than it was captured at;
+    the logits are those of the eager steps."""
+    import torch
+
+    from shrike_b200.config import load_config
+    from shrike_b200.engine.batch import StepEntry
+    from shrike_b200.engine.llm_engine import make_ops
+    from shrike_b200.engine.runner import ModelRunner
+    from shrike_b200.weights import load_weights
+
+    folder = make_model_folder(tmp_path, "C")   # windows on some layers: pages are given back on the way
+    config = load_config(str(folder))
+    ids = {"long": random_tokens(331, 150, 1), "short": random_tokens(331, 12, 2)}
+
+    def run(capture: bool):
+        tensors = load_weights(str(folder), config, getattr(torch, dtype), "cuda")
+        runner = ModelRunner(config, tensors, make_ops(dtype, "cuda"), "cuda", dtype, page_size=16, num_pages=24, max_slots=4)
+        assert runner.capture_portions
+        runner.capture_portions = capture
+        caches = {name: runner.cache.open() for name in ids}
+        runner.cache.append(caches["short"], 0, 5)
+        runner.step([StepEntry(caches["short"], ids["short"][:5], 0, [])])
+        fed, short_fed, rows = 0, 5, []
+        for _ in range(6):   # six steps of the same shape: one decoded token beside a portion of 24
+            runner.cache.append(caches["short"], short_fed, 1)
+            runner.cache.append(caches["long"], fed, 24)
+            logits = runner.step([StepEntry(caches["short"], ids["short"][short_fed: short_fed + 1], short_fed, [0]),
+                                  StepEntry(caches["long"], ids["long"][fed: fed + 24], fed, [0, 23])])
+            rows.append(logits.float().cpu().clone())
+            short_fed += 1
+            fed += 24
+            runner.cache.advance(caches["long"], fed)
+            runner.cache.advance(caches["short"], short_fed)
+        return torch.cat(rows), len(runner._graphs)
+
+    captured, graphs = run(True)
+    eager, none = run(False)
+    assert graphs >= 1 and none == 0
+    assert torch.equal(captured, eager) if dtype == "float32" else (captured - eager).abs().max() < 2e-2
