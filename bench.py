@@ -303,7 +303,7 @@ def run_ours(args) -> dict:
             runner.cache.free(cache)
         return statistics.median(times)
 
-    prefill_ms = prefill_run(5, 3)
+    prefill_ms = prefill_run(5, 6)   # warm-up long enough for the step's launch sequence to be captured, as in serving
     flops = prefill_flops(raw, layers, PREFILL_TOKENS)
     peak_flops = peaks["bf16_tflops"] * 1e12
 

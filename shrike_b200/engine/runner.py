@@ -75,7 +75,8 @@ class ModelRunner:
         # such as one that branches on a request's position, keep such batches uncaptured)
         self.capture_portions = bool(getattr(self.model, "capture_safe", False))
         self._graphs: dict = {}
-        self._seen: set = set()
+        self._seen: dict = {}
+        self.portion_sightings = 5   # a shape with portions is captured when it comes for the sixth time
         self._drawn = torch.zeros(4096, dtype=torch.int32, device=self.device)   # the sampled tokens of a step
         self._drawn_generation = 0
         self._fetch_host = [None, None]
@@ -163,19 +164,20 @@ class ModelRunner:
         CUDA graph and replayed afterwards, because at small batch the step is bound by
         launch latency otherwise (the remedy shrike's README names for its own per-layer
         dispatch cost).  Other batches are captured when their exact shape (every entry's
-        length, the wanted rows, the table widths) is seen a second time.  A captured sequence
+        length, the wanted rows, the table widths) has been seen a few times.  A captured sequence
         bakes in what the parts computed on the host from the shape; parts must not branch on
         other host-side values of the step (positions, slots) if they are to be captured."""
         staged, sample, graphable = prepared.staged, prepared.sample, prepared.graphable
         self.builder.commit(staged)
         key = prepared.key
-        if graphable and not prepared.decode and key not in self._graphs and key not in self._seen:
-            # a batch with portions: captured only when the same shape comes a second time (a long
-            # prompt cut into equal portions, a benchmark's repeats); most mixed batches never repeat
-            if len(self._seen) >= 256:
+        if graphable and not prepared.decode and key not in self._graphs:
+            # a batch with portions: captured only when the same shape has come several times (a long
+            # prompt cut into equal portions, a benchmark's repeats).  Capturing costs a few steps'
+            # time, and most shapes of a mixed workload come once or twice.
+            if len(self._seen) >= 1024:
                 self._seen.clear()
-            self._seen.add(key)
-            graphable = False
+            self._seen[key] = self._seen.get(key, 0) + 1
+            graphable = self._seen[key] > self.portion_sightings
         if not graphable:
             logits, tokens = self._run(self.builder.context(staged), sample)
             return (logits, tokens) if sample else logits

@@ -118,6 +118,7 @@ def test_batches_with_portions_are_captured_when_their_shape_repeats(tmp_path, d
         runner.cache.append(caches["short"], 0, 5)
         runner.step([StepEntry(caches["short"], ids["short"][:5], 0, [])])
         fed, short_fed, rows = 0, 5, []
+        runner.portion_sightings = 2
         for _ in range(6):   # six steps of the same shape: one decoded token beside a portion of 24
             runner.cache.append(caches["short"], short_fed, 1)
             runner.cache.append(caches["long"], fed, 24)
