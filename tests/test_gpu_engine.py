@@ -135,3 +135,23 @@ def test_batches_with_portions_are_captured_when_their_shape_repeats(tmp_path, d
     eager, none = run(False)
     assert graphs >= 1 and none == 0
     assert torch.equal(captured, eager) if dtype == "float32" else (captured - eager).abs().max() < 2e-2
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_launching_ahead_gives_the_tokens_of_the_plain_loop_on_the_gpu(tmp_path, dtype):
+    """Greedy and sampled requests of different lengths, long enough for the block tables to
+    widen (new launch sequences are captured while a step is in flight): the engine that
+    launches a step ahead of the host and the one that does not draw the same tokens."""
+    folder = make_model_folder(tmp_path, "C")
+    prompts = [random_tokens(331, n, 7 + n) for n in (3, 40, 130, 17)]
+    params = [SamplingParams(max_new_tokens=m, ignore_eos=True, temperature=t, top_p=p, seed=11)
+              for m, t, p in ((160, 0.0, 1.0), (120, 0.9, 0.95), (60, 0.0, 1.0), (150, 1.2, 1.0))]
+    outs = []
+    for ahead in (True, False):
+        engine = LLMEngine(str(folder), num_blocks=120, dtype=dtype, max_running=4)
+        engine.launch_ahead = ahead
+        outs.append(engine.generate(prompts, params))
+        assert engine.block_manager.whole() and not engine.requests
+        assert len(engine.runner._graphs) >= 3
+        engine.ops.check_status()
+    assert outs[0] == outs[1]
