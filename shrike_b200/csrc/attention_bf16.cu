@@ -784,17 +784,20 @@ single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   if (direct || partials == 1) return;
   // the CTA that arrives last combines all partials; the order of the sum is by partial
   // index, whoever does it
-  __threadfence();
+  // One thread speaks for the CTA: the barrier orders every thread's stores before its fence, the
+  // fence before its count; on the other side its count, then its fence, then the barrier come
+  // before every thread's loads (which bypass L1).  A fence in every thread would say no more.
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence();
     int* counter = p.arrivals + static_cast<size_t>(seq) * gridDim.y + blockIdx.y;
     const int before = atomicAdd(counter, 1);
     is_last = before == p.splits - 1;   // every CTA counts, whatever the cluster size
     if (is_last) *counter = 0;   // ready for the next launch
+    __threadfence();
   }
   __syncthreads();
   if (!is_last) return;
-  __threadfence();
   // Each thread takes four columns of one row and reads the (max, sum) pairs and the four
   // columns of up to eight partials in one go: the combine costs one memory round trip per
   // eight partials, not one per partial.  Chunks of eight are merged like attention tiles, in
