@@ -80,9 +80,7 @@ class Staged:
     slots: list
     host: object = None        # the pinned buffer that holds the block until `commit` copies it
     turn: int = 0
-    ids_at: int = 0            # where the token ids start in the block
     committed: bool = False
-    ids_missing: bool = False  # staged ahead of time: the token ids come later, through `fill_ids`
 
 
 class BatchBuilder:
@@ -118,16 +116,16 @@ class BatchBuilder:
         """Stages the entries and returns the device views of the step's metadata."""
         return self.context(self.stage(entries))
 
-    def stage(self, entries: list[StepEntry], defer: bool = False, ids_missing: bool = False) -> "Staged":
+    def stage(self, entries: list[StepEntry], defer: bool = False) -> "Staged":
         """Fills the pinned buffer and starts its copy to the device.  The returned record holds
         only host-side facts; `context` turns it into device views when a forward pass needs them
         (a replayed launch sequence does not).
 
-        `defer=True` fills the buffer only; `commit` starts the copy later.  That lets a caller
-        stage the next step while the device still runs this one; with `ids_missing=True` the
-        entries' tokens are placeholders and `fill_ids` supplies them before the commit.  A
-        deferred block must be committed (or dropped) before two more blocks are staged: there
-        are two pinned buffers."""
+        `defer=True` fills the buffer only; `commit` starts the copy later.  A deferred block
+        must be committed (or dropped) before two more blocks are staged: there are two pinned
+        buffers.  A token id of -1 - r stands for the token that the step before drew in its row
+        r (the embedding kernel fetches it on the device), which is how a step is staged and
+        launched before the host has seen those tokens."""
         page = self.page_size
         q_lens = [len(e.tokens) for e in entries]
         if not entries or min(q_lens) < 1:
@@ -208,24 +206,15 @@ class BatchBuilder:
             self._fill_general(entries, q_lens, parts, max_blocks, sampled, page, s)
 
         staged = Staged(n, s, r, max_blocks, sizes, offsets, total, sampled, q_lens, starts, ctx_lens, slots_host,
-                        host=host, turn=self._turn, ids_at=offsets[3], ids_missing=ids_missing)
+                        host=host, turn=self._turn)
         if not defer:
             self.commit(staged)
         return staged
-
-    def fill_ids(self, staged: "Staged", tokens) -> None:
-        """The token ids of a block staged with `ids_missing=True` (single tokens, entry order)."""
-        if staged.committed or len(tokens) != staged.n or staged.n != staged.s:
-            raise ValueError("fill_ids wants one token per entry of an uncommitted single-token block")
-        staged.host.numpy()[staged.ids_at: staged.ids_at + staged.n] = tokens
-        staged.ids_missing = False
 
     def commit(self, staged: "Staged") -> None:
         """Starts the copy of a staged block to the device."""
         if staged.committed:
             return
-        if staged.ids_missing:
-            raise ValueError("the block was staged without its token ids; call fill_ids first")
         if staged.host is not self._host[staged.turn]:
             raise ValueError("the staging buffers were replaced since this block was staged")
         self._dev[: staged.total].copy_(staged.host[: staged.total], non_blocking=True)

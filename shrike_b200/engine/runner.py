@@ -112,11 +112,10 @@ class ModelRunner:
         """Runs the entries' tokens as one batch: `launch(prepare(entries, sample))`."""
         return self.launch(self.prepare(entries, sample))
 
-    def prepare(self, entries: list[StepEntry], sample: bool = False, ids_missing: bool = False) -> "Prepared":
+    def prepare(self, entries: list[StepEntry], sample: bool = False) -> "Prepared":
         """The host half of a step: the batch's metadata packed into pinned memory, nothing sent
-        yet.  It may run while the device still works on the step before; with `ids_missing=True`
-        the entries' (single) tokens are placeholders, supplied later by `fill_ids`."""
-        staged = self.builder.stage(entries, defer=True, ids_missing=ids_missing)
+        yet.  It may run while the device still works on the step before."""
+        staged = self.builder.stage(entries, defer=True)
         if sample and not staged.sampled:
             raise ValueError("sample=True needs `sampling` on every entry that wants logits")
         decode = max(staged.q_lens) == 1 and staged.r == staged.s and all(e.want == [0] for e in entries)
@@ -125,9 +124,6 @@ class ModelRunner:
         # length (grids and shapes follow from them), the number of wanted rows, the table widths
         key = (staged.s if decode else tuple(staged.q_lens), staged.r, tuple(staged.max_blocks), sample)
         return Prepared(staged, sample, graphable, key, decode)
-
-    def fill_ids(self, prepared: "Prepared", tokens) -> None:
-        self.builder.fill_ids(prepared.staged, tokens)
 
     def fetch(self, tokens: torch.Tensor):
         """Starts the copy of a step's drawn tokens to pinned host memory and returns a handle for

@@ -129,10 +129,10 @@ def test_single_token_split_rule_keeps_its_bounds():
     assert CudaOps.single_token_splits(512, 4, resident) == (72, 8)     # a long context: nine clusters
 
 
-def _run_script(stage_ahead: bool, pool: int):
+def _run_script(launch_ahead: bool, pool: int):
     """Requests that arrive, stop on a token, run out of length and are aborted at fixed steps."""
     engine, _ = engine_for("B", max_tokens_per_step=32, max_running=4, num_blocks=pool)
-    engine.launch_ahead = stage_ahead
+    engine.launch_ahead = launch_ahead
     prompts = [random_tokens(384, n, 70 + n) for n in (5, 12, 30, 3, 17)]
     first = engine.generate([prompts[0]], SamplingParams(max_new_tokens=8, ignore_eos=True))[0]
     engine.eos_ids = {first[4]}   # the first request now stops at its fifth token (or earlier)
