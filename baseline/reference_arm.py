@@ -109,11 +109,12 @@ def run(args, raw_model: dict, context: int) -> dict:
             times.append((time.perf_counter() - began) * 1000.0)
         prefill_ms = statistics.median(times)
         return {
-            "metric": "decode_tokens_per_second_qwen2.5-7b_b8_ctx1024", "impl": "reference",
+            "metric": f"decode_tokens_per_second_qwen2.5-{getattr(args, 'shape', '7b')}_b{batch}_ctx{context}",
+            "impl": "reference",
             "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
             "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic: seeded random weights and uniform random token ids",
-            "config": {"model": "Qwen2.5-7B shape", "layers": raw["num_hidden_layers"],
+            "config": {"model": f"Qwen2.5-{getattr(args, 'shape', '7b').upper()} shape", "layers": raw["num_hidden_layers"],
                        "layers_full": raw_model["num_hidden_layers"], "global_batch": batch, "seq_len": context,
                        "block_size": 16, "parallelism": "single_gpu", "engine_defaults": "stock LLMEngine(model_dir)",
                        "l2": "inputs larger than L2"},

@@ -11,7 +11,8 @@ decode step must read (every weight once, the cache of the live requests) to its
 `points` holds decoding at batch 1 and 64.  Weights are random (seeded), token ids
 uniform random: no checkpoint and no dataset is read.  Peaks come from
 MEASURED_PEAKS.json beside this file when present, else from an earlier measurement
-on the same GPU pool.
+on the same GPU pool.  `--shape 14b --context 8192` (and the like) time the same
+workload at other layer sizes and context lengths; the default line is the 7B one.
 """
 
 from __future__ import annotations
@@ -41,6 +42,15 @@ MODEL_1_5B = dict(
     rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=True, max_position_embeddings=32768,
     eos_token_id=151643, torch_dtype="bfloat16",
 )
+MODEL_14B = dict(
+    architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=5120, intermediate_size=13824,
+    num_hidden_layers=48, num_attention_heads=40, num_key_value_heads=8, head_dim=128, vocab_size=152064,
+    rms_norm_eps=1e-5, rope_theta=1000000.0, tie_word_embeddings=False, max_position_embeddings=32768,
+    eos_token_id=151643, torch_dtype="bfloat16",
+)
+SHAPES = {"7b": ("Qwen2.5-7B shape", MODEL_7B), "14b": ("Qwen2.5-14B shape", MODEL_14B),
+          "1.5b": ("Qwen2.5-1.5B shape", MODEL_1_5B)}
+DEVICE_BYTES_LIMIT = 120e9   # weights and cache pool together stay under this, whatever the options
 CONTEXT = 1024
 PREFILL_TOKENS = 2048
 BLOCK_SIZE = 16
@@ -167,33 +177,42 @@ def run_ours(args) -> dict:
 
     torch.cuda.set_device(0)
     device = torch.device("cuda:0")
-    raw = dict(MODEL_7B)
+    shape_name, shape = SHAPES[args.shape]
+    raw = dict(shape)
+    context = args.context
     full_layers = raw["num_hidden_layers"]
     raw["num_hidden_layers"] = args.layers or full_layers
     layers = raw["num_hidden_layers"]
     config = parse_config(raw)
     tensors = random_tensors(config, seed=0, device=device, dtype=torch.bfloat16)
-    batches = sorted({args.batch, 1, 64})
-    pages = sum(b * (-(-(CONTEXT + args.steps + args.warmup + 8) // BLOCK_SIZE)) for b in batches[-1:]) + \
-        -(-PREFILL_TOKENS // BLOCK_SIZE) + 64
-    engine = LLMEngine(None, block_size=BLOCK_SIZE, num_blocks=pages, max_tokens_per_step=4096, max_running=64,
+    numbers = model_numbers(raw, layers)
+    budget = 4096   # the engine's tokens per step: long prompts are cut, and finish their prefill steps apart
+    spread = args.batch * -(-context // budget)   # steps from the first request's first token to the last one's
+    pages_per_request = -(-(context + args.steps + args.warmup + 8 + spread) // BLOCK_SIZE)
+    page_bytes = BLOCK_SIZE * numbers["kv_bytes_per_token"]
+    large = 64   # the large batch of `points`: 64, or what the memory limit leaves at this shape and context
+    while large > 1 and numbers["weight_bytes_per_step"] + large * pages_per_request * page_bytes > DEVICE_BYTES_LIMIT:
+        large //= 2
+    if args.batch > large:
+        raise SystemExit(f"--batch {args.batch} at --context {context} needs more than {DEVICE_BYTES_LIMIT / 1e9:.0f} GB")
+    pages = large * pages_per_request + -(-PREFILL_TOKENS // BLOCK_SIZE) + 64
+    engine = LLMEngine(None, block_size=BLOCK_SIZE, num_blocks=pages, max_tokens_per_step=budget, max_running=64,
                        dtype="bfloat16", config=config, tensors=tensors)
     del tensors
     runner, ops = engine.runner, engine.ops
     rng = np.random.default_rng(0)
     vocab = raw["vocab_size"]
-    numbers = model_numbers(raw, layers)
     peaks = load_peaks()
     sampler = ClockSampler()
     sampler.start()
     windows = []
 
     def fill(batch: int):
-        """`batch` requests with CONTEXT - 1 tokens in the cache (untimed)."""
+        """`batch` requests with context - 1 tokens in the cache (untimed)."""
         caches = []
         for _ in range(batch):
             cache = runner.cache.open()
-            ids = rng.integers(0, vocab, CONTEXT - 1).tolist()
+            ids = rng.integers(0, vocab, context - 1).tolist()
             runner.cache.append(cache, 0, len(ids))
             runner.step([StepEntry(cache, ids, 0, [])])
             caches.append(cache)
@@ -204,7 +223,7 @@ def run_ours(args) -> dict:
         """Device-timed decode through the step function and the sampling kernel."""
         caches = fill(batch)
         tokens = rng.integers(0, vocab, batch).tolist()
-        fed = CONTEXT - 1
+        fed = context - 1
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
         def launch(fed, tokens=None):
@@ -243,7 +262,7 @@ def run_ours(args) -> dict:
         launches = ops.launches - launches_before
         for cache in caches:
             runner.cache.free(cache)
-        mean_context = CONTEXT + warmup + (steps - 1) / 2.0
+        mean_context = context + warmup + (steps - 1) / 2.0
         return ms, launches, mean_context
 
     # ---- decode at the headline batch, device-timed -------------------------
@@ -254,9 +273,9 @@ def run_ours(args) -> dict:
 
     # ---- the same through the public entry point ------------------------------
     def e2e_run(batch: int, steps: int, warmup: int):
-        prompts = [rng.integers(0, vocab, CONTEXT - 1).tolist() for _ in range(batch)]
-        # every request decodes through all timed steps (prompts finish their prefill a step or two apart)
-        params = SamplingParams(max_new_tokens=steps + warmup + 8, ignore_eos=True)
+        prompts = [rng.integers(0, vocab, context - 1).tolist() for _ in range(batch)]
+        # every request decodes through all timed steps, although the prompts finish their prefill steps apart
+        params = SamplingParams(max_new_tokens=steps + warmup + 8 + spread, ignore_eos=True)
         for prompt in prompts:
             engine.add_request(prompt, params)
         while any(not r.prefill_done for r in engine.requests.values()) or engine.scheduler.waiting:
@@ -265,6 +284,7 @@ def run_ours(args) -> dict:
             engine.step()
         torch.cuda.synchronize()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        copied = runner.builder.copied_bytes
         t0 = time.perf_counter()
         start.record()
         produced = 0
@@ -277,8 +297,7 @@ def run_ours(args) -> dict:
         for req_id in list(engine.requests):
             engine.abort(req_id)
         assert engine.block_manager.whole()
-        blocks = -(-(CONTEXT + warmup + steps) // BLOCK_SIZE)
-        h2d = 4 * (3 * batch + (batch + 1) + 2 * batch + batch + batch + batch * blocks) + 8 * batch + 8 * batch
+        h2d = (runner.builder.copied_bytes - copied) // steps   # the packed metadata block of each step
         return produced / steps * 1000.0 / e2e_ms, h2d, 4 * batch
 
     e2e_value, h2d, d2h = e2e_run(args.batch, args.steps, args.warmup)
@@ -308,25 +327,25 @@ def run_ours(args) -> dict:
     peak_flops = peaks["bf16_tflops"] * 1e12
 
     points = {}
-    for batch in (1, 64):
+    for batch in (1, large):
         point_ms, _, _ = decode_run(batch, max(10, args.steps // 2), 3)
         points[f"decode_b{batch}"] = round(batch * 1000.0 / point_ms, 1)
 
-    kernels = dominant_kernels(ops, raw, args.batch, peaks) if not args.layers else {}
+    kernels = dominant_kernels(ops, raw, args.batch, peaks, context) if not args.layers else {}
     sampler.stop()
     clocks = sampler.summary(windows)
     return {
-        "metric": "decode_tokens_per_second_qwen2.5-7b_b8_ctx1024",
+        "metric": f"decode_tokens_per_second_qwen2.5-{args.shape}_b{args.batch}_ctx{context}",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded random weights and uniform random token ids",
         "impl": "ours",
         "config": {
-            "model": "Qwen2.5-7B shape", "layers": layers, "layers_full": full_layers, "hidden": raw["hidden_size"],
+            "model": shape_name, "layers": layers, "layers_full": full_layers, "hidden": raw["hidden_size"],
             "heads": raw["num_attention_heads"], "kv_heads": raw["num_key_value_heads"], "head_dim": raw["head_dim"],
             "intermediate": raw["intermediate_size"], "vocab": raw["vocab_size"], "global_batch": args.batch,
-            "seq_len": CONTEXT, "block_size": BLOCK_SIZE, "prefill_tokens": PREFILL_TOKENS,
-            "parallelism": "single_gpu", "l2": "inputs larger than L2 (weights read per step: 15 GB)",
+            "seq_len": context, "block_size": BLOCK_SIZE, "prefill_tokens": PREFILL_TOKENS,
+            "parallelism": "single_gpu", "l2": f"inputs larger than L2 (weights read per step: {numbers['weight_bytes_per_step'] / 1e9:.1f} GB)",
             "peaks": peaks["source"],
         },
         "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -341,7 +360,7 @@ def run_ours(args) -> dict:
     }
 
 
-def dominant_kernels(ops, raw: dict, batch: int, peaks: dict) -> dict:
+def dominant_kernels(ops, raw: dict, batch: int, peaks: dict, context: int = 0) -> dict:
     """Each dominant decode kernel alone, at the headline batch: microseconds per launch
     (CUDA events around a captured graph of back-to-back launches over rotated operands, so
     every launch reads HBM) and the fraction of the copy bandwidth its bytes ÷ time reaches."""
@@ -380,7 +399,8 @@ def dominant_kernels(ops, raw: dict, batch: int, peaks: dict) -> dict:
         gbs = n * k * 2 / us / 1e3
         out[name] = {"us": round(us, 1), "GBps": round(gbs, 0), "frac": round(gbs / peaks["hbm_gbs"], 3)}
         del weights
-    blocks = -(-CONTEXT // BLOCK_SIZE)
+    context = context or CONTEXT
+    blocks = -(-context // BLOCK_SIZE)
     sets = 4   # rotated key/value pools, so that a launch does not find its keys in L2
     pools = [(torch.randn(batch * blocks, BLOCK_SIZE, kv, d, device=dev, dtype=torch.bfloat16),
               torch.randn(batch * blocks, BLOCK_SIZE, kv, d, device=dev, dtype=torch.bfloat16)) for _ in range(sets)]
@@ -389,12 +409,12 @@ def dominant_kernels(ops, raw: dict, batch: int, peaks: dict) -> dict:
     table = torch.full((batch, width), -1, dtype=torch.int32, device=dev)
     table[:, :blocks] = torch.arange(batch * blocks, dtype=torch.int32, device=dev).view(batch, blocks)
     q_start = torch.arange(batch + 1, dtype=torch.int32, device=dev)
-    ctx = torch.full((batch,), CONTEXT, dtype=torch.int32, device=dev)
+    ctx = torch.full((batch,), context, dtype=torch.int32, device=dev)
     seq_of = torch.arange(batch, dtype=torch.int32, device=dev)
     attn = torch.empty_like(q)
     us = graph_us(lambda i: ops.paged_attention(q, pools[i % sets][0], pools[i % sets][1], table, q_start, ctx, seq_of,
                                                 heads, kv, d, d ** -0.5, None, attn, max_q_len=1, min_q_len=1), 2 * sets)
-    gbs = batch * CONTEXT * 2 * kv * d * 2 / us / 1e3
+    gbs = batch * context * 2 * kv * d * 2 / us / 1e3
     out["attention"] = {"us": round(us, 1), "GBps": round(gbs, 0), "frac": round(gbs / peaks["hbm_gbs"], 3)}
     return out
 
@@ -531,11 +551,12 @@ def run_timeline(args) -> dict:
     from shrike_b200.weights.random_init import random_tensors
 
     torch.cuda.set_device(0)
-    raw = dict(MODEL_7B)
+    raw = dict(SHAPES[args.shape][1])
+    context = args.context
     raw["num_hidden_layers"] = layers = args.layers or 6
     config = parse_config(raw)
     tensors = random_tensors(config, seed=0, device=torch.device("cuda:0"), dtype=torch.bfloat16)
-    pages = args.batch * (-(-(CONTEXT + 64) // BLOCK_SIZE)) + 64
+    pages = args.batch * (-(-(context + 64) // BLOCK_SIZE)) + 64
     engine = LLMEngine(None, block_size=BLOCK_SIZE, num_blocks=pages, max_tokens_per_step=4096, max_running=64,
                        dtype="bfloat16", config=config, tensors=tensors)
     del tensors
@@ -544,11 +565,11 @@ def run_timeline(args) -> dict:
     caches = []
     for _ in range(args.batch):
         cache = runner.cache.open()
-        ids = rng.integers(0, raw["vocab_size"], CONTEXT - 1).tolist()
+        ids = rng.integers(0, raw["vocab_size"], context - 1).tolist()
         runner.cache.append(cache, 0, len(ids))
         runner.step([StepEntry(cache, ids, 0, [])])
         caches.append(cache)
-    fed = [CONTEXT - 1]
+    fed = [context - 1]
 
     def one_step():
         entries = []
@@ -601,7 +622,7 @@ def run_timeline(args) -> dict:
         table.append({"kernel": labels[position], "name": samples[0][0], "in_situ_us": round(float(np.median([t for _, t in samples])), 2)})
     layer_us = round(sum(row["in_situ_us"] for row in table), 2)
     rest = rows[:first] + rows[first + layers * per_layer:]
-    return {"case": "timeline", "batch": args.batch, "layers": layers, "layer_us": layer_us, "per_layer": table,
+    return {"case": "timeline", "shape": args.shape, "context": context, "batch": args.batch, "layers": layers, "layer_us": layer_us, "per_layer": table,
             "outside_layers": [{"name": name, "in_situ_us": round(t, 2)} for name, t in rest],
             "step_us": round(step[-1].time_range.end - step[0].time_range.start, 1)}
 
@@ -612,7 +633,7 @@ def run_reference(args) -> dict:
         return {"impl": "reference", "unavailable": "the reference is not installed under baseline/_ref"}
     from baseline.reference_arm import run  # the unmodified reference through its own LLMEngine
 
-    return run(args, MODEL_7B, CONTEXT)
+    return run(args, SHAPES[args.shape][1], args.context)
 
 
 def main():
@@ -623,6 +644,8 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all)")
+    parser.add_argument("--shape", default="7b", choices=sorted(SHAPES), help="layer sizes of the decode workload")
+    parser.add_argument("--context", type=int, default=1024, help="tokens each sequence holds when decoding is timed")
     parser.add_argument("--workload", default="decode", choices=["decode", "mixed"],
                         help="decode: the headline line; mixed: 64 requests through the scheduler at 1.5B shape")
     parser.add_argument("--num-blocks", type=int, default=0, help="cache pages for --workload mixed (few pages force preemption)")

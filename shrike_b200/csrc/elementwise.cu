@@ -73,19 +73,20 @@ template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16*
 
 // `delta` may be a stack of `partials` arrays (the slices of a K-split matrix product),
 // `partial_stride` elements apart; they are added in ascending order.
-// PER_THREAD 1 (rows of up to 1024 groups): a thread holds one group, reads the norm weight
+// PER_THREAD 1 (few rows of up to 1024 groups): a thread holds one group, reads the norm weight
 // before the wait and has the residual and up to eight slices in flight together, so the
-// row costs one memory round trip.  PER_THREAD 8 (wider rows) adds slice by slice.
+// row costs one memory round trip.  PER_THREAD 2 (few rows of up to 2048 groups): the same,
+// one group after the other.  PER_THREAD 8 (many rows, or wider ones) adds slice by slice.
 template <typename TD, typename TO, bool HAS_DELTA, bool GATHER, int VEC, int PER_THREAD>
 __global__ void __launch_bounds__(1024, 1) add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
                                    const int* __restrict__ rows, const float* __restrict__ weight,
                                    float eps, TO* __restrict__ out, int width, int partials,
                                    long long partial_stride) {
   __shared__ float scratch[33];
-  constexpr int AHEAD = PER_THREAD == 1 ? 7 : 1;   // the first slice and seven more: a stack of eight in one go
+  constexpr int AHEAD = PER_THREAD <= 2 ? 7 : 1;   // the first slice and seven more: a stack of eight in one go
   let_dependents_start();
   const int groups = width / VEC;
-  constexpr bool GAIN_AHEAD = PER_THREAD == 1;   // registers allow it only for the narrow form
+  constexpr bool GAIN_AHEAD = PER_THREAD <= 2;   // registers allow it only for the narrow forms
   float gain[GAIN_AHEAD ? PER_THREAD : 1][VEC];   // the norm weight: no kernel writes it, so it is read ahead of the wait
 #pragma unroll
   for (int it = 0; it < (GAIN_AHEAD ? PER_THREAD : 0); ++it) {
@@ -188,8 +189,9 @@ static int launch_add_rmsnorm(float* resid, const void* delta, const int* rows, 
   const int groups = vec ? width / 4 : width;
   // Few rows (decode): latency counts, one group per thread.  Many rows (prompts): bandwidth
   // counts, small blocks whose threads each keep up to eight groups in flight.
-  const bool narrow = groups <= 1024 && n <= 256;
-  int threads = (groups + 31) / 32 * 32;
+  const bool narrow = groups <= 2048 && n <= 256;
+  const bool two = narrow && groups > 1024;   // rows of up to 8192: two groups per thread
+  int threads = ((two ? (groups + 1) / 2 : groups) + 31) / 32 * 32;
   if (!narrow) {
     threads = ((groups + NORM_MAX_PER_THREAD - 1) / NORM_MAX_PER_THREAD + 31) / 32 * 32;
     threads = threads < 128 ? 128 : (threads > 1024 ? 1024 : threads);
@@ -200,7 +202,8 @@ static int launch_add_rmsnorm(float* resid, const void* delta, const int* rows, 
                    static_cast<const TD*>(delta), rows, weight, eps, static_cast<TO*>(out), width, partials,  \
                    partial_stride)
 #define SHRIKE_NORM_LAUNCH(G, V)                                                                   \
-  do { if (narrow) SHRIKE_NORM_LAUNCH_T(G, V, 1); else SHRIKE_NORM_LAUNCH_T(G, V, NORM_MAX_PER_THREAD); } while (0)
+  do { if (two) SHRIKE_NORM_LAUNCH_T(G, V, 2); else if (narrow) SHRIKE_NORM_LAUNCH_T(G, V, 1);   \
+       else SHRIKE_NORM_LAUNCH_T(G, V, NORM_MAX_PER_THREAD); } while (0)
   if (rows) { if (vec) SHRIKE_NORM_LAUNCH(true, 4); else SHRIKE_NORM_LAUNCH(true, 1); }
   else { if (vec) SHRIKE_NORM_LAUNCH(false, 4); else SHRIKE_NORM_LAUNCH(false, 1); }
 #undef SHRIKE_NORM_LAUNCH

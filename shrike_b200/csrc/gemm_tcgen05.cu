@@ -242,7 +242,7 @@ gemm_swap_ab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 // three stages each measured 7% slower over a whole decode step).  A product of many waves
 // (an output head) does better with four shallower CTAs per SM.  0: choose by the shape.
 static int g_smem_budget = 0;
-static int g_target_ctas = 148;
+static int g_target_ctas = 0;   // 0: the device's SM count
 static int g_dependent_launch = 1;
 SHRIKE_API void shrike_gemm_tc_dependent_launch(int enabled) { g_dependent_launch = enabled ? 1 : 0; }
 SHRIKE_API void shrike_gemm_tc_tune(int smem_budget_bytes, int target_ctas) {
@@ -250,17 +250,33 @@ SHRIKE_API void shrike_gemm_tc_tune(int smem_budget_bytes, int target_ctas) {
   if (target_ctas >= 1) g_target_ctas = target_ctas;
 }
 
-// How K is split for a product with `tokens` rows: enough CTAs to keep every SM
-// streaming, at least four k-blocks per CTA.  The same function sizes the partial stack.
+// How K is split for a product with `tokens` rows.  Two CTAs live on an SM, and as long as
+// all CTAs of the product are resident together, more of them stream faster: measured at the
+// projection shapes of three model sizes, the time falls with every further split until the
+// grid exceeds the resident places (2 x 148), and jumps by a third right after.  So: the most
+// splits that keep the grid resident, at least three k-blocks each, none empty; at most 8 (what
+// the norm kernel adds in one round trip: a ninth slice costs it what the product gains), or 16
+// where eight would not even give every SM a CTA.  The same function sizes the partial stack.
 SHRIKE_API int shrike_gemm_tc_splits(int tokens, int n, int k) {
   (void)tokens;
   const int tiles = (n + tc::BM - 1) / tc::BM;
   const int kblocks = (k + tc::BK - 1) / tc::BK;
-  int splits = 1;
-  while (tiles * splits < g_target_ctas && splits < 16 && kblocks / (splits * 2) >= 4) splits *= 2;
-  // round so that no split is empty
-  const int per = (kblocks + splits - 1) / splits;
-  return (kblocks + per - 1) / per;
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sm_count <= 0)
+      sm_count = 148;
+  }
+  const int resident = 2 * (g_target_ctas ? g_target_ctas : sm_count);
+  const int most = tiles * 8 < resident / 2 ? 16 : 8;
+  int best = 1;
+  for (int splits = 2; splits <= most && tiles * splits <= resident; ++splits) {
+    const int per = (kblocks + splits - 1) / splits;
+    if (per < 3) break;
+    if ((kblocks + per - 1) / per == splits) best = splits;   // else the last split would be empty
+  }
+  return best;
 }
 
 // x [tokens, k] and w [n, k] bfloat16 row-major, k a multiple of 8 (TMA wants 16-byte row

@@ -97,6 +97,7 @@ class BatchBuilder:
         self._dev = None
         self._range = None
         self.generation = 0  # grows when the device buffer moves: captured launch sequences are stale then
+        self.copied_bytes = 0  # host-to-device bytes of all steps so far
 
     def _staging(self, count: int):
         pinned = self.device.type == "cuda"
@@ -218,6 +219,7 @@ class BatchBuilder:
         if staged.host is not self._host[staged.turn]:
             raise ValueError("the staging buffers were replaced since this block was staged")
         self._dev[: staged.total].copy_(staged.host[: staged.total], non_blocking=True)
+        self.copied_bytes += 4 * staged.total
         if self.device.type == "cuda":
             event = torch.cuda.Event()
             event.record()

@@ -40,7 +40,7 @@ def test_embed(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("width", [48, 200, 3584 + 16, 5000])
+@pytest.mark.parametrize("width", [48, 200, 3584 + 16, 5000, 8192, 8200])
 def test_add_rmsnorm(dtype, width):
     ops = cuda_ops(dtype)
     n, eps = 7, 3e-6
@@ -60,6 +60,25 @@ def test_add_rmsnorm(dtype, width):
         ops.gather_add_rmsnorm(x2, delta, rows, weight, eps, picked)
         assert torch.equal(x2, resid), "gather form must not write the residual"
         assert torch.equal(picked, out[rows.long()])
+
+
+@pytest.mark.parametrize("width", [3584, 5120, 8192, 16384, 1030])
+@pytest.mark.parametrize("partials", [3, 8, 11])
+@pytest.mark.parametrize("n", [2, 300])
+def test_add_rmsnorm_adds_a_stack_of_partials_in_order(width, partials, n):
+    """Every form of the kernel (one, two or eight groups per thread, few and many rows, the scalar
+    path) adds the slices of a K-split product in ascending order, then the residual: bitwise."""
+    ops = cuda_ops(torch.bfloat16)
+    resid, weight = rnd(n, width, seed=1, scale=3.0), 1 + 0.1 * rnd(width, seed=2)
+    stack = rnd(partials, n, width, seed=5)
+    x, out = resid.clone(), torch.empty(n, width, dtype=torch.bfloat16, device=DEV)
+    ops.add_rmsnorm(x, stack, weight, 1e-6, out)
+    total = stack[0].clone()
+    for p in range(1, partials):
+        total += stack[p]
+    total = resid + total
+    assert torch.equal(x, total)
+    close(out, pm.rms_norm(total.double(), weight.double(), 1e-6), 0.0, 2 ** -8, f"norm of a stack, width {width}")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
