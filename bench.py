@@ -42,14 +42,24 @@ MODEL_1_5B = dict(
     rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=True, max_position_embeddings=32768,
     eos_token_id=151643, torch_dtype="bfloat16",
 )
-MODEL_14B = dict(
-    architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=5120, intermediate_size=13824,
-    num_hidden_layers=48, num_attention_heads=40, num_key_value_heads=8, head_dim=128, vocab_size=152064,
-    rms_norm_eps=1e-5, rope_theta=1000000.0, tie_word_embeddings=False, max_position_embeddings=32768,
-    eos_token_id=151643, torch_dtype="bfloat16",
-)
-SHAPES = {"7b": ("Qwen2.5-7B shape", MODEL_7B), "14b": ("Qwen2.5-14B shape", MODEL_14B),
-          "1.5b": ("Qwen2.5-1.5B shape", MODEL_1_5B)}
+def _qwen(hidden, inter, layers, heads, kv, head_dim, vocab, tied, eps=1e-6):
+    return dict(
+        architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=hidden, intermediate_size=inter,
+        num_hidden_layers=layers, num_attention_heads=heads, num_key_value_heads=kv, head_dim=head_dim,
+        vocab_size=vocab, rms_norm_eps=eps, rope_theta=1000000.0, tie_word_embeddings=tied,
+        max_position_embeddings=32768, eos_token_id=151643, torch_dtype="bfloat16")
+
+
+# the layer sizes of the Qwen2.5 dense family; the larger ones run with --layers (or in --case timeline)
+SHAPES = {
+    "0.5b": ("Qwen2.5-0.5B shape", _qwen(896, 4864, 24, 14, 2, 64, 151936, True)),
+    "1.5b": ("Qwen2.5-1.5B shape", MODEL_1_5B),
+    "3b": ("Qwen2.5-3B shape", _qwen(2048, 11008, 36, 16, 2, 128, 151936, True)),
+    "7b": ("Qwen2.5-7B shape", MODEL_7B),
+    "14b": ("Qwen2.5-14B shape", _qwen(5120, 13824, 48, 40, 8, 128, 152064, False, 1e-5)),
+    "32b": ("Qwen2.5-32B shape", _qwen(5120, 27648, 64, 40, 8, 128, 152064, False, 1e-5)),
+    "72b": ("Qwen2.5-72B shape", _qwen(8192, 29568, 80, 64, 8, 128, 152064, False, 1e-5)),
+}
 DEVICE_BYTES_LIMIT = 120e9   # weights and cache pool together stay under this, whatever the options
 CONTEXT = 1024
 PREFILL_TOKENS = 2048
@@ -184,8 +194,11 @@ def run_ours(args) -> dict:
     raw["num_hidden_layers"] = args.layers or full_layers
     layers = raw["num_hidden_layers"]
     config = parse_config(raw)
-    tensors = random_tensors(config, seed=0, device=device, dtype=torch.bfloat16)
     numbers = model_numbers(raw, layers)
+    if numbers["weight_bytes_per_step"] > 0.8 * DEVICE_BYTES_LIMIT:
+        raise SystemExit(f"{shape_name} with {layers} layers holds {numbers['weight_bytes_per_step'] / 1e9:.0f} GB "
+                         "of weights: give --layers")
+    tensors = random_tensors(config, seed=0, device=device, dtype=torch.bfloat16)
     budget = 4096   # the engine's tokens per step: long prompts are cut, and finish their prefill steps apart
     spread = args.batch * -(-context // budget)   # steps from the first request's first token to the last one's
     pages_per_request = -(-(context + args.steps + args.warmup + 8 + spread) // BLOCK_SIZE)
@@ -644,7 +657,7 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all)")
-    parser.add_argument("--shape", default="7b", choices=sorted(SHAPES), help="layer sizes of the decode workload")
+    parser.add_argument("--shape", default="7b", choices=list(SHAPES), help="layer sizes of the decode workload")
     parser.add_argument("--context", type=int, default=1024, help="tokens each sequence holds when decoding is timed")
     parser.add_argument("--workload", default="decode", choices=["decode", "mixed"],
                         help="decode: the headline line; mixed: 64 requests through the scheduler at 1.5B shape")

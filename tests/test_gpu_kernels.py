@@ -129,7 +129,8 @@ def test_linear_bf16():
 
 
 @pytest.mark.parametrize("tokens,n,k", [(1, 64, 64), (8, 384, 192), (3, 331, 240), (16, 130, 320), (17, 4608, 3584),
-                                        (33, 3584, 1000), (64, 256, 18944), (5, 1188, 136), (64, 37888, 3584)])
+                                        (33, 3584, 1000), (64, 256, 18944), (5, 1188, 136), (64, 37888, 3584),
+                                        (8, 5120, 5120), (8, 5120, 13824), (4, 1152, 896), (8, 1536, 8960), (2, 10240, 8192)])
 def test_gemm_tcgen05(tokens, n, k):
     """The tensor-core product for few tokens (TMA + tcgen05, accumulator in tensor memory):
     float32 and bfloat16 outputs, bias, and the K-split stack of partial results."""
@@ -164,6 +165,27 @@ def test_gemm_tcgen05(tokens, n, k):
         ops.add_rmsnorm(resid, stack, torch.ones(n, device=DEV), 1e-6, out)
         assert torch.equal(resid, total), "the norm kernel must add the partials in order"
     ops.check_status()
+
+
+def test_gemm_tcgen05_splits_keep_their_bounds():
+    """How the product cuts K: no empty cut, at least three k-blocks (of 64) a cut, at most 16 cuts, the
+    grid of 128-row tiles times cuts resident at once (two CTAs per SM) unless there is a single cut;
+    and the choice depends on the matrix alone, never on the number of tokens, so that a position's
+    logits do not depend on what else is in the batch."""
+    ops = cuda_ops(torch.bfloat16)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    seen = set()
+    for n in (64, 128, 896, 1152, 1536, 2048, 2560, 3584, 4608, 5120, 7168, 8192, 10240, 18944, 152064):
+        for k in (64, 136, 192, 896, 1000, 1536, 3584, 4864, 5120, 8192, 8960, 13824, 18944, 29568):
+            cuts = ops.gemm_tc.shrike_gemm_tc_splits(8, n, k)
+            assert all(ops.gemm_tc.shrike_gemm_tc_splits(t, n, k) == cuts for t in (1, 17, 64))
+            tiles, kblocks = -(-n // 128), -(-k // 64)
+            each = -(-kblocks // cuts)
+            assert 1 <= cuts <= 16 and -(-kblocks // each) == cuts
+            assert cuts == 1 or (each >= 3 and tiles * cuts <= 2 * sms)
+            seen.add(cuts)
+    assert ops.gemm_tc.shrike_gemm_tc_splits(8, 3584, 18944) == 8 and ops.gemm_tc.shrike_gemm_tc_splits(8, 5120, 13824) == 7
+    assert len(seen) >= 6
 
 
 def interleave_rows(gate, up, run):
