@@ -324,7 +324,8 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const float*
                                      int num_heads, int num_kv_heads, int head_dim, long long num_slots,
                                      int partials, long long partial_stride, int wide) {
   let_dependents_start();
-  wait_for_previous();
+  // Before the wait: what no kernel writes (the step's positions and slots, the bias, the
+  // frequencies) and the angle of this thread's first pair, while the projection still runs.
   const int token = blockIdx.x;
   const int half = head_dim / 2;
   const int q_width = num_heads * head_dim, kv_width = num_kv_heads * head_dim;
@@ -336,6 +337,17 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const float*
   }
   const float pos = static_cast<float>(positions[token]);
   const int pairs = (num_heads + 2 * num_kv_heads) * half;
+  const int first = blockIdx.y * blockDim.x + threadIdx.x;
+  float first_s = 0.f, first_c = 1.f, first_bias_lo = 0.f, first_bias_hi = 0.f;
+  if (gridDim.y > 1 && first < pairs) {
+    const int head = first / half, j = first - head * half;
+    if (inv_freq != nullptr && head < num_heads + num_kv_heads) sincosf(__fmul_rn(pos, inv_freq[j]), &first_s, &first_c);
+    if (bias != nullptr) {
+      first_bias_lo = bias[head * head_dim + j];
+      first_bias_hi = bias[head * head_dim + j + half];
+    }
+  }
+  wait_for_previous();
   // A block that walks all heads of its token computes the token's angles once, not once per head.
   __shared__ float2 angle[128];
   const bool shared_angles = gridDim.y == 1 && inv_freq != nullptr && half <= 128;
@@ -399,20 +411,24 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const float*
     }
     return;
   }
-  for (int idx = blockIdx.y * blockDim.x + threadIdx.x; idx < pairs; idx += gridDim.y * blockDim.x) {
+  for (int idx = first; idx < pairs; idx += gridDim.y * blockDim.x) {
     const int head = idx / half, j = idx - head * half;
     const bool is_q = head < num_heads, is_k = !is_q && head < num_heads + num_kv_heads;
     const int lo = head * head_dim + j, hi = lo + half;  // columns of the row
+    const bool ahead = gridDim.y > 1 && idx == first;    // this pair's bias and angle are at hand
     float a = sum_partials(row + lo, partial_stride, partials);   // slices of a K-split projection, added in order
     float b = sum_partials(row + hi, partial_stride, partials);
     if (bias != nullptr) {
-      a = __fadd_rn(a, bias[lo]);
-      b = __fadd_rn(b, bias[hi]);
+      a = __fadd_rn(a, ahead ? first_bias_lo : bias[lo]);
+      b = __fadd_rn(b, ahead ? first_bias_hi : bias[hi]);
     }
     float ra = a, rb = b;
     if (inv_freq != nullptr && (is_q || is_k)) {
       float s, c;
-      if (shared_angles) {
+      if (ahead) {
+        s = first_s;
+        c = first_c;
+      } else if (shared_angles) {
         s = angle[j].x;
         c = angle[j].y;
       } else {

@@ -3,10 +3,11 @@
 Every method launches hand-written sm_100a code from `csrc/` through the C symbol
 of its launcher, on torch's current stream, with raw device pointers.  There is no
 CPU path and no library attention or model code: without a CUDA device, or when a
-kernel cannot be built, construction fails.  Matrix products in bfloat16 go to
-cuBLAS through `torch.mm` (Azimml/shrike's own GEMMs are cuBLAS calls through
-nn.Linear, shrike/models/qwen.py:111-136); in float32 they run on this package's own
-FFMA kernel, so the 32-bit path never touches a reduced-precision matrix mode.
+kernel cannot be built, construction fails.  Matrix products in bfloat16 run on this
+package's tcgen05 kernel for up to 64 tokens (decoding) and go to cuBLAS through
+`torch.mm` above that (Azimml/shrike's own GEMMs are cuBLAS calls through nn.Linear,
+shrike/models/qwen.py:111-136); in float32 they run on this package's own FFMA
+kernel, so the 32-bit path never touches a reduced-precision matrix mode.
 """
 
 from __future__ import annotations
@@ -256,6 +257,10 @@ class CudaOps:
 
     def rope_kv_write(self, qkv, bias, positions, inv_freq, q_out, keys, values, slots,
                       num_heads, num_kv_heads, head_dim, k_out=None, v_out=None):
+        """Bias, rotation and cache store of a fused q/k/v projection ([N, W] or a K-split stack).
+        `positions`, `slots`, `bias` and `inv_freq` are read while the kernels launched before may
+        still run (the angles are formed meanwhile): they must be the step's metadata or
+        parameters, not something a kernel of this step computes."""
         _dense(qkv, torch.float32, "qkv")
         _dense(q_out, self.dtype, "q")
         partials, stride = self._stack(qkv)
