@@ -491,6 +491,8 @@ def run_case(args) -> dict:
     torch.cuda.set_device(0)
     dev = "cuda"
     ops = CudaOps(torch.bfloat16, dev)
+    if args.case == "gemm_splits":
+        return run_gemm_splits(args, ops)
     raw = MODEL_7B
     h, inter = raw["hidden_size"], raw["intermediate_size"]
     heads, kv, d = raw["num_attention_heads"], raw["num_key_value_heads"], raw["head_dim"]
@@ -545,6 +547,58 @@ def run_case(args) -> dict:
     else:
         result["TFLOPs"] = round(work["flops"] / best / 1e6, 1)
     return result
+
+
+def run_gemm_splits(args, ops) -> dict:
+    """Every way of cutting K for the qkv, o and down products of --shape at --batch tokens: each
+    product alone as a CUDA graph over rotating weight copies (more than L2 together), microseconds
+    per launch.  `rule` is what the kernel library itself would take."""
+    import torch
+
+    from shrike_b200.ops.cuda_ops import _ptr
+
+    raw = SHAPES[args.shape][1]
+    h, inter = raw["hidden_size"], raw["intermediate_size"]
+    heads, kv, d = raw["num_attention_heads"], raw["num_key_value_heads"], raw["head_dim"]
+    tokens, dev = args.batch, "cuda"
+    table = {}
+    for name, (n, k) in {"qkv": ((heads + 2 * kv) * d, h), "o": (h, heads * d), "down": (h, inter)}.items():
+        copies = min(24, max(2, int(400e6 // (n * k * 2)) + 1))
+        weights = [torch.randn(n, k, device=dev, dtype=torch.bfloat16) for _ in range(copies)]
+        x = torch.randn(tokens, k, device=dev, dtype=torch.bfloat16)
+        kblocks, row = -(-k // 64), {}
+        for cuts in range(1, 17):
+            each = -(-kblocks // cuts)
+            if -(-kblocks // each) != cuts or (cuts > 1 and each < 3):
+                continue
+            out = torch.empty(cuts, tokens, n, device=dev, dtype=torch.float32)
+
+            def launch(i):
+                code = ops.gemm_tc.shrike_gemm_tc(_ptr(x), _ptr(weights[i % copies]), None, _ptr(out), 0, tokens, n, k,
+                                                  cuts, _ptr(ops.status), torch.cuda.current_stream().cuda_stream)
+                if code:
+                    raise SystemExit(f"gemm_tcgen05 returned {code}")
+
+            launch(0)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for i in range(2 * copies):
+                    launch(i)
+            graph.replay()
+            torch.cuda.synchronize()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(5):
+                graph.replay()
+            stop.record()
+            torch.cuda.synchronize()
+            row[cuts] = round(start.elapsed_time(stop) * 1e3 / (10 * copies), 1)
+        table[name] = {"tiles": -(-n // 128), "kblocks": kblocks, "rule": ops.gemm_tc.shrike_gemm_tc_splits(tokens, n, k),
+                       "MB": round(n * k * 2 / 1e6, 1), "us_by_cuts": row}
+        del weights
+    ops.check_status()
+    return {"case": "gemm_splits", "shape": args.shape, "tokens": tokens, "products": table}
 
 
 def run_timeline(args) -> dict:
@@ -665,7 +719,8 @@ def main():
     parser.add_argument("--case", default=None,
                         help="run a small single-kernel workload instead (for profiling): gemm_gate_up, gemm_down, "
                              "gemm_qkv, attention_single, attention_portions; --batch gives tokens / sequences.  timeline: per-kernel "
-                             "times inside one captured decode step (--layers, default 6)")
+                             "times inside one captured decode step (--layers, default 6).  gemm_splits: every way of "
+                             "cutting K for the projections of --shape")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU: this engine runs on a single B200 (asked for {args.gpus})")
