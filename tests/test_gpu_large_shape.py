@@ -1,5 +1,7 @@
-"""The serving shape: Qwen2.5-7B widths (hidden 3584, 28 / 4 heads of 128, intermediate
-18944, vocabulary 152064) with two layers, random weights made on the GPU.  A plain
+"""The serving shapes: Qwen2.5-7B widths (hidden 3584, 28 / 4 heads of 128, intermediate
+18944, vocabulary 152064) with two layers, and Qwen2.5-14B widths (hidden 5120, 40 / 8 heads,
+intermediate 13824; rows wider than 4,096 take another form of the norm kernel and the
+products other K cuts) with one layer and a short vocabulary, random weights made on the GPU.  A plain
 float64 pass of this size is out of reach on the CPU, so the checks are the engine against
 itself: float32 logits must not change with the cutting (they are bitwise equal), bfloat16
 must agree with float32 within the bfloat16 tolerance, and the tensor-core product for few
@@ -18,11 +20,18 @@ from tests.helpers import random_tokens
 
 pytestmark = pytest.mark.gpu
 
-SHAPE = dict(
-    architectures=["Qwen2ForCausalLM"], hidden_size=3584, intermediate_size=18944, num_hidden_layers=2,
-    num_attention_heads=28, num_key_value_heads=4, head_dim=128, vocab_size=152064, rms_norm_eps=1e-6,
-    rope_theta=1000000.0, tie_word_embeddings=False, max_position_embeddings=32768, eos_token_id=151643,
-)
+SHAPES = {
+    "7b": dict(
+        architectures=["Qwen2ForCausalLM"], hidden_size=3584, intermediate_size=18944, num_hidden_layers=2,
+        num_attention_heads=28, num_key_value_heads=4, head_dim=128, vocab_size=152064, rms_norm_eps=1e-6,
+        rope_theta=1000000.0, tie_word_embeddings=False, max_position_embeddings=32768, eos_token_id=151643,
+    ),
+    "14b": dict(
+        architectures=["Qwen2ForCausalLM"], hidden_size=5120, intermediate_size=13824, num_hidden_layers=1,
+        num_attention_heads=40, num_key_value_heads=8, head_dim=128, vocab_size=5003, rms_norm_eps=1e-5,
+        rope_theta=1000000.0, tie_word_embeddings=True, max_position_embeddings=32768, eos_token_id=5002,
+    ),
+}
 LENGTH = 150
 
 
@@ -38,10 +47,11 @@ def run(runner, tokens, cuts):
     return np.concatenate(rows)
 
 
-@pytest.fixture(scope="module")
-def logits():
-    config = parse_config(SHAPE)
-    tokens = random_tokens(SHAPE["vocab_size"], LENGTH, 11)
+@pytest.fixture(scope="module", params=list(SHAPES))
+def logits(request):
+    shape = SHAPES[request.param]
+    config = parse_config(shape)
+    tokens = random_tokens(shape["vocab_size"], LENGTH, 11)
     out = {}
     for dtype, torch_dtype in (("float32", torch.float32), ("bfloat16", torch.bfloat16)):
         tensors = random_tensors(config, 5, "cuda", torch.float32)
