@@ -78,6 +78,7 @@ class Staged:
     starts: list
     ctx_lens: list
     slots: list
+    rows: int = 0              # wanted rows that belong to entries (the rest of `r` is padding)
     host: object = None        # the pinned buffer that holds the block until `commit` copies it
     turn: int = 0
     committed: bool = False
@@ -117,7 +118,7 @@ class BatchBuilder:
         """Stages the entries and returns the device views of the step's metadata."""
         return self.context(self.stage(entries))
 
-    def stage(self, entries: list[StepEntry], defer: bool = False) -> "Staged":
+    def stage(self, entries: list[StepEntry], defer: bool = False, pad_to: int = 0) -> "Staged":
         """Fills the pinned buffer and starts its copy to the device.  The returned record holds
         only host-side facts; `context` turns it into device views when a forward pass needs them
         (a replayed launch sequence does not).
@@ -126,7 +127,13 @@ class BatchBuilder:
         must be committed (or dropped) before two more blocks are staged: there are two pinned
         buffers.  A token id of -1 - r stands for the token that the step before drew in its row
         r (the embedding kernel fetches it on the device), which is how a step is staged and
-        launched before the host has seen those tokens."""
+        launched before the host has seen those tokens.
+
+        `pad_to` > len(entries), for a batch of single tokens that all want their logits: the block
+        describes `pad_to` rows, so that one captured launch sequence serves every batch size up to
+        it.  A padding row is a one-token sequence at position 0 that stores nothing (slot -1, state
+        slot -1), reads page 0 of every group (whatever it holds) and is sampled greedily; its
+        logits and token come last and are dropped by the step function."""
         page = self.page_size
         q_lens = [len(e.tokens) for e in entries]
         if not entries or min(q_lens) < 1:
@@ -135,6 +142,12 @@ class BatchBuilder:
         r = sum(len(e.want) for e in entries)
         starts = [e.start for e in entries]
         ctx_lens = [st + q for st, q in zip(starts, q_lens)]
+        real = s
+        pad = pad_to - s if max(q_lens) == 1 and all(e.want == [0] for e in entries) else 0
+        if pad > 0:
+            n = s = r = pad_to
+        else:
+            pad = 0
         need_max = -(-max(ctx_lens) // page)
         max_blocks = [1] * self.num_groups
         for g in range(self.num_groups):
@@ -166,18 +179,22 @@ class BatchBuilder:
 
         if max(q_lens) == 1:
             # the steady state of decoding: one token per entry, filled without per-token work
-            ids[:] = [e.tokens[0] for e in entries]
-            pos[:] = starts
+            ids[:real] = [e.tokens[0] for e in entries]
+            pos[:real] = starts
             seq_of[:] = self._arange(s)
             q_start[:] = self._arange(s + 1)
-            ctx_arr[:] = ctx_lens
-            slot_arr[:] = slots_host
+            ctx_arr[:real] = ctx_lens
+            slot_arr[:real] = slots_host
+            if pad:
+                ids[real:], pos[real:], ctx_arr[real:], slot_arr[real:] = 0, 0, 1, -1
             if r == s and all(e.want == [0] for e in entries):
                 out_rows[:] = self._arange(s)
                 if sampled:
-                    temps[:] = [e.sampling[0] for e in entries]
-                    top_ps[:] = [e.sampling[1] for e in entries]
-                    seeds[:] = [e.sampling[2] for e in entries]
+                    temps[:real] = [e.sampling[0] for e in entries]
+                    top_ps[:real] = [e.sampling[1] for e in entries]
+                    seeds[:real] = [e.sampling[2] for e in entries]
+                    if pad:
+                        temps[real:], top_ps[real:], seeds[real:] = 0.0, 1.0, 0
             else:
                 row = 0
                 for index, e in enumerate(entries):
@@ -203,11 +220,17 @@ class BatchBuilder:
                     if page_of < 0:
                         raise ValueError(f"entry {index} writes into a page of group {g} it no longer holds")
                     slots[index] = page_of * page + p % page
+                if pad:
+                    slots[real:] = -1
+                    table2d[real:, 0] = 0
         else:
             self._fill_general(entries, q_lens, parts, max_blocks, sampled, page, s)
 
+        if pad:
+            q_lens, starts = q_lens + [1] * pad, starts + [0] * pad
+            ctx_lens, slots_host = ctx_lens + [1] * pad, slots_host + [-1] * pad
         staged = Staged(n, s, r, max_blocks, sizes, offsets, total, sampled, q_lens, starts, ctx_lens, slots_host,
-                        host=host, turn=self._turn)
+                        rows=r - pad, host=host, turn=self._turn)
         if not defer:
             self.commit(staged)
         return staged

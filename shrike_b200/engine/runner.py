@@ -24,7 +24,7 @@ TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 class Prepared:
     """A step whose metadata is staged on the host: what `ModelRunner.launch` needs."""
 
-    __slots__ = ("staged", "sample", "graphable", "key", "decode")
+    __slots__ = ("staged", "sample", "graphable", "key", "decode", "rows")
 
     def __init__(self, staged, sample: bool, graphable: bool, key=None, decode: bool = False):
         self.staged = staged
@@ -32,6 +32,7 @@ class Prepared:
         self.graphable = graphable
         self.key = key
         self.decode = decode
+        self.rows = staged.rows   # wanted rows without padding: what the caller gets back
 
 
 class ModelRunner:
@@ -74,6 +75,11 @@ class ModelRunner:
         # its forward() depends on the batch's shape alone (`capture_safe`; parts that do not say so,
         # such as one that branches on a request's position, keep such batches uncaptured)
         self.capture_portions = bool(getattr(self.model, "capture_safe", False))
+        # batches of single tokens are padded up to a few sizes (multiples of eight), so that a
+        # workload whose batch shrinks and grows request by request replays a handful of captured
+        # sequences instead of capturing one per size; on the same condition, because a padding
+        # row carries slot -1 and state slot -1, which a part with state of its own must skip
+        self.pad_decode = self.capture_portions
         self._graphs: dict = {}
         self._seen: dict = {}
         self.portion_sightings = 5   # a shape with portions is captured when it comes for the sixth time
@@ -115,10 +121,15 @@ class ModelRunner:
     def prepare(self, entries: list[StepEntry], sample: bool = False) -> "Prepared":
         """The host half of a step: the batch's metadata packed into pinned memory, nothing sent
         yet.  It may run while the device still works on the step before."""
-        staged = self.builder.stage(entries, defer=True)
+        pad_to = 0
+        if self.pad_decode and self.use_graphs and self.device.type == "cuda" and len(entries) > 8:
+            pad_to = -(-len(entries) // 8) * 8
+        staged = self.builder.stage(entries, defer=True, pad_to=pad_to)
         if sample and not staged.sampled:
             raise ValueError("sample=True needs `sampling` on every entry that wants logits")
         decode = max(staged.q_lens) == 1 and staged.r == staged.s and all(e.want == [0] for e in entries)
+        if not decode and staged.rows != staged.r:
+            raise AssertionError("only batches of single tokens that all want their logits are padded")
         graphable = self.use_graphs and self.device.type == "cuda" and (decode or self.capture_portions)
         # what a captured launch sequence has baked in: the number of entries, every entry's
         # length (grids and shapes follow from them), the number of wanted rows, the table widths
@@ -163,7 +174,7 @@ class ModelRunner:
         length, the wanted rows, the table widths) has been seen a few times.  A captured sequence
         bakes in what the parts computed on the host from the shape; parts must not branch on
         other host-side values of the step (positions, slots) if they are to be captured."""
-        staged, sample, graphable = prepared.staged, prepared.sample, prepared.graphable
+        staged, sample, graphable, rows = prepared.staged, prepared.sample, prepared.graphable, prepared.rows
         self.builder.commit(staged)
         key = prepared.key
         if graphable and not prepared.decode and key not in self._graphs:
@@ -176,13 +187,13 @@ class ModelRunner:
             graphable = self._seen[key] > self.portion_sightings
         if not graphable:
             logits, tokens = self._run(self.builder.context(staged), sample)
-            return (logits, tokens) if sample else logits
+            return (logits[:rows], tokens[:rows]) if sample else logits[:rows]
         held = self._graphs.get(key)
         if held is not None and held[0] == self._generation():
             held[1].replay()   # the metadata is already on its way; no views are needed
             self.ops.launches += held[4]
             self.ops.library_calls += held[5]
-            return (held[2], held[3]) if sample else held[2]
+            return (held[2][:rows], held[3][:rows]) if sample else held[2][:rows]
         ctx = self.builder.context(staged)
         # first time (or buffers moved): run eagerly for this step's result, then capture
         logits, tokens = self._run(ctx, sample)
@@ -197,4 +208,4 @@ class ModelRunner:
             if len(self._graphs) >= 64:
                 self._graphs.pop(next(iter(self._graphs)))
             self._graphs[key] = (generation, graph, g_logits, g_tokens, counted[0], counted[1])
-        return (logits, tokens) if sample else logits
+        return (logits[:rows], tokens[:rows]) if sample else logits[:rows]

@@ -190,3 +190,44 @@ def test_a_stop_token_while_the_next_step_is_in_flight_drops_that_row_only():
     assert engine.block_manager.whole() and not engine.requests
     # whatever was in flight when the last request ended is drained by the next call
     assert engine.generate([prompts[0]], SamplingParams(max_new_tokens=3, ignore_eos=True))[0] == free_run[0][:3]
+
+
+def test_padding_rows_of_a_decode_batch_store_nothing_and_come_last():
+    """A batch of single tokens padded to a fixed size: real rows first and unchanged, padding rows
+    are one-token sequences at position 0 over page 0 with slot -1 and state slot -1; batches
+    with a portion, or with a row that wants nothing, are never padded."""
+    from shrike_b200.engine.batch import BatchBuilder
+
+    engine, _ = engine_for("A", num_blocks=16)
+    cache_manager, builder = engine.block_manager, BatchBuilder(16, 1, "cpu", None)
+    caches = []
+    for length in (20, 3, 17):
+        cache = cache_manager.open()
+        cache_manager.append(cache, 0, length + 1)
+        caches.append((cache, length))
+    entries = [StepEntry(c, [7 + i], n, [0], (0.5, 0.9, 11 + i)) for i, (c, n) in enumerate(caches)]
+    plain = builder.stage(entries)
+    assert (plain.s, plain.r, plain.rows) == (3, 3, 3)
+    a = builder.context(plain)
+    rows_a = [t.clone() for t in (a.token_ids, a.positions, a.ctx_len, a.state_slot, a.groups[0].slot_mapping,
+                                   a.groups[0].block_table, a.sample_temperature, a.sample_seed)]
+    padded = builder.stage(entries, pad_to=8)
+    assert (padded.n, padded.s, padded.r, padded.rows) == (8, 8, 8, 3)
+    b = builder.context(padded)
+    rows_b = (b.token_ids, b.positions, b.ctx_len, b.state_slot, b.groups[0].slot_mapping,
+              b.groups[0].block_table, b.sample_temperature, b.sample_seed)
+    for x, y in zip(rows_a, rows_b):
+        assert torch.equal(x, y[:3])
+    assert b.token_ids[3:].tolist() == [0] * 5 and b.positions[3:].tolist() == [0] * 5
+    assert b.ctx_len[3:].tolist() == [1] * 5 and b.state_slot[3:].tolist() == [-1] * 5
+    assert b.groups[0].slot_mapping[3:].tolist() == [-1] * 5
+    assert b.groups[0].block_table[3:, 0].tolist() == [0] * 5 and (b.groups[0].block_table[3:, 1:] == -1).all()
+    assert b.sample_temperature[3:].tolist() == [0.0] * 5 and b.sample_top_p[3:].tolist() == [1.0] * 5
+    assert b.q_start.tolist() == list(range(9)) and b.out_rows.tolist() == list(range(8)) and b.all_single
+    silent = entries[:2] + [StepEntry(caches[2][0], [9], caches[2][1], [])]
+    assert builder.stage(silent, pad_to=8).s == 3
+    cache_manager.append(caches[0][0], 21, 1)
+    portion = [StepEntry(caches[0][0], [1, 2], 20, [1])] + entries[1:]
+    assert builder.stage(portion, pad_to=8).s == 3
+    for cache, _ in caches:
+        cache_manager.free(cache)

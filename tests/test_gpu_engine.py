@@ -155,3 +155,59 @@ def test_launching_ahead_gives_the_tokens_of_the_plain_loop_on_the_gpu(tmp_path,
         assert len(engine.runner._graphs) >= 3
         engine.ops.check_status()
     assert outs[0] == outs[1]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_batches_padded_to_a_few_sizes_give_the_same_logits_and_tokens(tmp_path, dtype):
+    """Batches of 9 to 17 single tokens run as batches of 16 and 24 (padding rows that store
+    nothing): the logits and drawn tokens of the real rows are those of the unpadded batch (in
+    float32 bit for bit), the cache is left as the unpadded run leaves it (the next steps agree
+    too), and far fewer launch sequences are captured."""
+    import torch
+
+    from shrike_b200.config import load_config
+    from shrike_b200.engine.batch import StepEntry
+    from shrike_b200.engine.llm_engine import make_ops
+    from shrike_b200.engine.runner import ModelRunner
+    from shrike_b200.weights import load_weights
+
+    folder = make_model_folder(tmp_path, "B")
+    config = load_config(str(folder))
+    prompts = [random_tokens(384, 3 + 5 * i, 20 + i) for i in range(17)]
+
+    def run(pad: bool):
+        tensors = load_weights(str(folder), config, getattr(torch, dtype), "cuda")
+        runner = ModelRunner(config, tensors, make_ops(dtype, "cuda"), "cuda", dtype, page_size=8, num_pages=300, max_slots=32)
+        assert runner.pad_decode
+        runner.pad_decode = pad
+        caches, fed = [], []
+        for ids in prompts:
+            cache = runner.cache.open()
+            runner.cache.append(cache, 0, len(ids))
+            runner.step([StepEntry(cache, ids, 0, [])])
+            caches.append(cache)
+            fed.append(len(ids))
+        logits, tokens = [], []
+        for step, live in enumerate([17, 16, 13, 12, 11, 9, 9, 10, 17, 8, 15]):   # requests pause and come back
+            entries = []
+            for i in range(live):
+                runner.cache.append(caches[i], fed[i], 1)
+                entries.append(StepEntry(caches[i], [(31 * step + 7 * i) % 384], fed[i], [0], (0.8 if i % 3 else 0.0, 0.9, 5 + i)))
+                fed[i] += 1
+            out, drawn = runner.step(entries, sample=True)
+            assert out.shape[0] == live and drawn.shape[0] == live
+            logits.append(out.float().cpu().clone())
+            tokens.append(drawn.cpu().tolist())
+        graphs = len(runner._graphs)
+        for cache in caches:
+            runner.cache.free(cache)
+        assert runner.cache.whole()
+        return torch.cat(logits), tokens, graphs
+
+    padded, padded_tokens, few = run(True)
+    exact, exact_tokens, many = run(False)
+    assert few <= 5 and many >= 9   # sizes 8, 16, 24 (times two table widths) against every size that came
+    if dtype == "float32":
+        assert torch.equal(padded, exact) and padded_tokens == exact_tokens
+    else:
+        assert (padded - exact).abs().max() < 2e-2
