@@ -31,6 +31,12 @@ be checked and the cache sized before anything is put on the device):
   block
       forward(resid_f32, delta, ctx, run) -> (resid_f32, delta)
           `delta` is a sum not yet added to the residual; the next norm adds it.
+
+A part may declare the class attribute `capture_safe = True`.  It then promises that forward()
+launches the same kernels with the same sizes for the same batch shape, whatever the positions,
+slots and pages of the step (so a recorded launch sequence can be replayed), and that it leaves
+rows alone whose cache slot and state slot are -1: the step function pads batches of single
+tokens with such rows up to a few fixed sizes.  A model is treated so only if all its parts say so.
 """
 
 from __future__ import annotations
