@@ -125,3 +125,50 @@ def run(args, raw_model: dict, context: int) -> dict:
         }
     finally:
         shutil.rmtree(work, ignore_errors=True)
+
+
+def run_mixed(args, raw_model: dict) -> dict:
+    """The reference's own offline benchmark shape (bench/bench_engine.py: 64 requests through
+    `LLMEngine.generate`, lengths drawn as bench/workload.py:15-22 draws them) on the prompts and
+    output lengths of bench.py's `--workload mixed`, with the stock constructor (budget 512)."""
+    import random
+
+    import torch
+
+    sys.path.insert(0, str(ROOT / "baseline" / "_ref"))
+    try:
+        from shrike.engine.engine import LLMEngine
+        from shrike.engine.request import SamplingParams
+    except Exception as error:  # noqa: BLE001
+        return {"impl": "reference", "unavailable": f"baseline/_ref does not import: {type(error).__name__}: {error}"[:300]}
+
+    raw = dict(raw_model)
+    if args.layers:
+        raw["num_hidden_layers"] = args.layers
+    work = Path(tempfile.mkdtemp(prefix="shrike_reference_"))
+    try:
+        write_model_folder(work, raw)
+        torch.cuda.empty_cache()
+        engine = LLMEngine(str(work))
+        rng = random.Random(20260718)
+        outputs = [rng.randint(32, 256) for _ in range(64)]
+        prompts = [[rng.randrange(raw["vocab_size"]) for _ in range(rng.randint(32, 2048))] for _ in range(64)]
+        params = [SamplingParams(max_new_tokens=n, temperature=0.0, ignore_eos=True) for n in outputs]
+        engine.generate(prompts[:4], params[:4], chat=False)   # warm-up, as in the other arm
+        torch.cuda.synchronize()
+        steps_before = engine.stats.steps
+        began = time.perf_counter()
+        results = engine.generate(prompts, params, chat=False)
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - began
+        generated = sum(len(r) for r in results)
+        return {
+            "impl": "reference", "workload": "mixed", "model": "Qwen2.5-1.5B shape", "layers": raw["num_hidden_layers"],
+            "requests": 64, "prompt_tokens": sum(len(p) for p in prompts), "generated_tokens": generated,
+            "seconds": round(seconds, 3), "value": round(generated / seconds, 1), "unit": "generated tok/s",
+            "steps": engine.stats.steps - steps_before, "budget": 512, "dtype": "bf16",
+            "engine_defaults": "stock LLMEngine(model_dir): prefix caching on, einsum attention",
+            "data": "synthetic: seeded random weights and uniform random token ids",
+        }
+    finally:
+        shutil.rmtree(work, ignore_errors=True)

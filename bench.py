@@ -698,8 +698,10 @@ def run_reference(args) -> dict:
     reference = ROOT / "baseline" / "_ref"
     if not (reference / "shrike").is_dir():
         return {"impl": "reference", "unavailable": "the reference is not installed under baseline/_ref"}
-    from baseline.reference_arm import run  # the unmodified reference through its own LLMEngine
+    from baseline.reference_arm import run, run_mixed  # the unmodified reference through its own LLMEngine
 
+    if args.workload == "mixed":
+        return run_mixed(args, MODEL_1_5B)
     return run(args, SHAPES[args.shape][1], args.context)
 
 
@@ -732,7 +734,7 @@ def main():
     if args.case:
         print(json.dumps(run_case(args)))
         return
-    if args.workload == "mixed":
+    if args.workload == "mixed" and args.impl != "reference":
         print(json.dumps(run_mixed(args)))
         return
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
