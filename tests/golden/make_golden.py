@@ -38,7 +38,9 @@ def weights_checksum(weights: dict) -> str:
 
 
 def main():
-    reference = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <checkout of Azimml/shrike>")
+    reference = sys.argv[1]
     sys.path.insert(0, reference)
     from shrike.models.qwen import NaiveKVBackend, QwenForCausalLM
 
