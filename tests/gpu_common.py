@@ -13,12 +13,14 @@ from tests.helpers import collect, max_live_tokens
 TOL = {"float32": 2e-5, "bfloat16": 2e-2}
 
 
-def replay(folder, dtype, steps, max_tokens=None, poison=False):
+def replay(folder, dtype, steps, max_tokens=None, poison=False, page_size=None, num_pages=None, max_live=None):
     """Runs a trace in-process through the replay program's session; returns
     per-request logits and the session."""
     from shrike_b200.replay import TraceSession
 
-    session = TraceSession(folder, dtype, max_tokens or max_live_tokens(steps))
+    if num_pages is None and max_tokens is None:
+        max_tokens = max_live_tokens(steps)
+    session = TraceSession(folder, dtype, max_tokens, page_size=page_size, num_pages=num_pages, max_live=max_live)
     if poison:  # whatever is read from a page before it was written shows as NaN
         for pool in session.runner.storage.kv:
             pool.fill_(float("nan"))

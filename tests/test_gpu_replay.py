@@ -46,31 +46,64 @@ WAYS = {
 }
 
 
+# every tiny configuration at the page size it is named with (A 16, B 8, C 16), and two more
+# page sizes so that a page's edge falls elsewhere among the same portions: 32, and 24, which
+# divides neither 64 nor the portion sizes
+MODEL_PAGES = [("A", 16), ("B", 8), ("C", 16), ("B", 32), ("A", 8), ("C", 24)]
+
+
 @pytest.mark.parametrize("way", list(WAYS))
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("key", ["A", "B", "C"])
-def test_replay_matches_plain(tmp_path_factory, key, dtype, way):
+@pytest.mark.parametrize("key,page", MODEL_PAGES)
+def test_replay_matches_plain(tmp_path_factory, key, page, dtype, way):
     folder, requests, want = setup(tmp_path_factory, key, dtype)
     steps = WAYS[way](requests)
-    got, session = replay(folder, dtype, steps, poison=way.startswith("mixed"))
+    got, session = replay(folder, dtype, steps, poison=way.startswith("mixed"), page_size=page, max_live=4)
+    assert session.page_size == page and session.runner.storage.kv[0].shape[3] == page
     assert session.runner.cache.whole(), "pages or slots were not given back"
     for ident in requests:
-        assert_close(got[ident], want[ident], TOL[dtype], f"{key} {dtype} {way} {ident}")
+        assert_close(got[ident], want[ident], TOL[dtype], f"{key} page {page} {dtype} {way} {ident}")
+
+
+def pages_needed(steps, page):
+    """The fewest pages a trace can run on: the most that live requests hold at once."""
+    held, worst = {}, 0
+    for record in steps:
+        for entry in record["entries"]:
+            held[entry["id"]] = held.get(entry["id"], 0) + len(entry["tokens"])
+        worst = max(worst, sum(-(-n // page) for n in held.values()))
+        for ident in record["end"]:
+            held.pop(ident, None)
+    return worst
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_mixed_replay_reuses_pages(tmp_path_factory, dtype):
-    folder, requests, want = setup(tmp_path_factory, "B", dtype)
+@pytest.mark.parametrize("key,page", [("B", 8), ("A", 16), ("B", 32)])
+def test_mixed_replay_reuses_pages(tmp_path_factory, key, page, dtype):
+    """The pool holds exactly as many pages as the trace needs at its fullest moment (given
+    with --num-blocks), so later requests can only run on pages that earlier ones gave back:
+    if `free` stopped returning pages, the replay would run out of them."""
+    folder, requests, want = setup(tmp_path_factory, key, dtype)
     steps = mixed_trace(requests, seed=5)
-    budget = max_live_tokens(steps)
-    assert budget < sum(-(-len(t) // 64) * 64 for t in requests.values()), "the trace never frees anything"
-    got, session = replay(folder, dtype, steps, max_tokens=budget, poison=True)
-    seen = {}
-    # a page id must have been held by more than one request over the trace
-    for pool in session.runner.cache.pools:
-        assert pool.num_free == pool.count
+    num_pages = pages_needed(steps, page)
+    assert num_pages < sum(-(-len(t) // page) for t in requests.values()), "the trace never frees anything"
+    got, session = replay(folder, dtype, steps, num_pages=num_pages, page_size=page, max_live=4, poison=True)
+    assert session.runner.cache.num_pages == [num_pages]
+    shared = {page_id: owners for page_id, owners in session.page_owners.items() if len(owners) > 1}
+    assert shared, "no page was held by more than one request over the trace"
+    assert len({owner for owners in shared.values() for owner in owners}) >= 4
+    assert session.runner.cache.whole()
     for ident in requests:
-        assert_close(got[ident], want[ident], TOL[dtype], f"reuse {dtype} {ident}")
+        assert_close(got[ident], want[ident], TOL[dtype], f"reuse {key} page {page} {dtype} {ident}")
+
+
+def test_replay_runs_out_of_pages_when_nothing_is_given_back(tmp_path_factory):
+    """The same tight pool with the `end` lists dropped: the replay must say that pages ran out."""
+    folder, requests, _ = setup(tmp_path_factory, "B", "float32")
+    steps = [dict(record, end=[]) for record in mixed_trace(requests, seed=5)]
+    num_pages = pages_needed(mixed_trace(requests, seed=5), 8)
+    with pytest.raises(RuntimeError, match="no pages left|raise --max-live"):
+        replay(folder, "float32", steps, num_pages=num_pages, page_size=8, max_live=8)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -80,7 +113,7 @@ def test_long_decoding_token_by_token(tmp_path_factory, dtype):
     want = plain_logits("C", read_weights(folder), tokens, bf16=(dtype == "bfloat16"))
     steps = [{"step": i, "entries": [{"id": "x", "tokens": [t], "want": [0]}], "end": ["x"] if i == 299 else []}
              for i, t in enumerate(tokens)]
-    got, session = replay(folder, dtype, steps)
+    got, session = replay(folder, dtype, steps, page_size=16)
     assert_close(got["x"], want, TOL[dtype], f"long decode {dtype}")
     assert session.runner.cache.whole()
 
