@@ -30,36 +30,18 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-MODEL_7B = dict(
-    architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=3584, intermediate_size=18944,
-    num_hidden_layers=28, num_attention_heads=28, num_key_value_heads=4, head_dim=128, vocab_size=152064,
-    rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False, max_position_embeddings=32768,
-    eos_token_id=151643, torch_dtype="bfloat16",
-)
-MODEL_1_5B = dict(
-    architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=1536, intermediate_size=8960,
-    num_hidden_layers=28, num_attention_heads=12, num_key_value_heads=2, head_dim=128, vocab_size=151936,
-    rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=True, max_position_embeddings=32768,
-    eos_token_id=151643, torch_dtype="bfloat16",
-)
-def _qwen(hidden, inter, layers, heads, kv, head_dim, vocab, tied, eps=1e-6):
-    return dict(
-        architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=hidden, intermediate_size=inter,
-        num_hidden_layers=layers, num_attention_heads=heads, num_key_value_heads=kv, head_dim=head_dim,
-        vocab_size=vocab, rms_norm_eps=eps, rope_theta=1000000.0, tie_word_embeddings=tied,
-        max_position_embeddings=32768, eos_token_id=151643, torch_dtype="bfloat16")
+def _shapes() -> dict:
+    """The layer sizes of the Qwen2.5 dense family, read from the package's shape files; the
+    larger ones run with --layers (or in --case timeline)."""
+    from shrike_b200.shapes import shape_config
+
+    return {key: (f"Qwen2.5-{key.upper()} shape", shape_config(f"qwen2.5-{key}"))
+            for key in ("0.5b", "1.5b", "3b", "7b", "14b", "32b", "72b")}
 
 
-# the layer sizes of the Qwen2.5 dense family; the larger ones run with --layers (or in --case timeline)
-SHAPES = {
-    "0.5b": ("Qwen2.5-0.5B shape", _qwen(896, 4864, 24, 14, 2, 64, 151936, True)),
-    "1.5b": ("Qwen2.5-1.5B shape", MODEL_1_5B),
-    "3b": ("Qwen2.5-3B shape", _qwen(2048, 11008, 36, 16, 2, 128, 151936, True)),
-    "7b": ("Qwen2.5-7B shape", MODEL_7B),
-    "14b": ("Qwen2.5-14B shape", _qwen(5120, 13824, 48, 40, 8, 128, 152064, False, 1e-5)),
-    "32b": ("Qwen2.5-32B shape", _qwen(5120, 27648, 64, 40, 8, 128, 152064, False, 1e-5)),
-    "72b": ("Qwen2.5-72B shape", _qwen(8192, 29568, 80, 64, 8, 128, 152064, False, 1e-5)),
-}
+SHAPES = _shapes()
+MODEL_7B = SHAPES["7b"][1]
+MODEL_1_5B = SHAPES["1.5b"][1]
 DEVICE_BYTES_LIMIT = 120e9   # weights and cache pool together stay under this, whatever the options
 CONTEXT = 1024
 PREFILL_TOKENS = 2048

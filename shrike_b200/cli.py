@@ -1,17 +1,23 @@
 """Interactive terminal chat over the in-process engine.
 
-The commands and their meanings are those of Azimml/shrike's REPL
-(shrike/cli.py:29-52,173-283): /help /clear /metrics /reset /temp /max /budget
-/bench /system /exit; chat defaults temperature 0.7, top_p 0.9, 512 new tokens
-(cli.py:110,169-170); a status line with tokens, seconds, tokens per second and the
-time to the first token after each reply (cli.py:145-150); Ctrl-C aborts the reply
-and frees its pages (cli.py:131-143).  `/spec` and `/cache` are gone with the
-features they switched.  A model folder without tokenizer files is served too: a
-line of space-separated token ids is the prompt then, and ids are printed back.
+The command names and what they do are Azimml/shrike's (shrike/CLI_SPEC.md, "Slash
+commands"; shrike/cli.py:29-52): /help /clear /metrics /reset /temp /max /budget /bench
+/system /exit; chat samples at temperature 0.7, top_p 0.9, up to 512 new tokens; every
+reply ends with a status line (tokens, seconds, tokens per second, time to the first
+token); Ctrl-C during a reply aborts it and gives its pages back, Ctrl-C at the prompt
+only prints a hint, Ctrl-D or /exit leaves.  `/spec` and `/cache` are gone with the
+features they switched.  The program itself is this package's own: a table of commands,
+each with one argument reader and one handler, and a `Console` that owns the
+conversation.  A model folder without tokenizer files is served too: a line of
+space-separated token ids is the prompt then, and ids are printed back.
 
-    python -m shrike_b200.cli --model DIR [--dtype bfloat16|float32] [--block-size 16]
-        [--num-blocks N] [--gpu-mem-util 0.85] [--max-tokens-per-step 512] [--max-running 256]
-        [--seed 0]
+    python -m shrike_b200.cli --model DIR | --random SHAPE [--seed 0]
+        [--dtype bfloat16|float32] [--block-size 16] [--num-blocks N] [--gpu-mem-util 0.85]
+        [--max-tokens-per-step 512] [--max-running 256]
+
+`--random SHAPE` starts without a checkpoint: SHAPE names one of the package's shape
+files (`shrike_b200/shapes/`, e.g. qwen2.5-7b, tiny) or is the path of a config.json, and
+the weights are drawn on the GPU from `--seed`.
 """
 
 from __future__ import annotations
@@ -19,250 +25,332 @@ from __future__ import annotations
 import argparse
 import sys
 import time
+from dataclasses import dataclass
+from typing import Callable
 
 from .engine.request import SamplingParams
 from .settings import DEFAULT_MODEL_DIR
 
-HELP = """Commands:
-  /help                Show this help
-  /clear               Clear conversation history
-  /metrics             Show engine metrics (steps, tokens, blocks, preemptions)
-  /reset               Zero the metrics counters (clean measurements)
-  /temp <float>        Set temperature; 0 uses greedy decoding
-  /max <int>           Set maximum new tokens
-  /budget <int>        Set scheduler token budget per step (chunked prefill)
-  /bench <n> [tokens]  Fire n concurrent requests (default 64 tokens each)
-                       and report aggregate throughput
-  /system <text>       Set or replace the system message
-  /exit                Quit
-
-Without tokenizer files in the model folder a prompt is a line of token ids: 12 7 105"""
+CHAT_TEMPERATURE, CHAT_TOP_P, CHAT_MAX_NEW_TOKENS = 0.7, 0.9, 512
 
 
-def parse_args(argv=None) -> argparse.Namespace:
-    parser = argparse.ArgumentParser(description="Chat with a local model through shrike_b200")
-    parser.add_argument("--model", default=DEFAULT_MODEL_DIR)
+def add_engine_options(parser: argparse.ArgumentParser) -> None:
+    """The options every entry point of the package shares: where the model comes from and how
+    the engine is sized.  The names are the constructor arguments of Azimml/shrike's LLMEngine
+    (shrike/engine/engine.py:42-53) with dashes."""
+    parser.add_argument("--model", default=None, help=f"model folder (default {DEFAULT_MODEL_DIR})")
+    parser.add_argument("--random", default=None, metavar="SHAPE",
+                        help="no checkpoint: a named shape or a config.json, filled with random weights")
+    parser.add_argument("--seed", type=int, default=0, help="seed of random weights and of sampling")
     parser.add_argument("--dtype", default=None, choices=["bfloat16", "float32"])
     parser.add_argument("--block-size", type=int, default=16)
     parser.add_argument("--num-blocks", type=int, default=None)
     parser.add_argument("--gpu-mem-util", type=float, default=0.85)
     parser.add_argument("--max-tokens-per-step", type=int, default=512)
     parser.add_argument("--max-running", type=int, default=256)
-    parser.add_argument("--seed", type=int, default=0)
+
+
+def open_engine(args):
+    """The engine the shared options describe, and a name for it."""
+    from .engine import llm_engine
+
+    if args.random is not None and args.model is not None:
+        raise SystemExit("give --model or --random, not both")
+    options = dict(block_size=args.block_size, gpu_mem_util=args.gpu_mem_util,
+                   max_tokens_per_step=args.max_tokens_per_step, max_running=args.max_running,
+                   num_blocks=args.num_blocks, dtype=args.dtype, seed=args.seed)
+    if args.random is not None:
+        return llm_engine.LLMEngine.from_random(args.random, **options), f"random weights, shape {args.random}"
+    model = args.model or DEFAULT_MODEL_DIR
+    return llm_engine.LLMEngine(model, **options), model
+
+
+def parse_args(argv=None) -> argparse.Namespace:
+    parser = argparse.ArgumentParser(description="Chat with a local model through shrike_b200")
+    add_engine_options(parser)
     return parser.parse_args(argv)
 
 
-def _dim(text: str, enabled: bool) -> str:
-    return f"\033[2m{text}\033[0m" if enabled else text
+# ---- argument readers: text after the command -> value, or ValueError ------------------
+def _number(kind, low, inclusive=True):
+    def read(text: str):
+        value = kind(text)
+        if value != value or value == float("inf") or value < low or (value == low and not inclusive):
+            raise ValueError(text)
+        return value
+    return read
 
 
-def run_bench(engine, count: int, tokens: int, out=print) -> None:
-    """n identical requests, greedy, fixed length (shrike/cli.py:55-77)."""
-    if engine.tokenizer is not None:
-        prompt = "Explain why paged memory management helps LLM serving."
-    else:
-        vocab = engine.config.vocab_size
-        prompt = [(7 * i + 3) % vocab for i in range(16)]
-    sampling = SamplingParams(max_new_tokens=tokens, temperature=0.0, ignore_eos=True)
-    try:
-        for _ in range(count):
-            engine.add_request(prompt, sampling)
-    except ValueError as error:
-        out(f"[error] {error}")
-        return
-    started = time.perf_counter()
-    generated = steps = 0
+def _bench_arguments(text: str):
+    fields = text.split()
+    if not 1 <= len(fields) <= 2:
+        raise ValueError(text)
+    count = _number(int, 1)(fields[0])
+    tokens = _number(int, 1)(fields[1]) if len(fields) == 2 else 64
+    return count, tokens
+
+
+def _text(text: str) -> str:
+    if not text:
+        raise ValueError(text)
+    return text
+
+
+@dataclass(frozen=True)
+class Command:
+    name: str
+    signature: str                       # how the argument is shown in /help and in a usage hint
+    summary: str
+    handler: Callable                    # Console method; gets the read argument when `read` is set
+    read: Callable | None = None
+
+
+class TokenPrinter:
+    """Turns a stream of token ids into printable text.  With a tokenizer, ids are held back
+    while they decode to half a character (shrike/CLI_SPEC.md, "Behavior"); without one the
+    ids themselves are printed."""
+
+    def __init__(self, tokenizer):
+        self.tokenizer = tokenizer
+        self.held: list[int] = []
+
+    def feed(self, token_id: int) -> str:
+        if self.tokenizer is None:
+            return f"{token_id} "
+        self.held.append(token_id)
+        text = self.tokenizer.decode(self.held, skip_special_tokens=True)
+        if text.endswith("�"):
+            return ""
+        self.held.clear()
+        return text
+
+
+def run_requests(engine, on_output=None) -> tuple[int, int]:
+    """Steps the engine until it is idle; returns (outputs seen, steps)."""
+    outputs = steps = 0
     while engine.has_work:
-        generated += len(engine.step())
+        for output in engine.step():
+            outputs += 1
+            if on_output is not None:
+                on_output(output)
         steps += 1
-    elapsed = time.perf_counter() - started
-    out(f"{count} reqs x {tokens} tok -> {generated} tok in {elapsed:.2f}s = {generated / elapsed:.0f} tok/s aggregate "
-        f"({generated / elapsed / count:.1f} tok/s per request, {steps} steps)")
+    return outputs, steps
 
 
-def stream_reply(engine, prompt_ids, temperature, max_new_tokens, use_color, out=None):
-    """Adds one request and prints its tokens as they come.  Returns the reply text
-    (or token ids as text), or None when the request was refused or aborted."""
-    out = out or sys.stdout
-    started = time.perf_counter()
-    first_at = None
-    generated: list[int] = []
-    pending: list[int] = []
-    parts: list[str] = []
-    request_id = None
-    try:
-        sampling = SamplingParams(max_new_tokens=max_new_tokens, temperature=temperature, top_p=0.9)
+class Console:
+    """One conversation with one engine: the settings the commands change, and the turns."""
+
+    def __init__(self, engine, write=print, color: bool = False):
+        self.engine = engine
+        self.write = write
+        self.color = color
+        self.turns: list[dict] = []          # {role, content[, ids]} as a chat template takes them
+        self.temperature = CHAT_TEMPERATURE
+        self.max_new_tokens = CHAT_MAX_NEW_TOKENS
+        self.commands = {c.name: c for c in (
+            Command("/help", "", "this list", Console.show_help),
+            Command("/clear", "", "forget the conversation so far", Console.clear),
+            Command("/metrics", "", "engine counters: steps, tokens, KV blocks, preemptions", Console.show_metrics),
+            Command("/reset", "", "set the counters of /metrics back to zero", Console.reset_metrics),
+            Command("/temp", "<float >= 0>", "sampling temperature; 0 decodes greedily", Console.set_temperature,
+                    _number(float, 0.0)),
+            Command("/max", "<int >= 1>", "most new tokens per reply", Console.set_max_new_tokens, _number(int, 1)),
+            Command("/budget", "<int >= 1>", "tokens the scheduler runs per step (chunked prefill)",
+                    Console.set_budget, _number(int, 1)),
+            Command("/bench", "<requests> [tokens each, default 64]",
+                    "run that many identical greedy requests at once and report the throughput",
+                    Console.bench, _bench_arguments),
+            Command("/system", "<text>", "set or replace the system message", Console.set_system, _text),
+            Command("/exit", "", "leave", Console.leave),
+        )}
+
+    # ---- dispatch ---------------------------------------------------------------
+    def handle(self, line: str) -> bool:
+        """One input line.  Returns False when the session is over."""
+        line = line.strip()
+        if not line:
+            return True
+        if not line.startswith("/"):
+            self.say(line)
+            return True
+        name, _, rest = line.partition(" ")
+        command = self.commands.get(name)
+        if command is None:
+            self.write(f"{name} is not a command here; /help lists them.")
+            return True
+        if command.read is None:
+            return command.handler(self) is not False
         try:
-            request_id = engine.add_request(prompt_ids, sampling, chat=False)
+            value = command.read(rest.strip())
+        except (ValueError, OverflowError):
+            self.write(f"usage: {command.name} {command.signature}")
+            return True
+        return command.handler(self, value) is not False
+
+    # ---- commands ---------------------------------------------------------------
+    def show_help(self):
+        width = max(len(f"{c.name} {c.signature}") for c in self.commands.values())
+        for c in self.commands.values():
+            self.write(f"  {f'{c.name} {c.signature}':<{width}}  {c.summary}")
+        if self.engine.tokenizer is None:
+            self.write("This model folder has no tokenizer: a prompt is a line of token ids, e.g. 12 7 105")
+
+    def clear(self):
+        self.turns.clear()
+        self.write("conversation cleared")
+
+    def show_metrics(self):
+        metrics = self.engine.metrics()
+        width = max(map(len, metrics))
+        for key, value in metrics.items():
+            self.write(f"{key:<{width}}  {value}")
+
+    def reset_metrics(self):
+        self.engine.reset_stats()
+        self.write("counters are back at zero")
+
+    def set_temperature(self, value: float):
+        self.temperature = value
+        self.write(f"temperature = {value:g}" + (" (greedy)" if value == 0 else ""))
+
+    def set_max_new_tokens(self, value: int):
+        self.max_new_tokens = value
+        self.write(f"replies stop after {value} new tokens")
+
+    def set_budget(self, value: int):
+        self.engine.scheduler.max_tokens_per_step = value
+        self.write(f"the scheduler now runs up to {value} tokens per step")
+
+    def set_system(self, text: str):
+        if self.engine.tokenizer is None:
+            self.write("a system message needs a tokenizer, and this model folder has none")
+            return
+        replaced = bool(self.turns) and self.turns[0]["role"] == "system"
+        if replaced:
+            self.turns[0]["content"] = text
+        else:
+            self.turns.insert(0, {"role": "system", "content": text})
+        self.write("system message replaced" if replaced else "system message set")
+
+    def leave(self):
+        return False
+
+    def bench(self, arguments):
+        """`count` identical greedy requests of fixed length, run together (the `/bench` of
+        shrike/cli.py:55-77; the prompt here is 16 fixed token ids, since random-weight folders
+        have no tokenizer)."""
+        count, tokens = arguments
+        vocab = self.engine.config.vocab_size
+        prompt = [(7 * i + 3) % vocab for i in range(16)]
+        sampling = SamplingParams(max_new_tokens=tokens, temperature=0.0, ignore_eos=True)
+        try:
+            for _ in range(count):
+                self.engine.add_request(prompt, sampling)
         except ValueError as error:
-            print(f"[error] {error}", file=out)
+            self.write(f"refused: {error}")
+            return
+        began = time.perf_counter()
+        generated, steps = run_requests(self.engine)
+        seconds = max(time.perf_counter() - began, 1e-9)
+        self.write(f"{count} requests x {tokens} tokens: {generated} tokens in {seconds:.2f} s, "
+                   f"{generated / seconds:.0f} tok/s in all, {generated / seconds / count:.1f} tok/s each, {steps} steps")
+
+    # ---- a turn -----------------------------------------------------------------
+    def _prompt_ids(self, line: str):
+        """Token ids of the conversation with `line` as the next user turn, and the turn."""
+        tokenizer = self.engine.tokenizer
+        if tokenizer is not None:
+            turn = {"role": "user", "content": line}
+            encoded = tokenizer.apply_chat_template(self.turns + [turn], add_generation_prompt=True)
+            return list(encoded["input_ids"] if isinstance(encoded, dict) else encoded), turn
+        try:
+            ids = [int(field) for field in line.split()]
+        except ValueError:
+            self.write("no tokenizer in this model folder: type token ids separated by spaces, or a /command")
+            return None, None
+        history = [token for turn in self.turns for token in turn.get("ids", [])]
+        return history + ids, {"role": "user", "content": line, "ids": ids}
+
+    def say(self, line: str):
+        ids, turn = self._prompt_ids(line)
+        if ids is None:
+            return
+        reply = self.stream(ids)
+        if reply is None:
+            return
+        text, generated = reply
+        self.turns.append(turn)
+        answer = {"role": "assistant", "content": text}
+        if self.engine.tokenizer is None:
+            answer["ids"] = generated
+        self.turns.append(answer)
+
+    def stream(self, prompt_ids):
+        """One request, printed as it is generated.  Returns (text, token ids), or None when
+        the request was refused or interrupted (its pages are back in the pool then)."""
+        sampling = SamplingParams(max_new_tokens=self.max_new_tokens, temperature=self.temperature, top_p=CHAT_TOP_P)
+        try:
+            request_id = self.engine.add_request(prompt_ids, sampling, chat=False)
+        except ValueError as error:
+            self.write(f"refused: {error}")
             return None
-        while engine.has_work:
-            for output in engine.step():
-                if output.req_id != request_id:
-                    continue
-                if first_at is None:
-                    first_at = time.perf_counter()
-                generated.append(output.token_id)
-                if engine.tokenizer is None:
-                    text = f"{output.token_id} "
-                else:
-                    pending.append(output.token_id)
-                    text = engine.tokenizer.decode(pending, skip_special_tokens=True)
-                    if text.endswith("�"):  # half a character: wait for the rest
-                        continue
-                    pending.clear()
-                print(text, end="", flush=True, file=out)
-                parts.append(text)
-    except KeyboardInterrupt:
-        if request_id is not None:
-            engine.abort(request_id)
-        print("\n[aborted]", file=out)
-        return None
-    elapsed = time.perf_counter() - started
-    ttft = (first_at - started) * 1000 if first_at is not None else 0.0
-    rate = len(generated) / max(elapsed, 1e-9)
-    print(file=out)
-    print(_dim(f"⏱ {len(generated)} tok · {elapsed:.1f}s · {rate:.0f} tok/s · TTFT {ttft:.0f}ms", use_color), file=out)
-    return "".join(parts)
+        printer = TokenPrinter(self.engine.tokenizer)
+        generated: list[int] = []
+        pieces: list[str] = []
+        began = time.perf_counter()
+        first = [None]
 
+        def show(output):
+            if output.req_id != request_id:
+                return
+            if first[0] is None:
+                first[0] = time.perf_counter()
+            generated.append(output.token_id)
+            piece = printer.feed(output.token_id)
+            if piece:
+                pieces.append(piece)
+                print(piece, end="", flush=True)
 
-def encode_turn(engine, messages, line):
-    """Token ids for the conversation so far; None (with a message printed) when the line cannot be used."""
-    if engine.tokenizer is not None:
-        encoded = engine.tokenizer.apply_chat_template(messages, add_generation_prompt=True)
-        return list(encoded["input_ids"] if isinstance(encoded, dict) else encoded)
-    try:
-        ids = [int(field) for field in line.split()]
-    except ValueError:
-        print("This model folder has no tokenizer: enter token ids separated by spaces, or a /command.")
-        return None
-    history = [tid for message in messages[:-1] for tid in message.get("ids", [])]
-    return history + ids
+        try:
+            run_requests(self.engine, show)
+        except KeyboardInterrupt:
+            self.engine.abort(request_id)
+            self.write("\n(interrupted; the reply is dropped)")
+            return None
+        seconds = max(time.perf_counter() - began, 1e-9)
+        waited = (first[0] - began) * 1000 if first[0] is not None else 0.0
+        status = (f"[{len(generated)} tok | {seconds:.1f} s | {len(generated) / seconds:.0f} tok/s | "
+                  f"first token after {waited:.0f} ms]")
+        self.write("")
+        self.write(f"\033[2m{status}\033[0m" if self.color else status)
+        return "".join(pieces), generated
 
 
 def main(argv=None) -> None:
     args = parse_args(argv)
     try:
-        import readline  # noqa: F401  (line editing at the prompt)
+        import readline  # noqa: F401  (line editing and history at the prompt)
     except ImportError:
         pass
-    from .engine.llm_engine import EngineStats, LLMEngine
-
-    use_color = sys.stdout.isatty()
-    print(f"Loading {args.model} ...", flush=True)
-    started = time.perf_counter()
-    engine = LLMEngine(
-        args.model, block_size=args.block_size, gpu_mem_util=args.gpu_mem_util,
-        max_tokens_per_step=args.max_tokens_per_step, max_running=args.max_running,
-        num_blocks=args.num_blocks, dtype=args.dtype, seed=args.seed,
-    )
-    print(f"shrike_b200 ready · {args.model} · {min(engine.block_manager.num_pages)} KV blocks "
-          f"· loaded in {time.perf_counter() - started:.1f}s")
-
-    messages: list[dict] = []
-    temperature, max_new_tokens = 0.7, 512
-    prompt = "\001\033[1;36m\002shrike> \001\033[0m\002" if use_color else "shrike> "
-    while True:
+    color = sys.stdout.isatty()
+    began = time.perf_counter()
+    print("loading ...", flush=True)
+    engine, name = open_engine(args)
+    print(f"shrike_b200 ready: {name}, {min(engine.block_manager.num_pages)} KV blocks of "
+          f"{engine.block_manager.page_size} tokens, {time.perf_counter() - began:.1f} s to load; /help lists commands")
+    console = Console(engine, color=color)
+    prompt = "\001\033[1;36m\002shrike_b200> \001\033[0m\002" if color else "shrike_b200> "
+    alive = True
+    while alive:
         try:
             line = input(prompt)
         except EOFError:
             print()
             break
         except KeyboardInterrupt:
-            print("\nUse /exit to quit.")
+            print("\n(/exit or Ctrl-D leaves)")
             continue
-        if not line.strip():
-            continue
-        if line.startswith("/"):
-            command, _, argument = line.strip().partition(" ")
-            argument = argument.strip()
-            if command == "/exit":
-                break
-            if command == "/help":
-                print(HELP)
-            elif command == "/clear":
-                messages.clear()
-                print("Conversation cleared.")
-            elif command == "/metrics":
-                metrics = engine.metrics()
-                width = max(len(key) for key in metrics)
-                for key, value in metrics.items():
-                    print(f"{key:<{width}}  {value}")
-            elif command == "/reset":
-                engine.stats = EngineStats()
-                engine.scheduler.num_preemptions = 0
-                print("Metrics counters reset.")
-            elif command == "/temp":
-                try:
-                    value = float(argument)
-                    if not 0 <= value < float("inf"):
-                        raise ValueError
-                except ValueError:
-                    print("Usage: /temp <non-negative float>")
-                else:
-                    temperature = value
-                    print(f"Temperature set to {temperature:g}.")
-            elif command == "/max":
-                try:
-                    value = int(argument)
-                    if value <= 0:
-                        raise ValueError
-                except ValueError:
-                    print("Usage: /max <positive int>")
-                else:
-                    max_new_tokens = value
-                    print(f"Maximum new tokens set to {max_new_tokens}.")
-            elif command == "/budget":
-                try:
-                    value = int(argument)
-                    if value < 1:
-                        raise ValueError
-                except ValueError:
-                    print("Usage: /budget <positive int>")
-                else:
-                    engine.scheduler.max_tokens_per_step = value
-                    print(f"Scheduler token budget set to {value} per step.")
-            elif command == "/bench":
-                fields = argument.split()
-                try:
-                    count = int(fields[0])
-                    tokens = int(fields[1]) if len(fields) > 1 else 64
-                    if count < 1 or tokens < 1:
-                        raise ValueError
-                except (IndexError, ValueError):
-                    print("Usage: /bench <num_requests> [tokens_each]")
-                else:
-                    run_bench(engine, count, tokens)
-            elif command == "/system":
-                if not argument:
-                    print("Usage: /system <text>")
-                elif engine.tokenizer is None:
-                    print("A system message needs a tokenizer; this model folder has none.")
-                elif messages and messages[0]["role"] == "system":
-                    messages[0]["content"] = argument
-                    print("System message updated.")
-                else:
-                    messages.insert(0, {"role": "system", "content": argument})
-                    print("System message set.")
-            else:
-                print(f"Unknown command: {command}. Type /help for commands.")
-            continue
-
-        messages.append({"role": "user", "content": line})
-        prompt_ids = encode_turn(engine, messages, line)
-        if prompt_ids is None:
-            messages.pop()
-            continue
-        if engine.tokenizer is None:
-            messages[-1]["ids"] = [int(field) for field in line.split()]
-        reply = stream_reply(engine, prompt_ids, temperature, max_new_tokens, use_color)
-        if reply is None:
-            messages.pop()
-        elif engine.tokenizer is None:
-            messages.append({"role": "assistant", "content": reply, "ids": [int(t) for t in reply.split()]})
-        else:
-            messages.append({"role": "assistant", "content": reply})
+        alive = console.handle(line)
 
 
 if __name__ == "__main__":

@@ -106,6 +106,25 @@ class LLMEngine:
         self.launch_ahead = True   # launch the next decode step before this one's tokens are read back
         self._flight = None        # (batch, sampled requests, fetch handle) of a step launched that way
 
+    @classmethod
+    def from_random(cls, shape: str, seed: int = 0, dtype: str | None = None, device: str = "cuda", **options):
+        """An engine without a checkpoint: `shape` names one of the package's shape files or is the
+        path of a config.json (`shrike_b200.shapes.shape_config`); the weights are drawn on the
+        device from `seed`, as `weights.random_init` draws them."""
+        from ..config.registry import parse_config
+        from ..shapes import shape_config
+        from ..weights.random_init import random_tensors
+
+        config = parse_config(shape_config(shape))
+        dtype = dtype or config.dtype
+        tensors = random_tensors(config, seed, device, TORCH_DTYPES[dtype])
+        return cls(None, dtype=dtype, seed=seed, device=device, config=config, tensors=tensors, **options)
+
+    def reset_stats(self) -> None:
+        """Zeroes what `metrics()` counts (the `/reset` of shrike/cli.py:246-252)."""
+        self.stats = EngineStats()
+        self.scheduler.num_preemptions = 0
+
     # ---- requests -------------------------------------------------------------
     def _tokenize(self, prompt: str, chat: bool) -> list[int]:
         if self.tokenizer is None:

@@ -43,12 +43,15 @@ class SamplingParams:
     seed: int | None = None
 
     def __post_init__(self) -> None:
-        if self.max_new_tokens < 1:
-            raise ValueError(f"max_new_tokens must be >= 1, got {self.max_new_tokens}")
-        if self.temperature < 0.0:
-            raise ValueError(f"temperature must be >= 0, got {self.temperature}")
+        problems = []
+        if not self.max_new_tokens >= 1:
+            problems.append(f"max_new_tokens={self.max_new_tokens!r}: a request generates at least one token")
+        if not self.temperature >= 0.0:
+            problems.append(f"temperature={self.temperature!r}: zero (greedy) or a positive number")
         if not 0.0 < self.top_p <= 1.0:
-            raise ValueError(f"top_p must be in (0, 1], got {self.top_p}")
+            problems.append(f"top_p={self.top_p!r}: a probability mass above 0 and at most 1")
+        if problems:
+            raise ValueError("SamplingParams: " + "; ".join(problems))
 
 
 _request_ids = itertools.count()

@@ -69,7 +69,7 @@ def rope_tables(positions: torch.Tensor, head_dim: int, theta: float, dtype) -> 
     duplicated to the full head size; the angle is formed in float32 as the
     reference does, whatever the working precision."""
     inv_freq = 1.0 / (theta ** (torch.arange(0, head_dim, 2).float() / head_dim))
-    freqs = torch.outer(positions.float(), inv_freq)
+    freqs = torch.outer(positions.float(), inv_freq.to(positions.device))
     emb = torch.cat((freqs, freqs), dim=-1)
     if dtype == torch.float64:
         emb = emb.double()
@@ -92,22 +92,25 @@ def causal_attention(q, k, v, window: int | None = None) -> torch.Tensor:
 
     shrike/engine/model_runner.py:129-136 (grouped heads: q head i uses kv head
     i // G; scale D^-0.5; softmax in the working precision) with the causal mask
-    of shrike/models/qwen.py:243-248.  q [n, H, D], k/v [n, Hkv, D] -> [n, H, D].
+    of shrike/models/qwen.py:243-248.  q [m, H, D], k/v [n, Hkv, D] -> [m, H, D].
+    With m < n the queries are the last m positions of the sequence, as the
+    reference's mask is aligned to the end of the keys (model_runner.py:137-147).
+    Runs on the device of its inputs.
     """
-    n, heads, dim = q.shape
-    kv_heads = k.shape[1]
+    m, heads, dim = q.shape
+    n, kv_heads = k.shape[0], k.shape[1]
     group = heads // kv_heads
-    qg = q.view(n, kv_heads, group, dim)
+    qg = q.view(m, kv_heads, group, dim)
     scores = torch.einsum("nkgd,skd->kgns", qg, k) * dim**-0.5
-    i = torch.arange(n)[:, None]
-    j = torch.arange(n)[None, :]
+    i = torch.arange(n - m, n, device=q.device)[:, None]
+    j = torch.arange(n, device=q.device)[None, :]
     hidden = j > i
     if window is not None:
         hidden = hidden | (i - j >= window)
     scores = scores.masked_fill(hidden[None, None], float("-inf"))
     probs = scores.softmax(-1)
     out = torch.einsum("kgns,skd->nkgd", probs, v)
-    return out.reshape(n, heads, dim)
+    return out.reshape(m, heads, dim)
 
 
 def attention_inputs(x, w, prefix, sizes, cos, sin, rnd: Rounder):
@@ -156,9 +159,10 @@ def forward(
     sizes = config_sizes(raw_config)
     rnd = Rounder(rounding)
     w = {name: t.to(dtype) for name, t in weights.items()}
-    ids = torch.as_tensor(token_ids, dtype=torch.long)
+    device = next(iter(w.values())).device
+    ids = torch.as_tensor(token_ids, dtype=torch.long, device=device)
     n = ids.shape[0]
-    cos, sin = rope_tables(torch.arange(n), sizes["head_dim"], sizes["theta"], dtype)
+    cos, sin = rope_tables(torch.arange(n, device=device), sizes["head_dim"], sizes["theta"], dtype)
     cos, sin = cos.to(dtype), sin.to(dtype)
     windows = windows or {}
     if order is None:

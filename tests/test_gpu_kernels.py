@@ -360,9 +360,8 @@ def run_attention(ops, case, heads, kv_heads, dim, window, q_lens, ctx_lens):
                         case["seq_of"], heads, kv_heads, dim, dim ** -0.5, window, out,
                         max_q_len=max(q_lens), max_ctx_len=max(ctx_lens))
     want = []
-    for (q, k, v), q_len in zip(case["seqs"], q_lens):
-        full = pm.causal_attention(q.double(), k.double(), v.double(), window)
-        want.append(full[len(q) - q_len:])
+    for (q, k, v), q_len in zip(case["seqs"], q_lens):   # the oracle runs on the GPU in float64: plain torch all the same
+        want.append(pm.causal_attention(q[len(q) - q_len:].double().to(DEV), k.double().to(DEV), v.double().to(DEV), window))
     return out, torch.cat(want).reshape(out.shape)
 
 
@@ -395,6 +394,73 @@ def test_paged_attention_portions_mixed_with_single_tokens(dtype, window, heads,
                 case["table"][s, b] = -1
     got, want = run_attention(ops, case, heads, kv_heads, dim, window, q_lens, ctx_lens)
     close(got, want, 2e-5 if dtype == torch.float32 else 2e-2, 0, f"mixed attention window {window}")
+
+
+def drop_passed_pages(case, page, window, ctx_lens, q_lens):
+    """Pages that every query's window has passed are gone: the kernel must not touch them."""
+    for s, (ctx, q_len) in enumerate(zip(ctx_lens, q_lens)):
+        first_needed = max(0, ctx - q_len - window + 1)
+        for b in range(first_needed // page):
+            pid = int(case["table"][s, b])
+            case["keys"][pid] = float("nan")
+            case["values"][pid] = float("nan")
+            case["table"][s, b] = -1
+
+
+# the lengths a serving run brings: a whole 2,048-token prompt, portions of 512 over a long cached
+# prefix, a window, and portions beside single tokens; at the head sizes of the tensor-core kernel
+SERVED = {
+    "prompt_2048": ([2048], [2048], None),
+    "512_over_1536": ([2048], [512], None),
+    "512_over_3584": ([4096], [512], None),
+    "window_1000": ([2048, 1500], [512, 300], 1000),
+    "two_portions_beside_eight_single_tokens": (
+        [1024, 777, 1, 2048, 513, 64, 1000, 1100, 2048, 1000], [1, 1, 1, 1, 1, 1, 1, 1, 512, 300], None),
+    "ragged_edges": ([2047, 129, 1153], [2047, 65, 127], None),
+}
+
+
+@pytest.mark.parametrize("name", list(SERVED))
+@pytest.mark.parametrize("heads,kv_heads,dim,page", [(28, 4, 128, 16), (14, 2, 64, 16), (12, 2, 128, 32)])
+def test_portions_attention_at_served_lengths(name, heads, kv_heads, dim, page):
+    """The tensor-core kernel for portions over walks of up to 64 key tiles (its rescaling of the
+    running sum, its look-ahead in the block table and its first and last tile only matter on
+    long walks), against the plain formula in float64."""
+    ctx_lens, q_lens, window = SERVED[name]
+    ops = cuda_ops(torch.bfloat16)
+    assert ops._attention_lib(dim).shrike_attention_tc_available()
+    case = paged_case(torch.bfloat16, heads, kv_heads, dim, page, ctx_lens, q_lens, seed=11)
+    if window is not None:
+        drop_passed_pages(case, page, window, ctx_lens, q_lens)
+    got, want = run_attention(ops, case, heads, kv_heads, dim, window, q_lens, ctx_lens)
+    close(got, want, 2e-2, 0, f"{name} heads {heads}/{kv_heads} D {dim} page {page}")
+    ops.check_status()
+
+
+def test_portions_attention_finds_a_far_key_among_thousands():
+    """One key far back is made to stand out for one query row (its score is large), so the
+    output of that row must be that key's value: a tile walked in the wrong order, a page looked up
+    a tile too late or a rescale that is skipped would blur it."""
+    ops = cuda_ops(torch.bfloat16)
+    heads, kv_heads, dim, page = 28, 4, 128, 16
+    ctx_lens, q_lens = [4096], [512]
+    case = paged_case(torch.bfloat16, heads, kv_heads, dim, page, ctx_lens, q_lens, seed=13)
+    q, k, v = case["seqs"][0]
+    for far_key, row in ((3, 500), (1031, 17), (3583, 0), (3600, 40), (2050, 511)):
+        direction = torch.zeros(dim)
+        direction[far_key % dim] = 1.0
+        k[far_key] = (14.0 * direction).to(torch.bfloat16)                       # every kv head
+        q[4096 - 512 + row] = (14.0 * direction).to(torch.bfloat16)                # every head: score 196 * D^-0.5 = 17.3
+        pid, at = int(case["table"][0, far_key // page]), far_key % page
+        case["keys"][pid, at] = k[far_key].to(DEV)
+    case["q"] = q[4096 - 512:].reshape(512, heads * dim).contiguous().to(DEV)
+    got, want = run_attention(ops, case, heads, kv_heads, dim, None, q_lens, ctx_lens)
+    close(got, want, 2e-2, 0, "far keys")
+    group = heads // kv_heads
+    for far_key, row in ((3, 500), (1031, 17), (3583, 0), (3600, 40), (2050, 511)):
+        for head in (0, 13, 27):
+            # the far key holds all but 3e-4 of the mass (its score leads by 17 over N(0, 1.2) scores)
+            close(got[row].view(heads, dim)[head], v[far_key, head // group].double(), 0.05, 0, f"row {row} key {far_key}")
 
 
 def test_single_token_attention_twice_in_a_row_leaves_its_counters_clean():
