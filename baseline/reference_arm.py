@@ -108,6 +108,12 @@ def run(args, raw_model: dict, context: int) -> dict:
             torch.cuda.synchronize()
             times.append((time.perf_counter() - began) * 1000.0)
         prefill_ms = statistics.median(times)
+        # the same `config` keys and values as the other arm prints for the same options
+        sys.path.insert(0, str(ROOT))
+        import bench
+
+        weight_gb = bench.model_numbers(raw, raw["num_hidden_layers"])["weight_bytes_per_step"] / 1e9
+        peaks_source = bench.load_peaks()["source"]
         return {
             "metric": f"decode_tokens_per_second_qwen2.5-{getattr(args, 'shape', '7b')}_b{batch}_ctx{context}",
             "impl": "reference",
@@ -115,9 +121,12 @@ def run(args, raw_model: dict, context: int) -> dict:
             "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic: seeded random weights and uniform random token ids",
             "config": {"model": f"Qwen2.5-{getattr(args, 'shape', '7b').upper()} shape", "layers": raw["num_hidden_layers"],
-                       "layers_full": raw_model["num_hidden_layers"], "global_batch": batch, "seq_len": context,
-                       "block_size": 16, "parallelism": "single_gpu", "engine_defaults": "stock LLMEngine(model_dir)",
-                       "l2": "inputs larger than L2"},
+                       "layers_full": raw_model["num_hidden_layers"], "hidden": raw["hidden_size"],
+                       "heads": raw["num_attention_heads"], "kv_heads": raw["num_key_value_heads"],
+                       "head_dim": raw["head_dim"], "intermediate": raw["intermediate_size"], "vocab": raw["vocab_size"],
+                       "global_batch": batch, "seq_len": context, "block_size": 16, "prefill_tokens": 2048,
+                       "parallelism": "single_gpu",
+                       "l2": f"inputs larger than L2 (weights read per step: {weight_gb:.1f} GB)", "peaks": peaks_source},
             "e2e": {"value": round(value, 1), "unit": "tok/s", "h2d_bytes_per_step": None, "d2h_bytes_per_step": None},
             "prefill": {"value": round(2048 * 1000.0 / prefill_ms, 1), "tokens": 2048, "ms": round(prefill_ms, 3),
                         "note": "through step() with the stock 512-token budget (four portions)"},

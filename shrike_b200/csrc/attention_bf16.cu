@@ -871,8 +871,9 @@ SHRIKE_API long long shrike_attention_bf16_scratch_floats(int num_seqs, int num_
 // splits = min(tiles, this / (seqs * kv heads * row tiles)).
 SHRIKE_API int shrike_attention_bf16_resident_ctas() {
   const size_t smem = bf16attn::SINGLE_SMEM + 1024;
-  const int per_sm = static_cast<int>((227 * 1024) / smem);
-  return 148 * (per_sm < 1 ? 1 : (per_sm > 4 ? 4 : per_sm));
+  const ShrikeDevice& device = shrike_device();
+  const int per_sm = static_cast<int>(static_cast<size_t>(device.max_smem) / smem);
+  return device.sm_count * (per_sm < 1 ? 1 : (per_sm > 4 ? 4 : per_sm));
 }
 
 // has_single / has_portions: whether the batch holds rows with q_len == 1 / q_len > 1

@@ -17,6 +17,28 @@ static inline int shrike_launch_status() {
   return err == cudaSuccess ? SHRIKE_OK : static_cast<int>(err);
 }
 
+// What launchers need to know of the current device (grids and shared-memory budgets follow
+// from it), asked once per device; the figures of a B200 stand in if the query fails.
+struct ShrikeDevice {
+  int sm_count = 0;
+  int max_smem = 0;   // most dynamic shared memory a CTA may ask for
+};
+static inline const ShrikeDevice& shrike_device() {
+  static ShrikeDevice facts[64];
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) device = 0;
+  ShrikeDevice& f = facts[device];
+  if (f.sm_count == 0) {
+    int sms = 0, smem = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) sms = 148;
+    if (cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, device) != cudaSuccess || smem <= 0)
+      smem = 227 * 1024;
+    f.max_smem = smem;
+    f.sm_count = sms;
+  }
+  return f;
+}
+
 template <typename T> __device__ __forceinline__ float to_float(T v);
 template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) {

@@ -291,7 +291,7 @@ static void launch_silu_mul(const void* gate_up, void* out, int n, int inter, in
   const size_t total = static_cast<size_t>(n) * inter;
   const size_t work = vec ? total / WIDE : total;
   const int threads = 256;
-  const int blocks = static_cast<int>(min(static_cast<size_t>(148 * 8), (work + 2 * threads - 1) / (2 * threads)));
+  const int blocks = static_cast<int>(min(static_cast<size_t>(shrike_device().sm_count * 8), (work + 2 * threads - 1) / (2 * threads)));
   if (vec)
     launch_dependent(silu_mul_kernel<T, WIDE>, blocks, threads, 0, stream, static_cast<const T*>(gate_up),
                      static_cast<T*>(out), inter, total, block);

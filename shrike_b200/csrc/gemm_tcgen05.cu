@@ -146,6 +146,9 @@ gemm_swap_ab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     if (lane == 0) {
       const unsigned idesc = instruction_descriptor(BM, args.tn, false);
       bool ok = true;
+      // the token tiles are loaded only after the kernel before this one has finished: wait for it
+      // here too, so that the bounded waits below measure this kernel's own loads alone
+      wait_for_previous();
       for (int i = 0; i < num_kb && ok; ++i) {
         const int s = i % args.stages;
         const unsigned phase = (i / args.stages) & 1;
@@ -236,20 +239,6 @@ gemm_swap_ab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
 }  // namespace tc
 
-// Shared memory one CTA may take for its stages.  Half an SM's worth lets two CTAs live on
-// an SM, so that one streams weights while the other starts up or stores its result, and
-// still gives each a pipeline deep enough to cover the memory latency alone (three CTAs of
-// three stages each measured 7% slower over a whole decode step).  A product of many waves
-// (an output head) does better with four shallower CTAs per SM.  0: choose by the shape.
-static int g_smem_budget = 0;
-static int g_target_ctas = 0;   // 0: the device's SM count
-static int g_dependent_launch = 1;
-SHRIKE_API void shrike_gemm_tc_dependent_launch(int enabled) { g_dependent_launch = enabled ? 1 : 0; }
-SHRIKE_API void shrike_gemm_tc_tune(int smem_budget_bytes, int target_ctas) {
-  if (smem_budget_bytes == 0 || (smem_budget_bytes >= 40 * 1024 && smem_budget_bytes <= 200 * 1024)) g_smem_budget = smem_budget_bytes;
-  if (target_ctas >= 1) g_target_ctas = target_ctas;
-}
-
 // How K is split for a product with `tokens` rows.  Two CTAs live on an SM, and as long as
 // all CTAs of the product are resident together, more of them stream faster: measured at the
 // projection shapes of three model sizes, the time falls with every further split until the
@@ -261,14 +250,7 @@ SHRIKE_API int shrike_gemm_tc_splits(int tokens, int n, int k) {
   (void)tokens;
   const int tiles = (n + tc::BM - 1) / tc::BM;
   const int kblocks = (k + tc::BK - 1) / tc::BK;
-  static int sm_count = 0;
-  if (sm_count == 0) {
-    int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess ||
-        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sm_count <= 0)
-      sm_count = 148;
-  }
-  const int resident = 2 * (g_target_ctas ? g_target_ctas : sm_count);
+  const int resident = 2 * shrike_device().sm_count;
   const int most = tiles * 8 < resident / 2 ? 16 : 8;
   int best = 1;
   for (int splits = 2; splits <= most && tiles * splits <= resident; ++splits) {
@@ -296,7 +278,13 @@ static int launch_gemm_tc(const void* x, const void* w, const float* bias, void*
   if ((kblocks + per_split - 1) / per_split != splits) return SHRIKE_BAD_ARGUMENT;
   const size_t stage_bytes = A_BYTES + static_cast<size_t>(tn) * BK * 2;
   const long long ctas = static_cast<long long>((n + BM - 1) / BM) * splits * token_tiles;
-  const int budget = g_smem_budget ? g_smem_budget : (tn <= 16 && ctas >= 6 * 148 ? 48 * 1024 : 100 * 1024);
+  // Shared memory one CTA may take for its stages.  Half an SM's worth lets two CTAs live on
+  // an SM, so that one streams weights while the other starts up or stores its result, and
+  // still gives each a pipeline deep enough to cover the memory latency alone (three CTAs of
+  // three stages each measured 7% slower over a whole decode step).  A product of many waves
+  // (an output head) does better with four shallower CTAs per SM.
+  const ShrikeDevice& device = shrike_device();
+  const int budget = tn <= 16 && ctas >= 6LL * device.sm_count ? 48 * 1024 : 100 * 1024;
   int stages = static_cast<int>(budget / stage_bytes);
   if (stages < 2) stages = 2;
   stages = stages > MAX_STAGES ? MAX_STAGES : stages;
@@ -304,7 +292,7 @@ static int launch_gemm_tc(const void* x, const void* w, const float* bias, void*
   const size_t smem = stage_bytes * stages + sizeof(Shared) + 1024;
   static bool configured = false;
   if (!configured) {
-    const cudaError_t err = cudaFuncSetAttribute(gemm_swap_ab_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    const cudaError_t err = cudaFuncSetAttribute(gemm_swap_ab_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, device.max_smem);
     if (err != cudaSuccess) return static_cast<int>(err);
     configured = true;
   }
@@ -332,7 +320,7 @@ static int launch_gemm_tc(const void* x, const void* w, const float* bias, void*
   config.stream = stream;
   cudaLaunchAttribute attribute;
   attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attribute.val.programmaticStreamSerializationAllowed = g_dependent_launch;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
   config.attrs = &attribute;
   config.numAttrs = 1;
   const cudaError_t err = cudaLaunchKernelEx(&config, gemm_swap_ab_kernel, map_w, map_x, args);

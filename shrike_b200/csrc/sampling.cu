@@ -64,6 +64,15 @@ __device__ Best block_best(Best mine, Best* scratch /* 33 entries */) {
   return scratch[32];
 }
 
+// A row whose logits are all NaN has no winner (no comparison with NaN holds): it yields token
+// 0, a valid id, and leaves ERR_NO_FINITE_LOGIT in the status word when the caller gave one.
+constexpr int ERR_NO_FINITE_LOGIT = 31;
+__device__ __forceinline__ int valid_token(int index, int vocab, int* status) {
+  if (index >= 0 && index < vocab) return index;
+  if (status != nullptr && *status == 0) *status = ERR_NO_FINITE_LOGIT;
+  return 0;
+}
+
 // Stage 1: the vocabulary of every row is cut into `chunks` slices; each block finds the
 // best (score, index) of its slice, the score being the logit (greedy) or
 // logit / T + Gumbel noise (sampled without top_p).  Rows with top_p < 1 are left to
@@ -104,7 +113,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
               const float* __restrict__ top_p, const long long* __restrict__ seeds, int* __restrict__ out,
               const float* __restrict__ partial_value, const int* __restrict__ partial_index, int vocab,
-              int chunks) {
+              int chunks, int* __restrict__ status) {
   __shared__ float scratch[33];
   __shared__ Best best_scratch[33];
   let_dependents_start();
@@ -120,7 +129,7 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
       mine = better(mine, Best{partial_value[static_cast<size_t>(row) * chunks + i],
                                partial_index[static_cast<size_t>(row) * chunks + i]});
     const Best top = block_best(mine, best_scratch);
-    if (threadIdx.x == 0) out[row] = top.index;
+    if (threadIdx.x == 0) out[row] = valid_token(top.index, vocab, status);
     return;
   }
 
@@ -156,7 +165,7 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
     if (p > threshold) mine = better(mine, Best{x[i] * inv_temp + gumbel(seed, i), i});
   }
   const Best top = block_best(mine, best_scratch);
-  if (threadIdx.x == 0) out[row] = top.index;
+  if (threadIdx.x == 0) out[row] = valid_token(top.index, vocab, status);
 }
 
 // How many slices stage 1 cuts a row into; scratch must hold rows * slices floats and ints.
@@ -167,14 +176,15 @@ SHRIKE_API int shrike_sample_slices(int vocab) {
 
 SHRIKE_API int shrike_sample(const float* logits, const float* temperature, const float* top_p,
                              const long long* seeds, int* out, float* scratch_value, int* scratch_index,
-                             int rows, int vocab, cudaStream_t stream) {
+                             int rows, int vocab, int* status, cudaStream_t stream) {
   if (rows <= 0) return SHRIKE_OK;
   if (vocab <= 0 || rows > 65535 || scratch_value == nullptr || scratch_index == nullptr) return SHRIKE_BAD_ARGUMENT;
   const int chunks = shrike_sample_slices(vocab);
   launch_dependent(sample_slices_kernel, dim3(chunks, rows), SLICE_THREADS, 0, stream, logits, temperature, top_p, seeds,
                    scratch_value, scratch_index, vocab, chunks);
   launch_dependent(sample_kernel, rows, SAMPLE_THREADS, 0, stream, logits, temperature, top_p, seeds, out,
-                   static_cast<const float*>(scratch_value), static_cast<const int*>(scratch_index), vocab, chunks);
+                   static_cast<const float*>(scratch_value), static_cast<const int*>(scratch_index), vocab, chunks,
+                   status);
   return shrike_launch_status();
 }
 
@@ -198,7 +208,7 @@ int no_alloc_scratch(void** address) {
   int device = -1;
   cudaError_t err = cudaGetDevice(&device);
   if (err != cudaSuccess) return static_cast<int>(err);
-  if (device < 0 || device >= NO_ALLOC_MAX_DEVICES) return SHRIKE_BAD_ARGUMENT;
+  if (device < 0 || device >= NO_ALLOC_MAX_DEVICES) return SHRIKE_SAMPLE_NO_ALLOC_BAD_DEVICE;
   std::lock_guard<std::mutex> guard(no_alloc_mutex);
   if (no_alloc_address[device] == nullptr) {
     void* found = nullptr;
@@ -226,7 +236,7 @@ SHRIKE_API int shrike_sample_no_alloc(const float* logits, const float* temperat
   sample_slices_kernel<<<dim3(chunks, rows), SLICE_THREADS, 0, stream>>>(logits, temperature, top_p, seeds,
                                                                          values, indices, vocab, chunks);
   sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, temperature, top_p, seeds, out, values, indices,
-                                                     vocab, chunks);
+                                                     vocab, chunks, nullptr);
   return shrike_launch_status();
 }
 
@@ -236,5 +246,8 @@ SHRIKE_API const char* shrike_sample_no_alloc_message(int code) {
     return "shrike_sample_no_alloc: more than 256 rows in one call; the fixed scratch array holds 256 "
            "(split the batch, or use shrike_sample with scratch of your own)";
   if (code == SHRIKE_BAD_ARGUMENT) return "shrike_sample_no_alloc: bad argument (vocab must be positive)";
+  if (code == SHRIKE_SAMPLE_NO_ALLOC_BAD_DEVICE)
+    return "shrike_sample_no_alloc: the current device's index is 64 or more; the library keeps the scratch "
+           "address of devices 0 to 63 only";
   return cudaGetErrorString(static_cast<cudaError_t>(code));
 }

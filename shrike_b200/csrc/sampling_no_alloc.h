@@ -25,6 +25,8 @@
 //   * The first call on each device looks up the array's device address
 //     (cudaGetSymbolAddress, with that device current).  Make that first call outside any
 //     stream capture.
+//   * Devices with an index of 64 or more are refused (SHRIKE_SAMPLE_NO_ALLOC_BAD_DEVICE).
+//   * A row whose logits are all NaN has no largest element; it yields token 0.
 //   * No cudaMalloc, cudaFree or other allocating routine is called, on any call.
 // The caller passes inputs and outputs exactly as for `shrike_sample`:
 //   logits [rows, vocab] float32, temperature [rows] float32, top_p [rows] float32,
@@ -37,6 +39,7 @@
 #define SHRIKE_SAMPLE_NO_ALLOC_MAX_SLICES 128
 #define SHRIKE_SAMPLE_NO_ALLOC_BYTES (SHRIKE_SAMPLE_NO_ALLOC_MAX_ROWS * SHRIKE_SAMPLE_NO_ALLOC_MAX_SLICES * 8)
 #define SHRIKE_SAMPLE_NO_ALLOC_TOO_MANY_ROWS (-2)
+#define SHRIKE_SAMPLE_NO_ALLOC_BAD_DEVICE (-3)
 
 extern "C" int shrike_sample_no_alloc(const float* logits, const float* temperature, const float* top_p,
                                       const long long* seeds, int* out, int rows, int vocab,

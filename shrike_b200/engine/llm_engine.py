@@ -248,7 +248,13 @@ class LLMEngine:
             flight = self._launch(batch, entries, sampled)
         batch, sampled, fetched = flight
         self._flight = self._launch_ahead(batch, sampled)
-        tokens = self.runner.wait(fetched) if sampled else []
+        try:
+            tokens = self.runner.wait(fetched) if sampled else []
+        except Exception:
+            # a kernel of this step gave up: nothing of it is appended, and the step launched ahead
+            # (computed from the same state) is dropped with it
+            self._flight = None
+            raise
 
         outputs: list[StepOutput] = []
         for request, token in zip(sampled, tokens):
@@ -267,12 +273,11 @@ class LLMEngine:
                 del self.requests[request.req_id]
                 self._request_seed.pop(request.req_id, None)
         self.stats.steps += 1
-        if self.stats.steps % 256 == 0:
-            self._check_kernels()
         return outputs
 
     def _check_kernels(self) -> None:
-        """Raises if a kernel gave up a bounded wait since the last check (one word read from the device)."""
+        """Raises if a kernel left a code in its status word.  Steps that sample see the word with
+        their tokens (`ModelRunner.wait`); this reads it once more at the end of `generate`."""
         check = getattr(self.ops, "check_status", None)
         if check is not None:
             check()

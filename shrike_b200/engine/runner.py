@@ -83,7 +83,12 @@ class ModelRunner:
         self._graphs: dict = {}
         self._seen: dict = {}
         self.portion_sightings = 5   # a shape with portions is captured when it comes for the sixth time
-        self._drawn = torch.zeros(4096, dtype=torch.int32, device=self.device)   # the sampled tokens of a step
+        # the kernels' status word and the sampled tokens of a step lie side by side, so that one
+        # copy brings both to the host: a step whose kernels gave up is seen before its tokens are used
+        self._status_block = torch.zeros(4 + 4096, dtype=torch.int32, device=self.device)
+        self._drawn = self._status_block[4:]
+        if hasattr(ops, "adopt_status"):
+            ops.adopt_status(self._status_block[:4])
         self._drawn_generation = 0
         self._fetch_host = [None, None]
         self._fetch_turn = 0
@@ -144,21 +149,29 @@ class ModelRunner:
         if self.device.type != "cuda":
             return tokens.tolist(), count, None
         self._fetch_turn ^= 1
-        if self._fetch_host[self._fetch_turn] is None or self._fetch_host[self._fetch_turn].numel() < count:
-            self._fetch_host[self._fetch_turn] = torch.empty(max(256, 2 * count), dtype=torch.int32, pin_memory=True)
+        if self._fetch_host[self._fetch_turn] is None or self._fetch_host[self._fetch_turn].numel() < 4 + count:
+            self._fetch_host[self._fetch_turn] = torch.zeros(max(256, 4 + 2 * count), dtype=torch.int32, pin_memory=True)
         host = self._fetch_host[self._fetch_turn]
-        host[:count].copy_(tokens, non_blocking=True)
+        if count and tokens.data_ptr() == self._drawn.data_ptr() and self._drawn.data_ptr() == self._status_block[4:].data_ptr():
+            host[: 4 + count].copy_(self._status_block[: 4 + count], non_blocking=True)   # status word and tokens at once
+        else:
+            host[:4].copy_(self._status_block[:4], non_blocking=True)
+            host[4: 4 + count].copy_(tokens, non_blocking=True)
         event = torch.cuda.Event()
         event.record()
         return host, count, event
 
-    @staticmethod
-    def wait(handle) -> list[int]:
+    def wait(self, handle) -> list[int]:
+        """The tokens of a fetched step.  Raises before handing them out when a kernel of that step
+        (or of one before it) left a code in the status word."""
         host, count, event = handle
         if event is None:
             return host
         event.synchronize()
-        return host[:count].tolist()
+        code = int(host[0])
+        if code:
+            self.ops.raise_status(code)
+        return host[4: 4 + count].tolist()
 
     @torch.inference_mode()
     def launch(self, prepared: "Prepared"):

@@ -71,7 +71,9 @@ class CudaOps:
         self.tensor_core_attention = True   # tcgen05 kernel for portions where the head and page sizes allow
         self.tensor_core_gemm_max_tokens = 64   # above this the library product is used
         self._partials = {}      # data_ptr of an output buffer -> its stack of K-split partial results
-        self.status = None
+        # one host-visible word (of four): the first kernel whose bounded wait ran out, or that met
+        # a row without a finite logit, leaves its code here; see `describe_status`
+        self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
         if dtype == torch.bfloat16:
             self.gemm_tc = build.tensor_core_gemm_library()
             self.gemm_tc.shrike_gemm_tc.argtypes = [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P]
@@ -80,7 +82,6 @@ class CudaOps:
             self.gemm_tc.shrike_gemm_tc_gated.restype = _I
             self.gemm_tc.shrike_gemm_tc_splits.argtypes = [_I, _I, _I]
             self.gemm_tc.shrike_gemm_tc_splits.restype = _I
-            self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._scratch = None     # partial results of split single-token attention
         self._sample_scratch = None  # per-slice winners of the sampling kernel
         self._arrivals = None    # per kv head: splits of single-token attention that have finished
@@ -102,7 +103,7 @@ class CudaOps:
         lib.shrike_rope_kv_write.argtypes = [_P] * 10 + [_I] * 5 + [_LL, _I, _LL, _P]
         lib.shrike_kv_write.argtypes = [_P] * 5 + [_I, _I, _I, _LL, _P]
         lib.shrike_gemm_fp32.argtypes = [_P, _P, _P, _P, _I, _I, _I, _P]
-        lib.shrike_sample.argtypes = [_P, _P, _P, _P, _P, _P, _P, _I, _I, _P]
+        lib.shrike_sample.argtypes = [_P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _P]
         lib.shrike_sample_slices.argtypes = [_I]
         lib.shrike_sample_slices.restype = _I
         for name in ("shrike_embed", "shrike_add_rmsnorm", "shrike_silu_mul", "shrike_rope_kv_write",
@@ -245,15 +246,48 @@ class CudaOps:
             self.generation += 1
         return held[:need].view(splits, n, o)
 
+    def adopt_status(self, word: torch.Tensor) -> None:
+        """Makes `word` (int32 [4] on the device, zeroed) the status word the kernels write, so that
+        the step function can bring it to the host in the same copy as a step's drawn tokens.  To be
+        called before the first launch: launch sequences that were captured keep the old address."""
+        if word.dtype != torch.int32 or word.numel() < 4 or word.device != self.status.device:
+            raise KernelError("the status word must be four int32 on the kernels' device")
+        word.zero_()
+        self.status = word
+        self.generation += 1
+
+    @staticmethod
+    def describe_status(code: int) -> str:
+        """What a nonzero status word means: which kernel gave up, and where."""
+        roles = {
+            1: "gemm_tcgen05: the TMA producer's wait for a free stage ran out",
+            2: "gemm_tcgen05: the MMA issuer's wait for a loaded stage ran out",
+            3: "gemm_tcgen05: the epilogue's wait for the accumulator ran out",
+            4: "gemm_tcgen05: copies still in flight after an aborted wait",
+            11: "attention_tcgen05 (portions): the loader's wait for a free key/value stage ran out",
+            12: "attention_tcgen05 (portions): the MMA issuer's wait ran out",
+            13: "attention_tcgen05 (portions): a softmax thread's wait ran out",
+            14: "attention_tcgen05 (portions): copies still in flight after an aborted wait",
+            15: "attention_tcgen05 (portions): shared memory was not aligned as the tiles need",
+            21: "attention_bf16 (single tokens, by pages): the wait for a page's tile ran out",
+            22: "attention_bf16 (single tokens, by pages): shared memory was not aligned as the tiles need",
+            31: "sampling: a row of logits had no finite element (NaN logits); token 0 was returned for it",
+        }
+        return roles.get(code, f"unknown status code {code}")
+
+    def raise_status(self, code: int):
+        """Clears the status word (and the counters an aborted kernel may have left half-way) and
+        raises: the results of the step that set `code` are not valid."""
+        self.status.zero_()
+        if self._arrivals is not None:
+            self._arrivals.zero_()
+        raise KernelError(f"{self.describe_status(code)}; the results of that step are not valid")
+
     def check_status(self):
-        """Raises when a tensor-core product gave up a bounded wait (reads one word from the device)."""
-        if self.status is None:
-            return
+        """Raises when a kernel left a code in the status word (reads one word from the device)."""
         code = int(self.status[0].item())
         if code:
-            self.status.zero_()
-            where = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue", 4: "draining copies"}.get(code, str(code))
-            raise KernelError(f"gemm_tcgen05: a wait ran out in {where}; the product of that step is not valid")
+            self.raise_status(code)
 
     def rope_kv_write(self, qkv, bias, positions, inv_freq, q_out, keys, values, slots,
                       num_heads, num_kv_heads, head_dim, k_out=None, v_out=None):
@@ -324,8 +358,6 @@ class CudaOps:
                 self._arrivals = torch.zeros(max(groups, 4096), dtype=torch.int32, device=self.device)
                 self.generation += 1
             scratch, arrivals = self._scratch, self._arrivals
-        if self.status is None:
-            self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
         tensor_core_portions = (has_portions and self.tensor_core_attention and lib.shrike_attention_tc_available()
                                 and page_size in (8, 16, 32, 64))
         self.launches += (1 if has_single else 0) + (1 if has_portions else 0)
@@ -413,4 +445,5 @@ class CudaOps:
         values, indices = self._sample_scratch
         self.launches += 2
         _check(self.core.shrike_sample(_ptr(logits), _ptr(temperature), _ptr(top_p), _ptr(seeds), _ptr(out),
-                                       _ptr(values), _ptr(indices), rows, vocab, self._stream()), "sample")
+                                       _ptr(values), _ptr(indices), rows, vocab, _ptr(self.status), self._stream()),
+               "sample")

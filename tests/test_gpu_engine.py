@@ -211,3 +211,31 @@ def test_decode_batches_padded_to_a_few_sizes_give_the_same_logits_and_tokens(tm
         assert torch.equal(padded, exact) and padded_tokens == exact_tokens
     else:
         assert (padded - exact).abs().max() < 2e-2
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_kernel_that_gave_up_is_seen_before_its_tokens_are_used(tmp_path, dtype):
+    """The status word comes to the host in the same copy as a step's tokens.  A code in it (set
+    by hand here; on the device a bounded wait that ran out sets it) makes `step` raise before
+    anything is appended or handed out, drops the step launched ahead, and clears the word; the
+    caller aborts what was running, and the engine serves on."""
+    from shrike_b200.ops.cuda_ops import KernelError
+
+    folder = make_model_folder(tmp_path, "A")
+    engine = LLMEngine(str(folder), num_blocks=32, dtype=dtype)
+    params = SamplingParams(max_new_tokens=20, ignore_eos=True)
+    first = engine.generate([random_tokens(256, 9, 1)], params)[0]
+    ids = [engine.add_request(random_tokens(256, n, 2 + n), params) for n in (9, 5)]
+    for _ in range(4):
+        engine.step()
+    lengths = {i: engine.requests[i].num_tokens for i in ids}
+    engine.ops.status[0] = 2
+    with pytest.raises(KernelError, match="MMA issuer"):
+        for _ in range(3):   # the word travels with the next step's tokens (or the one launched ahead)
+            engine.step()
+    assert engine._flight is None and int(engine.ops.status[0]) == 0
+    assert all(engine.requests[i].num_tokens <= lengths[i] + 2 for i in ids)
+    for i in ids:
+        engine.abort(i)
+    assert engine.block_manager.whole() and not engine.has_work
+    assert engine.generate([random_tokens(256, 9, 1)], params)[0] == first

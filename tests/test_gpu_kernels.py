@@ -589,6 +589,29 @@ def test_sampling_follows_the_distribution_and_top_p():
     assert set(out[:8].tolist()) == {int(probs.argmax())}
 
 
+def test_sampling_a_row_without_a_finite_logit_gives_a_valid_token_and_says_so():
+    """NaN compares with nothing, so such a row has no winner: the kernels return token 0 for it
+    (a valid id) and leave their code in the status word; rows beside it are not disturbed."""
+    from shrike_b200.ops.cuda_ops import KernelError
+
+    ops = cuda_ops(torch.float32)
+    vocab = 5000
+    logits = rnd(4, vocab, seed=3)
+    logits[1] = float("nan")
+    logits[3, ::2] = float("nan")   # half NaN: the finite half decides
+    temperature = torch.tensor([0.0, 0.0, 0.7, 0.0], device=DEV)
+    top_p = torch.tensor([1.0, 1.0, 1.0, 1.0], device=DEV)
+    seeds = torch.arange(4, dtype=torch.int64, device=DEV)
+    out = torch.full((4,), -1, dtype=torch.int32, device=DEV)
+    ops.sample(logits, temperature, top_p, seeds, out)
+    got = out.tolist()
+    assert got[1] == 0 and got[0] == int(logits[0].argmax()) and 0 <= got[2] < vocab
+    assert got[3] == int(torch.nan_to_num(logits[3], nan=-1e30).argmax()) and got[3] % 2 == 1
+    with pytest.raises(KernelError, match="no finite element"):
+        ops.check_status()
+    ops.check_status()   # cleared by the raise
+
+
 def test_sampling_mixes_greedy_and_sampled_rows():
     ops = cuda_ops(torch.float32)
     logits = rnd(4, 1000, seed=5)

@@ -44,17 +44,25 @@ def test_no_alloc_sampling_matches_the_allocating_entry_point():
     lib = _library()
     ops = CudaOps(torch.float32, "cuda")
     stream = torch.cuda.current_stream().cuda_stream
+    # a first call: it looks up the array's address (and whatever the driver sets up on the first use
+    # of a kernel happens here), so that the calls below can be held to "the device's free memory
+    # does not move", which a cudaMalloc behind torch's back would break
+    small = _inputs(2, 64, 0)
+    first = torch.empty(2, dtype=torch.int32, device="cuda")
+    assert lib.shrike_sample_no_alloc(*(t.data_ptr() for t in small), first.data_ptr(), 2, 64, stream) == 0
+    torch.cuda.synchronize()
     for rows, vocab, seed in ((7, 152064, 1), (256, 331, 2)):   # two calls in a row share the array
         logits, temperature, top_p, seeds = _inputs(rows, vocab, seed)
         want = torch.empty(rows, dtype=torch.int32, device="cuda")
         ops.sample(logits, temperature, top_p, seeds, want)
         got = torch.full((rows,), -7, dtype=torch.int32, device="cuda")
-        before = torch.cuda.memory_allocated()
+        torch.cuda.synchronize()
+        before = (torch.cuda.memory_allocated(), torch.cuda.mem_get_info()[0])
         code = lib.shrike_sample_no_alloc(logits.data_ptr(), temperature.data_ptr(), top_p.data_ptr(),
                                           seeds.data_ptr(), got.data_ptr(), rows, vocab, stream)
         assert code == 0, lib.shrike_sample_no_alloc_message(code).decode()
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
+        assert (torch.cuda.memory_allocated(), torch.cuda.mem_get_info()[0]) == before, "device memory was allocated"
         assert torch.equal(got, want), f"rows={rows} vocab={vocab}"
         assert int(got.min()) >= 0 and int(got.max()) < vocab
 
