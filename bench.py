@@ -502,7 +502,7 @@ def run_mixed(args) -> dict:
         "value": round(generated / seconds, 1), "unit": "generated tok/s",
         "total_tokens_per_second": round((generated + sum(len(p) for p in prompts)) / seconds, 1),
         "steps": engine.stats.steps - steps_before, "preemptions": engine.scheduler.num_preemptions,
-        "kv_blocks": min(engine.block_manager.num_pages), "budget": 512, "dtype": "bf16",
+        "kv_blocks": engine.block_manager.total_pages, "budget": 512, "dtype": "bf16",
         "data": "synthetic: seeded random weights and uniform random token ids",
     }
 

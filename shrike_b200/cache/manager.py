@@ -11,9 +11,12 @@ reference counts (:21-27), demand = ceil((computed + new) / page_size) - held
 (:60-70), `can_append` = demand <= free (:72-73), allocation of exactly the demand
 (:75-77), everything returned on free (:128-130).  Prefix caching is left out.
 
-Beyond it: groups; giving pages back while a request lives, once a window has
-passed them (their table entry becomes -1); and slots for per-request state of
-fixed size, taken with the first pages and returned with the last.
+Beyond it: groups, each with a pool sized for its own need (a group whose layers see a
+window of keys holds far fewer pages per request than one that keeps them all); giving pages
+back while a request lives, once a window has passed them (their table entry becomes -1); and
+slots for per-request state of fixed size, taken with the first pages and returned with the
+last.  Slots handed out since the last step are remembered (`take_opened`), so that the step
+function can zero their state before a new request's first token runs.
 """
 
 from __future__ import annotations
@@ -117,6 +120,7 @@ class CacheManager:
         self.pools = [IdPool(count) for count in counts]
         self.slots = IdPool(max_slots)
         self.has_windows = any(group.window is not None for group in self.groups)
+        self._opened: list[int] = []   # slots handed out since `take_opened` was last called
 
     # ---- figures -----------------------------------------------------------
     @property
@@ -127,6 +131,26 @@ class CacheManager:
     def num_free(self) -> list[int]:
         return [pool.num_free for pool in self.pools]
 
+    @property
+    def main_pool(self) -> IdPool | None:
+        """The largest pool: the one a user's "number of KV blocks" speaks of (None without pages)."""
+        return max(self.pools, key=lambda pool: pool.count) if self.pools else None
+
+    @property
+    def total_pages(self) -> int:
+        return self.main_pool.count if self.pools else 0
+
+    @property
+    def free_pages(self) -> int:
+        return self.main_pool.num_free if self.pools else 0
+
+    def portion_limit(self) -> int | None:
+        """The longest portion one request can be fed in a step, whatever else is free: a group
+        with a window must hold the window and the portion at once (None: no such bound)."""
+        limits = [max(1, (pool.count - 2) * self.page_size - group.window + 2)
+                  for pool, group in zip(self.pools, self.groups) if group.window is not None]
+        return min(limits) if limits else None
+
     def whole(self) -> bool:
         """True when nothing is held: every page and every slot is free."""
         return all(p.num_free == p.count for p in self.pools) and self.slots.num_free == self.slots.count
@@ -134,14 +158,24 @@ class CacheManager:
     def blocks_for(self, tokens: int) -> int:
         return -(-tokens // self.page_size)
 
-    def worst_case_pages(self, tokens: int) -> list[int]:
-        """Pages per group a request of `tokens` may hold at once, if it ran in one portion."""
-        return [self.blocks_for(tokens) for _ in self.groups]
+    def worst_case_pages(self, tokens: int, portion: int | None = None) -> list[int]:
+        """Pages per group a request of `tokens` may hold at once when it is fed at most `portion`
+        tokens a step (None: all at once).  A group with a window holds the pages that the
+        window and the portion in flight touch, whatever the request's length."""
+        return [pages_in_flight(self.blocks_for(tokens), group.window, min(portion or tokens, tokens), self.page_size)
+                for group in self.groups]
 
     # ---- a request's life ----------------------------------------------------
     def open(self) -> RequestCache:
         """Takes a state slot; pages come with `append`."""
-        return RequestCache(tables=[BlockTable() for _ in self.groups], slot=self.slots.take())
+        slot = self.slots.take()
+        self._opened.append(slot)
+        return RequestCache(tables=[BlockTable() for _ in self.groups], slot=slot)
+
+    def take_opened(self) -> list[int]:
+        """The state slots handed out since the last call: what the step function zeroes."""
+        opened, self._opened = self._opened, []
+        return opened
 
     def can_open(self) -> bool:
         return self.slots.num_free > 0
@@ -208,6 +242,34 @@ class CacheManager:
         self.slots.give_back(cache.slot)
         cache.slot = -1
         cache.live = False
+
+
+def pages_in_flight(whole: int, window: int | None, portion: int, page_size: int) -> int:
+    """Pages one request holds at most in a group: all `whole` of them, or, with a window, those
+    from the first key the portion's first query still sees to the portion's last token."""
+    if window is None:
+        return whole
+    return min(whole, (window + portion - 2) // page_size + 2)
+
+
+def pages_per_group(groups, page_size: int, budget_bytes: int, bytes_per_page: list[int], max_slots: int,
+                    max_portion: int) -> list[int]:
+    """Page counts for a budget of bytes: every group without a window gets the same count N, a
+    group with a window at most what `max_slots` requests fed `max_portion` tokens a step can
+    hold of it; N is as large as the budget allows."""
+    caps = [None if group.window is None else max_slots * pages_in_flight(1 << 40, group.window, max_portion, page_size)
+            for group in groups]
+    capped: set[int] = set()
+    while True:
+        spent = sum(caps[g] * bytes_per_page[g] for g in capped)
+        rest = sum(bytes_per_page[g] for g in range(len(groups)) if g not in capped)
+        if rest == 0:
+            return [caps[g] for g in range(len(groups))]
+        count = max(0, budget_bytes - spent) // rest
+        over = {g for g in range(len(groups)) if g not in capped and caps[g] is not None and caps[g] < count}
+        if not over:
+            return [caps[g] if g in capped else count for g in range(len(groups))]
+        capped |= over
 
 
 def group_caches(needs: dict[int, object]) -> list[KVGroupSpec]:

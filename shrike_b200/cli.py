@@ -336,7 +336,7 @@ def main(argv=None) -> None:
     began = time.perf_counter()
     print("loading ...", flush=True)
     engine, name = open_engine(args)
-    print(f"shrike_b200 ready: {name}, {min(engine.block_manager.num_pages)} KV blocks of "
+    print(f"shrike_b200 ready: {name}, {engine.block_manager.total_pages} KV blocks of "
           f"{engine.block_manager.page_size} tokens, {time.perf_counter() - began:.1f} s to load; /help lists commands")
     console = Console(engine, color=color)
     prompt = "\001\033[1;36m\002shrike_b200> \001\033[0m\002" if color else "shrike_b200> "

@@ -46,7 +46,7 @@ def main(argv=None) -> int:
     began = time.perf_counter()
     engine, name = open_engine(args)
     print(f"[{name}: engine up in {time.perf_counter() - began:.1f} s, "
-          f"{min(engine.block_manager.num_pages)} KV blocks]", file=sys.stderr, flush=True)
+          f"{engine.block_manager.total_pages} KV blocks]", file=sys.stderr, flush=True)
     default = "Explain in two sentences what a paged key/value cache is." if engine.tokenizer is not None else DEFAULT_IDS
     prompt = read_prompt(args.prompt if args.prompt is not None else default, engine)
     try:

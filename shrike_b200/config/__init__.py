@@ -4,10 +4,12 @@ from .model_config import (  # noqa: F401
     GatedMLPSpec,
     LayerRun,
     LayerSpec,
+    LMHeadSpec,
     ModelConfig,
     PartSpec,
     RMSNormSpec,
     RotarySpec,
+    TokenEmbeddingSpec,
     normalise_dtype,
     read_config_json,
 )

@@ -89,14 +89,55 @@ class GatedMLPSpec(PartSpec):
 
 
 @dataclass(frozen=True)
+class TokenEmbeddingSpec(PartSpec):
+    """One table row per token id, copied into the residual (shrike/models/qwen.py:161)."""
+
+    vocab: int
+    width: int
+    kind: str = field(init=False, default="token_embedding")
+
+
+@dataclass(frozen=True)
+class LMHeadSpec(PartSpec):
+    """Normed hidden rows times a [vocab, width] matrix, which may be the embedding's table
+    (shrike/models/qwen.py:192,211-212)."""
+
+    width: int
+    vocab: int
+    tied: bool = False
+    kind: str = field(init=False, default="lm_head")
+
+
+STANDARD_ROLES = (
+    ("mixer", "mixer"),
+    ("mixer_norm", "norm"),
+    ("feed_forward", "feed_forward"),
+    ("feed_forward_norm", "norm"),
+)
+
+
+@dataclass(frozen=True)
 class LayerSpec:
-    """One layer: which parts, and how they are arranged (`block`)."""
+    """One layer: which parts, and how they are arranged (`block`).
+
+    The four named parts are what a pre-norm block takes.  A block that arranges more parts
+    (norms after its branches, a third branch) lists them in `extra` as (role, category, spec);
+    the block class is built with every role as a keyword and the architecture names the
+    tensors of every role.
+    """
 
     mixer: PartSpec
     mixer_norm: PartSpec
     feed_forward: PartSpec
     feed_forward_norm: PartSpec
     block: str = "pre_norm"
+    extra: tuple = ()
+
+    def roles(self):
+        """(role, category, spec) of every part of the layer."""
+        for role, category in STANDARD_ROLES:
+            yield role, category, getattr(self, role)
+        yield from self.extra
 
 
 @dataclass(frozen=True)
@@ -126,6 +167,16 @@ class ModelConfig:
     eos_token_ids: list[int]
     dtype: str  # "bfloat16" | "float32": what config.json asks for
     raw: dict[str, Any] = field(default_factory=dict, repr=False)
+    # how token ids become the residual and how normed rows become logits: parts like the others,
+    # chosen by `kind`.  None: one table, and a plain (or tied) matrix, from the sizes above.
+    embedding: PartSpec | None = None
+    head: PartSpec | None = None
+
+    def __post_init__(self):
+        if self.embedding is None:
+            self.embedding = TokenEmbeddingSpec(vocab=self.vocab_size, width=self.hidden_size)
+        if self.head is None:
+            self.head = LMHeadSpec(width=self.hidden_size, vocab=self.vocab_size, tied=self.tie_word_embeddings)
 
     @property
     def num_layers(self) -> int:

@@ -20,14 +20,33 @@ class TensorNames:
     """Where an architecture keeps its tensors.
 
     `layer_part(layer, role)` gives the prefix for a layer's part, role being one of
-    "mixer", "mixer_norm", "feed_forward", "feed_forward_norm"; a part's own
-    parameter names (e.g. "q_proj.weight") are appended to it.
+    "mixer", "mixer_norm", "feed_forward", "feed_forward_norm" (or a role the layer lists
+    in `extra`); a part's own parameter names (e.g. "q_proj.weight") are appended to it.
+    `embedding` and `lm_head` are the full names of the token table and the output
+    matrix: the parameter "weight" of the embedding part and of the head part.  Further
+    parameters of those two parts (an embedding that also holds a position table, say) are
+    named `embedding_prefix + local` and `head_prefix + local`; the prefixes default to the
+    two names without their trailing "weight".
     """
 
     embedding: str
     final_norm_prefix: str
     lm_head: str
     layer_part: Callable[[int, str], str]
+    embedding_prefix: str | None = None
+    head_prefix: str | None = None
+
+    def embedding_name(self, local: str) -> str:
+        return self.embedding if local == "weight" else _prefix(self.embedding_prefix, self.embedding) + local
+
+    def head_name(self, local: str) -> str:
+        return self.lm_head if local == "weight" else _prefix(self.head_prefix, self.lm_head) + local
+
+
+def _prefix(given: str | None, weight_name: str) -> str:
+    if given is not None:
+        return given
+    return weight_name[: -len("weight")] if weight_name.endswith("weight") else weight_name + "."
 
 
 @dataclass(frozen=True)

@@ -19,6 +19,9 @@ import numpy as np
 import torch
 
 
+FIRST_GROUP = 11   # index of the first per-group part of the packed block (see BatchBuilder.stage)
+
+
 @dataclass
 class StepEntry:
     cache: object  # cache.RequestCache
@@ -46,6 +49,7 @@ class StepContext:
     q_start: torch.Tensor  # int32 [S + 1]
     ctx_len: torch.Tensor  # int32 [S], new tokens included
     state_slot: torch.Tensor  # int32 [S]
+    seq_start: torch.Tensor  # int32 [S]: position of each entry's first token (0: the request begins)
     out_rows: torch.Tensor  # int32 [R]
     groups: list[GroupView]
     storage: object  # cache.storage.CacheStorage
@@ -163,9 +167,9 @@ class BatchBuilder:
         max_blocks = [max(8, 1 << (mb - 1).bit_length()) for mb in max_blocks]
         sampled = r > 0 and all(e.sampling is not None for e in entries if e.want)
 
-        sizes = [2 * r, r, r, n, n, n, s + 1, s, s, r]
+        sizes = [2 * r, r, r, n, n, n, s + 1, s, s, r, s]
         for g in range(self.num_groups):
-            sizes += [n, s * max_blocks[g]]
+            sizes += [n, s * max_blocks[g]]   # parts[FIRST_GROUP + 2 g], parts[FIRST_GROUP + 2 g + 1]
         offsets = [0]
         for size in sizes:
             offsets.append(offsets[-1] + size)
@@ -174,8 +178,11 @@ class BatchBuilder:
         flat = host.numpy()
         parts = [flat[offsets[i]: offsets[i + 1]] for i in range(len(sizes))]
         seeds, temps, top_ps = parts[0].view(np.int64), parts[1].view(np.float32), parts[2].view(np.float32)
-        ids, pos, seq_of, q_start, ctx_arr, slot_arr, out_rows = parts[3:10]
+        ids, pos, seq_of, q_start, ctx_arr, slot_arr, out_rows, start_arr = parts[3:11]
         slots_host = [e.cache.slot for e in entries]
+        start_arr[:real] = starts
+        if pad > 0:
+            start_arr[real:] = 0
 
         if max(q_lens) == 1:
             # the steady state of decoding: one token per entry, filled without per-token work
@@ -206,8 +213,8 @@ class BatchBuilder:
                             temps[row], top_ps[row], seeds[row] = e.sampling
                         row += 1
             for g in range(self.num_groups):
-                slots = parts[10 + 2 * g]
-                table2d = parts[11 + 2 * g].reshape(s, max_blocks[g])
+                slots = parts[FIRST_GROUP + 2 * g]
+                table2d = parts[FIRST_GROUP + 1 + 2 * g].reshape(s, max_blocks[g])
                 table2d[:] = -1
                 width = max_blocks[g]
                 for index, e in enumerate(entries):
@@ -260,14 +267,14 @@ class BatchBuilder:
         dev = self._dev[: staged.total]
         views = [dev[offsets[i]: offsets[i + 1]] for i in range(len(sizes))]
         groups = [
-            GroupView(views[10 + 2 * g], views[11 + 2 * g].view(s, max_blocks[g]), max_blocks[g])
+            GroupView(views[FIRST_GROUP + 2 * g], views[FIRST_GROUP + 1 + 2 * g].view(s, max_blocks[g]), max_blocks[g])
             for g in range(self.num_groups)
         ]
         sampled = staged.sampled
         return StepContext(
             num_tokens=n, num_seqs=s, num_rows=r,
             token_ids=views[3], positions=views[4], seq_of_token=views[5], q_start=views[6],
-            ctx_len=views[7], state_slot=views[8], out_rows=views[9], groups=groups,
+            ctx_len=views[7], state_slot=views[8], seq_start=views[10], out_rows=views[9], groups=groups,
             storage=self.storage, max_q_len=max(staged.q_lens), min_q_len=min(staged.q_lens),
             max_ctx_len=max(staged.ctx_lens), q_lens=staged.q_lens, starts=staged.starts, slots=staged.slots,
             all_single=max(staged.q_lens) == 1,
@@ -302,8 +309,8 @@ class BatchBuilder:
             cursor += q
 
         for g in range(self.num_groups):
-            slots = parts[10 + 2 * g]
-            table_flat = parts[11 + 2 * g]
+            slots = parts[FIRST_GROUP + 2 * g]
+            table_flat = parts[FIRST_GROUP + 1 + 2 * g]
             table_flat[:] = -1
             table2d = table_flat.reshape(s, max_blocks[g])
             cursor = 0

@@ -94,6 +94,7 @@ class LLMEngine:
         self.runner = ModelRunner(
             config, tensors, self.ops, self.device, self.dtype, page_size=block_size,
             num_pages=num_blocks, gpu_mem_util=gpu_mem_util, max_slots=max_running,
+            max_portion=max_tokens_per_step,
         )
         self.block_manager = self.runner.cache
         self.scheduler = Scheduler(self.block_manager, max_tokens_per_step, max_running)
@@ -151,12 +152,12 @@ class LLMEngine:
                 f"{len(token_ids)} prompt + {sampling.max_new_tokens} generated tokens exceed "
                 f"max_position_embeddings={self.config.max_position_embeddings}"
             )
-        worst = self.block_manager.worst_case_pages(total)
+        worst = self.block_manager.worst_case_pages(total, self.scheduler.max_tokens_per_step)
         if any(w > have for w, have in zip(worst, self.block_manager.num_pages)):
             raise ValueError(
                 f"request needs up to {max(worst)} KV blocks ({len(token_ids)} prompt + "
                 f"{sampling.max_new_tokens} generated tokens, block_size={self.block_manager.page_size}) "
-                f"but the pool has only {min(self.block_manager.num_pages)}; it could never be scheduled: "
+                f"but the pool has only {self.block_manager.total_pages}; it could never be scheduled: "
                 "shorten the prompt, lower max_new_tokens, or raise gpu_mem_util / num_blocks"
             )
         request = Request(token_ids=token_ids, sampling=sampling)
@@ -302,7 +303,7 @@ class LLMEngine:
             "avg_tokens_per_sec": round(self.stats.tokens_generated / max(elapsed, 1e-9), 1),
             "running": len(self.scheduler.running),
             "waiting": len(self.scheduler.waiting),
-            "kv_blocks_total": min(self.block_manager.num_pages),
-            "kv_blocks_free": min(self.block_manager.num_free),
+            "kv_blocks_total": self.block_manager.total_pages,
+            "kv_blocks_free": self.block_manager.free_pages,
             "preemptions": self.scheduler.num_preemptions,
         }

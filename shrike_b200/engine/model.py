@@ -1,9 +1,10 @@
 """The model as data: parts built from the configuration, run in the listed order.
 
-Embedding, the layer runs, the final norm on the wanted rows only and the LM head
-(shrike/models/qwen.py:160-164,181-192).  Which class serves a part comes from the
-spec's `kind` through the part registries; which layer runs when, and on which
-cache, comes from `config.order`.
+Embedding, the layer runs, the final norm on the wanted rows only and the head
+(shrike/models/qwen.py:160-164,181-192).  Which class serves a part (the embedding and
+the head included) comes from the spec's `kind` through the part registries; which parts
+a layer has from its spec's roles; which layer runs when, and on which cache, from
+`config.order`.
 """
 
 from __future__ import annotations
@@ -12,7 +13,7 @@ import torch
 
 from ..config.model_config import ModelConfig
 from ..parts.base import part_class
-from ..weights.expected import LAYER_ROLES, tensor_names
+from ..weights.expected import tensor_names
 
 
 class Runtime:
@@ -66,26 +67,36 @@ class DecoderModel:
         self.ops = ops
         self.runtime = runtime
         names = tensor_names(config)
-        self.embedding = tensors[names.embedding]
-        self.lm_head = tensors.get(names.lm_head)
-        if self.lm_head is None:
-            if not config.tie_word_embeddings:
-                raise KeyError(f"{names.lm_head} is absent and the configuration does not tie it to the embedding")
-            self.lm_head = self.embedding
+        spec = config.embedding
+        cls = part_class("embedding", spec.kind)
+        self.embedding = cls(spec, {local: tensors[names.embedding_name(local)] for local in cls.parameters(spec)},
+                             ops, runtime)
+        parts = [self.embedding]
         self.blocks = []
         for index, layer in enumerate(config.layers):
             built = {}
-            for role, category in LAYER_ROLES:
-                spec = getattr(layer, role)
+            for role, category, spec in layer.roles():
                 cls = part_class(category, spec.kind)
-                local = _take(tensors, names.layer_part(index, role), cls.parameters(spec))
-                built[role] = cls(spec, local, ops, runtime)
+                built[role] = cls(spec, _take(tensors, names.layer_part(index, role), cls.parameters(spec)), ops, runtime)
             self.blocks.append(part_class("block", layer.block)(**built))
-            self.capture_safe = getattr(self, "capture_safe", True) and all(
-                getattr(part, "capture_safe", False) for part in (*built.values(), self.blocks[-1]))
+            parts += [*built.values(), self.blocks[-1]]
         norm = config.final_norm
         cls = part_class("norm", norm.kind)
         self.final_norm = cls(norm, _take(tensors, names.final_norm_prefix, cls.parameters(norm)), ops, runtime)
+        spec = config.head
+        cls = part_class("head", spec.kind)
+        local_tensors = {}
+        for local in cls.parameters(spec):
+            name = names.head_name(local)
+            if name in tensors:
+                local_tensors[local] = tensors[name]
+            elif local == "weight" and getattr(spec, "tied", False) and getattr(self.embedding, "table", None) is not None:
+                local_tensors[local] = self.embedding.table
+            else:
+                raise KeyError(f"{name} is absent and the configuration does not tie it to the embedding")
+        self.head = cls(spec, local_tensors, ops, runtime)
+        parts += [self.final_norm, self.head]
+        self.capture_safe = all(getattr(part, "capture_safe", False) for part in parts)
 
     def cache_needs(self):
         """cache id -> KVNeed, and cache id -> StateNeed, over the run order."""
@@ -103,37 +114,31 @@ class DecoderModel:
         return kv, state
 
     def weight_bytes(self) -> int:
+        """Bytes of every distinct tensor the parts hold (a tied table counts once)."""
         seen, total = set(), 0
 
         def visit(obj):
             nonlocal total
             for value in vars(obj).values():
-                if isinstance(value, torch.Tensor) and value.data_ptr() not in seen:
-                    seen.add(value.data_ptr())
-                    total += value.numel() * value.element_size()
+                if isinstance(value, torch.Tensor):
+                    if value.data_ptr() not in seen:
+                        seen.add(value.data_ptr())
+                        total += value.numel() * value.element_size()
                 elif hasattr(value, "__dict__") and not isinstance(value, (Runtime, type)) and value is not self.ops:
                     if id(value) not in seen:
                         seen.add(id(value))
                         visit(value)
 
-        for block in self.blocks:
-            visit(block)
-        for tensor in (self.embedding, self.lm_head, self.final_norm.weight):
-            if tensor.data_ptr() not in seen:
-                seen.add(tensor.data_ptr())
-                total += tensor.numel() * tensor.element_size()
+        for part in (self.embedding, *self.blocks, self.final_norm, self.head):
+            visit(part)
         return total
 
     def forward(self, ctx) -> torch.Tensor:
         """float32 logits [R, vocab] at `ctx.out_rows`."""
-        rt, ops = self.runtime, self.ops
-        resid = rt.buffer("resid", (ctx.num_tokens, self.config.hidden_size), torch.float32)
-        ops.embed(ctx.token_ids, self.embedding, resid, ctx.previous_tokens)
+        resid = self.embedding.forward(ctx)
         delta = None
         for run in self.config.order:
             resid, delta = self.blocks[run.layer].forward(resid, delta, ctx, run)
-        logits = rt.buffer("logits", (ctx.num_rows, self.config.vocab_size), torch.float32)
-        if ctx.num_rows:
-            hidden = self.final_norm.gather_norm(resid, delta, ctx.out_rows)
-            ops.linear(hidden, self.lm_head, logits)
-        return logits
+        if not ctx.num_rows:
+            return self.runtime.buffer("logits", (0, self.config.vocab_size), torch.float32)
+        return self.head.forward(self.final_norm.gather_norm(resid, delta, ctx.out_rows))

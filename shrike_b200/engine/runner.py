@@ -12,8 +12,8 @@ from __future__ import annotations
 
 import torch
 
-from ..cache.manager import CacheManager, group_caches
-from ..cache.storage import CacheStorage, page_bytes
+from ..cache.manager import CacheManager, group_caches, pages_in_flight, pages_per_group
+from ..cache.storage import CacheStorage, page_bytes, state_bytes
 from ..config.model_config import ModelConfig
 from .batch import BatchBuilder, StepEntry
 from .model import DecoderModel, Runtime
@@ -47,7 +47,12 @@ class ModelRunner:
         num_pages: int | None = None,
         gpu_mem_util: float = 0.85,
         max_slots: int = 256,
+        max_portion: int | None = None,
     ):
+        """`num_pages`: pages of every group (an int) or of each group (a list); None sizes the pools
+        from free device memory: `gpu_mem_util` of it, less the per-request state of `max_slots`
+        requests, shared out by `pages_per_group` (groups that keep every key get equal counts, a
+        group with a window what `max_slots` requests fed `max_portion` tokens a step can hold)."""
         self.config = config
         self.device = torch.device(device)
         self.dtype = TORCH_DTYPES[dtype]
@@ -58,23 +63,36 @@ class ModelRunner:
         self.groups = group_caches(kv_needs)
         self.page_size = page_size
         element = torch.empty((), dtype=self.dtype).element_size()
-        self.bytes_per_page = sum(page_bytes(g, page_size, element) for g in self.groups)
+        per_group = [page_bytes(g, page_size, element) for g in self.groups]
+        self.bytes_per_page = sum(per_group)
+        self.state_bytes = state_bytes(state_needs, max_slots)
         if num_pages is None:
             free, _total = torch.cuda.mem_get_info(self.device)
-            num_pages = int(free * gpu_mem_util) // max(1, self.bytes_per_page)
-        if num_pages < 1:
+            budget = int(free * gpu_mem_util) - self.state_bytes
+            num_pages = pages_per_group(self.groups, page_size, budget, per_group, max_slots,
+                                        max_portion or config.max_position_embeddings)
+        elif isinstance(num_pages, int):
+            # an explicit count: that many pages for a group that keeps every key, and no more than its
+            # requests can ever hold for a group with a window
+            portion = max_portion or config.max_position_embeddings
+            num_pages = [num_pages if g.window is None else
+                         min(num_pages, max_slots * pages_in_flight(1 << 40, g.window, portion, page_size))
+                         for g in self.groups]
+        if any(count < 1 for count in num_pages):
             raise ValueError("no room for a single cache page; lower the model size or raise gpu_mem_util")
-        self.num_pages = num_pages
+        self.num_pages = list(num_pages)
         self.cache = CacheManager(self.groups, page_size, num_pages, max_slots)
         self.storage = CacheStorage(
             self.groups, page_size, num_pages, state_needs, max_slots, self.dtype, self.device
         )
         self.builder = BatchBuilder(page_size, len(self.groups), self.device, self.storage)
         self.use_graphs = True
-        # also capture batches with portions, once their shape repeats: only if every part says that
-        # its forward() depends on the batch's shape alone (`capture_safe`; parts that do not say so,
-        # such as one that branches on a request's position, keep such batches uncaptured)
-        self.capture_portions = bool(getattr(self.model, "capture_safe", False))
+        # steps are recorded as CUDA graphs (decode batches at once, batches with portions once their
+        # shape repeats) only if every part says that its forward() depends on the batch's shape alone
+        # (`capture_safe`; a model with a part that does not say so, such as one that branches on a
+        # request's position on the host, runs every step kernel by kernel)
+        self.capture_safe = bool(getattr(self.model, "capture_safe", False))
+        self.capture_portions = self.capture_safe
         # batches of single tokens are padded up to a few sizes (multiples of eight), so that a
         # workload whose batch shrinks and grows request by request replays a handful of captured
         # sequences instead of capturing one per size; on the same condition, because a padding
@@ -135,7 +153,11 @@ class ModelRunner:
         decode = max(staged.q_lens) == 1 and staged.r == staged.s and all(e.want == [0] for e in entries)
         if not decode and staged.rows != staged.r:
             raise AssertionError("only batches of single tokens that all want their logits are padded")
-        graphable = self.use_graphs and self.device.type == "cuda" and (decode or self.capture_portions)
+        # a launch sequence is recorded and replayed only if every part promises that its forward pass
+        # depends on the batch's shape alone (`capture_safe`): a part that reads positions or slots on
+        # the host would replay the values of the step it was recorded in
+        graphable = (self.use_graphs and self.device.type == "cuda" and self.capture_safe
+                     and (decode or self.capture_portions))
         # what a captured launch sequence has baked in: the number of entries, every entry's
         # length (grids and shapes follow from them), the number of wanted rows, the table widths
         key = (staged.s if decode else tuple(staged.q_lens), staged.r, tuple(staged.max_blocks), sample)
@@ -188,6 +210,7 @@ class ModelRunner:
         bakes in what the parts computed on the host from the shape; parts must not branch on
         other host-side values of the step (positions, slots) if they are to be captured."""
         staged, sample, graphable, rows = prepared.staged, prepared.sample, prepared.graphable, prepared.rows
+        self.storage.zero_slots(self.cache.take_opened())   # requests opened since the last step start from zero state
         self.builder.commit(staged)
         key = prepared.key
         if graphable and not prepared.decode and key not in self._graphs:

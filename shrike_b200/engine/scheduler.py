@@ -58,10 +58,20 @@ class Scheduler:
         self.waiting.appendleft(victim)
         return victim is not for_request
 
+    def preempt_newest(self) -> Request | None:
+        """Preempts the newest running request as a shortage of pages would (an operator's lever,
+        and what tests of recomputation use); returns it, or None when nothing runs."""
+        if not self.running:
+            return None
+        victim = self.running[-1]
+        self._preempt_newest(victim)
+        return victim
+
     def schedule(self) -> list[tuple[Request, int]]:
         singles: list[tuple[Request, int]] = []
         portions: list[tuple[Request, int]] = []
         budget = self.max_tokens_per_step
+        longest = self.cache.portion_limit() or budget   # what a windowed group's pool can hold of one request
 
         for request in list(self.running):
             if budget == 0:
@@ -71,7 +81,7 @@ class Scheduler:
             if request.prefill_done:
                 num_new = 1
             else:
-                num_new = min(request.num_prompt_tokens - request.num_computed_tokens, budget)
+                num_new = min(request.num_prompt_tokens - request.num_computed_tokens, budget, longest)
             if not self.cache.has_room(request.cache, request.num_computed_tokens + num_new):
                 while not self.cache.can_append(request.cache, request.num_computed_tokens, num_new):
                     if not self._preempt_newest(request):
@@ -85,7 +95,7 @@ class Scheduler:
 
         while self.waiting and budget > 0 and len(self.running) < self.max_running:
             request = self.waiting[0]
-            num_new = min(request.num_prompt_tokens - request.num_computed_tokens, budget)
+            num_new = min(request.num_prompt_tokens - request.num_computed_tokens, budget, longest)
             if not self.cache.can_append(None, request.num_computed_tokens, num_new):
                 break
             self.waiting.popleft()
@@ -106,18 +116,16 @@ class Scheduler:
                 self.cache.advance(request.cache, request.num_computed_tokens)
 
     def finish(self, request: Request, reason: str) -> None:
+        """Ends a request and gives back what it holds.  It is usually running; it may be waiting
+        when it was preempted while the step that produced its last token was still in flight."""
         request.status = Status.FINISHED
         request.finish_reason = reason
-        self.running.remove(request)
+        if request in self.running:
+            self.running.remove(request)
+        elif request in self.waiting:
+            self.waiting.remove(request)
         self._release(request)
 
     def abort(self, request: Request) -> None:
         """Ends a request wherever it is (shrike/cli.py:131-141)."""
-        if request in self.running:
-            self.finish(request, "aborted")
-            return
-        if request in self.waiting:
-            self.waiting.remove(request)
-        self._release(request)
-        request.status = Status.FINISHED
-        request.finish_reason = "aborted"
+        self.finish(request, "aborted")

@@ -29,8 +29,17 @@ be checked and the cache sized before anything is put on the device):
   feed-forward
       forward(x[N,W], ctx) -> delta[N,W]
   block
+      __init__(**parts by role)   ("mixer", "mixer_norm", "feed_forward", "feed_forward_norm"
+          and whatever further roles the layer's spec lists in `extra`)
       forward(resid_f32, delta, ctx, run) -> (resid_f32, delta)
           `delta` is a sum not yet added to the residual; the next norm adds it.
+  embedding
+      forward(ctx) -> resid_f32[N,W]   the residual stream of the step's tokens.  A token id of
+          -1 - r stands for `ctx.previous_tokens[r]` (what the step before drew in its row r).
+      `table`: the [vocab, W] tensor a tied head may share, or None
+  head
+      forward(hidden[R,W]) -> float32 logits [R, vocab]   (hidden: the final norm's output on the
+          wanted rows); built with tensors {"weight": ...}, the embedding's table when tied
 
 A part may declare the class attribute `capture_safe = True`.  It then promises that forward()
 launches the same kernels with the same sizes for the same batch shape, whatever the positions,
@@ -77,8 +86,12 @@ FEED_FORWARDS: dict[str, type] = {}
 NORMS: dict[str, type] = {}
 POSITIONS: dict[str, type] = {}
 BLOCKS: dict[str, type] = {}
+EMBEDDINGS: dict[str, type] = {}
+HEADS: dict[str, type] = {}
 
 _CATEGORIES = {
+    "embedding": EMBEDDINGS,
+    "head": HEADS,
     "mixer": MIXERS,
     "feed_forward": FEED_FORWARDS,
     "norm": NORMS,
@@ -88,7 +101,8 @@ _CATEGORIES = {
 
 
 def register_part(category: str, kind: str, cls: type) -> type:
-    """Adds a part class; `category` is one of mixer, feed_forward, norm, position, block."""
+    """Adds a part class; `category` is one of mixer, feed_forward, norm, position, block,
+    embedding, head."""
     _CATEGORIES[category][kind] = cls
     return cls
 

@@ -68,7 +68,6 @@ def load_weights(model_dir, config: ModelConfig, engine_dtype: torch.dtype, devi
     """name -> tensor on `device`; raises WeightError unless the folder fits."""
     expected = expected_tensors(config)
     head = tensor_names(config).lm_head
-    embedding = tensor_names(config).embedding
     where: dict[str, SafetensorsFile] = {}
     duplicates = []
     for shard in open_shards(model_dir):
@@ -78,7 +77,7 @@ def load_weights(model_dir, config: ModelConfig, engine_dtype: torch.dtype, devi
             where[name] = shard
 
     missing = [name for name in expected if name not in where]
-    if config.tie_word_embeddings and head in missing:
+    if getattr(config.head, "tied", config.tie_word_embeddings) and head in missing:
         missing.remove(head)
     unexpected = [name for name in where if name not in expected]
     wrong = [
@@ -96,6 +95,6 @@ def load_weights(model_dir, config: ModelConfig, engine_dtype: torch.dtype, devi
         view = where[name].tensor(name)
         target = kept_dtype(view.dtype, view.dim(), engine_dtype)
         tensors[name] = view.to(device=device, dtype=target, copy=True)
-    if head not in tensors:
-        tensors[head] = tensors[embedding]
+    if head not in tensors:   # tied and left out of the file: the same tensor under both names
+        tensors[head] = tensors[tensor_names(config).embedding]
     return tensors

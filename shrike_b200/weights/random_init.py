@@ -44,7 +44,7 @@ def random_tensors(config, seed: int, device="cpu", dtype=torch.float32) -> dict
     head = tensor_names(config).lm_head
     tensors = {}
     for name, spec in expected_tensors(config).items():
-        if name == head and config.tie_word_embeddings:
+        if name == head and getattr(config.head, "tied", config.tie_word_embeddings):
             continue
         tensors[name] = random_tensor(name, spec, seed, device, dtype)
     return tensors

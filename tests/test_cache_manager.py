@@ -144,3 +144,46 @@ def test_random_orders_lose_nothing(seed):
     for cache, _ in live:
         manager.free(cache)
     assert manager.whole()
+
+
+def test_pools_are_sized_by_need():
+    """Groups that keep every key share the budget in equal page counts; a group with a window
+    gets no more than its requests can hold at once; per-request state comes off the budget first
+    (that is the caller's part: the budget given here is what is left for pages)."""
+    from shrike_b200.cache.manager import pages_in_flight, pages_per_group
+
+    page = 16
+    full, window = KVGroupSpec((0,), 2, 16, None), KVGroupSpec((1,), 2, 16, 100)
+    # a window of 100 and portions of 64: from key p - 99 to key p + 63 -> at most 12 pages of 16
+    assert pages_in_flight(1000, 100, 64, page) == (100 + 64 - 2) // 16 + 2 == 12
+    assert pages_in_flight(5, 100, 64, page) == 5 and pages_in_flight(1000, None, 64, page) == 1000
+    bytes_per_page = [1000, 1000]
+    counts = pages_per_group([full, window], page, 1_000_000, bytes_per_page, 4, 64)
+    assert counts == [1_000_000 // 1000 - 48, 48]          # 4 requests x 12 pages, the rest to the full group
+    assert pages_per_group([full, window], page, 50_000, bytes_per_page, 4, 64) == [25, 25]   # too little to reach the cap
+    assert pages_per_group([window], page, 1_000_000, [1000], 4, 64) == [48]
+    assert pages_per_group([], page, 1_000_000, [], 4, 64) == []
+    manager = CacheManager([full, window], page, counts, 4)
+    assert manager.total_pages == counts[0] and manager.portion_limit() == (48 - 2) * 16 - 100 + 2
+    assert manager.worst_case_pages(5000, 64) == [313, 12] and manager.worst_case_pages(5000) == [313, 313]
+    assert CacheManager([full], page, 8, 4).portion_limit() is None
+
+
+def test_opened_slots_are_remembered_until_taken():
+    manager = CacheManager([FULL], 4, 8, 3)
+    a, b = manager.open(), manager.open()
+    assert manager.take_opened() == [a.slot, b.slot] and manager.take_opened() == []
+    manager.free(a)
+    c = manager.open()
+    assert manager.take_opened() == [c.slot]
+
+
+def test_a_manager_without_page_groups_keeps_slots_only():
+    manager = CacheManager([], 16, [], 2)
+    assert manager.can_append(None, 0, 1000) and manager.total_pages == 0 and manager.free_pages == 0
+    a, b = manager.open(), manager.open()
+    manager.append(a, 0, 500)
+    assert not manager.can_append(None, 0, 1) and manager.has_room(a, 10_000)
+    manager.free(a)
+    manager.free(b)
+    assert manager.whole()

@@ -153,3 +153,38 @@ def test_empty_schedule_when_nothing_fits():
     scheduler.add(request(9))
     assert scheduler.schedule() == []
     assert scheduler.has_work
+
+
+def test_preempt_newest_is_an_operators_lever_and_a_preempted_request_may_still_finish():
+    manager, scheduler = make(num_pages=16)
+    a, b = request(6, max_new_tokens=4), request(5, max_new_tokens=4)
+    scheduler.add(a)
+    scheduler.add(b)
+    run_step(scheduler)
+    assert scheduler.running == [a, b]
+    assert scheduler.preempt_newest() is b and scheduler.num_preemptions == 1
+    assert b.status is Status.WAITING and b.num_computed_tokens == 0 and b.cache is None and scheduler.waiting[0] is b
+    scheduler.finish(b, "length")          # the step in flight when it was preempted produced its last token
+    assert b.status is Status.FINISHED and not scheduler.waiting
+    scheduler.finish(a, "stop")
+    assert manager.whole() and scheduler.preempt_newest() is None
+
+
+def test_a_portion_never_outgrows_a_windowed_groups_pool():
+    """A group with a window has a small pool of its own.  The scheduler cuts a prompt so that
+    the window and the portion fit in it, however large the token budget is."""
+    full, window = KVGroupSpec((0,), 2, 16, None), KVGroupSpec((1,), 2, 16, 6)
+    manager = CacheManager([full, window], 4, [64, 6], 4)      # the windowed pool: 6 pages of 4
+    scheduler = Scheduler(manager, max_tokens_per_step=64, max_running=4)
+    assert manager.portion_limit() == (6 - 2) * 4 - 6 + 2 == 12
+    long_prompt = request(50, max_new_tokens=2)
+    scheduler.add(long_prompt)
+    fed = []
+    while not long_prompt.prefill_done:
+        batch = scheduler.schedule()
+        assert batch, "the prompt can never be scheduled"
+        fed.append(batch[0][1])
+        scheduler.postprocess(batch)
+    assert max(fed) == 12 and sum(fed) == 50 and scheduler.num_preemptions == 0
+    scheduler.finish(long_prompt, "length")
+    assert manager.whole()
