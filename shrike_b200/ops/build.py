@@ -148,9 +148,14 @@ def tensor_core_gemm_library() -> ctypes.CDLL:
     return load_library("shrike_gemm_tcgen05", ["gemm_tcgen05.cu"])
 
 
+def layer_program_library() -> ctypes.CDLL:
+    return load_library("shrike_layer_program", ["layer_program.cu"])
+
+
 def build_all(head_dims=(16, 32, 48, 64, 128, 256)) -> list[Path]:
     """Everything the package can load, for the usual head sizes."""
-    built = [compile_library("shrike_core", CORE_SOURCES), compile_library("shrike_gemm_tcgen05", ["gemm_tcgen05.cu"])]
+    built = [compile_library("shrike_core", CORE_SOURCES), compile_library("shrike_gemm_tcgen05", ["gemm_tcgen05.cu"]),
+             compile_library("shrike_layer_program", ["layer_program.cu"])]
     for head_dim in head_dims:
         built.append(compile_library(f"shrike_attention_d{head_dim}", ATTENTION_SOURCES,
                                      {"SHRIKE_HEAD_DIM": head_dim}))

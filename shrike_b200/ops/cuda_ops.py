@@ -27,6 +27,16 @@ class KernelError(RuntimeError):
     pass
 
 
+class AttentionPlan:
+    """What `CudaOps.attention_plan` decides for a batch shape."""
+
+    __slots__ = ("has_single", "has_portions", "tc_portions", "splits", "cluster", "scratch", "arrivals")
+
+    def __init__(self, has_single, has_portions, tc_portions, splits, cluster, scratch, arrivals):
+        self.has_single, self.has_portions, self.tc_portions = has_single, has_portions, tc_portions
+        self.splits, self.cluster, self.scratch, self.arrivals = splits, cluster, scratch, arrivals
+
+
 def _ptr(tensor):
     return None if tensor is None else tensor.data_ptr()
 
@@ -87,6 +97,8 @@ class CudaOps:
         self._arrivals = None    # per kv head: splits of single-token attention that have finished
         self.generation = 0      # grows when the scratch moves
         self._held_stream = None
+        self._layer_program = None   # the native per-layer issue, built on first use
+        self.native_layers = True    # whole layers are issued by one native call where the parts allow it
         self.launches = 0        # launches of this package's own kernels
         self.library_calls = 0   # matrix products handed to cuBLAS
         # library matrix products keep float32 accumulation end to end: no TF32 for float32
@@ -148,6 +160,16 @@ class CudaOps:
             raise KernelError(
                 f"head size {head_dim} is not served: the attention kernels take multiples of 16 from 16 to 256"
             )
+
+    def layer_program(self):
+        """The native per-layer issue (`ops/layer_program.py`), or None when it is switched off."""
+        if not self.native_layers or self.dtype != torch.bfloat16:
+            return None
+        if self._layer_program is None:
+            from .layer_program import LayerProgram
+
+            self._layer_program = LayerProgram(self)
+        return self._layer_program
 
     # ---- kernels ------------------------------------------------------------
     def embed(self, ids, table, out, previous=None):
@@ -339,8 +361,31 @@ class CudaOps:
                 _ptr(ctx_len), _ptr(seq_of_token), self.code, q.shape[0], num_heads, num_kv_heads,
                 page_size, num_pages, scale, window or 0, _ptr(out), self._stream()), "paged_attention")
             return
+        plan = self.attention_plan(num_heads, num_kv_heads, head_dim, num_seqs, max_blocks, page_size, max_q_len, min_q_len)
+        self.launches += plan.has_single + plan.has_portions
+        has_portions = plan.has_portions
+        if plan.tc_portions:
+            _check(lib.shrike_paged_attention_tc_portions(
+                _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), max_blocks, _ptr(q_start), _ptr(ctx_len),
+                q.shape[0], num_seqs, num_heads, num_kv_heads, page_size, num_pages, scale, window or 0, _ptr(out),
+                plan.has_single, max_q_len, _ptr(self.status), self._stream()), "paged_attention_tc_portions")
+            has_portions = 0
+            if not plan.has_single:
+                return
+        _check(lib.shrike_paged_attention_bf16(
+            _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), max_blocks, _ptr(q_start), _ptr(ctx_len),
+            num_seqs, num_heads, num_kv_heads, page_size, num_pages, scale, window or 0, _ptr(out),
+            plan.has_single, has_portions, max_q_len, plan.splits, plan.cluster, _ptr(plan.scratch), _ptr(plan.arrivals),
+            _ptr(self.status), self._stream()),
+            "paged_attention_bf16")
+
+    def attention_plan(self, num_heads, num_kv_heads, head_dim, num_seqs, max_blocks, page_size, max_q_len, min_q_len):
+        """How a bfloat16 batch's attention is cut: which kernels run (single tokens, portions, the
+        tensor-core form of the latter), the key splits and clusters of the single-token kernel and
+        its scratch.  A function of the batch's shape alone."""
         if max_q_len < 1:
             raise KernelError("paged_attention in bfloat16 needs max_q_len, the longest entry of the batch")
+        lib = self._attention_lib(head_dim)
         has_single = min_q_len <= 1
         has_portions = max_q_len > 1
         splits, cluster, scratch, arrivals = 1, 1, None, None
@@ -358,23 +403,9 @@ class CudaOps:
                 self._arrivals = torch.zeros(max(groups, 4096), dtype=torch.int32, device=self.device)
                 self.generation += 1
             scratch, arrivals = self._scratch, self._arrivals
-        tensor_core_portions = (has_portions and self.tensor_core_attention and lib.shrike_attention_tc_available()
-                                and page_size in (8, 16, 32, 64))
-        self.launches += (1 if has_single else 0) + (1 if has_portions else 0)
-        if tensor_core_portions:
-            _check(lib.shrike_paged_attention_tc_portions(
-                _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), max_blocks, _ptr(q_start), _ptr(ctx_len),
-                q.shape[0], num_seqs, num_heads, num_kv_heads, page_size, num_pages, scale, window or 0, _ptr(out),
-                int(has_single), max_q_len, _ptr(self.status), self._stream()), "paged_attention_tc_portions")
-            has_portions = False
-            if not has_single:
-                return
-        _check(lib.shrike_paged_attention_bf16(
-            _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), max_blocks, _ptr(q_start), _ptr(ctx_len),
-            num_seqs, num_heads, num_kv_heads, page_size, num_pages, scale, window or 0, _ptr(out),
-            int(has_single), int(has_portions), max_q_len, splits, cluster, _ptr(scratch), _ptr(arrivals),
-            _ptr(self.status), self._stream()),
-            "paged_attention_bf16")
+        tc_portions = bool(has_portions and self.tensor_core_attention and lib.shrike_attention_tc_available()
+                           and page_size in (8, 16, 32, 64))
+        return AttentionPlan(int(has_single), int(has_portions), int(tc_portions), splits, cluster, scratch, arrivals)
 
     @staticmethod
     def single_token_splits(tiles: int, groups: int, resident: int):

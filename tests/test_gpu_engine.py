@@ -239,3 +239,63 @@ def test_a_kernel_that_gave_up_is_seen_before_its_tokens_are_used(tmp_path, dtyp
         engine.abort(i)
     assert engine.block_manager.whole() and not engine.has_work
     assert engine.generate([random_tokens(256, 9, 1)], params)[0] == first
+
+
+@pytest.mark.parametrize("shape", ["tiny_c", "d64", "d128"])
+def test_layers_issued_by_one_native_call_equal_the_part_by_part_path(tmp_path, shape):
+    """A whole layer issued by one native call launches the same kernels with the same arguments
+    as the parts do one by one: steps of up to 64 tokens give the same bits.  Longer steps send
+    their products to the library through another door (cublasGemmEx instead of torch.mm), which
+    may choose another kernel: those are held to the bfloat16 tolerance."""
+    import torch
+
+    from shrike_b200.config import parse_config
+    from shrike_b200.engine.batch import StepEntry
+    from shrike_b200.engine.llm_engine import make_ops
+    from shrike_b200.engine.runner import ModelRunner
+    from shrike_b200.weights import random_tensors
+
+    raw = {
+        "tiny_c": TINY["C"],
+        "d64": dict(TINY["B"], hidden_size=448, num_attention_heads=7, num_key_value_heads=1, head_dim=64,
+                    intermediate_size=608, vocab_size=1000, num_hidden_layers=2),
+        "d128": dict(TINY["B"], hidden_size=512, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+                     intermediate_size=1376, vocab_size=777, num_hidden_layers=2),
+    }[shape]
+    config = parse_config(raw)
+    weights = random_tensors(config, 3, "cuda", torch.float32)
+    vocab = raw["vocab_size"]
+    ids = {"long": random_tokens(vocab, 400, 1), "short": random_tokens(vocab, 40, 2), "third": random_tokens(vocab, 90, 3)}
+    plan = [{"long": 200}, {"long": 100, "short": 30}, {"long": 1, "short": 1, "third": 62}, {"long": 3, "short": 1, "third": 2},
+            {"long": 1, "short": 1, "third": 1}, {"long": 95, "short": 1, "third": 25}]
+
+    def run(native: bool):
+        tensors = {k: (v.to(torch.bfloat16) if v.dim() >= 2 else v.clone()) for k, v in weights.items()}
+        ops = make_ops("bfloat16", "cuda")
+        ops.native_layers = native
+        runner = ModelRunner(config, tensors, ops, "cuda", "bfloat16", page_size=16, num_pages=48, max_slots=4)
+        runner.use_graphs = False
+        caches = {name: runner.cache.open() for name in ids}
+        fed = {name: 0 for name in ids}
+        rows = []
+        for step in plan:
+            entries = []
+            for name in sorted(step, key=lambda nm: step[nm] > 1):
+                count = step[name]
+                runner.cache.append(caches[name], fed[name], count)
+                entries.append(StepEntry(caches[name], ids[name][fed[name]: fed[name] + count], fed[name], [0, count - 1]))
+                fed[name] += count
+            rows.append(runner.step(entries).float().cpu().clone())
+            for name in step:
+                runner.cache.advance(caches[name], fed[name])
+        ops.check_status()
+        return rows, ops.launches, ops.library_calls
+
+    native, native_launches, native_library = run(True)
+    parts, parts_launches, parts_library = run(False)
+    assert (native_launches, native_library) == (parts_launches, parts_library)
+    for step, a, b in zip(plan, native, parts):
+        if sum(step.values()) <= 64:
+            assert torch.equal(a, b), f"step {step}: the two ways of issuing differ"
+        else:
+            assert (a - b).abs().max() <= 2e-2 * max(1.0, float(b.abs().max())), f"step {step}"
