@@ -22,6 +22,10 @@
 // Rows of a page beyond the context may hold anything (a page is reused without clearing):
 // scores are masked by selection, and the value rows beyond the context are zeroed in shared
 // memory before PV, because 0 * NaN would not be 0.
+// Few query tiles and many keys (a portion of a long prompt beside decoding requests) would leave
+// most of the GPU idle: the keys of a query tile are then split across `splits` CTAs, each of which
+// leaves its unnormalised output rows with their (base, sum) in scratch, and a second small kernel
+// adds the splits up (combine_portions_kernel).
 // Every wait is bounded (status word, CTA-wide abort flag); no TMA load uses multicast.
 // Tensor memory is allocated BEFORE dependents are allowed to start, so that a dependent
 // kernel that also wants tensor memory cannot starve a CTA of this one it is waiting for.
@@ -76,24 +80,69 @@ struct Args {
   int* status;
   int max_blocks, num_heads, num_kv_heads, page_size, num_pages, window, skip_single;
   float scale_log2;
+  int splits;          // CTAs that share a query tile's keys; > 1: results go to the scratch below
+  float* partial_o;    // [splits][tokens][heads][D] unnormalised output rows
+  float* partial_ml;   // [splits][tokens][heads][2] their base (log2 domain) and sum
+  int num_tokens;
+  int num_seqs;
+  const int* seq_of_token;   // [tokens], for the combine
 };
+
+// Which (sequence, query tile) a CTA with work index `work` owns: sequences in order, each with its
+// query tiles of BM rows, the last (longest to walk) first; sequences of one token own none when
+// skip_single.  Every lane of the calling warp gets the answer; tile_start < 0: no such work.
+__device__ __forceinline__ void find_work(const Args& args, int work, int& seq_out, int& tile_start_out) {
+  const int lane = threadIdx.x & 31;
+  int before = 0;
+  seq_out = -1;
+  tile_start_out = -1;
+  for (int base = 0; base < args.num_seqs; base += 32) {
+    const int s = base + lane;
+    int tiles = 0;
+    if (s < args.num_seqs) {
+      const int q_len = args.q_start[s + 1] - args.q_start[s];
+      tiles = (q_len == 1 && args.skip_single) ? 0 : (q_len + BM - 1) / BM;
+    }
+    int inclusive = tiles;
+#pragma unroll
+    for (int offset = 1; offset < 32; offset <<= 1) {
+      const int other = __shfl_up_sync(0xffffffffu, inclusive, offset);
+      if (lane >= offset) inclusive += other;
+    }
+    const int first = before + inclusive - tiles;            // work index of this sequence's first tile
+    const bool mine = tiles > 0 && work >= first && work < first + tiles;
+    const unsigned owner = __ballot_sync(0xffffffffu, mine);
+    if (owner != 0) {
+      const int src = __ffs(owner) - 1;
+      const int first_of_owner = __shfl_sync(0xffffffffu, first, src);
+      const int tiles_of_owner = __shfl_sync(0xffffffffu, tiles, src);
+      seq_out = base + src;
+      tile_start_out = (tiles_of_owner - 1 - (work - first_of_owner)) * BM;
+      return;
+    }
+    before += __shfl_sync(0xffffffffu, inclusive, 31);
+  }
+}
 
 __global__ void __launch_bounds__(THREADS, 2)
 portions_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const Args args) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  // CTAs are handed out x first: the longest query tiles of every head and sequence go first
-  // (a causal tile's work grows with its position), and the heads of a group, which read the
-  // same keys and values, run side by side.
-  const int head = blockIdx.x, seq = blockIdx.y;
-  const int tile_start = (gridDim.z - 1 - blockIdx.z) * BM;
-  const int start = args.q_start[seq];                          // metadata: written before the step's kernels
-  const int q_len = args.q_start[seq + 1] - start;
-  if (tile_start >= q_len || (q_len == 1 && args.skip_single)) {
+  // CTAs are handed out x first: the heads of a group, which read the same keys and values, run
+  // side by side; within a sequence the longest query tiles go first (a causal tile's work grows
+  // with its position).
+  // CTAs are numbered (head, work, split): `work` counts the query tiles of the batch's portions
+  // (find_work), so no CTA is spent on a sequence of one token or on rows a sequence does not have.
+  const int head = blockIdx.x, split = blockIdx.z;
+  int seq, tile_start;
+  find_work(args, blockIdx.y, seq, tile_start);                 // metadata: written before the step's kernels
+  if (tile_start < 0) {
     let_dependents_start();
     wait_for_previous();
     return;
   }
+  const int start = args.q_start[seq];
+  const int q_len = args.q_start[seq + 1] - start;
   if (smem_u32(smem_raw) & 1023u) {   // the swizzled tiles need 1 KiB alignment
     if (threadIdx.x == 0 && args.status != nullptr) *args.status = ERR_ALIGNMENT;
     let_dependents_start();
@@ -134,8 +183,12 @@ portions_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   const int rows_here = min(BM, q_len - tile_start);
   const int lo = args.window > 0 ? max(0, pos0 + tile_start - args.window + 1) : 0;
   const int hi = pos0 + tile_start + rows_here - 1;             // last key any row of this tile sees
-  const int tile_lo = lo / BN, tile_hi = hi / BN;
-  const int num_tiles = tile_hi - tile_lo + 1;
+  const int tile_hi = hi / BN;
+  // this CTA's share of the key tiles [lo / BN, tile_hi]: `per` tiles from tile_lo on (none: an empty split)
+  const int all_tiles = tile_hi - lo / BN + 1;
+  const int per = (all_tiles + args.splits - 1) / args.splits;
+  const int tile_lo = lo / BN + split * per;
+  const int num_tiles = max(0, min(tile_hi, tile_lo + per - 1) - tile_lo + 1);
 
   if (warp == 0) {
     // The whole warp runs the loop: lane 0 waits for the stage and arms its barrier, then lane
@@ -143,7 +196,7 @@ portions_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const int* table = args.block_table + static_cast<size_t>(seq) * args.max_blocks;
     const int pages_per_tile = BN / args.page_size;
     const int nowhere = args.num_pages * args.page_size;      // a row coordinate outside the cache: reads zeros
-    if (lane == 0) {
+    if (lane == 0 && num_tiles > 0) {
       mbar_expect_tx(&sh->q_full, Q_BYTES);
       for (int h = 0; h < HALVES; ++h) tma_load_2d(q_tile + h * Q_HALF, &map_q, &sh->q_full, head * D + h * 64, start + tile_start);
     }
@@ -195,7 +248,7 @@ portions_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           landed = mbar_try_wait(&sh->k_full[i % STAGES], (i / STAGES) & 1) && mbar_try_wait(&sh->v_full[i % STAGES], (i / STAGES) & 1);
         if (!landed && args.status != nullptr) *args.status = ERR_DRAIN;
       }
-      bool landed = false;
+      bool landed = num_tiles <= 0;
       for (unsigned tries = 0; tries < WAIT_LIMIT && !landed; ++tries) landed = mbar_try_wait(&sh->q_full, 0);
     }
   } else if (warp == 1) {
@@ -218,7 +271,7 @@ portions_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         umma_commit(&sh->k_free[st]);
         return true;
       };
-      bool ok = mbar_wait(&sh->q_full, 0, &sh->abort, args.status, ERR_MMA);
+      bool ok = num_tiles > 0 && mbar_wait(&sh->q_full, 0, &sh->abort, args.status, ERR_MMA);
       if (ok) ok = issue_scores(0);
       for (int i = 0; i < num_tiles && ok; ++i) {
         // buffer (i + 1) mod 2 was last read for tile i - 1, whose P has arrived: it is free
@@ -333,10 +386,31 @@ portions_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       fence_async_shared();
       mbar_arrive(&sh->p_full);
     }
-    if (ok) ok = mbar_wait(&sh->pv_done, (num_tiles - 1) & 1, &sh->abort, args.status, ERR_SOFTMAX);
+    if (ok && num_tiles > 0) ok = mbar_wait(&sh->pv_done, (num_tiles - 1) & 1, &sh->abort, args.status, ERR_SOFTMAX);
     ok = __all_sync(0xffffffffu, ok);
     fence_after_sync();
-    if (ok) {
+    if (ok && args.splits > 1) {
+      // a split's share: the unnormalised row as it stands in tensor memory, its base and its sum
+      const size_t at = (static_cast<size_t>(split) * args.num_tokens + start + t) * args.num_heads + head;
+      if (t < q_len) {
+        args.partial_ml[2 * at] = num_tiles > 0 ? row_max : -INFINITY;
+        args.partial_ml[2 * at + 1] = num_tiles > 0 ? row_sum : 0.f;
+      }
+      if (num_tiles > 0) {
+        float* dst = args.partial_o + at * D;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          unsigned o[32];
+          tmem_load32(tmem_o + lane_base + c * 32, o);
+          tmem_wait_load();
+          if (t < q_len) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              *reinterpret_cast<uint4*>(dst + c * 32 + j) = make_uint4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+          }
+        }
+      }
+    } else if (ok) {
       const float inv = row_sum > 0.f ? 1.0f / row_sum : 0.f;
       __nv_bfloat16* dst = args.out + (static_cast<size_t>(start + t) * args.num_heads + head) * D;
 #pragma unroll
@@ -367,9 +441,68 @@ portions_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   }
 }
 
+// Adds up the splits of every query row of the portions: out = sum_s O_s 2^(base_s - M) / sum_s l_s 2^(base_s - M)
+// with M the largest base.  One warp per (token, head), lanes over the splits first (bases and sums),
+// then over the head size.  Tokens of one-token sequences belong to the other kernel and are left alone.
+__global__ void __launch_bounds__(256)
+combine_portions_kernel(const Args args) {
+  let_dependents_start();
+  wait_for_previous();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int token = blockIdx.y * 8 + warp, head = blockIdx.x;
+  if (token >= args.num_tokens) return;
+  const int seq = args.seq_of_token[token];
+  if (args.skip_single && args.q_start[seq + 1] - args.q_start[seq] == 1) return;
+  const size_t token_head = static_cast<size_t>(token) * args.num_heads + head;
+  const size_t slice = static_cast<size_t>(args.num_tokens) * args.num_heads;
+  float m = -INFINITY, l = 0.f;                       // lane s holds split s (at most 32 splits)
+  if (lane < args.splits) {
+    m = args.partial_ml[2 * (lane * slice + token_head)];
+    l = args.partial_ml[2 * (lane * slice + token_head) + 1];
+    if (!(l > 0.f)) m = -INFINITY;                    // a split that saw no key of this row
+  }
+  float base = m;
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) base = fmaxf(base, __shfl_xor_sync(0xffffffffu, base, offset));
+  const float weight = m == -INFINITY ? 0.f : fast_exp2(m - base);
+  float total = l * weight;
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) total += __shfl_xor_sync(0xffffffffu, total, offset);
+  float acc[D / 32];
+#pragma unroll
+  for (int c = 0; c < D / 32; ++c) acc[c] = 0.f;
+  for (int s = 0; s < args.splits; ++s) {
+    const float w = __shfl_sync(0xffffffffu, weight, s);
+    if (w == 0.f) continue;                           // its output row was never written
+    const float* src = args.partial_o + (s * slice + token_head) * D;
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c) acc[c] += src[c * 32 + lane] * w;
+  }
+  const float inv = total > 0.f ? 1.0f / total : 0.f;
+  __nv_bfloat16* dst = args.out + token_head * D;
+#pragma unroll
+  for (int c = 0; c < D / 32; ++c) dst[c * 32 + lane] = __float2bfloat16_rn(acc[c] * inv);
+}
+
 }  // namespace tcattn
 
 SHRIKE_API int shrike_attention_tc_available() { return 1; }
+
+// How many CTAs should share the keys of a query tile, for a batch of `num_tokens` new tokens whose
+// block tables are `max_blocks` pages wide: as many as fill the GPU twice, each with at least four
+// key tiles, at most 16; 1 when the query tiles alone fill it.  The scratch for splits > 1 is
+// splits * num_tokens * num_heads * (D + 2) floats.
+SHRIKE_API int shrike_attention_tc_portions_splits(int num_tokens, int num_heads, int max_blocks, int page_size) {
+  const int ctas = num_heads * ((num_tokens + tcattn::BM - 1) / tcattn::BM + 1);
+  const int key_tiles = (max_blocks * page_size + tcattn::BN - 1) / tcattn::BN;
+  int splits = (2 * shrike_device().sm_count) / (ctas < 1 ? 1 : ctas);
+  if (splits > key_tiles / 4) splits = key_tiles / 4;
+  if (splits > 16) splits = 16;
+  return splits < 1 ? 1 : splits;   // the kernels take up to 32
+}
+SHRIKE_API long long shrike_attention_tc_portions_scratch_floats(int num_tokens, int num_heads, int splits) {
+  return splits <= 1 ? 0 : static_cast<long long>(splits) * num_tokens * num_heads * (tcattn::D + 2);
+}
 
 // Portions (q_len > 1) of a batch; entries with q_len == 1 are skipped when skip_single.
 // q [tokens, heads * D] and out alike; caches [pages, page_size, kv heads, D]; page_size one of
@@ -379,11 +512,17 @@ SHRIKE_API int shrike_paged_attention_tc_portions(const void* q, const void* k_c
                                                   const int* ctx_len, int num_tokens, int num_seqs, int num_heads,
                                                   int num_kv_heads, int page_size, int num_pages, float scale,
                                                   int window, void* out, int skip_single, int max_q_len, int* status,
+                                                  int splits, float* scratch, int portion_tiles, const int* seq_of_token,
                                                   cudaStream_t stream) {
   using namespace tcattn;
   if (num_seqs <= 0 || num_tokens <= 0) return SHRIKE_OK;
+  if (splits < 1 || splits > 32 || (splits > 1 && (scratch == nullptr || seq_of_token == nullptr))) return SHRIKE_BAD_ARGUMENT;
+  // query tiles of the batch's portions: the caller's count, or what `num_tokens` tokens in
+  // `num_seqs` sequences can make at most
+  const int most_tiles = (num_tokens + BM - 1) / BM + num_seqs;
+  const int work = portion_tiles > 0 && portion_tiles < most_tiles ? portion_tiles : most_tiles;
   if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || max_blocks <= 0 || max_q_len < 1 ||
-      num_seqs > 65535 || (max_q_len + BM - 1) / BM > 65535 || !(page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64))
+      num_seqs > 65535 || (num_tokens + BM - 1) / BM + num_seqs > 65535 || !(page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64))
     return SHRIKE_BAD_ARGUMENT;
   static bool configured = false;
   if (!configured) {
@@ -412,18 +551,30 @@ SHRIKE_API int shrike_paged_attention_tc_portions(const void* q, const void* k_c
   args.window = window;
   args.skip_single = skip_single;
   args.scale_log2 = scale * LOG2E;
-  const dim3 grid(num_heads, num_seqs, (max_q_len + BM - 1) / BM);
-  const cudaError_t err = launch_dependent(portions_tc_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, map_q, map_k, map_v, args);
+  args.splits = splits;
+  args.num_tokens = num_tokens;
+  args.num_seqs = num_seqs;
+  args.seq_of_token = seq_of_token;
+  args.partial_o = splits > 1 ? scratch : nullptr;   // rows first (16-byte stores), then the (base, sum) pairs
+  args.partial_ml = splits > 1 ? scratch + static_cast<long long>(splits) * num_tokens * num_heads * D : nullptr;
+  cudaError_t err = launch_dependent(portions_tc_kernel, dim3(num_heads, work, splits), dim3(THREADS), SMEM_BYTES, stream,
+                                     map_q, map_k, map_v, args);
   if (err != cudaSuccess) return static_cast<int>(err);
+  if (splits > 1) {
+    err = launch_dependent(combine_portions_kernel, dim3(num_heads, (num_tokens + 7) / 8), dim3(256), 0, stream, args);
+    if (err != cudaSuccess) return static_cast<int>(err);
+  }
   return shrike_launch_status();
 }
 
 #else  // other head sizes: the mma.sync kernel serves them
 
 SHRIKE_API int shrike_attention_tc_available() { return 0; }
+SHRIKE_API int shrike_attention_tc_portions_splits(int, int, int, int) { return 1; }
+SHRIKE_API long long shrike_attention_tc_portions_scratch_floats(int, int, int) { return 0; }
 SHRIKE_API int shrike_paged_attention_tc_portions(const void*, const void*, const void*, const int*, int, const int*,
                                                   const int*, int, int, int, int, int, int, float, int, void*, int, int,
-                                                  int*, cudaStream_t) {
+                                                  int*, int, float*, int, const int*, cudaStream_t) {
   return SHRIKE_BAD_ARGUMENT;
 }
 

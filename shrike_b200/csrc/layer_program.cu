@@ -29,7 +29,7 @@ typedef int (*GemmTcGatedFn)(const void*, const void*, void*, int, int, int, int
 typedef int (*RopeKvWriteFn)(const float*, const float*, const int*, const float*, void*, void*, void*, const int*, void*, void*,
                              int, int, int, int, int, long long, int, long long, cudaStream_t);
 typedef int (*AttentionTcFn)(const void*, const void*, const void*, const int*, int, const int*, const int*, int, int, int, int,
-                             int, int, float, int, void*, int, int, int*, cudaStream_t);
+                             int, int, float, int, void*, int, int, int*, int, float*, int, const int*, cudaStream_t);
 typedef int (*AttentionBf16Fn)(const void*, const void*, const void*, const int*, int, const int*, const int*, int, int, int,
                                int, int, float, int, void*, int, int, int, int, int, float*, int*, int*, cudaStream_t);
 typedef int (*SiluMulFn)(const void*, void*, int, int, int, int, cudaStream_t);
@@ -90,11 +90,14 @@ struct ShrikeLayerStep {
   int use_library;                           // 1: the four products go to cuBLAS
   int gated_fused;                           // 1: gate_up and its activation are one tensor-core kernel
   int has_single, has_portions, tc_portions, attn_splits, attn_cluster;
+  int portion_splits;                        // key splits of the tensor-core portions kernel
+  int portion_tiles;                         // query tiles the batch's portions make (0: not known)
   const int* positions;
   const int* slots;
   const int* block_table;
   const int* q_start;
   const int* ctx_len;
+  const int* seq_of_token;
   float* resid;                              // [tokens][width] float32
   void* normed;                              // [tokens][width] bfloat16
   float* qkv;                                // [qkv_splits][tokens][(heads + 2 kv_heads) head_dim]
@@ -106,6 +109,7 @@ struct ShrikeLayerStep {
   float* down_out;                           // [down_splits][tokens][width]
   float* attn_scratch;
   int* attn_arrivals;
+  float* portion_scratch;
   int* status;
   void* workspace;                           // for cuBLAS
   long long workspace_bytes;
@@ -190,7 +194,7 @@ SHRIKE_API int shrike_decoder_layer(const ShrikeLayerFns* fns, const ShrikeLayer
   if (portions_left && c.tc_portions) {
     SHRIKE_TRY(fn.attention_tc_portions(c.q, l.read_keys, l.read_values, c.block_table, c.max_blocks, c.q_start, c.ctx_len, c.tokens, c.seqs,
                                         l.heads, l.kv_heads, l.page_size, l.num_pages, l.scale, l.window, c.attn_out, c.has_single,
-                                        c.max_q_len, c.status, stream));
+                                        c.max_q_len, c.status, c.portion_splits, c.portion_scratch, c.portion_tiles, c.seq_of_token, stream));
     portions_left = false;
   }
   if (c.has_single || portions_left)
@@ -218,7 +222,7 @@ SHRIKE_API int shrike_decoder_layer(const ShrikeLayerFns* fns, const ShrikeLayer
 SHRIKE_API int shrike_decoder_layer_launches(const ShrikeLayerStep* step) {
   const ShrikeLayerStep& c = *step;
   const int own = 3 /* two norms, rotary */ + (c.has_portions ? 1 : 0) + (c.has_single ? 1 : 0) + (c.gated_fused ? 0 : 1) +
-                  (c.use_library ? 0 : 4);
+                  (c.use_library ? 0 : 4) + (c.has_portions && c.tc_portions && c.portion_splits > 1 ? 1 : 0);
   const int library = c.use_library ? 4 : 0;
   return own | (library << 16);
 }

@@ -30,11 +30,14 @@ class KernelError(RuntimeError):
 class AttentionPlan:
     """What `CudaOps.attention_plan` decides for a batch shape."""
 
-    __slots__ = ("has_single", "has_portions", "tc_portions", "splits", "cluster", "scratch", "arrivals")
+    __slots__ = ("has_single", "has_portions", "tc_portions", "splits", "cluster", "scratch", "arrivals",
+                 "portion_splits", "portion_scratch")
 
-    def __init__(self, has_single, has_portions, tc_portions, splits, cluster, scratch, arrivals):
+    def __init__(self, has_single, has_portions, tc_portions, splits, cluster, scratch, arrivals,
+                 portion_splits=1, portion_scratch=None):
         self.has_single, self.has_portions, self.tc_portions = has_single, has_portions, tc_portions
         self.splits, self.cluster, self.scratch, self.arrivals = splits, cluster, scratch, arrivals
+        self.portion_splits, self.portion_scratch = portion_splits, portion_scratch   # the tensor-core portions kernel's key splits
 
 
 def _ptr(tensor):
@@ -66,6 +69,8 @@ def _dense(tensor, dtype, what):
 
 
 class CudaOps:
+    PORTION_SCRATCH_FLOATS = 32 << 20   # at most 128 MiB of partial rows for the split portions kernel
+
     def __init__(self, dtype: torch.dtype, device="cuda"):
         if dtype not in _DTYPE_CODE:
             raise KernelError(f"no kernels for {dtype}; bfloat16 and float32 are served")
@@ -95,6 +100,9 @@ class CudaOps:
         self._scratch = None     # partial results of split single-token attention
         self._sample_scratch = None  # per-slice winners of the sampling kernel
         self._arrivals = None    # per kv head: splits of single-token attention that have finished
+        self._portion_scratch = None   # partial rows of the portions kernel when a query tile's keys are split
+        self._portion_tiles = None
+        self.portion_splits = 0  # 0: the kernel library's rule; n: that many key splits for portions (tests)
         self.generation = 0      # grows when the scratch moves
         self._held_stream = None
         self._layer_program = None   # the native per-layer issue, built on first use
@@ -140,9 +148,13 @@ class CudaOps:
             lib.shrike_attention_bf16_resident_ctas.restype = _I
             lib.shrike_attention_tc_available.restype = _I
             lib.shrike_paged_attention_tc_portions.argtypes = (
-                [_P, _P, _P, _P, _I, _P, _P] + [_I] * 6 + [_F, _I, _P, _I, _I, _P, _P]
+                [_P, _P, _P, _P, _I, _P, _P] + [_I] * 6 + [_F, _I, _P, _I, _I, _P, _I, _P, _I, _P, _P]
             )
             lib.shrike_paged_attention_tc_portions.restype = _I
+            lib.shrike_attention_tc_portions_splits.argtypes = [_I, _I, _I, _I]
+            lib.shrike_attention_tc_portions_splits.restype = _I
+            lib.shrike_attention_tc_portions_scratch_floats.argtypes = [_I, _I, _I]
+            lib.shrike_attention_tc_portions_scratch_floats.restype = _LL
             self._attention[head_dim] = lib
         return lib
 
@@ -342,9 +354,10 @@ class CudaOps:
 
     def paged_attention(self, q, keys, values, block_table, q_start, ctx_len, seq_of_token,
                         num_heads, num_kv_heads, head_dim, scale, window, out,
-                        max_q_len=0, max_ctx_len=0, min_q_len=0):
+                        max_q_len=0, max_ctx_len=0, min_q_len=0, q_lens=None):
         """Attention of the batch's new tokens over the paged cache.  `max_q_len` and
-        `min_q_len` are the longest and shortest entry of the batch (0: not known)."""
+        `min_q_len` are the longest and shortest entry of the batch (0: not known); `q_lens`, every
+        entry's length (host list), lets the portions kernel launch exactly the CTAs it needs."""
         _dense(q, self.dtype, "q")
         _dense(keys, self.dtype, "key cache")
         _dense(values, self.dtype, "value cache")
@@ -361,14 +374,16 @@ class CudaOps:
                 _ptr(ctx_len), _ptr(seq_of_token), self.code, q.shape[0], num_heads, num_kv_heads,
                 page_size, num_pages, scale, window or 0, _ptr(out), self._stream()), "paged_attention")
             return
-        plan = self.attention_plan(num_heads, num_kv_heads, head_dim, num_seqs, max_blocks, page_size, max_q_len, min_q_len)
-        self.launches += plan.has_single + plan.has_portions
+        plan = self.attention_plan(num_heads, num_kv_heads, head_dim, num_seqs, max_blocks, page_size, max_q_len, min_q_len,
+                                   q.shape[0])
+        self.launches += plan.has_single + plan.has_portions + (1 if plan.portion_splits > 1 else 0)
         has_portions = plan.has_portions
         if plan.tc_portions:
             _check(lib.shrike_paged_attention_tc_portions(
                 _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), max_blocks, _ptr(q_start), _ptr(ctx_len),
                 q.shape[0], num_seqs, num_heads, num_kv_heads, page_size, num_pages, scale, window or 0, _ptr(out),
-                plan.has_single, max_q_len, _ptr(self.status), self._stream()), "paged_attention_tc_portions")
+                plan.has_single, max_q_len, _ptr(self.status), plan.portion_splits, _ptr(plan.portion_scratch),
+                self.portion_tiles(q_lens, plan.has_single), _ptr(seq_of_token), self._stream()), "paged_attention_tc_portions")
             has_portions = 0
             if not plan.has_single:
                 return
@@ -379,10 +394,22 @@ class CudaOps:
             _ptr(self.status), self._stream()),
             "paged_attention_bf16")
 
-    def attention_plan(self, num_heads, num_kv_heads, head_dim, num_seqs, max_blocks, page_size, max_q_len, min_q_len):
+    def portion_tiles(self, q_lens, skip_single) -> int:
+        """Query tiles (of 128 rows) that the batch's portions make; 0 when the lengths are not known."""
+        if q_lens is None:
+            return 0
+        held = self._portion_tiles
+        if held is not None and held[0] is q_lens and held[1] == skip_single:
+            return held[2]
+        tiles = sum(-(-q // 128) for q in q_lens if q > 1 or not skip_single)
+        self._portion_tiles = (q_lens, skip_single, tiles)
+        return tiles
+
+    def attention_plan(self, num_heads, num_kv_heads, head_dim, num_seqs, max_blocks, page_size, max_q_len, min_q_len,
+                       num_tokens=0):
         """How a bfloat16 batch's attention is cut: which kernels run (single tokens, portions, the
-        tensor-core form of the latter), the key splits and clusters of the single-token kernel and
-        its scratch.  A function of the batch's shape alone."""
+        tensor-core form of the latter), the key splits and clusters of the single-token kernel, the
+        key splits of the portions kernel, and their scratch.  A function of the batch's shape alone."""
         if max_q_len < 1:
             raise KernelError("paged_attention in bfloat16 needs max_q_len, the longest entry of the batch")
         lib = self._attention_lib(head_dim)
@@ -405,7 +432,20 @@ class CudaOps:
             scratch, arrivals = self._scratch, self._arrivals
         tc_portions = bool(has_portions and self.tensor_core_attention and lib.shrike_attention_tc_available()
                            and page_size in (8, 16, 32, 64))
-        return AttentionPlan(int(has_single), int(has_portions), int(tc_portions), splits, cluster, scratch, arrivals)
+        portion_splits, portion_scratch = 1, None
+        if tc_portions and num_tokens > 0:
+            portion_splits = self.portion_splits or lib.shrike_attention_tc_portions_splits(num_tokens, num_heads, max_blocks, page_size)
+            need = lib.shrike_attention_tc_portions_scratch_floats(num_tokens, num_heads, portion_splits)
+            if need > self.PORTION_SCRATCH_FLOATS:   # bound the scratch: fewer splits, never a refusal
+                portion_splits = max(1, portion_splits * self.PORTION_SCRATCH_FLOATS // need)
+                need = lib.shrike_attention_tc_portions_scratch_floats(num_tokens, num_heads, portion_splits)
+            if portion_splits > 1:
+                if self._portion_scratch is None or self._portion_scratch.numel() < need:
+                    self._portion_scratch = torch.empty(max(need, 1 << 22), dtype=torch.float32, device=self.device)
+                    self.generation += 1
+                portion_scratch = self._portion_scratch
+        return AttentionPlan(int(has_single), int(has_portions), int(tc_portions), splits, cluster, scratch, arrivals,
+                             portion_splits, portion_scratch)
 
     @staticmethod
     def single_token_splits(tiles: int, groups: int, resident: int):

@@ -50,9 +50,11 @@ class LayerStep(_c.Structure):
 
     _fields_ = (
         [(n, _I) for n in ("tokens", "seqs", "max_blocks", "max_q_len", "qkv_splits", "o_splits", "down_splits", "use_library",
-                           "gated_fused", "has_single", "has_portions", "tc_portions", "attn_splits", "attn_cluster")]
-        + [(n, _P) for n in ("positions", "slots", "block_table", "q_start", "ctx_len", "resid", "normed", "qkv", "q", "attn_out",
-                             "o_out", "gate_up", "act", "down_out", "attn_scratch", "attn_arrivals", "status", "workspace")]
+                           "gated_fused", "has_single", "has_portions", "tc_portions", "attn_splits", "attn_cluster",
+                           "portion_splits", "portion_tiles")]
+        + [(n, _P) for n in ("positions", "slots", "block_table", "q_start", "ctx_len", "seq_of_token", "resid", "normed", "qkv", "q", "attn_out",
+                             "o_out", "gate_up", "act", "down_out", "attn_scratch", "attn_arrivals", "portion_scratch", "status",
+                             "workspace")]
         + [("workspace_bytes", _LL)]
     )
 
@@ -174,7 +176,11 @@ class LayerProgram:
         step.down_splits = 1 if library else splits_of(n, width, inter)
         step.gated_fused = int(bool(feed_forward.run) and not library and (2 * inter) % 32 == 0)
         plan = ops.attention_plan(spec.num_heads, spec.num_kv_heads, spec.head_dim, ctx.num_seqs, view.max_blocks, page_size,
-                                  ctx.max_q_len, ctx.min_q_len)
+                                  ctx.max_q_len, ctx.min_q_len, n)
+        step.portion_splits = plan.portion_splits
+        step.portion_tiles = ops.portion_tiles(ctx.q_lens, plan.has_single)
+        step.seq_of_token = ctx.seq_of_token.data_ptr()
+        step.portion_scratch = None if plan.portion_scratch is None else plan.portion_scratch.data_ptr()
         step.has_single, step.has_portions, step.tc_portions = plan.has_single, plan.has_portions, plan.tc_portions
         step.attn_splits, step.attn_cluster = plan.splits, plan.cluster
         step.attn_scratch = None if plan.scratch is None else plan.scratch.data_ptr()

@@ -99,7 +99,7 @@ class PagedAttention:
         ops.paged_attention(
             q, keys, values, view.block_table, ctx.q_start, ctx.ctx_len, ctx.seq_of_token,
             spec.num_heads, spec.num_kv_heads, spec.head_dim, spec.scale, spec.window, attn,
-            max_q_len=ctx.max_q_len, max_ctx_len=ctx.max_ctx_len, min_q_len=ctx.min_q_len,
+            max_q_len=ctx.max_q_len, max_ctx_len=ctx.max_ctx_len, min_q_len=ctx.min_q_len, q_lens=ctx.q_lens,
         )
         delta = rt.buffer("mixer_delta", (n, spec.width), torch.float32)
         return ops.linear(attn, self.w_o, delta, bias=self.b_o, allow_partials=True)

@@ -93,7 +93,7 @@ class EmulatedOps:
 
     def paged_attention(self, q, keys, values, block_table, q_start, ctx_len, seq_of_token,
                         num_heads, num_kv_heads, head_dim, scale, window, out,
-                        max_q_len=0, max_ctx_len=0, min_q_len=0):
+                        max_q_len=0, max_ctx_len=0, min_q_len=0, q_lens=None):
         page = keys.shape[1]
         group = num_heads // num_kv_heads
         n = q.shape[0]

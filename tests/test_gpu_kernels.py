@@ -358,7 +358,8 @@ def run_attention(ops, case, heads, kv_heads, dim, window, q_lens, ctx_lens):
     out = torch.empty_like(case["q"])
     ops.paged_attention(case["q"], case["keys"], case["values"], case["table"], case["q_start"], case["ctx_len"],
                         case["seq_of"], heads, kv_heads, dim, dim ** -0.5, window, out,
-                        max_q_len=max(q_lens), max_ctx_len=max(ctx_lens))
+                        max_q_len=max(q_lens), max_ctx_len=max(ctx_lens), min_q_len=min(q_lens),
+                        q_lens=list(q_lens) if sum(ctx_lens) % 2 else None)   # with and without the exact CTA count
     want = []
     for (q, k, v), q_len in zip(case["seqs"], q_lens):   # the oracle runs on the GPU in float64: plain torch all the same
         want.append(pm.causal_attention(q[len(q) - q_len:].double().to(DEV), k.double().to(DEV), v.double().to(DEV), window))
@@ -421,13 +422,17 @@ SERVED = {
 
 
 @pytest.mark.parametrize("name", list(SERVED))
+@pytest.mark.parametrize("splits", [0, 1, 3, 7])
 @pytest.mark.parametrize("heads,kv_heads,dim,page", [(28, 4, 128, 16), (14, 2, 64, 16), (12, 2, 128, 32)])
-def test_portions_attention_at_served_lengths(name, heads, kv_heads, dim, page):
+def test_portions_attention_at_served_lengths(name, heads, kv_heads, dim, page, splits):
     """The tensor-core kernel for portions over walks of up to 64 key tiles (its rescaling of the
     running sum, its look-ahead in the block table and its first and last tile only matter on
-    long walks), against the plain formula in float64."""
+    long walks), against the plain formula in float64; with the keys of a query tile walked by one
+    CTA, shared by as many as the library's rule says (0), or by 3 or 7 (splits that see no key,
+    and rows whose keys all lie in other splits, among them)."""
     ctx_lens, q_lens, window = SERVED[name]
     ops = cuda_ops(torch.bfloat16)
+    ops.portion_splits = splits
     assert ops._attention_lib(dim).shrike_attention_tc_available()
     case = paged_case(torch.bfloat16, heads, kv_heads, dim, page, ctx_lens, q_lens, seed=11)
     if window is not None:
@@ -435,6 +440,19 @@ def test_portions_attention_at_served_lengths(name, heads, kv_heads, dim, page):
     got, want = run_attention(ops, case, heads, kv_heads, dim, window, q_lens, ctx_lens)
     close(got, want, 2e-2, 0, f"{name} heads {heads}/{kv_heads} D {dim} page {page}")
     ops.check_status()
+
+
+def test_a_portion_beside_decoding_requests_is_split_over_the_gpu():
+    """The rule: 492 new tokens of 12 heads over block tables of 2,048 keys would occupy 60 CTAs;
+    their keys are shared out until the GPU is filled twice, no split with fewer than four key
+    tiles.  A whole 2,048-token prompt of 28 heads fills the GPU by itself: no split."""
+    ops = cuda_ops(torch.bfloat16)
+    lib = ops._attention_lib(128)
+    assert lib.shrike_attention_tc_portions_splits(512, 12, 128, 16) == 4
+    assert lib.shrike_attention_tc_portions_splits(2048, 28, 128, 16) == 1
+    assert lib.shrike_attention_tc_portions_splits(64, 2, 16, 16) == 1        # four key tiles in all
+    assert lib.shrike_attention_tc_portions_splits(64, 2, 4096, 16) == 16     # never more than 16
+    assert lib.shrike_attention_tc_portions_scratch_floats(512, 12, 4) == 4 * 512 * 12 * 130
 
 
 def test_portions_attention_finds_a_far_key_among_thousands():
