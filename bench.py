@@ -539,8 +539,8 @@ def run_case(args) -> dict:
     elif args.case in ("attention_single", "attention_portions"):
         single = args.case == "attention_single"
         seqs = tokens if single else 1
-        ctx_len = CONTEXT if single else PREFILL_TOKENS
-        q_len = 1 if single else PREFILL_TOKENS
+        ctx_len = CONTEXT if single else args.prefill_tokens
+        q_len = 1 if single else args.prefill_tokens
         blocks = -(-ctx_len // BLOCK_SIZE)
         pages = seqs * blocks + 8
         keys = torch.randn(pages, BLOCK_SIZE, kv, d, device=dev, dtype=torch.bfloat16)
@@ -556,7 +556,7 @@ def run_case(args) -> dict:
         for _ in range(6):
             start.record()
             ops.paged_attention(q, keys, values, table, q_start, ctx, seq_of, heads, kv, d, d ** -0.5, None, out,
-                                max_q_len=q_len, min_q_len=q_len)
+                                max_q_len=q_len, min_q_len=q_len, q_lens=[q_len] * seqs)
             stop.record()
             torch.cuda.synchronize()
             times.append(start.elapsed_time(stop) * 1e3)
@@ -690,6 +690,8 @@ def main():
     parser.add_argument("--workload", default="decode", choices=["decode", "mixed"],
                         help="decode: the headline line; mixed: 64 requests through the scheduler at 1.5B shape")
     parser.add_argument("--num-blocks", type=int, default=0, help="cache pages for --workload mixed (few pages force preemption)")
+    parser.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
+                        help="prompt length of --case attention_portions")
     parser.add_argument("--case", default=None,
                         help="run a small single-kernel workload instead (for profiling): gemm_gate_up, gemm_down, "
                              "gemm_qkv, attention_single, attention_portions; --batch gives tokens / sequences.  timeline: per-kernel "

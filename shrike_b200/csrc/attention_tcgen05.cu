@@ -1,31 +1,39 @@
 // Paged causal attention for portions (q_len > 1) in bfloat16 on the fifth-generation
-// tensor cores.  One CTA owns 128 queries of one head of one sequence and walks the keys
-// 64 at a time:
-//   S = Q K^T      tcgen05.mma, M 128 x N 64 x K head size, accumulator in tensor memory
-//   softmax        four warps, ONE THREAD PER QUERY ROW: the row of S comes out of tensor
-//                  memory with tcgen05.ld, scale, mask, running maximum and sum in float32,
-//                  probabilities go to shared memory as bfloat16 in the MMA's swizzled layout
-//   O += P V       tcgen05.mma, M 128 x N head size x K 64; O stays in tensor memory across
-//                  tiles and is rescaled there (tcgen05.ld / st) when a row's maximum moved
-// Keys and values arrive by TMA, one box per page and 64-element half of the head (the
-// block table is read by the producer thread), double-buffered; the query tile by TMA once.
+// tensor cores.  One CTA owns 256 query rows of one head of one sequence, as two chains of
+// 128 rows, and walks the keys 128 at a time:
+//   S_c = Q_c K^T   tcgen05.mma, M 128 x N 128 x K head size, accumulator in tensor memory
+//   softmax         four warps per chain, ONE THREAD PER QUERY ROW: the row of S comes out of
+//                   tensor memory with tcgen05.ld, scale, mask, running maximum and sum in
+//                   float32; the probabilities go back INTO tensor memory as packed bfloat16
+//                   over the first 64 columns of the chain's own S (tcgen05.st)
+//   O_c += P_c V    tcgen05.mma with its A operand in tensor memory, M 128 x N head size x K 128;
+//                   O stays in tensor memory across tiles and is rescaled there when a row's
+//                   maximum moved by more than 2^8
+// The tensor pipe runs its instructions in order: S of the next tile, issued after PV, cannot
+// overwrite P before PV has read it, and a softmax thread that sees S of tile i + 1 knows PV of
+// tile i is done, so O may be rescaled then without another wait.  While one chain's softmax
+// runs, the tensor pipe works for the other; both chains read the same key and value stages (two
+// each), so a tile is loaded once for 256 rows.  The later chain sees up to one key tile more than
+// the earlier one; a chain without rows (a sequence's last 128 or fewer) has no tiles.
+// Keys and values arrive by TMA, one box per page and 64-element half of the head (the block
+// table is read by the producer warp, three tiles ahead), the two query tiles by TMA once.
 // Roles: warp 0 TMA producer, warp 1 MMA issuer (one elected lane), warps 2..5 softmax and
-// epilogue.  S has two buffers in tensor memory: the scores of tile i + 1 are computed while
-// the softmax warps work on tile i, and their exponentials while PV of tile i still runs;
-// only writing P (one buffer) and rescaling O wait for that PV (barrier pv_done).
-// Keys and values have stages and barriers of their own: a key stage is free again as soon
-// as its S is computed, long before the value stage of the same tile, so the keys of the tile
-// after next are already on their way while this tile's softmax runs.
-// tcgen05.commit arrives on mbarriers: s_full[b] and k_free after S into buffer b, v_free and
-// pv_done after PV.
+// epilogue of chain 0, warps 6..9 of chain 1.  tcgen05.commit arrives on mbarriers: s_full[c] after
+// S of chain c, k_free / v_free after the last chain's use of a stage, pv_done[c] after a chain's
+// last PV.  All of tensor memory (2 x (128 + D) <= 512 columns) and 96 + D KiB of shared memory:
+// one CTA per SM.
 // Mask and window as everywhere: a query at position p sees keys [max(0, p - window + 1), p].
 // Rows of a page beyond the context may hold anything (a page is reused without clearing):
 // scores are masked by selection, and the value rows beyond the context are zeroed in shared
 // memory before PV, because 0 * NaN would not be 0.
-// Few query tiles and many keys (a portion of a long prompt beside decoding requests) would leave
-// most of the GPU idle: the keys of a query tile are then split across `splits` CTAs, each of which
-// leaves its unnormalised output rows with their (base, sum) in scratch, and a second small kernel
-// adds the splits up (combine_portions_kernel).
+// The grid holds exactly the query tiles the batch's portions make (find_work).  Few query tiles
+// and many keys (a portion of a long prompt beside decoding requests) would leave most of the GPU
+// idle: the keys of a query tile are then split across `splits` CTAs, each of which leaves its
+// unnormalised output rows with their (base, sum) in scratch, and a second small kernel adds the
+// splits up (combine_portions_kernel).
+// An earlier form (one query tile per CTA, 64 keys a step, probabilities through shared memory, two
+// CTAs per SM) was bound by the hand-overs between its roles; this one does twice the work per
+// hand-over: 5 to 14 % faster from 512-token portions to 8,192-token prompts.
 // Every wait is bounded (status word, CTA-wide abort flag); no TMA load uses multicast.
 // Tensor memory is allocated BEFORE dependents are allowed to start, so that a dependent
 // kernel that also wants tensor memory cannot starve a CTA of this one it is waiting for.
@@ -44,26 +52,13 @@ namespace tcattn {
 using namespace bw;
 
 constexpr int D = SHRIKE_HEAD_DIM;
-constexpr int BM = 128, BN = 64;
+constexpr int BM = 128;                         // query rows of one chain
 constexpr int HALVES = D / 64;                 // 64-element groups of the head size
-constexpr int THREADS = 192;
-constexpr int STAGES = 2;
-constexpr int Q_HALF = BM * 128, KV_HALF = BN * 128;          // bytes of one 64-element-wide sub-tile
-constexpr int Q_BYTES = HALVES * Q_HALF, KV_BYTES = HALVES * KV_HALF, P_BYTES = BM * BN * 2;
-constexpr unsigned TMEM_COLS = 256;                            // S: 2 x 64 columns, O: D columns from column 128
+constexpr int Q_HALF = BM * 128;               // bytes of one 64-element-wide sub-tile of a query tile
+constexpr int Q_BYTES = HALVES * Q_HALF;
 constexpr float LOG2E = 1.4426950408889634f;
 
 enum : int { ERR_PRODUCER = 11, ERR_MMA = 12, ERR_SOFTMAX = 13, ERR_DRAIN = 14, ERR_ALIGNMENT = 15 };
-
-struct Shared {
-  unsigned long long q_full, s_full[2], p_full, pv_done;
-  unsigned long long k_full[STAGES], k_free[STAGES], v_full[STAGES], v_free[STAGES];
-  unsigned tmem_base;
-  volatile int abort;
-};
-// two CTAs must fit an SM (233,472 bytes, 1 KiB reserved per CTA): no slack for alignment is added; the
-// dynamic window starts 1 KiB-aligned (declared so below), and the kernel checks that it does.
-constexpr size_t SMEM_BYTES = Q_BYTES + STAGES * 2 * KV_BYTES + P_BYTES + sizeof(Shared);
 
 // 2^x on the special-function unit; -inf gives 0.
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -89,9 +84,9 @@ struct Args {
 };
 
 // Which (sequence, query tile) a CTA with work index `work` owns: sequences in order, each with its
-// query tiles of BM rows, the last (longest to walk) first; sequences of one token own none when
+// query tiles of `rows` rows, the last (longest to walk) first; sequences of one token own none when
 // skip_single.  Every lane of the calling warp gets the answer; tile_start < 0: no such work.
-__device__ __forceinline__ void find_work(const Args& args, int work, int& seq_out, int& tile_start_out) {
+__device__ __forceinline__ void find_work(const Args& args, int work, int rows, int& seq_out, int& tile_start_out) {
   const int lane = threadIdx.x & 31;
   int before = 0;
   seq_out = -1;
@@ -101,7 +96,7 @@ __device__ __forceinline__ void find_work(const Args& args, int work, int& seq_o
     int tiles = 0;
     if (s < args.num_seqs) {
       const int q_len = args.q_start[s + 1] - args.q_start[s];
-      tiles = (q_len == 1 && args.skip_single) ? 0 : (q_len + BM - 1) / BM;
+      tiles = (q_len == 1 && args.skip_single) ? 0 : (q_len + rows - 1) / rows;
     }
     int inclusive = tiles;
 #pragma unroll
@@ -117,51 +112,69 @@ __device__ __forceinline__ void find_work(const Args& args, int work, int& seq_o
       const int first_of_owner = __shfl_sync(0xffffffffu, first, src);
       const int tiles_of_owner = __shfl_sync(0xffffffffu, tiles, src);
       seq_out = base + src;
-      tile_start_out = (tiles_of_owner - 1 - (work - first_of_owner)) * BM;
+      tile_start_out = (tiles_of_owner - 1 - (work - first_of_owner)) * rows;
       return;
     }
     before += __shfl_sync(0xffffffffu, inclusive, 31);
   }
 }
 
-__global__ void __launch_bounds__(THREADS, 2)
-portions_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                   const __grid_constant__ CUtensorMap map_v, const Args args) {
+namespace pair {
+constexpr int ROWS = 2 * BM;                  // query rows per CTA
+constexpr int KEYS = 128;                     // keys per step
+constexpr int PSTAGES = 2;
+constexpr int PTHREADS = 64 + 2 * 128;
+constexpr int KV_TILE_HALF = KEYS * 128;      // bytes of one 64-element-wide sub-tile of a key (or value) tile
+constexpr int KV_TILE = HALVES * KV_TILE_HALF;
+constexpr unsigned CHAIN_COLS = 256;          // S at +0 (P over its first 64 columns), O at +128
+constexpr unsigned PAIR_TMEM_COLS = 512;
+
+struct PairShared {
+  unsigned long long q_full, s_full[2], p_full[2], pv_done[2];
+  unsigned long long k_full[PSTAGES], k_free[PSTAGES], v_full[PSTAGES], v_free[PSTAGES];
+  unsigned tmem_base;
+  volatile int abort;
+};
+constexpr size_t PAIR_SMEM = 2 * Q_BYTES + PSTAGES * 2 * KV_TILE + sizeof(PairShared);
+
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (probabilities, bfloat16 packed two to a column, one
+// row per lane) comes from tensor memory.
+__device__ __forceinline__ void umma_a_in_tmem(unsigned tmem_d, unsigned tmem_a, unsigned long long b, unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+__global__ void __launch_bounds__(PTHREADS, 1)
+portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                     const __grid_constant__ CUtensorMap map_v, const Args args) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  // CTAs are handed out x first: the heads of a group, which read the same keys and values, run
-  // side by side; within a sequence the longest query tiles go first (a causal tile's work grows
-  // with its position).
-  // CTAs are numbered (head, work, split): `work` counts the query tiles of the batch's portions
-  // (find_work), so no CTA is spent on a sequence of one token or on rows a sequence does not have.
   const int head = blockIdx.x, split = blockIdx.z;
   int seq, tile_start;
-  find_work(args, blockIdx.y, seq, tile_start);                 // metadata: written before the step's kernels
-  if (tile_start < 0) {
+  find_work(args, blockIdx.y, ROWS, seq, tile_start);           // metadata: written before the step's kernels
+  if (tile_start < 0 || (smem_u32(smem_raw) & 1023u)) {
+    if (tile_start >= 0 && threadIdx.x == 0 && args.status != nullptr) *args.status = ERR_ALIGNMENT;
     let_dependents_start();
     wait_for_previous();
     return;
   }
   const int start = args.q_start[seq];
   const int q_len = args.q_start[seq + 1] - start;
-  if (smem_u32(smem_raw) & 1023u) {   // the swizzled tiles need 1 KiB alignment
-    if (threadIdx.x == 0 && args.status != nullptr) *args.status = ERR_ALIGNMENT;
-    let_dependents_start();
-    wait_for_previous();
-    return;
-  }
-  unsigned char* q_tile = smem_raw;
-  unsigned char* kv_tiles = q_tile + Q_BYTES;                   // [STAGES][K | V]
-  unsigned char* p_tile = kv_tiles + STAGES * 2 * KV_BYTES;
-  Shared* sh = reinterpret_cast<Shared*>(p_tile + P_BYTES);
+  unsigned char* q_tiles = smem_raw;                             // [2 chains][Q_BYTES]
+  unsigned char* k_tiles = q_tiles + 2 * Q_BYTES;                // [PSTAGES][KV_TILE]
+  unsigned char* v_tiles = k_tiles + PSTAGES * KV_TILE;          // [PSTAGES][KV_TILE]
+  PairShared* sh = reinterpret_cast<PairShared*>(v_tiles + PSTAGES * KV_TILE);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     mbar_init(&sh->q_full, 1);
-    mbar_init(&sh->s_full[0], 1);
-    mbar_init(&sh->s_full[1], 1);
-    mbar_init(&sh->p_full, 128);
-    mbar_init(&sh->pv_done, 1);
-    for (int s = 0; s < STAGES; ++s) {
+    for (int c = 0; c < 2; ++c) {
+      mbar_init(&sh->s_full[c], 1);
+      mbar_init(&sh->p_full[c], 128);
+      mbar_init(&sh->pv_done[c], 1);
+    }
+    for (int s = 0; s < PSTAGES; ++s) {
       mbar_init(&sh->k_full[s], 1);
       mbar_init(&sh->k_free[s], 1);
       mbar_init(&sh->v_full[s], 1);
@@ -170,41 +183,45 @@ portions_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     sh->abort = 0;
     mbar_init_fence();
   }
-  if (warp == 1) tmem_alloc(&sh->tmem_base, TMEM_COLS);
+  if (warp == 1) tmem_alloc(&sh->tmem_base, PAIR_TMEM_COLS);
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
   let_dependents_start();
   wait_for_previous();   // the query and the newest keys come from the kernel before this one
 
-  const unsigned tmem_s = sh->tmem_base, tmem_o = sh->tmem_base + 2 * BN;   // S buffer b at columns b * 64
   const int pos0 = args.ctx_len[seq] - q_len;                   // position of the first new token
   const int kv_head = head / (args.num_heads / args.num_kv_heads);
-  const int rows_here = min(BM, q_len - tile_start);
-  const int lo = args.window > 0 ? max(0, pos0 + tile_start - args.window + 1) : 0;
-  const int hi = pos0 + tile_start + rows_here - 1;             // last key any row of this tile sees
-  const int tile_hi = hi / BN;
-  // this CTA's share of the key tiles [lo / BN, tile_hi]: `per` tiles from tile_lo on (none: an empty split)
-  const int all_tiles = tile_hi - lo / BN + 1;
+  // chain c owns rows tile_start + 128 c ...; rows_c <= 0: the chain has none
+  const int rows_0 = min(BM, q_len - tile_start), rows_1 = min(BM, q_len - tile_start - BM);
+  const int lo = args.window > 0 ? max(0, pos0 + tile_start - args.window + 1) : 0;   // first key any row sees
+  const int hi_0 = pos0 + tile_start + rows_0 - 1;              // last key chain 0 sees
+  const int hi_1 = rows_1 > 0 ? hi_0 + rows_1 : -1;
+  const int hi = max(hi_0, hi_1);
+  const int tile_hi = hi / KEYS;
+  const int all_tiles = tile_hi - lo / KEYS + 1;
   const int per = (all_tiles + args.splits - 1) / args.splits;
-  const int tile_lo = lo / BN + split * per;
-  const int num_tiles = max(0, min(tile_hi, tile_lo + per - 1) - tile_lo + 1);
+  const int tile_lo = lo / KEYS + split * per;                  // this CTA's share: tiles tile_lo ... (none: an empty split)
+  const int last_tile = min(tile_hi, tile_lo + per - 1);
+  const int count_0 = max(0, min(last_tile, hi_0 / KEYS) - tile_lo + 1);
+  const int count_1 = rows_1 > 0 ? max(0, min(last_tile, hi_1 / KEYS) - tile_lo + 1) : 0;
+  const int num_tiles = max(count_0, count_1);
 
   if (warp == 0) {
-    // The whole warp runs the loop: lane 0 waits for the stage and arms its barrier, then lane
-    // pg looks up page pg of the tile and issues that page's four boxes (K and V, both halves).
+    // lane 0 waits for the stage and arms its barrier, then lane pg looks up page pg of the tile and
+    // issues that page's boxes (K and V, every 64-element half)
     const int* table = args.block_table + static_cast<size_t>(seq) * args.max_blocks;
-    const int pages_per_tile = BN / args.page_size;
+    const int pages_per_tile = KEYS / args.page_size;
     const int nowhere = args.num_pages * args.page_size;      // a row coordinate outside the cache: reads zeros
     if (lane == 0 && num_tiles > 0) {
-      mbar_expect_tx(&sh->q_full, Q_BYTES);
-      for (int h = 0; h < HALVES; ++h) tma_load_2d(q_tile + h * Q_HALF, &map_q, &sh->q_full, head * D + h * 64, start + tile_start);
+      mbar_expect_tx(&sh->q_full, 2 * Q_BYTES);
+      for (int c = 0; c < 2; ++c)
+        for (int h = 0; h < HALVES; ++h)
+          tma_load_2d(q_tiles + c * Q_BYTES + h * Q_HALF, &map_q, &sh->q_full, head * D + h * 64, start + tile_start + c * BM);
     }
-    // page ids are looked up three tiles ahead of their use, so that the table's latency never
-    // sits between a stage becoming free and its copy being issued
     auto look_up = [&](int i) -> int {
       if (lane >= pages_per_tile || i >= num_tiles) return -1;
-      const int key0 = (tile_lo + i) * BN + lane * args.page_size;
+      const int key0 = (tile_lo + i) * KEYS + lane * args.page_size;
       const int block = key0 / args.page_size;
       const int page = (key0 <= hi && block < args.max_blocks) ? table[block] : -1;
       return page >= args.num_pages ? -1 : page;
@@ -212,40 +229,40 @@ portions_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     int page = look_up(0), page_1 = look_up(1), page_2 = look_up(2);
     int issued = 0;
     for (int i = 0; i < num_tiles; ++i) {
-      const int s = i % STAGES;
-      const unsigned phase = (i / STAGES) & 1;
+      const int s = i % PSTAGES;
+      const unsigned phase = (i / PSTAGES) & 1;
       const int page_3 = look_up(i + 3);
-      unsigned char* k_tile = kv_tiles + s * 2 * KV_BYTES;
-      unsigned char* v_tile = k_tile + KV_BYTES;
+      unsigned char* k_tile = k_tiles + s * KV_TILE;
+      unsigned char* v_tile = v_tiles + s * KV_TILE;
       const int y = page < 0 ? nowhere : page * args.page_size;
       const int at = lane * args.page_size * 128;
       int ok = 1;
       if (lane == 0) {
         ok = mbar_wait(&sh->k_free[s], phase ^ 1, &sh->abort, args.status, ERR_PRODUCER) ? 1 : 0;
-        if (ok) mbar_expect_tx(&sh->k_full[s], KV_BYTES);
+        if (ok) mbar_expect_tx(&sh->k_full[s], KV_TILE);
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       if (lane < pages_per_tile)
-        for (int h = 0; h < HALVES; ++h) tma_load_2d(k_tile + h * KV_HALF + at, &map_k, &sh->k_full[s], kv_head * D + h * 64, y);
+        for (int h = 0; h < HALVES; ++h) tma_load_2d(k_tile + h * KV_TILE_HALF + at, &map_k, &sh->k_full[s], kv_head * D + h * 64, y);
       if (lane == 0) {
         ok = mbar_wait(&sh->v_free[s], phase ^ 1, &sh->abort, args.status, ERR_PRODUCER) ? 1 : 0;
-        if (ok) mbar_expect_tx(&sh->v_full[s], KV_BYTES);
+        if (ok) mbar_expect_tx(&sh->v_full[s], KV_TILE);
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       if (lane < pages_per_tile)
-        for (int h = 0; h < HALVES; ++h) tma_load_2d(v_tile + h * KV_HALF + at, &map_v, &sh->v_full[s], kv_head * D + h * 64, y);
+        for (int h = 0; h < HALVES; ++h) tma_load_2d(v_tile + h * KV_TILE_HALF + at, &map_v, &sh->v_full[s], kv_head * D + h * 64, y);
       issued = i + 1;
       page = page_1;
       page_1 = page_2;
       page_2 = page_3;
     }
     if (lane == 0 && sh->abort) {   // copies may still be in flight: wait for the stages armed last
-      for (int i = max(0, issued - STAGES); i < issued; ++i) {
+      for (int i = max(0, issued - PSTAGES); i < issued; ++i) {
         bool landed = false;
         for (unsigned tries = 0; tries < WAIT_LIMIT && !landed; ++tries)
-          landed = mbar_try_wait(&sh->k_full[i % STAGES], (i / STAGES) & 1) && mbar_try_wait(&sh->v_full[i % STAGES], (i / STAGES) & 1);
+          landed = mbar_try_wait(&sh->k_full[i % PSTAGES], (i / PSTAGES) & 1) && mbar_try_wait(&sh->v_full[i % PSTAGES], (i / PSTAGES) & 1);
         if (!landed && args.status != nullptr) *args.status = ERR_DRAIN;
       }
       bool landed = num_tiles <= 0;
@@ -253,155 +270,166 @@ portions_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const unsigned idesc_s = instruction_descriptor(BM, BN, false);
+      const unsigned idesc_s = instruction_descriptor(BM, KEYS, false);
       const unsigned idesc_o = instruction_descriptor(BM, D, true);
-      const unsigned q_addr = smem_u32(q_tile), p_addr = smem_u32(p_tile);
-      // S of tile i into buffer i mod 2; issued one tile ahead of the softmax
-      auto issue_scores = [&](int i) -> bool {
-        const int st = i % STAGES;
-        if (!mbar_wait(&sh->k_full[st], (i / STAGES) & 1, &sh->abort, args.status, ERR_MMA)) return false;
-        fence_after_sync();
-        const unsigned k_addr = smem_u32(kv_tiles + st * 2 * KV_BYTES);
+      const unsigned tmem = sh->tmem_base;
+      const int count[2] = {count_0, count_1};
+      // S of chain c for tile i; the chain that needs a key stage last hands it back
+      auto issue_scores = [&](int c, int i) {
+        const unsigned q_addr = smem_u32(q_tiles + c * Q_BYTES), k_addr = smem_u32(k_tiles + (i % PSTAGES) * KV_TILE);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const unsigned off = (kk / 4) * Q_HALF + (kk % 4) * 32, koff = (kk / 4) * KV_HALF + (kk % 4) * 32;
-          umma(tmem_s + (i & 1) * BN, smem_descriptor(q_addr + off), smem_descriptor(k_addr + koff), idesc_s, kk > 0 ? 1u : 0u);
+          const unsigned off = (kk / 4) * Q_HALF + (kk % 4) * 32, koff = (kk / 4) * KV_TILE_HALF + (kk % 4) * 32;
+          umma(tmem + c * CHAIN_COLS, smem_descriptor(q_addr + off), smem_descriptor(k_addr + koff), idesc_s, kk > 0 ? 1u : 0u);
         }
-        umma_commit(&sh->s_full[i & 1]);
-        umma_commit(&sh->k_free[st]);
-        return true;
+        umma_commit(&sh->s_full[c]);
+        if (c == 1 || i >= count_1) umma_commit(&sh->k_free[i % PSTAGES]);
       };
       bool ok = num_tiles > 0 && mbar_wait(&sh->q_full, 0, &sh->abort, args.status, ERR_MMA);
-      if (ok) ok = issue_scores(0);
-      for (int i = 0; i < num_tiles && ok; ++i) {
-        // buffer (i + 1) mod 2 was last read for tile i - 1, whose P has arrived: it is free
-        if (i + 1 < num_tiles) ok = issue_scores(i + 1);
-        if (!ok) break;
-        ok = mbar_wait(&sh->v_full[i % STAGES], (i / STAGES) & 1, &sh->abort, args.status, ERR_MMA) &&
-             mbar_wait(&sh->p_full, i & 1, &sh->abort, args.status, ERR_MMA);
-        if (!ok) break;
+      if (ok) ok = mbar_wait(&sh->k_full[0], 0, &sh->abort, args.status, ERR_MMA);
+      if (ok) {
         fence_after_sync();
-        const unsigned v_addr = smem_u32(kv_tiles + (i % STAGES) * 2 * KV_BYTES) + KV_BYTES;
+        if (count_0 > 0) issue_scores(0, 0);
+        if (count_1 > 0) issue_scores(1, 0);
+      }
+      for (int i = 0; i < num_tiles && ok; ++i) {
+        const int st = i % PSTAGES;
+        bool keys_checked = false;
+        for (int c = 0; c < 2 && ok; ++c) {
+          if (i >= count[c]) continue;
+          if (c == 0 || i >= count_0)   // the first chain of this tile waits for the values
+            ok = mbar_wait(&sh->v_full[st], (i / PSTAGES) & 1, &sh->abort, args.status, ERR_MMA);
+          if (ok) ok = mbar_wait(&sh->p_full[c], i & 1, &sh->abort, args.status, ERR_MMA);
+          if (!ok) break;
+          fence_after_sync();
+          const unsigned v_addr = smem_u32(v_tiles + st * KV_TILE);
+          const unsigned tmem_p = tmem + c * CHAIN_COLS, tmem_o = tmem_p + KEYS;
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk)   // 16 keys a step: P advances 32 bytes in its rows, V 16 rows
-          umma(tmem_o, smem_descriptor(p_addr + kk * 32), smem_descriptor(v_addr + kk * 16 * 128, KV_HALF, 1024), idesc_o,
-               (i > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(&sh->v_free[i % STAGES]);
-        umma_commit(&sh->pv_done);
+          for (int kk = 0; kk < KEYS / 16; ++kk)   // 16 keys a step: 8 packed columns of P, 16 rows of V
+            umma_a_in_tmem(tmem_o, tmem_p + kk * 8, smem_descriptor(v_addr + kk * 16 * 128, KV_TILE_HALF, 1024), idesc_o,
+                           (i > 0 || kk > 0) ? 1u : 0u);
+          if (c == 1 || i >= count_1) umma_commit(&sh->v_free[st]);
+          if (i + 1 == count[c]) umma_commit(&sh->pv_done[c]);
+          if (i + 1 < count[c]) {
+            if (!keys_checked) {
+              ok = mbar_wait(&sh->k_full[(i + 1) % PSTAGES], ((i + 1) / PSTAGES) & 1, &sh->abort, args.status, ERR_MMA);
+              keys_checked = true;
+              if (!ok) break;
+              fence_after_sync();
+            }
+            issue_scores(c, i + 1);
+          }
+        }
       }
     }
   } else {
-    const int quarter = warp & 3;
+    const int chain = (warp - 2) >> 2, quarter = warp & 3;
     const int row = quarter * 32 + lane;
-    const int t = tile_start + row;
+    const int t = tile_start + chain * BM + row;
+    const int my_count = chain == 0 ? count_0 : count_1;
     const int last = t < q_len ? pos0 + t : -1;
     const int first = args.window > 0 ? max(0, last - args.window + 1) : 0;
     const unsigned lane_base = static_cast<unsigned>(quarter * 32) << 16;
+    const unsigned tmem_s = sh->tmem_base + chain * CHAIN_COLS + lane_base, tmem_o = tmem_s + KEYS;
     float row_max = -INFINITY, row_sum = 0.f;
     bool ok = true;
-    for (int i = 0; i < num_tiles && ok; ++i) {
-      const int s = i % STAGES;
-      ok = mbar_wait(&sh->s_full[i & 1], (i >> 1) & 1, &sh->abort, args.status, ERR_SOFTMAX);
+    for (int i = 0; i < my_count && ok; ++i) {
+      ok = mbar_wait(&sh->s_full[chain], i & 1, &sh->abort, args.status, ERR_SOFTMAX);
       ok = __all_sync(0xffffffffu, ok);   // the warp stays together: the tensor-memory accesses below are warp-wide
       if (!ok) break;
       fence_after_sync();
-      unsigned v0[32], v1[32];
-      tmem_load32(tmem_s + (i & 1) * BN + lane_base, v0);
-      tmem_load32(tmem_s + (i & 1) * BN + lane_base + 32, v1);
-      tmem_wait_load();
-      const int key_base = (tile_lo + i) * BN;
-      // most tiles lie wholly inside the row's visible range: only the others pay for masking
-      if (key_base < first || key_base + BN - 1 > last) {
+      unsigned v[4][32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int k0 = key_base + j, k1 = key_base + 32 + j;
-          if (k0 < first || k0 > last) v0[j] = 0xff800000u;   // -inf
-          if (k1 < first || k1 > last) v1[j] = 0xff800000u;
-        }
+      for (int g = 0; g < 4; ++g) tmem_load32(tmem_s + g * 32, v[g]);
+      tmem_wait_load();
+      const int key_base = (tile_lo + i) * KEYS;
+      if (key_base < first || key_base + KEYS - 1 > last) {   // only tiles at the edge of the row's range pay for masking
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int key = key_base + g * 32 + j;
+            if (key < first || key > last) v[g][j] = 0xff800000u;   // -inf
+          }
       }
       float tile_max = -INFINITY;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) tile_max = fmaxf(tile_max, fmaxf(__uint_as_float(v0[j]), __uint_as_float(v1[j])));
-      tile_max *= args.scale_log2;   // the scale is positive: the maximum of the raw scores is the one to scale
+      for (int g = 0; g < 4; ++g)
+#pragma unroll
+        for (int j = 0; j < 32; ++j) tile_max = fmaxf(tile_max, __uint_as_float(v[g][j]));
+      tile_max *= args.scale_log2;
       // The base of the exponentials follows the running maximum lazily: it moves (and O is
       // rescaled) only when the maximum has grown by more than 2^8; until then probabilities
       // are at most 2^8, which float32 sums and bfloat16 products hold without loss.
       float correction = 1.0f;
       if (tile_max > row_max + 8.0f || row_max == -INFINITY) {
         const float new_max = fmaxf(row_max, tile_max);
-        const float base = new_max == -INFINITY ? 0.f : new_max;   // a row that has seen no key yet
+        const float base = new_max == -INFINITY ? 0.f : new_max;
         correction = row_max == -INFINITY ? 0.f : fast_exp2(row_max - base);
         row_max = new_max;
       }
       const float base = row_max == -INFINITY ? 0.f : row_max;
       float sum = 0.f;
-      unsigned packed[32];   // the row's 64 probabilities as bfloat16 pairs
 #pragma unroll
-      for (int j = 0; j < 64; j += 2) {
-        const float x0 = fast_exp2(fmaf(__uint_as_float(j < 32 ? v0[j] : v1[j - 32]), args.scale_log2, -base));
-        const float x1 = fast_exp2(fmaf(__uint_as_float(j + 1 < 32 ? v0[j + 1] : v1[j + 1 - 32]), args.scale_log2, -base));
-        sum += x0 + x1;
-        const __nv_bfloat162 pair = __floats2bfloat162_rn(x0, x1);
-        packed[j / 2] = *reinterpret_cast<const unsigned*>(&pair);
-      }
-      row_sum = row_sum * correction + sum;
-      // P has one buffer and O one accumulator: both belong to PV of the tile before until it is done
-      if (i > 0) {
-        ok = mbar_wait(&sh->pv_done, (i - 1) & 1, &sh->abort, args.status, ERR_SOFTMAX);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        fence_after_sync();
-      }
-      unsigned char* p_row = p_tile + row * 128;
+      for (int g = 0; g < 4; ++g) {
 #pragma unroll
-      for (int c = 0; c < 8; ++c)   // eight 16-byte chunks of the row, chunk c at (c xor row mod 8)
-        *reinterpret_cast<uint4*>(p_row + ((c ^ (row & 7)) << 4)) =
-            make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-      // value rows beyond the context: zero them (only the tile that holds the last key has any)
-      if (tile_lo + i == tile_hi && (hi + 1) % BN != 0) {
-        ok = mbar_wait(&sh->v_full[s], (i / STAGES) & 1, &sh->abort, args.status, ERR_SOFTMAX);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        unsigned char* v_tile = kv_tiles + s * 2 * KV_BYTES + KV_BYTES;
-        const int first_bad = hi + 1 - key_base;
-        for (int idx = threadIdx.x - 64; idx < (BN - first_bad) * HALVES * 8; idx += 128) {
-          const int r = first_bad + idx / (HALVES * 8), rest = idx % (HALVES * 8);
-          *reinterpret_cast<uint4*>(v_tile + (rest / 8) * KV_HALF + r * 128 + (rest % 8) * 16) = make_uint4(0u, 0u, 0u, 0u);
+        for (int j = 0; j < 32; j += 2) {
+          const float x0 = fast_exp2(fmaf(__uint_as_float(v[g][j]), args.scale_log2, -base));
+          const float x1 = fast_exp2(fmaf(__uint_as_float(v[g][j + 1]), args.scale_log2, -base));
+          sum += x0 + x1;
+          const __nv_bfloat162 two = __floats2bfloat162_rn(x0, x1);
+          v[g >> 1][(g & 1) * 16 + j / 2] = *reinterpret_cast<const unsigned*>(&two);   // packed over the scores already used
         }
       }
-      // O of the tiles before is scaled by `correction`; skipped when no row of the warp moved
+      row_sum = row_sum * correction + sum;
+      // P over the first 64 columns of S (keys 2 j and 2 j + 1 in column j); PV of the tile before is
+      // done (S of this tile was issued after it, and the pipe runs in order)
+      tmem_store32(tmem_s, v[0]);
+      tmem_store32(tmem_s + 32, v[1]);
+      // value rows beyond the context: zero them (only the tile that holds the sequence's last key has any)
+      if (tile_lo + i == tile_hi && (hi + 1) % KEYS != 0) {
+        const int s = i % PSTAGES;
+        ok = mbar_wait(&sh->v_full[s], (i / PSTAGES) & 1, &sh->abort, args.status, ERR_SOFTMAX);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        unsigned char* v_tile = v_tiles + s * KV_TILE;
+        const int first_bad = hi + 1 - key_base;
+        for (int idx = row; idx < (KEYS - first_bad) * HALVES * 8; idx += 128) {
+          const int r = first_bad + idx / (HALVES * 8), rest = idx % (HALVES * 8);
+          *reinterpret_cast<uint4*>(v_tile + (rest / 8) * KV_TILE_HALF + r * 128 + (rest % 8) * 16) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        fence_async_shared();
+      }
       if (i > 0 && __any_sync(0xffffffffu, correction != 1.0f)) {
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
           unsigned o[32];
-          tmem_load32(tmem_o + lane_base + c * 32, o);
+          tmem_load32(tmem_o + c * 32, o);
           tmem_wait_load();
 #pragma unroll
           for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * correction);
-          tmem_store32(tmem_o + lane_base + c * 32, o);
+          tmem_store32(tmem_o + c * 32, o);
         }
-        tmem_wait_store();
       }
+      tmem_wait_store();
       fence_before_sync();
-      fence_async_shared();
-      mbar_arrive(&sh->p_full);
+      mbar_arrive(&sh->p_full[chain]);
     }
-    if (ok && num_tiles > 0) ok = mbar_wait(&sh->pv_done, (num_tiles - 1) & 1, &sh->abort, args.status, ERR_SOFTMAX);
+    if (ok && my_count > 0) ok = mbar_wait(&sh->pv_done[chain], 0, &sh->abort, args.status, ERR_SOFTMAX);
     ok = __all_sync(0xffffffffu, ok);
     fence_after_sync();
     if (ok && args.splits > 1) {
-      // a split's share: the unnormalised row as it stands in tensor memory, its base and its sum
       const size_t at = (static_cast<size_t>(split) * args.num_tokens + start + t) * args.num_heads + head;
       if (t < q_len) {
-        args.partial_ml[2 * at] = num_tiles > 0 ? row_max : -INFINITY;
-        args.partial_ml[2 * at + 1] = num_tiles > 0 ? row_sum : 0.f;
+        args.partial_ml[2 * at] = my_count > 0 ? row_max : -INFINITY;
+        args.partial_ml[2 * at + 1] = my_count > 0 ? row_sum : 0.f;
       }
-      if (num_tiles > 0) {
+      if (my_count > 0) {
         float* dst = args.partial_o + at * D;
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
           unsigned o[32];
-          tmem_load32(tmem_o + lane_base + c * 32, o);
+          tmem_load32(tmem_o + c * 32, o);
           tmem_wait_load();
           if (t < q_len) {
 #pragma unroll
@@ -410,13 +438,13 @@ portions_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           }
         }
       }
-    } else if (ok) {
+    } else if (ok && my_count > 0) {
       const float inv = row_sum > 0.f ? 1.0f / row_sum : 0.f;
       __nv_bfloat16* dst = args.out + (static_cast<size_t>(start + t) * args.num_heads + head) * D;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         unsigned o[32];
-        tmem_load32(tmem_o + lane_base + c * 32, o);
+        tmem_load32(tmem_o + c * 32, o);
         tmem_wait_load();
         if (t < q_len) {
 #pragma unroll
@@ -424,8 +452,8 @@ portions_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             unsigned packed[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              const __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(o[j + 2 * e]) * inv, __uint_as_float(o[j + 2 * e + 1]) * inv);
-              packed[e] = *reinterpret_cast<const unsigned*>(&pair);
+              const __nv_bfloat162 two = __floats2bfloat162_rn(__uint_as_float(o[j + 2 * e]) * inv, __uint_as_float(o[j + 2 * e + 1]) * inv);
+              packed[e] = *reinterpret_cast<const unsigned*>(&two);
             }
             *reinterpret_cast<uint4*>(dst + c * 32 + j) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
           }
@@ -437,9 +465,11 @@ portions_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   __syncthreads();
   if (warp == 1) {
     fence_after_sync();
-    tmem_free(sh->tmem_base, TMEM_COLS);
+    tmem_free(sh->tmem_base, PAIR_TMEM_COLS);
   }
 }
+
+}  // namespace pair
 
 // Adds up the splits of every query row of the portions: out = sum_s O_s 2^(base_s - M) / sum_s l_s 2^(base_s - M)
 // with M the largest base.  One warp per (token, head), lanes over the splits first (bases and sums),
@@ -488,17 +518,34 @@ combine_portions_kernel(const Args args) {
 
 SHRIKE_API int shrike_attention_tc_available() { return 1; }
 
+// Query rows a CTA owns: what the caller counts the portions' query tiles in.
+SHRIKE_API int shrike_attention_tc_portions_rows() { return tcattn::pair::ROWS; }
+
 // How many CTAs should share the keys of a query tile, for a batch of `num_tokens` new tokens whose
-// block tables are `max_blocks` pages wide: as many as fill the GPU twice, each with at least four
-// key tiles, at most 16; 1 when the query tiles alone fill it.  The scratch for splits > 1 is
-// splits * num_tokens * num_heads * (D + 2) floats.
-SHRIKE_API int shrike_attention_tc_portions_splits(int num_tokens, int num_heads, int max_blocks, int page_size) {
-  const int ctas = num_heads * ((num_tokens + tcattn::BM - 1) / tcattn::BM + 1);
-  const int key_tiles = (max_blocks * page_size + tcattn::BN - 1) / tcattn::BN;
-  int splits = (2 * shrike_device().sm_count) / (ctas < 1 ? 1 : ctas);
-  if (splits > key_tiles / 4) splits = key_tiles / 4;
-  if (splits > 16) splits = 16;
-  return splits < 1 ? 1 : splits;   // the kernels take up to 32
+// portions make `portion_tiles` query tiles (0: not known; the most they can make is assumed) and whose
+// block tables are `max_blocks` pages wide.  The GPU holds `capacity` CTAs at once; with s splits the
+// launch takes ceil(heads * tiles * s / capacity) rounds of ceil(key tiles / s) steps each, plus a fixed
+// cost per round and, for s > 1, the combine: the s that makes this smallest, with at least two key
+// steps per split and at most 16.  The scratch for s > 1 is s * num_tokens * num_heads * (D + 2) floats.
+SHRIKE_API int shrike_attention_tc_portions_splits(int num_tokens, int num_heads, int max_blocks, int page_size, int portion_tiles) {
+  const int rows = shrike_attention_tc_portions_rows();
+  const int most = (num_tokens + rows - 1) / rows + 1;
+  const int tiles = portion_tiles > 0 && portion_tiles < most ? portion_tiles : most;
+  const long long ctas = static_cast<long long>(num_heads) * tiles;
+  const int keys = tcattn::pair::KEYS;
+  const int key_steps = (max_blocks * page_size + keys - 1) / keys;
+  const long long capacity = shrike_device().sm_count;   // one CTA per SM
+  int best = 1;
+  long long best_cost = -1;
+  for (int s = 1; s <= 16 && (s == 1 || key_steps / s >= 2); ++s) {
+    const long long rounds = (ctas * s + capacity - 1) / capacity;
+    const long long cost = rounds * ((key_steps + s - 1) / s + 2) + (s > 1 ? 3 : 0);
+    if (best_cost < 0 || cost < best_cost) {
+      best_cost = cost;
+      best = s;
+    }
+  }
+  return best;   // the kernels take up to 32
 }
 SHRIKE_API long long shrike_attention_tc_portions_scratch_floats(int num_tokens, int num_heads, int splits) {
   return splits <= 1 ? 0 : static_cast<long long>(splits) * num_tokens * num_heads * (tcattn::D + 2);
@@ -519,14 +566,16 @@ SHRIKE_API int shrike_paged_attention_tc_portions(const void* q, const void* k_c
   if (splits < 1 || splits > 32 || (splits > 1 && (scratch == nullptr || seq_of_token == nullptr))) return SHRIKE_BAD_ARGUMENT;
   // query tiles of the batch's portions: the caller's count, or what `num_tokens` tokens in
   // `num_seqs` sequences can make at most
-  const int most_tiles = (num_tokens + BM - 1) / BM + num_seqs;
+  const int rows = shrike_attention_tc_portions_rows();
+  const int most_tiles = (num_tokens + rows - 1) / rows + num_seqs;
   const int work = portion_tiles > 0 && portion_tiles < most_tiles ? portion_tiles : most_tiles;
   if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || max_blocks <= 0 || max_q_len < 1 ||
       num_seqs > 65535 || (num_tokens + BM - 1) / BM + num_seqs > 65535 || !(page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64))
     return SHRIKE_BAD_ARGUMENT;
   static bool configured = false;
   if (!configured) {
-    const cudaError_t err = cudaFuncSetAttribute(portions_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES));
+    const cudaError_t err = cudaFuncSetAttribute(pair::portions_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 static_cast<int>(pair::PAIR_SMEM));
     if (err != cudaSuccess) return static_cast<int>(err);
     configured = true;
   }
@@ -557,8 +606,8 @@ SHRIKE_API int shrike_paged_attention_tc_portions(const void* q, const void* k_c
   args.seq_of_token = seq_of_token;
   args.partial_o = splits > 1 ? scratch : nullptr;   // rows first (16-byte stores), then the (base, sum) pairs
   args.partial_ml = splits > 1 ? scratch + static_cast<long long>(splits) * num_tokens * num_heads * D : nullptr;
-  cudaError_t err = launch_dependent(portions_tc_kernel, dim3(num_heads, work, splits), dim3(THREADS), SMEM_BYTES, stream,
-                                     map_q, map_k, map_v, args);
+  cudaError_t err = launch_dependent(pair::portions_pair_kernel, dim3(num_heads, work, splits), dim3(pair::PTHREADS), pair::PAIR_SMEM,
+                                     stream, map_q, map_k, map_v, args);
   if (err != cudaSuccess) return static_cast<int>(err);
   if (splits > 1) {
     err = launch_dependent(combine_portions_kernel, dim3(num_heads, (num_tokens + 7) / 8), dim3(256), 0, stream, args);
@@ -570,7 +619,8 @@ SHRIKE_API int shrike_paged_attention_tc_portions(const void* q, const void* k_c
 #else  // other head sizes: the mma.sync kernel serves them
 
 SHRIKE_API int shrike_attention_tc_available() { return 0; }
-SHRIKE_API int shrike_attention_tc_portions_splits(int, int, int, int) { return 1; }
+SHRIKE_API int shrike_attention_tc_portions_rows() { return 128; }
+SHRIKE_API int shrike_attention_tc_portions_splits(int, int, int, int, int) { return 1; }
 SHRIKE_API long long shrike_attention_tc_portions_scratch_floats(int, int, int) { return 0; }
 SHRIKE_API int shrike_paged_attention_tc_portions(const void*, const void*, const void*, const int*, int, const int*,
                                                   const int*, int, int, int, int, int, int, float, int, void*, int, int,

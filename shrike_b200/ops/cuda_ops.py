@@ -151,7 +151,8 @@ class CudaOps:
                 [_P, _P, _P, _P, _I, _P, _P] + [_I] * 6 + [_F, _I, _P, _I, _I, _P, _I, _P, _I, _P, _P]
             )
             lib.shrike_paged_attention_tc_portions.restype = _I
-            lib.shrike_attention_tc_portions_splits.argtypes = [_I, _I, _I, _I]
+            lib.shrike_attention_tc_portions_rows.restype = _I
+            lib.shrike_attention_tc_portions_splits.argtypes = [_I, _I, _I, _I, _I]
             lib.shrike_attention_tc_portions_splits.restype = _I
             lib.shrike_attention_tc_portions_scratch_floats.argtypes = [_I, _I, _I]
             lib.shrike_attention_tc_portions_scratch_floats.restype = _LL
@@ -375,7 +376,7 @@ class CudaOps:
                 page_size, num_pages, scale, window or 0, _ptr(out), self._stream()), "paged_attention")
             return
         plan = self.attention_plan(num_heads, num_kv_heads, head_dim, num_seqs, max_blocks, page_size, max_q_len, min_q_len,
-                                   q.shape[0])
+                                   q.shape[0], q_lens)
         self.launches += plan.has_single + plan.has_portions + (1 if plan.portion_splits > 1 else 0)
         has_portions = plan.has_portions
         if plan.tc_portions:
@@ -383,7 +384,8 @@ class CudaOps:
                 _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), max_blocks, _ptr(q_start), _ptr(ctx_len),
                 q.shape[0], num_seqs, num_heads, num_kv_heads, page_size, num_pages, scale, window or 0, _ptr(out),
                 plan.has_single, max_q_len, _ptr(self.status), plan.portion_splits, _ptr(plan.portion_scratch),
-                self.portion_tiles(q_lens, plan.has_single), _ptr(seq_of_token), self._stream()), "paged_attention_tc_portions")
+                self.portion_tiles(q_lens, plan.has_single, lib.shrike_attention_tc_portions_rows()), _ptr(seq_of_token),
+                self._stream()), "paged_attention_tc_portions")
             has_portions = 0
             if not plan.has_single:
                 return
@@ -394,19 +396,19 @@ class CudaOps:
             _ptr(self.status), self._stream()),
             "paged_attention_bf16")
 
-    def portion_tiles(self, q_lens, skip_single) -> int:
-        """Query tiles (of 128 rows) that the batch's portions make; 0 when the lengths are not known."""
+    def portion_tiles(self, q_lens, skip_single, rows) -> int:
+        """Query tiles of `rows` rows that the batch's portions make; 0 when the lengths are not known."""
         if q_lens is None:
             return 0
         held = self._portion_tiles
-        if held is not None and held[0] is q_lens and held[1] == skip_single:
+        if held is not None and held[0] is q_lens and held[1] == (skip_single, rows):
             return held[2]
-        tiles = sum(-(-q // 128) for q in q_lens if q > 1 or not skip_single)
-        self._portion_tiles = (q_lens, skip_single, tiles)
+        tiles = sum(-(-q // rows) for q in q_lens if q > 1 or not skip_single)
+        self._portion_tiles = (q_lens, (skip_single, rows), tiles)
         return tiles
 
     def attention_plan(self, num_heads, num_kv_heads, head_dim, num_seqs, max_blocks, page_size, max_q_len, min_q_len,
-                       num_tokens=0):
+                       num_tokens=0, q_lens=None):
         """How a bfloat16 batch's attention is cut: which kernels run (single tokens, portions, the
         tensor-core form of the latter), the key splits and clusters of the single-token kernel, the
         key splits of the portions kernel, and their scratch.  A function of the batch's shape alone."""
@@ -434,7 +436,9 @@ class CudaOps:
                            and page_size in (8, 16, 32, 64))
         portion_splits, portion_scratch = 1, None
         if tc_portions and num_tokens > 0:
-            portion_splits = self.portion_splits or lib.shrike_attention_tc_portions_splits(num_tokens, num_heads, max_blocks, page_size)
+            tiles = self.portion_tiles(q_lens, has_single, lib.shrike_attention_tc_portions_rows())
+            portion_splits = self.portion_splits or lib.shrike_attention_tc_portions_splits(
+                num_tokens, num_heads, max_blocks, page_size, tiles)
             need = lib.shrike_attention_tc_portions_scratch_floats(num_tokens, num_heads, portion_splits)
             if need > self.PORTION_SCRATCH_FLOATS:   # bound the scratch: fewer splits, never a refusal
                 portion_splits = max(1, portion_splits * self.PORTION_SCRATCH_FLOATS // need)

@@ -176,9 +176,10 @@ class LayerProgram:
         step.down_splits = 1 if library else splits_of(n, width, inter)
         step.gated_fused = int(bool(feed_forward.run) and not library and (2 * inter) % 32 == 0)
         plan = ops.attention_plan(spec.num_heads, spec.num_kv_heads, spec.head_dim, ctx.num_seqs, view.max_blocks, page_size,
-                                  ctx.max_q_len, ctx.min_q_len, n)
+                                  ctx.max_q_len, ctx.min_q_len, n, ctx.q_lens)
         step.portion_splits = plan.portion_splits
-        step.portion_tiles = ops.portion_tiles(ctx.q_lens, plan.has_single)
+        step.portion_tiles = ops.portion_tiles(ctx.q_lens, plan.has_single,
+                                               ops._attention_lib(spec.head_dim).shrike_attention_tc_portions_rows())
         step.seq_of_token = ctx.seq_of_token.data_ptr()
         step.portion_scratch = None if plan.portion_scratch is None else plan.portion_scratch.data_ptr()
         step.has_single, step.has_portions, step.tc_portions = plan.has_single, plan.has_portions, plan.tc_portions

@@ -418,12 +418,16 @@ SERVED = {
     "two_portions_beside_eight_single_tokens": (
         [1024, 777, 1, 2048, 513, 64, 1000, 1100, 2048, 1000], [1, 1, 1, 1, 1, 1, 1, 1, 512, 300], None),
     "ragged_edges": ([2047, 129, 1153], [2047, 65, 127], None),
+    # a CTA's two chains of 128 rows: a second chain of one row, of none, of all; first rows at positions that
+    # are no multiple of the key step, so that the two chains' last keys fall into the same or into different steps
+    "chain_edges": ([300, 334, 133, 900, 256, 131], [129, 257, 128, 385, 256, 2], None),
+    "chain_edges_window": ([300, 334, 700, 900], [129, 257, 300, 385], 100),
 }
 
 
 @pytest.mark.parametrize("name", list(SERVED))
 @pytest.mark.parametrize("splits", [0, 1, 3, 7])
-@pytest.mark.parametrize("heads,kv_heads,dim,page", [(28, 4, 128, 16), (14, 2, 64, 16), (12, 2, 128, 32)])
+@pytest.mark.parametrize("heads,kv_heads,dim,page", [(28, 4, 128, 16), (14, 2, 64, 16), (12, 2, 128, 32), (5, 1, 64, 8)])
 def test_portions_attention_at_served_lengths(name, heads, kv_heads, dim, page, splits):
     """The tensor-core kernel for portions over walks of up to 64 key tiles (its rescaling of the
     running sum, its look-ahead in the block table and its first and last tile only matter on
@@ -433,7 +437,8 @@ def test_portions_attention_at_served_lengths(name, heads, kv_heads, dim, page, 
     ctx_lens, q_lens, window = SERVED[name]
     ops = cuda_ops(torch.bfloat16)
     ops.portion_splits = splits
-    assert ops._attention_lib(dim).shrike_attention_tc_available()
+    lib = ops._attention_lib(dim)
+    assert lib.shrike_attention_tc_available()
     case = paged_case(torch.bfloat16, heads, kv_heads, dim, page, ctx_lens, q_lens, seed=11)
     if window is not None:
         drop_passed_pages(case, page, window, ctx_lens, q_lens)
@@ -443,15 +448,22 @@ def test_portions_attention_at_served_lengths(name, heads, kv_heads, dim, page, 
 
 
 def test_a_portion_beside_decoding_requests_is_split_over_the_gpu():
-    """The rule: 492 new tokens of 12 heads over block tables of 2,048 keys would occupy 60 CTAs;
-    their keys are shared out until the GPU is filled twice, no split with fewer than four key
-    tiles.  A whole 2,048-token prompt of 28 heads fills the GPU by itself: no split."""
+    """The rule: the query tiles of 492 new tokens of 12 heads over block tables of 2,048 keys would
+    occupy a fraction of the GPU; their keys are shared out so that the launch takes the fewest
+    rounds of key steps, never fewer than two steps a split.  A whole 2,048-token prompt of 28 heads
+    fills the GPU by itself: no split."""
     ops = cuda_ops(torch.bfloat16)
     lib = ops._attention_lib(128)
-    assert lib.shrike_attention_tc_portions_splits(512, 12, 128, 16) == 4
-    assert lib.shrike_attention_tc_portions_splits(2048, 28, 128, 16) == 1
-    assert lib.shrike_attention_tc_portions_splits(64, 2, 16, 16) == 1        # four key tiles in all
-    assert lib.shrike_attention_tc_portions_splits(64, 2, 4096, 16) == 16     # never more than 16
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    rows, keys = 256, 128
+    assert lib.shrike_attention_tc_portions_rows() == rows
+    tiles = -(-492 // rows)
+    splits = lib.shrike_attention_tc_portions_splits(512, 12, 128, 16, tiles)
+    assert 2 <= splits <= 16 and (2048 // keys) // splits >= 2
+    assert 12 * tiles * splits <= 2 * sms                                        # at most two rounds, one CTA per SM
+    assert lib.shrike_attention_tc_portions_splits(2048, 28, 128, 16, 2048 // rows) == 1
+    assert lib.shrike_attention_tc_portions_splits(64, 2, 8, 16, 1) == 1         # one key step in all
+    assert lib.shrike_attention_tc_portions_splits(64, 2, 4096, 16, 1) == 16     # never more than 16
     assert lib.shrike_attention_tc_portions_scratch_floats(512, 12, 4) == 4 * 512 * 12 * 130
 
 
