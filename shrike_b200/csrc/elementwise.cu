@@ -247,38 +247,40 @@ SHRIKE_API int shrike_add_rmsnorm(float* resid, const void* delta, int delta_dty
 // (the order in which a fused gate/up matrix keeps its rows for the tensor-core product's own
 // activation epilogue); b is a multiple of VEC.
 template <typename T, int VEC>
-__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total, int block) {
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, int rows, int block) {
   let_dependents_start();
   wait_for_previous();
+  // blockIdx.y walks the rows, blockIdx.x and the threads a row's groups of VEC columns: no division
+  // by the row length anywhere.  Two groups per thread and round, so that four loads are in flight
+  // before the arithmetic starts.
+  constexpr int ROUND = 2;
   const int groups_per_row = inter / VEC;
-  const size_t groups = total / VEC;
-  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  const int stride = gridDim.x * blockDim.x;
   struct alignas(sizeof(T) * VEC) Pack { T v[VEC]; };
-  // two groups per round, so that four loads are in flight before the arithmetic starts
-  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < groups; i += 2 * stride) {
-    Pack g[2], u[2];
-    size_t at[2];
-    bool live[2];
+  for (int row = blockIdx.y; row < rows; row += gridDim.y) {
+    const T* in_row = gate_up + static_cast<size_t>(row) * 2 * inter;
+    T* out_row = out + static_cast<size_t>(row) * inter;
+    for (int first = blockIdx.x * blockDim.x + threadIdx.x; first < groups_per_row; first += ROUND * stride) {
+      Pack g[ROUND], u[ROUND];
 #pragma unroll
-    for (int k = 0; k < 2; ++k) {
-      const size_t index = i + k * stride;
-      live[k] = index < groups;
-      const size_t row = live[k] ? index / groups_per_row : 0;
-      const int col = live[k] ? static_cast<int>(index - row * groups_per_row) * VEC : 0;
-      at[k] = row * inter + col;
-      const T* g_ptr = gate_up + row * 2 * inter + (block > 0 ? (col / block) * 2 * block + col % block : col);
-      if (live[k]) {
-        g[k] = *reinterpret_cast<const Pack*>(g_ptr);
-        u[k] = *reinterpret_cast<const Pack*>(g_ptr + (block > 0 ? block : inter));
+      for (int k = 0; k < ROUND; ++k) {
+        const int group = first + k * stride;
+        if (group < groups_per_row) {
+          const int col = group * VEC;
+          const T* g_ptr = in_row + (block > 0 ? (col / block) * 2 * block + col % block : col);
+          g[k] = *reinterpret_cast<const Pack*>(g_ptr);
+          u[k] = *reinterpret_cast<const Pack*>(g_ptr + (block > 0 ? block : inter));
+        }
       }
-    }
 #pragma unroll
-    for (int k = 0; k < 2; ++k) {
-      if (!live[k]) continue;
-      Pack r;
+      for (int k = 0; k < ROUND; ++k) {
+        const int group = first + k * stride;
+        if (group >= groups_per_row) continue;
+        Pack r;
 #pragma unroll
-      for (int j = 0; j < VEC; ++j) r.v[j] = from_float<T>(silu_times<T>(to_float(g[k].v[j]), to_float(u[k].v[j])));
-      *reinterpret_cast<Pack*>(out + at[k]) = r;
+        for (int j = 0; j < VEC; ++j) r.v[j] = from_float<T>(silu_times<T>(to_float(g[k].v[j]), to_float(u[k].v[j])));
+        *reinterpret_cast<Pack*>(out_row + group * VEC) = r;
+      }
     }
   }
 }
@@ -288,16 +290,18 @@ static void launch_silu_mul(const void* gate_up, void* out, int n, int inter, in
   constexpr int WIDE = 16 / sizeof(T);
   const bool vec = inter % WIDE == 0 && block % WIDE == 0 &&
                    (reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) % 16 == 0;
-  const size_t total = static_cast<size_t>(n) * inter;
-  const size_t work = vec ? total / WIDE : total;
+  const int groups_per_row = vec ? inter / WIDE : inter;
   const int threads = 256;
-  const int blocks = static_cast<int>(min(static_cast<size_t>(shrike_device().sm_count * 8), (work + 2 * threads - 1) / (2 * threads)));
+  // a row's groups over as many blocks as give each thread one round of two; one row of blocks per row
+  const int across = max(1, min(64, (groups_per_row + 2 * threads - 1) / (2 * threads)));
+  const int down = max(1, min(n, 65535));
+  const dim3 grid(across, down);
   if (vec)
-    launch_dependent(silu_mul_kernel<T, WIDE>, blocks, threads, 0, stream, static_cast<const T*>(gate_up),
-                     static_cast<T*>(out), inter, total, block);
+    launch_dependent(silu_mul_kernel<T, WIDE>, grid, threads, 0, stream, static_cast<const T*>(gate_up),
+                     static_cast<T*>(out), inter, n, block);
   else
-    launch_dependent(silu_mul_kernel<T, 1>, blocks, threads, 0, stream, static_cast<const T*>(gate_up),
-                     static_cast<T*>(out), inter, total, block);
+    launch_dependent(silu_mul_kernel<T, 1>, grid, threads, 0, stream, static_cast<const T*>(gate_up),
+                     static_cast<T*>(out), inter, n, block);
 }
 
 SHRIKE_API int shrike_silu_mul(const void* gate_up, void* out, int dtype, int n, int inter, int block, cudaStream_t stream) {
