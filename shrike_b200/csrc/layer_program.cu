@@ -127,19 +127,30 @@ struct Blas {
 std::mutex blas_mutex;
 Blas blas_of_device[64];
 
+// The library's handle of the current device, made on first use (that takes a tenth of a second:
+// shrike_layer_program_warm does it when the engine is built, not in a request's first step).
+int blas_of_current_device(const ShrikeLayerFns& fn, Blas** out) {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return SHRIKE_BAD_ARGUMENT;
+  Blas& blas = blas_of_device[device];
+  if (blas.handle == nullptr) {
+    if (fn.cublas_create(&blas.handle) != CUBLAS_STATUS_SUCCESS) return 2000;
+    fn.cublas_set_math_mode(blas.handle, static_cast<cublasMath_t>(CUBLAS_DEFAULT_MATH | CUBLAS_MATH_DISALLOW_REDUCED_PRECISION_REDUCTION));
+  }
+  *out = &blas;
+  return SHRIKE_OK;
+}
+
 // out[tokens][columns] = x[tokens][k] * w[columns][k]^T in bfloat16 with float32 accumulation, no
 // reduced-precision partial sums.  Row-major operands are column-major ones transposed: C^T = W X^T.
 int library_product(const ShrikeLayerFns& fn, const ShrikeLayerStep& c, const void* x, const void* w, void* out, bool out_f32,
                     int columns, int k, cudaStream_t stream) {
-  int device = 0;
-  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return SHRIKE_BAD_ARGUMENT;
-  Blas& blas = blas_of_device[device];
+  Blas* found = nullptr;
   {
     std::lock_guard<std::mutex> guard(blas_mutex);
-    if (blas.handle == nullptr) {
-      if (fn.cublas_create(&blas.handle) != CUBLAS_STATUS_SUCCESS) return 2000;
-      fn.cublas_set_math_mode(blas.handle, static_cast<cublasMath_t>(CUBLAS_DEFAULT_MATH | CUBLAS_MATH_DISALLOW_REDUCED_PRECISION_REDUCTION));
-    }
+    const int rc = blas_of_current_device(fn, &found);
+    if (rc != SHRIKE_OK) return rc;
+    Blas& blas = *found;
     if (blas.workspace != c.workspace && c.workspace != nullptr) {
       if (fn.cublas_set_workspace(blas.handle, c.workspace, static_cast<size_t>(c.workspace_bytes)) != CUBLAS_STATUS_SUCCESS) return 2001;
       blas.workspace = c.workspace;
@@ -152,6 +163,7 @@ int library_product(const ShrikeLayerFns& fn, const ShrikeLayerStep& c, const vo
       blas.stream_set = true;
     }
   }
+  Blas& blas = *found;
   const float one = 1.0f, zero = 0.0f;
   const cublasStatus_t rc = fn.cublas_gemm_ex(blas.handle, CUBLAS_OP_T, CUBLAS_OP_N, columns, c.tokens, k, &one, w, CUDA_R_16BF, k, x,
                                               CUDA_R_16BF, k, &zero, out, out_f32 ? CUDA_R_32F : CUDA_R_16BF, columns,
@@ -160,6 +172,13 @@ int library_product(const ShrikeLayerFns& fn, const ShrikeLayerStep& c, const vo
 }
 
 }  // namespace
+
+// Makes the library's handle for the current device now rather than in the first step that needs it.
+SHRIKE_API int shrike_layer_program_warm(const ShrikeLayerFns* fns) {
+  std::lock_guard<std::mutex> guard(blas_mutex);
+  Blas* found = nullptr;
+  return blas_of_current_device(*fns, &found);
+}
 
 #define SHRIKE_TRY(call)          \
   do {                            \

@@ -79,6 +79,8 @@ class DecoderModel:
                 cls = part_class(category, spec.kind)
                 built[role] = cls(spec, _take(tensors, names.layer_part(index, role), cls.parameters(spec)), ops, runtime)
             self.blocks.append(part_class("block", layer.block)(**built))
+            if hasattr(self.blocks[-1], "prepare"):
+                self.blocks[-1].prepare()
             parts += [*built.values(), self.blocks[-1]]
         norm = config.final_norm
         cls = part_class("norm", norm.kind)

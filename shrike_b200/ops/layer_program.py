@@ -88,6 +88,7 @@ class LayerProgram:
         self._fns: dict[int, LayerFns] = {}   # head size -> launcher table
         self._fn_refs: dict = {}
         self._workspace = None
+        self._warm = False
         self._layers: dict = {}
 
     # ---- which layers -------------------------------------------------------------
@@ -106,7 +107,23 @@ class LayerProgram:
             return False
         if mixer.b_o is not None:
             return False
-        return mixer.spec.width % 8 == 0 and mixer.q_width % 8 == 0 and feed_forward.spec.intermediate % 8 == 0
+        if not (mixer.spec.width % 8 == 0 and mixer.q_width % 8 == 0 and feed_forward.spec.intermediate % 8 == 0):
+            return False
+        self.warm(mixer.spec.head_dim)
+        return True
+
+    def warm(self, head_dim: int) -> None:
+        """What would otherwise fall into a request's first long step: the library's handle (a tenth
+        of a second to make) and its workspace."""
+        if self._warm:
+            return
+        self._warm = True
+        self.lib.shrike_layer_program_warm.argtypes = [_P]
+        self.lib.shrike_layer_program_warm.restype = _I
+        with torch.cuda.device(self.ops.device):
+            self.lib.shrike_layer_program_warm(self._fn_ref(head_dim))
+        if self._workspace is None:
+            self._workspace = torch.empty(self.WORKSPACE_BYTES, dtype=torch.uint8, device=self.ops.device)
 
     def _launchers(self, head_dim: int) -> LayerFns:
         fns = self._fns.get(head_dim)

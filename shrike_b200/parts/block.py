@@ -31,6 +31,11 @@ class PreNormBlock:
                 self._program = program
         return self._program
 
+    def prepare(self) -> None:
+        """Called once when the model is built: settles how the layer is issued, so that what that
+        takes (the native library's set-up) does not fall into a request's first step."""
+        self._native()
+
     def forward(self, resid, delta, ctx, run):
         program = self._native()
         if program is not None and getattr(program.ops, "native_layers", False):
