@@ -274,14 +274,20 @@ portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       const unsigned idesc_o = instruction_descriptor(BM, D, true);
       const unsigned tmem = sh->tmem_base;
       const int count[2] = {count_0, count_1};
+      // One thread issues every MMA of the CTA, 32 per step, so what it does between two of them counts:
+      // the operand descriptors are formed once (a descriptor's low bits are the address in 16-byte
+      // units, so a tile further on is an addition), not per instruction.
+      const unsigned long long q_desc[2] = {smem_descriptor(smem_u32(q_tiles)), smem_descriptor(smem_u32(q_tiles + Q_BYTES))};
+      const unsigned long long k_desc0 = smem_descriptor(smem_u32(k_tiles));
+      const unsigned long long v_desc0 = smem_descriptor(smem_u32(v_tiles), KV_TILE_HALF, 1024);
       // S of chain c for tile i; the chain that needs a key stage last hands it back
       auto issue_scores = [&](int c, int i) {
-        const unsigned q_addr = smem_u32(q_tiles + c * Q_BYTES), k_addr = smem_u32(k_tiles + (i % PSTAGES) * KV_TILE);
+        const unsigned long long q_base = q_desc[c], k_base = k_desc0 + static_cast<unsigned>(((i % PSTAGES) * KV_TILE) >> 4);
+        const unsigned tmem_s = tmem + c * CHAIN_COLS;
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const unsigned off = (kk / 4) * Q_HALF + (kk % 4) * 32, koff = (kk / 4) * KV_TILE_HALF + (kk % 4) * 32;
-          umma(tmem + c * CHAIN_COLS, smem_descriptor(q_addr + off), smem_descriptor(k_addr + koff), idesc_s, kk > 0 ? 1u : 0u);
-        }
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma(tmem_s, q_base + (((kk / 4) * Q_HALF + (kk % 4) * 32) >> 4), k_base + (((kk / 4) * KV_TILE_HALF + (kk % 4) * 32) >> 4), idesc_s,
+               kk > 0 ? 1u : 0u);
         umma_commit(&sh->s_full[c]);
         if (c == 1 || i >= count_1) umma_commit(&sh->k_free[i % PSTAGES]);
       };
@@ -302,12 +308,11 @@ portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           if (ok) ok = mbar_wait(&sh->p_full[c], i & 1, &sh->abort, args.status, ERR_MMA);
           if (!ok) break;
           fence_after_sync();
-          const unsigned v_addr = smem_u32(v_tiles + st * KV_TILE);
+          const unsigned long long v_base = v_desc0 + static_cast<unsigned>((st * KV_TILE) >> 4);
           const unsigned tmem_p = tmem + c * CHAIN_COLS, tmem_o = tmem_p + KEYS;
 #pragma unroll
           for (int kk = 0; kk < KEYS / 16; ++kk)   // 16 keys a step: 8 packed columns of P, 16 rows of V
-            umma_a_in_tmem(tmem_o, tmem_p + kk * 8, smem_descriptor(v_addr + kk * 16 * 128, KV_TILE_HALF, 1024), idesc_o,
-                           (i > 0 || kk > 0) ? 1u : 0u);
+            umma_a_in_tmem(tmem_o, tmem_p + kk * 8, v_base + ((kk * 16 * 128) >> 4), idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
           if (c == 1 || i >= count_1) umma_commit(&sh->v_free[st]);
           if (i + 1 == count[c]) umma_commit(&sh->pv_done[c]);
           if (i + 1 < count[c]) {

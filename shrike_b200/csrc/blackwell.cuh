@@ -11,8 +11,11 @@
 
 namespace bw {
 
-constexpr unsigned WAIT_HINT_NS = 20000;   // one try_wait may sleep this long
-constexpr unsigned WAIT_LIMIT = 100000;    // tries before a wait gives up: about two seconds
+#ifndef SHRIKE_WAIT_HINT_NS
+#define SHRIKE_WAIT_HINT_NS 20000
+#endif
+constexpr unsigned WAIT_HINT_NS = SHRIKE_WAIT_HINT_NS;   // one try_wait may sleep this long
+constexpr unsigned WAIT_LIMIT = 2000000000u / (WAIT_HINT_NS < 100 ? 100 : WAIT_HINT_NS);   // tries before a wait gives up: about two seconds
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
 
