@@ -231,3 +231,49 @@ def test_padding_rows_of_a_decode_batch_store_nothing_and_come_last():
     assert builder.stage(portion, pad_to=8).s == 3
     for cache, _ in caches:
         cache_manager.free(cache)
+
+
+def test_batch_metadata_carries_each_entrys_first_position_and_pads_with_zero():
+    """`seq_start` lies beside `state_slot` in the packed block: a part with state can tell a request's
+    first portion from a later one without a host-side list."""
+    config = parse_config(TINY["A"])
+    runner = ModelRunner(config, dict(random_tensors(config, 0)), EmulatedOps(), "cpu", "float32", page_size=16,
+                         num_pages=16, max_slots=4)
+    caches = [runner.cache.open() for _ in range(3)]
+    starts, counts = [0, 7, 20], [5, 1, 3]
+    for cache, start, count in zip(caches, starts, counts):
+        runner.cache.append(cache, 0, start + count)
+    entries = [StepEntry(cache, [1] * count, start, [count - 1]) for cache, start, count in zip(caches, starts, counts)]
+    ctx = runner.builder.build(sorted(entries, key=lambda e: len(e.tokens) > 1))
+    assert ctx.seq_start.tolist() == [7, 0, 20] and ctx.state_slot.tolist() == [caches[1].slot, caches[0].slot, caches[2].slot]
+    assert ctx.q_start.tolist() == [0, 1, 6, 9] and ctx.ctx_len.tolist() == [8, 5, 23]
+    singles = [StepEntry(cache, [1], start + count, [0]) for cache, start, count in zip(caches, starts, counts)]
+    for cache, start, count in zip(caches, starts, counts):
+        runner.cache.append(cache, start + count, 1)
+    staged = runner.builder.stage(singles, pad_to=8)
+    padded = runner.builder.context(staged)
+    assert padded.seq_start.tolist() == [5, 8, 23, 0, 0, 0, 0, 0] and padded.state_slot.tolist()[3:] == [-1] * 5
+    for cache in caches:
+        runner.cache.free(cache)
+    assert runner.cache.whole()
+
+
+def test_opening_a_request_zeroes_its_state_before_the_step():
+    """The step function clears the state slots of requests opened since the last step; nothing else is touched."""
+    from shrike_b200.cache.manager import CacheManager
+    from shrike_b200.cache.storage import CacheStorage, state_bytes
+    from shrike_b200.parts.base import StateNeed
+
+    needs = {3: StateNeed((4, 2), "float32"), 5: StateNeed((6,), "float32")}
+    assert state_bytes(needs, 10) == 10 * (8 + 6) * 4
+    manager = CacheManager([], 16, [], 4)
+    storage = CacheStorage([], 16, [], needs, 4, torch.float32, "cpu")
+    for tensor in storage.state.values():
+        tensor.fill_(9.0)
+    a = manager.open()
+    storage.zero_slots(manager.take_opened())
+    assert float(storage.state[3][a.slot].abs().sum()) == 0 and float(storage.state[5][a.slot].abs().sum()) == 0
+    others = [s for s in range(4) if s != a.slot]
+    assert all(float(storage.state[3][s].min()) == 9.0 for s in others)
+    storage.zero_slots(manager.take_opened())   # nothing opened since: nothing cleared
+    assert all(float(storage.state[5][s].min()) == 9.0 for s in others)
