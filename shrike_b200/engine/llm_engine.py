@@ -195,41 +195,60 @@ class LLMEngine:
         return entries, sampled
 
     def _launch_ahead(self, batch, sampled):
-        """While the device runs a decode step: schedules, stages and launches the step after it,
-        whose input tokens the embedding kernel takes on the device from what this step draws.
-        Only in the steady state: every running request decodes, nobody waits, nobody reaches its
-        length limit with this token, and the pages for everybody's next token are there (so that
-        scheduling early preempts nobody whom a stop token, seen a moment later, would have
-        spared).  Returns the step in flight, or None.
+        """While the device runs a step: schedules, stages and launches the step after it.  A
+        request whose token is being drawn by the step in flight goes into the next one with the
+        id -1 - row, which the embedding kernel replaces on the device by what that row drew, so
+        neither the device nor the host waits for the other.  Done only when it changes nothing
+        but the timing: nobody reaches its length limit with the token in flight (its end frees
+        pages and a slot that scheduling early would not see), and the pages for whatever the
+        next step takes are free, so that scheduling early preempts nobody whom a stop token, seen
+        a moment later, would have spared.  Returns the step in flight, or None.
 
         A request that ends on a stop token while the next step is already in flight has one
         token computed in vain; its row of that step's output is dropped.  Its pages go back at
         once: whatever is given them later is launched later, and the device runs in order."""
-        if not self.launch_ahead or len(sampled) != len(batch) or self.scheduler.waiting:
-            return None
-        if len(batch) != len(self.scheduler.running) or any(n != 1 for _, n in batch):
+        if not self.launch_ahead:
             return None
         if any(r.num_generated + 1 >= r.sampling.max_new_tokens for r in sampled):
             return None
-        need = [0] * len(self.block_manager.num_free)
-        for request in sampled:
-            for group, pages in enumerate(self.block_manager.pages_needed(request.cache, request.num_computed_tokens, 1)):
-                need[group] += pages
-        if any(n > free for n, free in zip(need, self.block_manager.num_free)):
+        scheduler, manager = self.scheduler, self.block_manager
+        steady = (len(sampled) == len(batch) and not scheduler.waiting and len(batch) == len(scheduler.running)
+                  and all(n == 1 for _, n in batch))
+        if steady:   # every running request decodes: what the next step takes is known exactly
+            need = [0] * len(manager.num_free)
+            for request in sampled:
+                for group, pages in enumerate(manager.pages_needed(request.cache, request.num_computed_tokens, 1)):
+                    need[group] += pages
+        else:        # portions, arrivals: at most the token budget in new pages, and one more per request that may run
+            candidates = min(len(scheduler.running) + len(scheduler.waiting), scheduler.max_running)
+            need = [manager.blocks_for(scheduler.max_tokens_per_step) + candidates + 1] * len(manager.num_free)
+        if any(n > free for n, free in zip(need, manager.num_free)):
             return None
-        preemptions = self.scheduler.num_preemptions
-        ahead = self.scheduler.schedule()
-        if (self.scheduler.num_preemptions != preemptions or len(ahead) != len(batch)
-                or any(n != 1 or not r.prefill_done for r, n in ahead)):
+        preemptions = scheduler.num_preemptions
+        ahead = scheduler.schedule()
+        if not ahead or scheduler.num_preemptions != preemptions:
             return None   # scheduling again at the next step does no harm: reserved pages are kept
         row_of = {request.req_id: row for row, request in enumerate(sampled)}
-        entries = []
-        for request, _ in ahead:   # this step's token is not appended yet: it will sit at num_tokens
+        entries, sampled_ahead = [], []
+        for request, num_new in ahead:
+            start, known = request.num_computed_tokens, request.num_tokens
             params = request.sampling
-            sampling = (params.temperature, params.top_p,
-                        step_seed(self._request_seed[request.req_id], request.num_tokens + 1))
-            entries.append(StepEntry(request.cache, [-1 - row_of[request.req_id]], request.num_computed_tokens, [0], sampling))
-        return self._launch(ahead, entries, [r for r, _ in ahead])
+            if request.req_id in row_of:
+                # its newest token is still on the device: it will sit at position `known`
+                if start != known or num_new != 1:
+                    raise AssertionError("a request whose token is in flight was scheduled for anything but that token")
+                sampling = (params.temperature, params.top_p, step_seed(self._request_seed[request.req_id], known + 1))
+                entries.append(StepEntry(request.cache, [-1 - row_of[request.req_id]], start, [0], sampling))
+                sampled_ahead.append(request)
+                continue
+            reaches_end = start + num_new >= known
+            sampling = None
+            if reaches_end:
+                sampling = (params.temperature, params.top_p, step_seed(self._request_seed[request.req_id], known))
+                sampled_ahead.append(request)
+            entries.append(StepEntry(request.cache, request.token_ids[start: start + num_new], start,
+                                     [num_new - 1] if reaches_end else [], sampling))
+        return self._launch(ahead, entries, sampled_ahead)
 
     def _launch(self, batch, entries, sampled):
         result = self.runner.step(entries, sample=bool(sampled))

@@ -17,6 +17,7 @@ part-by-part path: `LayerProgram.serves` says which.
 from __future__ import annotations
 
 import ctypes
+import weakref
 
 import torch
 
@@ -78,7 +79,7 @@ class LayerProgram:
     WORKSPACE_BYTES = 32 << 20
 
     def __init__(self, ops):
-        self.ops = ops
+        self.ops = weakref.proxy(ops)   # the kernels own this object, not the other way round: no cycle to collect
         self.lib = build.layer_program_library()
         self.lib.shrike_decoder_layer.argtypes = [_P, _P, _P, _P, _I, _I, _LL, _P]
         self.lib.shrike_decoder_layer.restype = _I
@@ -89,7 +90,6 @@ class LayerProgram:
         self._fn_refs: dict = {}
         self._workspace = None
         self._warm = False
-        self._layers: dict = {}
 
     # ---- which layers -------------------------------------------------------------
     def serves(self, mixer, mixer_norm, feed_forward, feed_forward_norm) -> bool:
@@ -148,10 +148,11 @@ class LayerProgram:
         return ref
 
     # ---- one layer ----------------------------------------------------------------
-    def _constants(self, mixer, mixer_norm, feed_forward, feed_forward_norm, ctx, run):
-        """The layer's ShrikeLayerConst, built once per (layer, run of the order, cache pool)."""
-        key = (id(mixer), run.cache, run.writes_cache, id(ctx.storage))
-        held = self._layers.get(key)
+    def _constants(self, held_by_block: dict, mixer, mixer_norm, feed_forward, feed_forward_norm, ctx, run):
+        """The layer's ShrikeLayerConst, built once per (run of the order, cache pool) and kept by the
+        block (`held_by_block`): addresses only, valid as long as the block's parts and the pool are."""
+        key = (run.cache, run.writes_cache, id(ctx.storage))
+        held = held_by_block.get(key)
         if held is None:
             spec, ffn = mixer.spec, feed_forward.spec
             group, keys, values = ctx.storage.keys_values(run.cache)
@@ -167,8 +168,7 @@ class LayerProgram:
                 w_down=feed_forward.w_down.data_ptr(), inv_freq=None if table is None else table.data_ptr(),
                 keys=keys.data_ptr() if run.writes_cache else None, values=values.data_ptr() if run.writes_cache else None,
                 read_keys=keys.data_ptr(), read_values=values.data_ptr())
-            held = (const, group, keys.shape[1], (mixer, feed_forward, mixer_norm, feed_forward_norm, keys, values))
-            self._layers[key] = held
+            held = held_by_block[key] = (const, group, keys.shape[1])
         return held
 
     def _step(self, mixer, feed_forward, ctx, group, page_size):
@@ -229,11 +229,12 @@ class LayerProgram:
         cache[key] = held
         return held
 
-    def run(self, mixer, mixer_norm, feed_forward, feed_forward_norm, resid, delta, ctx, run):
+    def run(self, held_by_block, mixer, mixer_norm, feed_forward, feed_forward_norm, resid, delta, ctx, run):
         """Issues the layer; returns what the next norm has to add to the residual (the
-        feed-forward's output: an array [N, W] or a stack of K-split slices)."""
+        feed-forward's output: an array [N, W] or a stack of K-split slices).  `held_by_block` is a
+        dictionary the calling block keeps for this program's per-layer constants."""
         ops = self.ops
-        const, group, page_size, _alive = self._constants(mixer, mixer_norm, feed_forward, feed_forward_norm, ctx, run)
+        const, group, page_size = self._constants(held_by_block, mixer, mixer_norm, feed_forward, feed_forward_norm, ctx, run)
         step, down_target, own, library = self._step(mixer, feed_forward, ctx, group, page_size)
         step.resid = resid.data_ptr()
         if delta is None:

@@ -21,6 +21,7 @@ class PreNormBlock:
         self.feed_forward_norm = feed_forward_norm
         self._program = None
         self._asked = False
+        self._native_constants: dict = {}   # what the native issue keeps per run of this layer
 
     def _native(self):
         if not self._asked:
@@ -39,7 +40,8 @@ class PreNormBlock:
     def forward(self, resid, delta, ctx, run):
         program = self._native()
         if program is not None and getattr(program.ops, "native_layers", False):
-            return resid, program.run(self.mixer, self.mixer_norm, self.feed_forward, self.feed_forward_norm, resid, delta, ctx, run)
+            return resid, program.run(self._native_constants, self.mixer, self.mixer_norm, self.feed_forward,
+                                      self.feed_forward_norm, resid, delta, ctx, run)
         hidden = self.mixer_norm.add_norm(resid, delta)
         delta = self.mixer.forward(hidden, ctx, run)
         hidden = self.feed_forward_norm.add_norm(resid, delta)

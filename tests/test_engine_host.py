@@ -140,8 +140,10 @@ def _run_script(launch_ahead: bool, pool: int):
            engine.add_request(prompts[1], SamplingParams(max_new_tokens=9, temperature=0.8, top_p=0.9, seed=3)),
            engine.add_request(prompts[2], SamplingParams(max_new_tokens=25, ignore_eos=True))]
     log, staged_steps, step = [], 0, 0
+    mixed_ahead = 0
     while engine.has_work:
         staged_steps += engine._flight is not None
+        mixed_ahead += engine._flight is not None and any(n > 1 for _, n in engine._flight[0])
         for out in engine.step():
             log.append((out.req_id - ids[0], out.token_id, out.finished, out.finish_reason))
         step += 1
@@ -151,8 +153,8 @@ def _run_script(launch_ahead: bool, pool: int):
             engine.abort(ids[2])
         if step == 11:
             ids.append(engine.add_request(prompts[4], SamplingParams(max_new_tokens=5, temperature=1.1, seed=9)))
-    assert engine.block_manager.whole() and not engine.requests 
-    return log, staged_steps, engine.scheduler.num_preemptions
+    assert engine.block_manager.whole() and not engine.requests
+    return log, (staged_steps, mixed_ahead), engine.scheduler.num_preemptions
 
 
 def _by_request(log):
@@ -164,14 +166,17 @@ def _by_request(log):
 
 @pytest.mark.parametrize("pool", [40, 8])
 def test_launching_the_next_step_ahead_changes_no_token(pool):
-    """In steady decoding the engine launches a step before the tokens of the step before it
-    are read back (the embedding takes them on the device).  Arrivals, a stop token, length
+    """The engine launches a step before the tokens of the step before it are read back (the
+    embedding takes them on the device): in steady decoding, and, where pages are plenty, also
+    steps with portions of prompts and newly admitted requests.  Arrivals, a stop token, length
     limits, an abort and (with the small pool) preemption all fall between such steps; every
     request gets the tokens, the end and the reason of the plain loop.  Only the interleaving
     may differ: a request that arrives while a step is in flight joins one step later."""
-    plain, none_ahead, _ = _run_script(False, pool)
-    ahead, launched_ahead, preemptions = _run_script(True, pool)
+    plain, (none_ahead, _), _ = _run_script(False, pool)
+    ahead, (launched_ahead, with_portions), preemptions = _run_script(True, pool)
     assert none_ahead == 0 and launched_ahead >= 4
+    if pool == 40:
+        assert with_portions >= 1, "no step with a portion was launched ahead although pages were plenty"
     assert _by_request(ahead) == _by_request(plain)
     assert any(reason == "stop" for *_, reason in plain) and any(reason == "length" for *_, reason in plain)
     if pool == 8:
