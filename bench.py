@@ -8,7 +8,8 @@ at batch 8 and a context of 1,024 tokens, timed with CUDA events around exactly 
 steps; `e2e` is the same measured through `LLMEngine.step()`, host token ids in and
 out; `prefill` is one 2,048-token prompt in one step; `roofline` relates the bytes a
 decode step must read (every weight once, the cache of the live requests) to its time;
-`points` holds decoding at batch 1 and 64.  Weights are random (seeded), token ids
+`points` holds decoding at batch 1 and 64; `mixed` the scheduler end to end (64 requests of mixed
+lengths at Qwen2.5-1.5B widths, `--workload mixed` alone).  Weights are random (seeded), token ids
 uniform random: no checkpoint and no dataset is read.  Peaks come from
 MEASURED_PEAKS.json beside this file when present, else from an earlier measurement
 on the same GPU pool.  `--shape 14b --context 8192` (and the like) time the same
@@ -690,6 +691,7 @@ def main():
     parser.add_argument("--workload", default="decode", choices=["decode", "mixed"],
                         help="decode: the headline line; mixed: 64 requests through the scheduler at 1.5B shape")
     parser.add_argument("--num-blocks", type=int, default=0, help="cache pages for --workload mixed (few pages force preemption)")
+    parser.add_argument("--skip-mixed", action="store_true", help="leave the mixed workload out of the default line")
     parser.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                         help="prompt length of --case attention_portions")
     parser.add_argument("--case", default=None,
@@ -711,6 +713,18 @@ def main():
         print(json.dumps(run_mixed(args)))
         return
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if args.impl != "reference" and args.shape == "7b" and not args.layers and not args.skip_mixed:
+        # the scheduler end to end, beside the headline: 64 requests of mixed lengths at 1.5B widths
+        import gc
+
+        import torch
+
+        gc.collect()
+        torch.cuda.empty_cache()
+        mixed_args = argparse.Namespace(**vars(args))
+        mixed_args.layers, mixed_args.num_blocks = 0, 0
+        mixed = run_mixed(mixed_args)
+        result["mixed"] = {key: mixed[key] for key in ("value", "unit", "seconds", "steps", "requests", "model", "budget", "preemptions")}
     print(json.dumps(result))
 
 

@@ -22,6 +22,7 @@ from tests.tiny_configs import TINY
 
 pytestmark = pytest.mark.gpu
 LENGTHS = [5, 17, 33, 70, 1, 130, 2, 64]
+LONG = {"D": [5, 300, 33, 70, 1, 130, 2, 64]}   # tiny D: one request long enough for several key steps of the tensor-core kernel
 _cache = {}
 
 
@@ -29,7 +30,7 @@ def setup(tmp_path_factory, key, dtype):
     if key not in _cache:
         folder = make_model_folder(tmp_path_factory.mktemp(f"model_{key}"), key)
         weights = read_weights(folder)
-        requests = {f"r{i}": random_tokens(TINY[key]["vocab_size"], n, 100 + i) for i, n in enumerate(LENGTHS)}
+        requests = {f"r{i}": random_tokens(TINY[key]["vocab_size"], n, 100 + i) for i, n in enumerate(LONG.get(key, LENGTHS))}
         _cache[key] = (folder, weights, requests, {})
     folder, weights, requests, refs = _cache[key]
     if dtype not in refs:
@@ -49,7 +50,7 @@ WAYS = {
 # every tiny configuration at the page size it is named with (A 16, B 8, C 16), and two more
 # page sizes so that a page's edge falls elsewhere among the same portions: 32, and 24, which
 # divides neither 64 nor the portion sizes
-MODEL_PAGES = [("A", 16), ("B", 8), ("C", 16), ("B", 32), ("A", 8), ("C", 24)]
+MODEL_PAGES = [("A", 16), ("B", 8), ("C", 16), ("B", 32), ("A", 8), ("C", 24), ("D", 16), ("D", 8)]
 
 
 @pytest.mark.parametrize("way", list(WAYS))

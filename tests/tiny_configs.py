@@ -30,9 +30,20 @@ TINY_C = dict(
     max_position_embeddings=4096, eos_token_id=330, torch_dtype="float32",
 )
 
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
-SEEDS = {"A": 0, "B": 1, "C": 2}
-PAGE_SIZES = {"A": 16, "B": 8, "C": 16}
+# Heads of 64: the head size (with 128) that the tensor-core attention kernel for portions and the
+# page-wise single-token kernel serve, so that a replay goes through them; width 384,
+# six query heads on two kv heads, vocabulary 509 (prime), untied.
+TINY_D = dict(
+    architectures=["Qwen2ForCausalLM"], model_type="qwen2",
+    hidden_size=384, intermediate_size=416, num_hidden_layers=2,
+    num_attention_heads=6, num_key_value_heads=2, head_dim=64, vocab_size=509,
+    rms_norm_eps=2e-6, rope_theta=300000.0, tie_word_embeddings=False,
+    max_position_embeddings=4096, eos_token_id=[508, 507], torch_dtype="float32",
+)
+
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3}
+PAGE_SIZES = {"A": 16, "B": 8, "C": 16, "D": 16}
 
 
 def windows_of(raw: dict) -> dict:
