@@ -67,6 +67,32 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// The softmax threads are short of issue slots, not of arithmetic: the maximum of three in one
+// instruction, and multiply-add and add on pairs of floats (one instruction for two elements).
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ unsigned long long pair_of(float lo, float hi) {
+  unsigned long long d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+  return d;
+}
+__device__ __forceinline__ void halves_of(unsigned long long v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma_pair(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ unsigned long long add_pair(unsigned long long a, unsigned long long b) {
+  unsigned long long d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
 struct Args {
   const int* block_table;
   const int* q_start;
@@ -123,14 +149,15 @@ namespace pair {
 constexpr int ROWS = 2 * BM;                  // query rows per CTA
 constexpr int KEYS = 128;                     // keys per step
 constexpr int PSTAGES = 2;
-constexpr int PTHREADS = 64 + 2 * 128;
+constexpr int PTHREADS = 128 + 2 * 128;   // producer, two issuers, tensor-memory owner; four softmax warps per chain
 constexpr int KV_TILE_HALF = KEYS * 128;      // bytes of one 64-element-wide sub-tile of a key (or value) tile
 constexpr int KV_TILE = HALVES * KV_TILE_HALF;
-constexpr unsigned CHAIN_COLS = 256;          // S at +0 (P over its first 64 columns), O at +128
+constexpr int HALF_KEYS = KEYS / 2;            // keys per softmax step: S has two buffers of this many columns
+constexpr unsigned CHAIN_COLS = 256;          // S buffers at +0 and +64 (P over a buffer's first 32 columns), O at +128
 constexpr unsigned PAIR_TMEM_COLS = 512;
 
 struct PairShared {
-  unsigned long long q_full, s_full[2], p_full[2], pv_done[2];
+  unsigned long long q_full, s_full[2][2], p_full[2][2], pv_done[2], pv_last[2], stagger;   // [chain][S buffer]
   unsigned long long k_full[PSTAGES], k_free[PSTAGES], v_full[PSTAGES], v_free[PSTAGES];
   unsigned tmem_base;
   volatile int abort;
@@ -167,29 +194,7 @@ portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   PairShared* sh = reinterpret_cast<PairShared*>(v_tiles + PSTAGES * KV_TILE);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  if (threadIdx.x == 0) {
-    mbar_init(&sh->q_full, 1);
-    for (int c = 0; c < 2; ++c) {
-      mbar_init(&sh->s_full[c], 1);
-      mbar_init(&sh->p_full[c], 128);
-      mbar_init(&sh->pv_done[c], 1);
-    }
-    for (int s = 0; s < PSTAGES; ++s) {
-      mbar_init(&sh->k_full[s], 1);
-      mbar_init(&sh->k_free[s], 1);
-      mbar_init(&sh->v_full[s], 1);
-      mbar_init(&sh->v_free[s], 1);
-    }
-    sh->abort = 0;
-    mbar_init_fence();
-  }
-  if (warp == 1) tmem_alloc(&sh->tmem_base, PAIR_TMEM_COLS);
-  fence_before_sync();
-  __syncthreads();
-  fence_after_sync();
-  let_dependents_start();
-  wait_for_previous();   // the query and the newest keys come from the kernel before this one
-
+  // (lengths and positions are step metadata, written before the step's kernels: readable before the wait below)
   const int pos0 = args.ctx_len[seq] - q_len;                   // position of the first new token
   const int kv_head = head / (args.num_heads / args.num_kv_heads);
   // chain c owns rows tile_start + 128 c ...; rows_c <= 0: the chain has none
@@ -206,195 +211,242 @@ portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   const int count_0 = max(0, min(last_tile, hi_0 / KEYS) - tile_lo + 1);
   const int count_1 = rows_1 > 0 ? max(0, min(last_tile, hi_1 / KEYS) - tile_lo + 1) : 0;
   const int num_tiles = max(count_0, count_1);
+  // the same in steps of 64 keys: a chain's last tile may need its first half only
+  const int steps_0 = count_0 > 0 ? min(2 * count_0, hi_0 / HALF_KEYS - 2 * tile_lo + 1) : 0;
+  const int steps_1 = count_1 > 0 ? min(2 * count_1, hi_1 / HALF_KEYS - 2 * tile_lo + 1) : 0;
 
-  if (warp == 0) {
-    // lane 0 waits for the stage and arms its barrier, then lane pg looks up page pg of the tile and
-    // issues that page's boxes (K and V, every 64-element half)
+  const unsigned users = (steps_0 > 0 ? 1u : 0u) + (steps_1 > 0 ? 1u : 0u);   // chains that read the key and value stages
+  if (threadIdx.x == 0) {
+    mbar_init(&sh->q_full, 1);
+    for (int c = 0; c < 2; ++c) {
+      for (int b = 0; b < 2; ++b) {
+        mbar_init(&sh->s_full[c][b], 1);
+        mbar_init(&sh->p_full[c][b], 128);
+      }
+      mbar_init(&sh->pv_done[c], 1);
+      mbar_init(&sh->pv_last[c], 1);
+    }
+    for (int s = 0; s < PSTAGES; ++s) {
+      mbar_init(&sh->k_full[s], 1);
+      mbar_init(&sh->k_free[s], users > 0 ? users : 1u);
+      mbar_init(&sh->v_full[s], 1);
+      mbar_init(&sh->v_free[s], users > 0 ? users : 1u);
+    }
+    mbar_init(&sh->stagger, 1);
+    sh->abort = 0;
+    mbar_init_fence();
+  }
+  if (warp == 3) tmem_alloc(&sh->tmem_base, PAIR_TMEM_COLS);
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  let_dependents_start();
+  wait_for_previous();   // the query and the newest keys come from the kernel before this one
+
+  if (warp == 0 || warp == 3) {
+    // Warp 0 brings the query tiles and the keys, warp 3 the values: lane 0 waits for the stage and arms
+    // its barrier, then lane pg issues the boxes of page pg of the tile (every 64-element half).  Handing
+    // a box to the copy engine costs the issuing warp about 50 ns, and a tile of 16-token pages is 16
+    // boxes of keys and 16 of values: one warp for both would need longer per tile than the tensor
+    // pipe does.
+    const bool for_keys = warp == 0;
     const int* table = args.block_table + static_cast<size_t>(seq) * args.max_blocks;
     const int pages_per_tile = KEYS / args.page_size;
     const int nowhere = args.num_pages * args.page_size;      // a row coordinate outside the cache: reads zeros
-    if (lane == 0 && num_tiles > 0) {
+    if (for_keys && lane == 0 && num_tiles > 0) {
       mbar_expect_tx(&sh->q_full, 2 * Q_BYTES);
       for (int c = 0; c < 2; ++c)
         for (int h = 0; h < HALVES; ++h)
           tma_load_2d(q_tiles + c * Q_BYTES + h * Q_HALF, &map_q, &sh->q_full, head * D + h * 64, start + tile_start + c * BM);
     }
-    auto look_up = [&](int i) -> int {
-      if (lane >= pages_per_tile || i >= num_tiles) return -1;
-      const int key0 = (tile_lo + i) * KEYS + lane * args.page_size;
+    // Page ids come a chunk of 32 at a time (lane l: page l of the chunk, several tiles' worth), the
+    // next chunk while this one is used: a lookup per tile would stall the warp for a trip to L2 in
+    // every iteration.
+    const int tiles_per_chunk = 32 / pages_per_tile;
+    auto load_chunk = [&](int chunk) -> int {
+      const int key0 = tile_lo * KEYS + (chunk * 32 + lane) * args.page_size;
       const int block = key0 / args.page_size;
-      const int page = (key0 <= hi && block < args.max_blocks) ? table[block] : -1;
-      return page >= args.num_pages ? -1 : page;
+      return (chunk * tiles_per_chunk < num_tiles && key0 <= hi && block < args.max_blocks) ? table[block] : -1;
     };
-    int page = look_up(0), page_1 = look_up(1), page_2 = look_up(2);
+    unsigned char* const tiles = for_keys ? k_tiles : v_tiles;
+    unsigned long long* const full = for_keys ? sh->k_full : sh->v_full;
+    unsigned long long* const free_again = for_keys ? sh->k_free : sh->v_free;
+    const CUtensorMap* const map = for_keys ? &map_k : &map_v;
+    int chunk_pages = load_chunk(0), next_pages = load_chunk(1);
     int issued = 0;
     for (int i = 0; i < num_tiles; ++i) {
       const int s = i % PSTAGES;
       const unsigned phase = (i / PSTAGES) & 1;
-      const int page_3 = look_up(i + 3);
-      unsigned char* k_tile = k_tiles + s * KV_TILE;
-      unsigned char* v_tile = v_tiles + s * KV_TILE;
+      const int within = i % tiles_per_chunk;
+      if (within == 0 && i > 0) {
+        chunk_pages = next_pages;
+        next_pages = load_chunk(i / tiles_per_chunk + 1);
+      }
+      int page = __shfl_sync(0xffffffffu, chunk_pages, within * pages_per_tile + (lane % pages_per_tile));
+      if (page >= args.num_pages) page = -1;
+      unsigned char* tile = tiles + s * KV_TILE;
       const int y = page < 0 ? nowhere : page * args.page_size;
       const int at = lane * args.page_size * 128;
       int ok = 1;
       if (lane == 0) {
-        ok = mbar_wait(&sh->k_free[s], phase ^ 1, &sh->abort, args.status, ERR_PRODUCER) ? 1 : 0;
-        if (ok) mbar_expect_tx(&sh->k_full[s], KV_TILE);
+        ok = mbar_wait(&free_again[s], phase ^ 1, &sh->abort, args.status, ERR_PRODUCER) ? 1 : 0;
+        if (ok) mbar_expect_tx(&full[s], KV_TILE);
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       if (lane < pages_per_tile)
-        for (int h = 0; h < HALVES; ++h) tma_load_2d(k_tile + h * KV_TILE_HALF + at, &map_k, &sh->k_full[s], kv_head * D + h * 64, y);
-      if (lane == 0) {
-        ok = mbar_wait(&sh->v_free[s], phase ^ 1, &sh->abort, args.status, ERR_PRODUCER) ? 1 : 0;
-        if (ok) mbar_expect_tx(&sh->v_full[s], KV_TILE);
-      }
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) break;
-      if (lane < pages_per_tile)
-        for (int h = 0; h < HALVES; ++h) tma_load_2d(v_tile + h * KV_TILE_HALF + at, &map_v, &sh->v_full[s], kv_head * D + h * 64, y);
+        for (int h = 0; h < HALVES; ++h) tma_load_2d(tile + h * KV_TILE_HALF + at, map, &full[s], kv_head * D + h * 64, y);
       issued = i + 1;
-      page = page_1;
-      page_1 = page_2;
-      page_2 = page_3;
     }
     if (lane == 0 && sh->abort) {   // copies may still be in flight: wait for the stages armed last
       for (int i = max(0, issued - PSTAGES); i < issued; ++i) {
         bool landed = false;
-        for (unsigned tries = 0; tries < WAIT_LIMIT && !landed; ++tries)
-          landed = mbar_try_wait(&sh->k_full[i % PSTAGES], (i / PSTAGES) & 1) && mbar_try_wait(&sh->v_full[i % PSTAGES], (i / PSTAGES) & 1);
+        for (unsigned tries = 0; tries < WAIT_LIMIT && !landed; ++tries) landed = mbar_try_wait(&full[i % PSTAGES], (i / PSTAGES) & 1);
         if (!landed && args.status != nullptr) *args.status = ERR_DRAIN;
       }
-      bool landed = num_tiles <= 0;
+      bool landed = !for_keys || num_tiles <= 0;
       for (unsigned tries = 0; tries < WAIT_LIMIT && !landed; ++tries) landed = mbar_try_wait(&sh->q_full, 0);
     }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      const unsigned idesc_s = instruction_descriptor(BM, KEYS, false);
+  } else if (warp == 1 || warp == 2) {
+    // One issuing thread per chain: each waits for its own chain's probabilities only, and the two
+    // share the work of forming descriptors and issuing (a single thread was the CTA's bottleneck).
+    const int c = warp - 1;
+    const int steps = c == 0 ? steps_0 : steps_1;
+    if (lane == 0 && steps > 0) {
+      const unsigned idesc_s = instruction_descriptor(BM, HALF_KEYS, false);
       const unsigned idesc_o = instruction_descriptor(BM, D, true);
-      const unsigned tmem = sh->tmem_base;
-      const int count[2] = {count_0, count_1};
-      // One thread issues every MMA of the CTA, 32 per step, so what it does between two of them counts:
-      // the operand descriptors are formed once (a descriptor's low bits are the address in 16-byte
-      // units, so a tile further on is an addition), not per instruction.
-      const unsigned long long q_desc[2] = {smem_descriptor(smem_u32(q_tiles)), smem_descriptor(smem_u32(q_tiles + Q_BYTES))};
+      const unsigned tmem_chain = sh->tmem_base + c * CHAIN_COLS, tmem_o = tmem_chain + KEYS;
+      // operand descriptors are formed once (a descriptor's low bits are the address in 16-byte
+      // units, so a tile further on is an addition), not per instruction
+      const unsigned long long q_base = smem_descriptor(smem_u32(q_tiles + c * Q_BYTES));
       const unsigned long long k_desc0 = smem_descriptor(smem_u32(k_tiles));
       const unsigned long long v_desc0 = smem_descriptor(smem_u32(v_tiles), KV_TILE_HALF, 1024);
-      // S of chain c for tile i; the chain that needs a key stage last hands it back
-      auto issue_scores = [&](int c, int i) {
-        const unsigned long long q_base = q_desc[c], k_base = k_desc0 + static_cast<unsigned>(((i % PSTAGES) * KV_TILE) >> 4);
-        const unsigned tmem_s = tmem + c * CHAIN_COLS;
+      bool ok = mbar_wait(&sh->q_full, 0, &sh->abort, args.status, ERR_MMA);
+      int keys_ready = -1, values_ready = -1;   // the newest tile whose keys (values) are known to have landed
+      // S for step h (keys 64 h ... of this CTA's share) into the chain's buffer h & 1; the chain's last
+      // use of a stage hands it back (the stage is free when every chain that uses it has)
+      auto issue_scores = [&](int h) {
+        const int i = h >> 1, st = i % PSTAGES;
+        if (keys_ready < i) {
+          ok = mbar_wait(&sh->k_full[st], (i / PSTAGES) & 1, &sh->abort, args.status, ERR_MMA);
+          if (!ok) return;
+          keys_ready = i;
+          fence_after_sync();
+        }
+        const unsigned long long k_base = k_desc0 + static_cast<unsigned>((st * KV_TILE + (h & 1) * HALF_KEYS * 128) >> 4);
+        const unsigned tmem_s = tmem_chain + (h & 1) * HALF_KEYS;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
           umma(tmem_s, q_base + (((kk / 4) * Q_HALF + (kk % 4) * 32) >> 4), k_base + (((kk / 4) * KV_TILE_HALF + (kk % 4) * 32) >> 4), idesc_s,
                kk > 0 ? 1u : 0u);
-        umma_commit(&sh->s_full[c]);
-        if (c == 1 || i >= count_1) umma_commit(&sh->k_free[i % PSTAGES]);
+        umma_commit(&sh->s_full[c][h & 1]);
+        if ((h & 1) || h + 1 == steps) umma_commit(&sh->k_free[st]);
       };
-      bool ok = num_tiles > 0 && mbar_wait(&sh->q_full, 0, &sh->abort, args.status, ERR_MMA);
-      if (ok) ok = mbar_wait(&sh->k_full[0], 0, &sh->abort, args.status, ERR_MMA);
-      if (ok) {
-        fence_after_sync();
-        if (count_0 > 0) issue_scores(0, 0);
-        if (count_1 > 0) issue_scores(1, 0);
-      }
-      for (int i = 0; i < num_tiles && ok; ++i) {
-        const int st = i % PSTAGES;
-        bool keys_checked = false;
-        for (int c = 0; c < 2 && ok; ++c) {
-          if (i >= count[c]) continue;
-          if (c == 0 || i >= count_0)   // the first chain of this tile waits for the values
-            ok = mbar_wait(&sh->v_full[st], (i / PSTAGES) & 1, &sh->abort, args.status, ERR_MMA);
-          if (ok) ok = mbar_wait(&sh->p_full[c], i & 1, &sh->abort, args.status, ERR_MMA);
-          if (!ok) break;
-          fence_after_sync();
-          const unsigned long long v_base = v_desc0 + static_cast<unsigned>((st * KV_TILE) >> 4);
-          const unsigned tmem_p = tmem + c * CHAIN_COLS, tmem_o = tmem_p + KEYS;
-#pragma unroll
-          for (int kk = 0; kk < KEYS / 16; ++kk)   // 16 keys a step: 8 packed columns of P, 16 rows of V
-            umma_a_in_tmem(tmem_o, tmem_p + kk * 8, v_base + ((kk * 16 * 128) >> 4), idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
-          if (c == 1 || i >= count_1) umma_commit(&sh->v_free[st]);
-          if (i + 1 == count[c]) umma_commit(&sh->pv_done[c]);
-          if (i + 1 < count[c]) {
-            if (!keys_checked) {
-              ok = mbar_wait(&sh->k_full[(i + 1) % PSTAGES], ((i + 1) / PSTAGES) & 1, &sh->abort, args.status, ERR_MMA);
-              keys_checked = true;
-              if (!ok) break;
-              fence_after_sync();
-            }
-            issue_scores(c, i + 1);
-          }
+      // The two chains share the tensor pipe; started together they stay in step, issue their
+      // instructions in the same bursts and idle in the same gaps.  The later chain starts when the
+      // earlier one has its first probabilities: half a period behind.
+      if (ok && c == 1 && steps_0 > 0) ok = mbar_wait(&sh->stagger, 0, &sh->abort, args.status, ERR_MMA);
+      if (ok) fence_after_sync();
+      for (int h = 0; h < 2 && h < steps && ok; ++h) issue_scores(h);
+      for (int h = 0; h < steps && ok; ++h) {
+        const int i = h >> 1, st = i % PSTAGES;
+        if (values_ready < i) {
+          ok = mbar_wait(&sh->v_full[st], (i / PSTAGES) & 1, &sh->abort, args.status, ERR_MMA);
+          values_ready = i;
         }
+        if (ok) ok = mbar_wait(&sh->p_full[c][h & 1], (h >> 1) & 1, &sh->abort, args.status, ERR_MMA);
+        if (!ok) break;
+        if (c == 0 && h == 0) mbar_arrive(&sh->stagger);
+        fence_after_sync();
+        const unsigned long long v_base = v_desc0 + static_cast<unsigned>((st * KV_TILE + (h & 1) * HALF_KEYS * 128) >> 4);
+        const unsigned tmem_p = tmem_chain + (h & 1) * HALF_KEYS;
+#pragma unroll
+        for (int kk = 0; kk < HALF_KEYS / 16; ++kk)   // 16 keys a step: 8 packed columns of P, 16 rows of V
+          umma_a_in_tmem(tmem_o, tmem_p + kk * 8, v_base + ((kk * 16 * 128) >> 4), idesc_o, (h > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&sh->pv_done[c]);          // phase h of the chain: O holds the keys up to step h
+        if (h + 1 == steps) umma_commit(&sh->pv_last[c]);
+        if ((h & 1) || h + 1 == steps) umma_commit(&sh->v_free[st]);
+        if (h + 2 < steps) issue_scores(h + 2);   // into the buffer whose P was just read (the pipe runs a thread's instructions in order)
       }
     }
-  } else {
-    const int chain = (warp - 2) >> 2, quarter = warp & 3;
+  } else if (warp >= 4) {
+    const int chain = (warp - 4) >> 2, quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const int t = tile_start + chain * BM + row;
-    const int my_count = chain == 0 ? count_0 : count_1;
+    const int my_steps = chain == 0 ? steps_0 : steps_1;
     const int last = t < q_len ? pos0 + t : -1;
     const int first = args.window > 0 ? max(0, last - args.window + 1) : 0;
     const unsigned lane_base = static_cast<unsigned>(quarter * 32) << 16;
-    const unsigned tmem_s = sh->tmem_base + chain * CHAIN_COLS + lane_base, tmem_o = tmem_s + KEYS;
+    const unsigned tmem_chain = sh->tmem_base + chain * CHAIN_COLS + lane_base, tmem_o = tmem_chain + KEYS;
     float row_max = -INFINITY, row_sum = 0.f;
     bool ok = true;
-    for (int i = 0; i < my_count && ok; ++i) {
-      ok = mbar_wait(&sh->s_full[chain], i & 1, &sh->abort, args.status, ERR_SOFTMAX);
+    for (int h = 0; h < my_steps && ok; ++h) {
+      const unsigned tmem_s = tmem_chain + (h & 1) * HALF_KEYS;
+      ok = mbar_wait(&sh->s_full[chain][h & 1], (h >> 1) & 1, &sh->abort, args.status, ERR_SOFTMAX);
       ok = __all_sync(0xffffffffu, ok);   // the warp stays together: the tensor-memory accesses below are warp-wide
       if (!ok) break;
       fence_after_sync();
-      unsigned v[4][32];
-#pragma unroll
-      for (int g = 0; g < 4; ++g) tmem_load32(tmem_s + g * 32, v[g]);
+      unsigned v[2][32];
+      tmem_load32(tmem_s, v[0]);
+      tmem_load32(tmem_s + 32, v[1]);
       tmem_wait_load();
-      const int key_base = (tile_lo + i) * KEYS;
-      if (key_base < first || key_base + KEYS - 1 > last) {   // only tiles at the edge of the row's range pay for masking
+      const int key_base = tile_lo * KEYS + h * HALF_KEYS;
+      if (key_base < first || key_base + HALF_KEYS - 1 > last) {   // only steps at the edge of the row's range pay for masking
 #pragma unroll
-        for (int g = 0; g < 4; ++g)
+        for (int g = 0; g < 2; ++g)
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const int key = key_base + g * 32 + j;
             if (key < first || key > last) v[g][j] = 0xff800000u;   // -inf
           }
       }
-      float tile_max = -INFINITY;
+      float part_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains of dependent instructions, not one
 #pragma unroll
-      for (int g = 0; g < 4; ++g)
+      for (int g = 0; g < 2; ++g)
 #pragma unroll
-        for (int j = 0; j < 32; ++j) tile_max = fmaxf(tile_max, __uint_as_float(v[g][j]));
-      tile_max *= args.scale_log2;
+        for (int j = 0; j < 32; j += 8)
+#pragma unroll
+          for (int a = 0; a < 4; ++a) part_max[a] = max3(part_max[a], __uint_as_float(v[g][j + 2 * a]), __uint_as_float(v[g][j + 2 * a + 1]));
+      float step_max = fmaxf(max3(part_max[0], part_max[1], part_max[2]), part_max[3]);
+      step_max *= args.scale_log2;
       // The base of the exponentials follows the running maximum lazily: it moves (and O is
       // rescaled) only when the maximum has grown by more than 2^8; until then probabilities
       // are at most 2^8, which float32 sums and bfloat16 products hold without loss.
       float correction = 1.0f;
-      if (tile_max > row_max + 8.0f || row_max == -INFINITY) {
-        const float new_max = fmaxf(row_max, tile_max);
+      if (step_max > row_max + 8.0f || row_max == -INFINITY) {
+        const float new_max = fmaxf(row_max, step_max);
         const float base = new_max == -INFINITY ? 0.f : new_max;
-        correction = row_max == -INFINITY ? 0.f : fast_exp2(row_max - base);
+        // a row that has seen no key yet has O = 0 and a sum of 0: nothing to rescale
+        correction = row_max == -INFINITY ? 1.0f : fast_exp2(row_max - base);
         row_max = new_max;
       }
       const float base = row_max == -INFINITY ? 0.f : row_max;
-      float sum = 0.f;
+      const unsigned long long scale_pair = pair_of(args.scale_log2, args.scale_log2), base_pair = pair_of(-base, -base);
+      unsigned long long sum_pair[2] = {pair_of(0.f, 0.f), pair_of(0.f, 0.f)};
 #pragma unroll
-      for (int g = 0; g < 4; ++g) {
+      for (int g = 0; g < 2; ++g) {
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
-          const float x0 = fast_exp2(fmaf(__uint_as_float(v[g][j]), args.scale_log2, -base));
-          const float x1 = fast_exp2(fmaf(__uint_as_float(v[g][j + 1]), args.scale_log2, -base));
-          sum += x0 + x1;
+          float x0, x1;
+          halves_of(fma_pair(pair_of(__uint_as_float(v[g][j]), __uint_as_float(v[g][j + 1])), scale_pair, base_pair), x0, x1);
+          x0 = fast_exp2(x0);
+          x1 = fast_exp2(x1);
+          sum_pair[(j >> 1) & 1] = add_pair(sum_pair[(j >> 1) & 1], pair_of(x0, x1));
           const __nv_bfloat162 two = __floats2bfloat162_rn(x0, x1);
-          v[g >> 1][(g & 1) * 16 + j / 2] = *reinterpret_cast<const unsigned*>(&two);   // packed over the scores already used
+          v[0][g * 16 + j / 2] = *reinterpret_cast<const unsigned*>(&two);   // packed over the scores already used
         }
       }
-      row_sum = row_sum * correction + sum;
-      // P over the first 64 columns of S (keys 2 j and 2 j + 1 in column j); PV of the tile before is
-      // done (S of this tile was issued after it, and the pipe runs in order)
+      float sum_lo, sum_hi;
+      halves_of(add_pair(sum_pair[0], sum_pair[1]), sum_lo, sum_hi);
+      row_sum = row_sum * correction + (sum_lo + sum_hi);
+      // P over the first 32 columns of this S buffer (keys 2 j and 2 j + 1 in column j): the PV that
+      // read the buffer's last P is done, because these scores were issued after it
       tmem_store32(tmem_s, v[0]);
-      tmem_store32(tmem_s + 32, v[1]);
-      // value rows beyond the context: zero them (only the tile that holds the sequence's last key has any)
-      if (tile_lo + i == tile_hi && (hi + 1) % KEYS != 0) {
-        const int s = i % PSTAGES;
-        ok = mbar_wait(&sh->v_full[s], (i / PSTAGES) & 1, &sh->abort, args.status, ERR_SOFTMAX);
+      // value rows beyond the context: zero them (only the tile that holds the sequence's last key has
+      // any), at the tile's first step, before either of its PV
+      if ((h & 1) == 0 && tile_lo + (h >> 1) == tile_hi && (hi + 1) % KEYS != 0) {
+        const int s = (h >> 1) % PSTAGES;
+        ok = mbar_wait(&sh->v_full[s], ((h >> 1) / PSTAGES) & 1, &sh->abort, args.status, ERR_SOFTMAX);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         unsigned char* v_tile = v_tiles + s * KV_TILE;
@@ -405,7 +457,12 @@ portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         }
         fence_async_shared();
       }
-      if (i > 0 && __any_sync(0xffffffffu, correction != 1.0f)) {
+      if (h > 0 && __any_sync(0xffffffffu, correction != 1.0f)) {
+        // O still takes the step before: wait for its PV (phase h - 1 of pv_done), then rescale
+        ok = mbar_wait(&sh->pv_done[chain], (h - 1) & 1, &sh->abort, args.status, ERR_SOFTMAX);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        fence_after_sync();
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
           unsigned o[32];
@@ -418,9 +475,11 @@ portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       }
       tmem_wait_store();
       fence_before_sync();
-      mbar_arrive(&sh->p_full[chain]);
+      mbar_arrive(&sh->p_full[chain][h & 1]);
     }
-    if (ok && my_count > 0) ok = mbar_wait(&sh->pv_done[chain], 0, &sh->abort, args.status, ERR_SOFTMAX);
+    const int my_count = my_steps;
+    // (pv_done cannot serve here: this thread may be two of its phases behind, and a parity tells only one apart)
+    if (ok && my_steps > 0) ok = mbar_wait(&sh->pv_last[chain], 0, &sh->abort, args.status, ERR_SOFTMAX);
     ok = __all_sync(0xffffffffu, ok);
     fence_after_sync();
     if (ok && args.splits > 1) {
@@ -468,7 +527,7 @@ portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   }
   fence_before_sync();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == 3) {
     fence_after_sync();
     tmem_free(sh->tmem_base, PAIR_TMEM_COLS);
   }
