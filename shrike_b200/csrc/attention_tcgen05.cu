@@ -1,27 +1,35 @@
 // Paged causal attention for portions (q_len > 1) in bfloat16 on the fifth-generation
 // tensor cores.  One CTA owns 256 query rows of one head of one sequence, as two chains of
-// 128 rows, and walks the keys 128 at a time:
-//   S_c = Q_c K^T   tcgen05.mma, M 128 x N 128 x K head size, accumulator in tensor memory
+// 128 rows; a chain walks the keys 64 at a time:
+//   S = Q K^T       tcgen05.mma, M 128 x N 64 x K head size, into the chain's 64 score columns
 //   softmax         four warps per chain, ONE THREAD PER QUERY ROW: the row of S comes out of
 //                   tensor memory with tcgen05.ld, scale, mask, running maximum and sum in
 //                   float32; the probabilities go back INTO tensor memory as packed bfloat16
-//                   over the first 64 columns of the chain's own S (tcgen05.st)
-//   O_c += P_c V    tcgen05.mma with its A operand in tensor memory, M 128 x N head size x K 128;
-//                   O stays in tensor memory across tiles and is rescaled there when a row's
+//                   (tcgen05.st), into one of the chain's two probability buffers of 32 columns
+//   O += P V        tcgen05.mma with its A operand in tensor memory, M 128 x N head size x K 64;
+//                   O stays in tensor memory across steps and is rescaled there when a row's
 //                   maximum moved by more than 2^8
-// The tensor pipe runs its instructions in order: S of the next tile, issued after PV, cannot
-// overwrite P before PV has read it, and a softmax thread that sees S of tile i + 1 knows PV of
-// tile i is done, so O may be rescaled then without another wait.  While one chain's softmax
-// runs, the tensor pipe works for the other; both chains read the same key and value stages (two
-// each), so a tile is loaded once for 256 rows.  The later chain sees up to one key tile more than
-// the earlier one; a chain without rows (a sequence's last 128 or fewer) has no tiles.
-// Keys and values arrive by TMA, one box per page and 64-element half of the head (the block
-// table is read by the producer warp, three tiles ahead), the two query tiles by TMA once.
-// Roles: warp 0 TMA producer, warp 1 MMA issuer (one elected lane), warps 2..5 softmax and
-// epilogue of chain 0, warps 6..9 of chain 1.  tcgen05.commit arrives on mbarriers: s_full[c] after
-// S of chain c, k_free / v_free after the last chain's use of a stage, pv_done[c] after a chain's
-// last PV.  All of tensor memory (2 x (128 + D) <= 512 columns) and 96 + D KiB of shared memory:
-// one CTA per SM.
+// A chain's tensor memory is 64 (S) + 2 x 32 (P) + head size (O) columns; two chains fill the
+// 512.  The scores of step h + 1 need only the keys and the score columns, and those are free
+// as soon as the softmax threads hold step h in registers (s_read): they are computed while the
+// softmax of step h runs, so a softmax thread finds its next scores waiting.  P(h) is written to
+// the buffer P(h - 2) was in once PV(h - 2) has read it (pv_done), and O is rescaled only after
+// PV(h - 1) (the same barrier, the other buffer).
+// Both chains read the same key and value stages (two each, 128 keys a stage), so a tile is
+// loaded once for 256 rows.  The later chain sees up to one key tile more than the earlier one;
+// a chain without rows (a sequence's last 128 or fewer) has no steps.
+// Keys and values arrive by TMA, one box per page and 64-element half of the head, the two
+// query tiles by TMA once.  Handing a box to the copy engine costs the issuing warp about
+// 50 ns, and a tile of 16-token pages is 16 boxes of keys and 16 of values: warp 0 brings the
+// keys and warp 3 the values, each with the page ids of the next tiles fetched 32 at a time (a
+// lookup per tile would stall the warp for a trip to L2 in every iteration).
+// Roles: warp 0 keys (and the query tiles), warp 3 values (and the tensor-memory allocation),
+// warp 1 / warp 2 one issuing thread for chain 0 / chain 1 (a single thread for both chains was
+// the CTA's bottleneck), warps 4..7 softmax and epilogue of chain 0, warps 8..11 of chain 1.
+// tcgen05.commit arrives on mbarriers: s_full[c] after S of chain c, pv_done[c][buffer] after a
+// PV, k_free / v_free after a chain's last use of a stage (a stage is free when every chain that
+// reads it has arrived), pv_last[c] after a chain's last PV.  A wait on pv_done cannot stand in
+// for pv_last: a thread that has skipped phases cannot tell them apart by parity.
 // Mask and window as everywhere: a query at position p sees keys [max(0, p - window + 1), p].
 // Rows of a page beyond the context may hold anything (a page is reused without clearing):
 // scores are masked by selection, and the value rows beyond the context are zeroed in shared
@@ -31,9 +39,11 @@
 // idle: the keys of a query tile are then split across `splits` CTAs, each of which leaves its
 // unnormalised output rows with their (base, sum) in scratch, and a second small kernel adds the
 // splits up (combine_portions_kernel).
-// An earlier form (one query tile per CTA, 64 keys a step, probabilities through shared memory, two
-// CTAs per SM) was bound by the hand-overs between its roles; this one does twice the work per
-// hand-over: 5 to 14 % faster from 512-token portions to 8,192-token prompts.
+// Earlier forms, each slower: one query tile per CTA with probabilities through shared memory; two
+// chains with 128-key steps whose probabilities lay over the scores (the next scores could only be
+// issued after PV, so the softmax threads waited for the tensor pipe and it for them); one chain of
+// 128 rows with two threads per row (twice the key traffic and CTAs, and the two warps of a
+// sub-partition in step with each other).
 // Every wait is bounded (status word, CTA-wide abort flag); no TMA load uses multicast.
 // Tensor memory is allocated BEFORE dependents are allowed to start, so that a dependent
 // kernel that also wants tensor memory cannot starve a CTA of this one it is waiting for.
@@ -152,12 +162,14 @@ constexpr int PSTAGES = 2;
 constexpr int PTHREADS = 128 + 2 * 128;   // producer, two issuers, tensor-memory owner; four softmax warps per chain
 constexpr int KV_TILE_HALF = KEYS * 128;      // bytes of one 64-element-wide sub-tile of a key (or value) tile
 constexpr int KV_TILE = HALVES * KV_TILE_HALF;
-constexpr int HALF_KEYS = KEYS / 2;            // keys per softmax step: S has two buffers of this many columns
-constexpr unsigned CHAIN_COLS = 256;          // S buffers at +0 and +64 (P over a buffer's first 32 columns), O at +128
+constexpr int HALF_KEYS = KEYS / 2;           // keys per softmax step
+constexpr unsigned CHAIN_COLS = 256;          // a chain's tensor memory: scores of one step (64 columns),
+constexpr unsigned P_COL = 64;                // two probability buffers of 32 columns (bfloat16 pairs),
+constexpr unsigned O_COL = 128;               // the output accumulator (head size columns)
 constexpr unsigned PAIR_TMEM_COLS = 512;
 
 struct PairShared {
-  unsigned long long q_full, s_full[2][2], p_full[2][2], pv_done[2], pv_last[2], stagger;   // [chain][S buffer]
+  unsigned long long q_full, s_full[2], s_read[2], p_full[2][2], pv_done[2][2], pv_last[2];   // [chain]([P buffer])
   unsigned long long k_full[PSTAGES], k_free[PSTAGES], v_full[PSTAGES], v_free[PSTAGES];
   unsigned tmem_base;
   volatile int abort;
@@ -171,6 +183,28 @@ __device__ __forceinline__ void umma_a_in_tmem(unsigned tmem_d, unsigned tmem_a,
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
       ::"r"(tmem_d), "r"(tmem_a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// Rarely run parts of the softmax loop, kept out of line: the loop's body should stay small (its
+// instructions are fetched again in every step).
+__device__ __noinline__ void rescale_output_row(unsigned tmem_o, float correction) {
+#pragma unroll
+  for (int c = 0; c < D / 32; ++c) {
+    unsigned o[32];
+    tmem_load32(tmem_o + c * 32, o);
+    tmem_wait_load();
+#pragma unroll
+    for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * correction);
+    tmem_store32(tmem_o + c * 32, o);
+  }
+}
+// Zeroes the rows first_bad .. 127 of a value tile (128 threads share the work).
+__device__ __noinline__ void zero_value_rows(unsigned char* v_tile, int first_bad, int row) {
+  for (int idx = row; idx < (KEYS - first_bad) * HALVES * 8; idx += 128) {
+    const int r = first_bad + idx / (HALVES * 8), rest = idx % (HALVES * 8);
+    *reinterpret_cast<uint4*>(v_tile + (rest / 8) * KV_TILE_HALF + r * 128 + (rest % 8) * 16) = make_uint4(0u, 0u, 0u, 0u);
+  }
+  fence_async_shared();
 }
 
 __global__ void __launch_bounds__(PTHREADS, 1)
@@ -219,11 +253,12 @@ portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   if (threadIdx.x == 0) {
     mbar_init(&sh->q_full, 1);
     for (int c = 0; c < 2; ++c) {
+      mbar_init(&sh->s_full[c], 1);
+      mbar_init(&sh->s_read[c], 128);
       for (int b = 0; b < 2; ++b) {
-        mbar_init(&sh->s_full[c][b], 1);
         mbar_init(&sh->p_full[c][b], 128);
+        mbar_init(&sh->pv_done[c][b], 1);
       }
-      mbar_init(&sh->pv_done[c], 1);
       mbar_init(&sh->pv_last[c], 1);
     }
     for (int s = 0; s < PSTAGES; ++s) {
@@ -232,7 +267,6 @@ portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       mbar_init(&sh->v_full[s], 1);
       mbar_init(&sh->v_free[s], users > 0 ? users : 1u);
     }
-    mbar_init(&sh->stagger, 1);
     sh->abort = 0;
     mbar_init_fence();
   }
@@ -308,14 +342,16 @@ portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       for (unsigned tries = 0; tries < WAIT_LIMIT && !landed; ++tries) landed = mbar_try_wait(&sh->q_full, 0);
     }
   } else if (warp == 1 || warp == 2) {
-    // One issuing thread per chain: each waits for its own chain's probabilities only, and the two
-    // share the work of forming descriptors and issuing (a single thread was the CTA's bottleneck).
+    // One issuing thread per chain.  The scores of step h + 1 need nothing but the keys and the
+    // chain's score columns, which are free as soon as the softmax threads hold step h in registers
+    // (s_read); the probabilities have columns of their own, two buffers of them.  So the thread
+    // follows the chain's events in the order they come: s_read(h) -> S(h + 1), p_full(h) -> PV(h).
     const int c = warp - 1;
     const int steps = c == 0 ? steps_0 : steps_1;
     if (lane == 0 && steps > 0) {
       const unsigned idesc_s = instruction_descriptor(BM, HALF_KEYS, false);
       const unsigned idesc_o = instruction_descriptor(BM, D, true);
-      const unsigned tmem_chain = sh->tmem_base + c * CHAIN_COLS, tmem_o = tmem_chain + KEYS;
+      const unsigned tmem_chain = sh->tmem_base + c * CHAIN_COLS, tmem_o = tmem_chain + O_COL;
       // operand descriptors are formed once (a descriptor's low bits are the address in 16-byte
       // units, so a tile further on is an addition), not per instruction
       const unsigned long long q_base = smem_descriptor(smem_u32(q_tiles + c * Q_BYTES));
@@ -323,32 +359,32 @@ portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       const unsigned long long v_desc0 = smem_descriptor(smem_u32(v_tiles), KV_TILE_HALF, 1024);
       bool ok = mbar_wait(&sh->q_full, 0, &sh->abort, args.status, ERR_MMA);
       int keys_ready = -1, values_ready = -1;   // the newest tile whose keys (values) are known to have landed
-      // S for step h (keys 64 h ... of this CTA's share) into the chain's buffer h & 1; the chain's last
-      // use of a stage hands it back (the stage is free when every chain that uses it has)
+      // S for step h (keys 64 h ... of this CTA's share); the chain's last use of a stage hands it back
+      // (the stage is free when every chain that uses it has)
       auto issue_scores = [&](int h) {
         const int i = h >> 1, st = i % PSTAGES;
         if (keys_ready < i) {
           ok = mbar_wait(&sh->k_full[st], (i / PSTAGES) & 1, &sh->abort, args.status, ERR_MMA);
           if (!ok) return;
           keys_ready = i;
-          fence_after_sync();
         }
+        fence_after_sync();
         const unsigned long long k_base = k_desc0 + static_cast<unsigned>((st * KV_TILE + (h & 1) * HALF_KEYS * 128) >> 4);
-        const unsigned tmem_s = tmem_chain + (h & 1) * HALF_KEYS;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          umma(tmem_s, q_base + (((kk / 4) * Q_HALF + (kk % 4) * 32) >> 4), k_base + (((kk / 4) * KV_TILE_HALF + (kk % 4) * 32) >> 4), idesc_s,
+          umma(tmem_chain, q_base + (((kk / 4) * Q_HALF + (kk % 4) * 32) >> 4), k_base + (((kk / 4) * KV_TILE_HALF + (kk % 4) * 32) >> 4), idesc_s,
                kk > 0 ? 1u : 0u);
-        umma_commit(&sh->s_full[c][h & 1]);
+        umma_commit(&sh->s_full[c]);
         if ((h & 1) || h + 1 == steps) umma_commit(&sh->k_free[st]);
       };
-      // The two chains share the tensor pipe; started together they stay in step, issue their
-      // instructions in the same bursts and idle in the same gaps.  The later chain starts when the
-      // earlier one has its first probabilities: half a period behind.
-      if (ok && c == 1 && steps_0 > 0) ok = mbar_wait(&sh->stagger, 0, &sh->abort, args.status, ERR_MMA);
-      if (ok) fence_after_sync();
-      for (int h = 0; h < 2 && h < steps && ok; ++h) issue_scores(h);
+      if (ok) issue_scores(0);
       for (int h = 0; h < steps && ok; ++h) {
+        if (h + 1 < steps) {
+          ok = mbar_wait(&sh->s_read[c], h & 1, &sh->abort, args.status, ERR_MMA);
+          if (!ok) break;
+          issue_scores(h + 1);
+          if (!ok) break;
+        }
         const int i = h >> 1, st = i % PSTAGES;
         if (values_ready < i) {
           ok = mbar_wait(&sh->v_full[st], (i / PSTAGES) & 1, &sh->abort, args.status, ERR_MMA);
@@ -356,17 +392,15 @@ portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         }
         if (ok) ok = mbar_wait(&sh->p_full[c][h & 1], (h >> 1) & 1, &sh->abort, args.status, ERR_MMA);
         if (!ok) break;
-        if (c == 0 && h == 0) mbar_arrive(&sh->stagger);
         fence_after_sync();
         const unsigned long long v_base = v_desc0 + static_cast<unsigned>((st * KV_TILE + (h & 1) * HALF_KEYS * 128) >> 4);
-        const unsigned tmem_p = tmem_chain + (h & 1) * HALF_KEYS;
+        const unsigned tmem_p = tmem_chain + P_COL + (h & 1) * 32;
 #pragma unroll
-        for (int kk = 0; kk < HALF_KEYS / 16; ++kk)   // 16 keys a step: 8 packed columns of P, 16 rows of V
+        for (int kk = 0; kk < HALF_KEYS / 16; ++kk)   // 16 keys an instruction: 8 packed columns of P, 16 rows of V
           umma_a_in_tmem(tmem_o, tmem_p + kk * 8, v_base + ((kk * 16 * 128) >> 4), idesc_o, (h > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(&sh->pv_done[c]);          // phase h of the chain: O holds the keys up to step h
+        umma_commit(&sh->pv_done[c][h & 1]);
         if (h + 1 == steps) umma_commit(&sh->pv_last[c]);
         if ((h & 1) || h + 1 == steps) umma_commit(&sh->v_free[st]);
-        if (h + 2 < steps) issue_scores(h + 2);   // into the buffer whose P was just read (the pipe runs a thread's instructions in order)
       }
     }
   } else if (warp >= 4) {
@@ -377,19 +411,20 @@ portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const int last = t < q_len ? pos0 + t : -1;
     const int first = args.window > 0 ? max(0, last - args.window + 1) : 0;
     const unsigned lane_base = static_cast<unsigned>(quarter * 32) << 16;
-    const unsigned tmem_chain = sh->tmem_base + chain * CHAIN_COLS + lane_base, tmem_o = tmem_chain + KEYS;
+    const unsigned tmem_chain = sh->tmem_base + chain * CHAIN_COLS + lane_base, tmem_o = tmem_chain + O_COL;
     float row_max = -INFINITY, row_sum = 0.f;
     bool ok = true;
     for (int h = 0; h < my_steps && ok; ++h) {
-      const unsigned tmem_s = tmem_chain + (h & 1) * HALF_KEYS;
-      ok = mbar_wait(&sh->s_full[chain][h & 1], (h >> 1) & 1, &sh->abort, args.status, ERR_SOFTMAX);
+      ok = mbar_wait(&sh->s_full[chain], h & 1, &sh->abort, args.status, ERR_SOFTMAX);
       ok = __all_sync(0xffffffffu, ok);   // the warp stays together: the tensor-memory accesses below are warp-wide
       if (!ok) break;
       fence_after_sync();
       unsigned v[2][32];
-      tmem_load32(tmem_s, v[0]);
-      tmem_load32(tmem_s + 32, v[1]);
+      tmem_load32(tmem_chain, v[0]);
+      tmem_load32(tmem_chain + 32, v[1]);
       tmem_wait_load();
+      fence_before_sync();
+      mbar_arrive(&sh->s_read[chain]);    // the scores are in registers: their columns may take the next step
       const int key_base = tile_lo * KEYS + h * HALF_KEYS;
       if (key_base < first || key_base + HALF_KEYS - 1 > last) {   // only steps at the edge of the row's range pay for masking
 #pragma unroll
@@ -439,9 +474,14 @@ portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       float sum_lo, sum_hi;
       halves_of(add_pair(sum_pair[0], sum_pair[1]), sum_lo, sum_hi);
       row_sum = row_sum * correction + (sum_lo + sum_hi);
-      // P over the first 32 columns of this S buffer (keys 2 j and 2 j + 1 in column j): the PV that
-      // read the buffer's last P is done, because these scores were issued after it
-      tmem_store32(tmem_s, v[0]);
+      // P(h) goes where P(h - 2) was: the PV of step h - 2 must have read it (it has, long ago)
+      if (h >= 2) {
+        ok = mbar_wait(&sh->pv_done[chain][h & 1], ((h >> 1) & 1) ^ 1, &sh->abort, args.status, ERR_SOFTMAX);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        fence_after_sync();
+      }
+      tmem_store32(tmem_chain + P_COL + (h & 1) * 32, v[0]);   // keys 2 j and 2 j + 1 of the step in column j
       // value rows beyond the context: zero them (only the tile that holds the sequence's last key has
       // any), at the tile's first step, before either of its PV
       if ((h & 1) == 0 && tile_lo + (h >> 1) == tile_hi && (hi + 1) % KEYS != 0) {
@@ -449,36 +489,21 @@ portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         ok = mbar_wait(&sh->v_full[s], ((h >> 1) / PSTAGES) & 1, &sh->abort, args.status, ERR_SOFTMAX);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        unsigned char* v_tile = v_tiles + s * KV_TILE;
-        const int first_bad = hi + 1 - key_base;
-        for (int idx = row; idx < (KEYS - first_bad) * HALVES * 8; idx += 128) {
-          const int r = first_bad + idx / (HALVES * 8), rest = idx % (HALVES * 8);
-          *reinterpret_cast<uint4*>(v_tile + (rest / 8) * KV_TILE_HALF + r * 128 + (rest % 8) * 16) = make_uint4(0u, 0u, 0u, 0u);
-        }
-        fence_async_shared();
+        zero_value_rows(v_tiles + s * KV_TILE, hi + 1 - key_base, row);
       }
       if (h > 0 && __any_sync(0xffffffffu, correction != 1.0f)) {
-        // O still takes the step before: wait for its PV (phase h - 1 of pv_done), then rescale
-        ok = mbar_wait(&sh->pv_done[chain], (h - 1) & 1, &sh->abort, args.status, ERR_SOFTMAX);
+        // O still takes the step before: wait for its PV, then rescale
+        ok = mbar_wait(&sh->pv_done[chain][(h - 1) & 1], ((h - 1) >> 1) & 1, &sh->abort, args.status, ERR_SOFTMAX);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         fence_after_sync();
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          unsigned o[32];
-          tmem_load32(tmem_o + c * 32, o);
-          tmem_wait_load();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * correction);
-          tmem_store32(tmem_o + c * 32, o);
-        }
+        rescale_output_row(tmem_o, correction);
       }
       tmem_wait_store();
       fence_before_sync();
       mbar_arrive(&sh->p_full[chain][h & 1]);
     }
     const int my_count = my_steps;
-    // (pv_done cannot serve here: this thread may be two of its phases behind, and a parity tells only one apart)
     if (ok && my_steps > 0) ok = mbar_wait(&sh->pv_last[chain], 0, &sh->abort, args.status, ERR_SOFTMAX);
     ok = __all_sync(0xffffffffu, ok);
     fence_after_sync();

@@ -39,9 +39,20 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned 
       : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(WAIT_HINT_NS) : "memory");
   return ok != 0;
 }
+// One look at the barrier without suspending: about 15 clocks, against 50 for a try_wait with a time hint.
+__device__ __forceinline__ bool mbar_test_wait(unsigned long long* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
 // Waits for the phase with the given parity.  Returns false when the wait ran out (the
 // caller's code `who` goes to *status, *abort is raised) or when another role raised *abort.
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* abort, int* status, int who) {
+  if (mbar_test_wait(bar, parity)) return true;   // the usual case in a pipeline that runs ahead
   for (unsigned tries = 0; tries < WAIT_LIMIT; ++tries) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort) return false;
