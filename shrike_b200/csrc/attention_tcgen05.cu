@@ -612,10 +612,14 @@ SHRIKE_API int shrike_attention_tc_portions_rows() { return tcattn::pair::ROWS; 
 
 // How many CTAs should share the keys of a query tile, for a batch of `num_tokens` new tokens whose
 // portions make `portion_tiles` query tiles (0: not known; the most they can make is assumed) and whose
-// block tables are `max_blocks` pages wide.  The GPU holds `capacity` CTAs at once; with s splits the
-// launch takes ceil(heads * tiles * s / capacity) rounds of ceil(key tiles / s) steps each, plus a fixed
-// cost per round and, for s > 1, the combine: the s that makes this smallest, with at least two key
-// steps per split and at most 16.  The scratch for s > 1 is s * num_tokens * num_heads * (D + 2) floats.
+// block tables are `max_blocks` pages wide.  The GPU holds one CTA per SM.  Splitting pays only while
+// every CTA still starts at once (measured: 512 new tokens of 28 heads over 7,680 cached take 156 us
+// unsplit, 97 with two splits, which make 112 CTAs, and 124 with three, which need a second round; a
+// whole prompt, whose query tiles outnumber the SMs, is best left alone at every length).  Among the
+// split counts that keep the launch to one round, with at least two key steps per split and at most
+// 16, the one with the fewest steps per CTA, counting three steps' worth for a CTA's start and three
+// more for the second kernel that adds the splits up.  The scratch for s > 1 is
+// s * num_tokens * num_heads * (D + 2) floats.
 SHRIKE_API int shrike_attention_tc_portions_splits(int num_tokens, int num_heads, int max_blocks, int page_size, int portion_tiles) {
   const int rows = shrike_attention_tc_portions_rows();
   const int most = (num_tokens + rows - 1) / rows + 1;
@@ -626,9 +630,8 @@ SHRIKE_API int shrike_attention_tc_portions_splits(int num_tokens, int num_heads
   const long long capacity = shrike_device().sm_count;   // one CTA per SM
   int best = 1;
   long long best_cost = -1;
-  for (int s = 1; s <= 16 && (s == 1 || key_steps / s >= 2); ++s) {
-    const long long rounds = (ctas * s + capacity - 1) / capacity;
-    const long long cost = rounds * ((key_steps + s - 1) / s + 2) + (s > 1 ? 3 : 0);
+  for (int s = 1; s <= 16 && (s == 1 || (key_steps / s >= 2 && ctas * s <= capacity)); ++s) {
+    const long long cost = (key_steps + s - 1) / s + 3 + (s > 1 ? 3 : 0);
     if (best_cost < 0 || cost < best_cost) {
       best_cost = cost;
       best = s;

@@ -449,9 +449,9 @@ def test_portions_attention_at_served_lengths(name, heads, kv_heads, dim, page, 
 
 def test_a_portion_beside_decoding_requests_is_split_over_the_gpu():
     """The rule: the query tiles of 492 new tokens of 12 heads over block tables of 2,048 keys would
-    occupy a fraction of the GPU; their keys are shared out so that the launch takes the fewest
-    rounds of key steps, never fewer than two steps a split.  A whole 2,048-token prompt of 28 heads
-    fills the GPU by itself: no split."""
+    occupy a fraction of the GPU; their keys are shared out as far as every CTA still starts at once
+    (one per SM), never fewer than two key steps a split.  A whole prompt, whose query tiles of 28
+    heads outnumber the SMs, is not split at any length."""
     ops = cuda_ops(torch.bfloat16)
     lib = ops._attention_lib(128)
     sms = torch.cuda.get_device_properties(0).multi_processor_count
@@ -460,8 +460,9 @@ def test_a_portion_beside_decoding_requests_is_split_over_the_gpu():
     tiles = -(-492 // rows)
     splits = lib.shrike_attention_tc_portions_splits(512, 12, 128, 16, tiles)
     assert 2 <= splits <= 16 and (2048 // keys) // splits >= 2
-    assert 12 * tiles * splits <= 2 * sms                                        # at most two rounds, one CTA per SM
-    assert lib.shrike_attention_tc_portions_splits(2048, 28, 128, 16, 2048 // rows) == 1
+    assert 12 * tiles * splits <= sms                                            # one round, one CTA per SM
+    for prompt in (2048, 4096, 8192):
+        assert lib.shrike_attention_tc_portions_splits(prompt, 28, prompt // 16, 16, prompt // rows) == 1
     assert lib.shrike_attention_tc_portions_splits(64, 2, 8, 16, 1) == 1         # one key step in all
     assert lib.shrike_attention_tc_portions_splits(64, 2, 4096, 16, 1) == 16     # never more than 16
     assert lib.shrike_attention_tc_portions_scratch_floats(512, 12, 4) == 4 * 512 * 12 * 130
