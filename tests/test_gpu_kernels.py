@@ -427,7 +427,7 @@ SERVED = {
 
 @pytest.mark.parametrize("name", list(SERVED))
 @pytest.mark.parametrize("splits", [0, 1, 3, 7])
-@pytest.mark.parametrize("heads,kv_heads,dim,page", [(28, 4, 128, 16), (14, 2, 64, 16), (12, 2, 128, 32), (5, 1, 64, 8)])
+@pytest.mark.parametrize("heads,kv_heads,dim,page", [(28, 4, 128, 16), (14, 2, 64, 16), (12, 2, 128, 32), (5, 1, 64, 8), (6, 2, 128, 64)])
 def test_portions_attention_at_served_lengths(name, heads, kv_heads, dim, page, splits):
     """The tensor-core kernel for portions over walks of up to 64 key tiles (its rescaling of the
     running sum, its look-ahead in the block table and its first and last tile only matter on
