@@ -285,8 +285,46 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
   }
 }
 
+// Rows whose gate and up columns alternate in runs of 16 bfloat16 (32 bytes each): a thread takes a
+// whole run pair, 64 contiguous bytes in and 32 out, so a warp reads 2 KiB in one piece.  (With a
+// thread per 16-byte group the gate loads of a warp touch every other 32 bytes, the up loads the
+// rest: the same bytes, twice the lines per instruction.)
+__global__ void silu_mul_runs16_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, int inter, int rows) {
+  let_dependents_start();
+  wait_for_previous();
+  const int runs_per_row = inter / 16;
+  const int stride = gridDim.x * blockDim.x;
+  for (int row = blockIdx.y; row < rows; row += gridDim.y) {
+    const uint4* in_row = reinterpret_cast<const uint4*>(gate_up + static_cast<size_t>(row) * 2 * inter);
+    uint4* out_row = reinterpret_cast<uint4*>(out + static_cast<size_t>(row) * inter);
+    for (int run = blockIdx.x * blockDim.x + threadIdx.x; run < runs_per_row; run += stride) {
+      uint4 in[4];   // gate 0..7, gate 8..15, up 0..7, up 8..15
+#pragma unroll
+      for (int k = 0; k < 4; ++k) in[k] = in_row[run * 4 + k];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(&in[half]);
+        const __nv_bfloat16* u = reinterpret_cast<const __nv_bfloat16*>(&in[2 + half]);
+        uint4 packed;
+        __nv_bfloat16* r = reinterpret_cast<__nv_bfloat16*>(&packed);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) r[j] = from_float<__nv_bfloat16>(silu_times<__nv_bfloat16>(to_float(g[j]), to_float(u[j])));
+        out_row[run * 2 + half] = packed;
+      }
+    }
+  }
+}
+
 template <typename T>
 static void launch_silu_mul(const void* gate_up, void* out, int n, int inter, int block, cudaStream_t stream) {
+  if (sizeof(T) == 2 && block == 16 && inter % 16 == 0 &&
+      (reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) % 16 == 0) {
+    const int threads = 256, runs_per_row = inter / 16;
+    const dim3 grid(max(1, min(64, (runs_per_row + threads - 1) / threads)), max(1, min(n, 65535)));
+    launch_dependent(silu_mul_runs16_kernel, grid, threads, 0, stream, static_cast<const __nv_bfloat16*>(gate_up),
+                     static_cast<__nv_bfloat16*>(out), inter, n);
+    return;
+  }
   constexpr int WIDE = 16 / sizeof(T);
   const bool vec = inter % WIDE == 0 && block % WIDE == 0 &&
                    (reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) % 16 == 0;
