@@ -48,6 +48,8 @@ def add_engine_options(parser: argparse.ArgumentParser) -> None:
     parser.add_argument("--gpu-mem-util", type=float, default=0.85)
     parser.add_argument("--max-tokens-per-step", type=int, default=512)
     parser.add_argument("--max-running", type=int, default=256)
+    parser.add_argument("--warm-up", action="store_true",
+                        help="run a throw-away step per usual token count before the first request (LLMEngine.warm_up)")
 
 
 def open_engine(args):
@@ -60,9 +62,13 @@ def open_engine(args):
                    max_tokens_per_step=args.max_tokens_per_step, max_running=args.max_running,
                    num_blocks=args.num_blocks, dtype=args.dtype, seed=args.seed)
     if args.random is not None:
-        return llm_engine.LLMEngine.from_random(args.random, **options), f"random weights, shape {args.random}"
-    model = args.model or DEFAULT_MODEL_DIR
-    return llm_engine.LLMEngine(model, **options), model
+        engine, name = llm_engine.LLMEngine.from_random(args.random, **options), f"random weights, shape {args.random}"
+    else:
+        name = args.model or DEFAULT_MODEL_DIR
+        engine = llm_engine.LLMEngine(name, **options)
+    if getattr(args, "warm_up", False):
+        engine.warm_up()
+    return engine, name
 
 
 def parse_args(argv=None) -> argparse.Namespace:

@@ -126,6 +126,33 @@ class LLMEngine:
         self.stats = EngineStats()
         self.scheduler.num_preemptions = 0
 
+    def warm_up(self, token_counts=(1, 16, 64, 128, 256, 512)) -> float:
+        """Runs one throw-away step per token count (one request fed that many tokens at once), so that
+        what happens once per kernel and per product shape (loading a kernel's code, the matrix library's
+        choice of a product kernel for a token count above 64: 15 to 70 ms a shape) does not fall into
+        the first real requests.  Counts above the step's token budget or the pool's size are left out.
+        Only with no request in the engine; the pools and the counters are as before afterwards.
+        Returns the seconds it took.  Not in the reference; nothing calls it unless asked to."""
+        if self.requests or self._flight is not None:
+            raise RuntimeError("warm_up() wants an engine without requests")
+        began = time.perf_counter()
+        cache_manager = self.runner.cache
+        limit = min(self.scheduler.max_tokens_per_step, self.config.max_position_embeddings)
+        if self.block_manager.portion_limit() is not None:
+            limit = min(limit, self.block_manager.portion_limit())
+        for count in sorted({int(c) for c in token_counts if 0 < int(c) <= limit}):
+            if any(w > have for w, have in zip(self.block_manager.worst_case_pages(count, count), self.block_manager.num_pages)):
+                continue
+            cache = cache_manager.open()
+            try:
+                cache_manager.append(cache, 0, count)
+                self.runner.step([StepEntry(cache, [0] * count, 0, [count - 1], (0.0, 1.0, 0))], sample=True)
+            finally:
+                cache_manager.free(cache)
+        torch.cuda.synchronize(self.device)
+        self.ops.check_status()
+        return time.perf_counter() - began
+
     # ---- requests -------------------------------------------------------------
     def _tokenize(self, prompt: str, chat: bool) -> list[int]:
         if self.tokenizer is None:

@@ -299,3 +299,24 @@ def test_layers_issued_by_one_native_call_equal_the_part_by_part_path(tmp_path, 
             assert torch.equal(a, b), f"step {step}: the two ways of issuing differ"
         else:
             assert (a - b).abs().max() <= 2e-2 * max(1.0, float(b.abs().max())), f"step {step}"
+
+
+@pytest.mark.parametrize("key", ["A", "C"])
+def test_warm_up_leaves_the_engine_as_it_was(tmp_path, key):
+    """warm_up() runs throw-away steps (those counts that the step's budget, the window's pool and the
+    pool's size allow), gives every page and slot back, counts nothing, and the tokens generated after
+    it are those of an engine that never warmed up."""
+    folder = make_model_folder(tmp_path, key)
+    prompts = [random_tokens(TINY[key]["vocab_size"], n, 70 + n) for n in (7, 45)]
+    params = SamplingParams(max_new_tokens=6, ignore_eos=True)
+    plain = LLMEngine(str(folder), block_size=PAGE_SIZES[key], num_blocks=24, dtype="bfloat16")
+    want = plain.generate(prompts, params)
+    warmed = LLMEngine(str(folder), block_size=PAGE_SIZES[key], num_blocks=24, max_tokens_per_step=100, dtype="bfloat16")
+    launches = warmed.ops.launches
+    seconds = warmed.warm_up(token_counts=(1, 16, 64, 100, 4096))
+    assert seconds > 0 and warmed.ops.launches > launches
+    assert warmed.block_manager.whole() and warmed.stats.steps == 0 and warmed.stats.tokens_generated == 0
+    assert warmed.generate(prompts, params) == want
+    warmed.add_request(prompts[0], params)
+    with pytest.raises(RuntimeError):
+        warmed.warm_up()
