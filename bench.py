@@ -524,6 +524,17 @@ def run_case(args) -> dict:
     tokens = args.batch
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     times = []
+    filler = []
+
+    def keep_busy():
+        """The device is kept busy (about 0.2 ms) while the host prepares the timed launch (plan, tensor
+        maps: about 25 us), so that the events bracket the kernel and not the host's work before it."""
+        if hasattr(torch.cuda, "_sleep"):
+            torch.cuda._sleep(400_000)
+        else:
+            if not filler:
+                filler.append(torch.empty(1 << 30, dtype=torch.uint8, device=dev))
+            filler[0].zero_()
     if args.case.startswith("gemm_"):
         shapes = {"gemm_gate_up": (2 * inter, h), "gemm_down": (h, inter), "gemm_qkv": ((heads + 2 * kv) * d, h)}
         n, k = shapes[args.case]
@@ -531,7 +542,7 @@ def run_case(args) -> dict:
         x = torch.randn(tokens, k, device=dev, dtype=torch.bfloat16)
         out = torch.empty(tokens, n, device=dev, dtype=torch.bfloat16 if args.case == "gemm_gate_up" else torch.float32)
         for i in range(6):
-            torch.cuda._sleep(400_000)   # the device stays busy while the host prepares the launch (see the attention cases)
+            keep_busy()
             start.record()
             ops.linear(x, weights[i % 3], out, allow_partials=args.case != "gemm_gate_up")
             stop.record()
@@ -556,9 +567,7 @@ def run_case(args) -> dict:
         seq_of = torch.arange(seqs, dtype=torch.int32, device=dev).repeat_interleave(q_len)
         out = torch.empty_like(q)
         for _ in range(6):
-            # the device is kept busy while the host prepares the launch (plan, tensor maps), so that the
-            # events bracket the kernel and not the host's work before it
-            torch.cuda._sleep(400_000)
+            keep_busy()
             start.record()
             ops.paged_attention(q, keys, values, table, q_start, ctx, seq_of, heads, kv, d, d ** -0.5, None, out,
                                 max_q_len=q_len, min_q_len=q_len, q_lens=[q_len] * seqs)
