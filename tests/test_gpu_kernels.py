@@ -651,3 +651,35 @@ def test_sampling_mixes_greedy_and_sampled_rows():
     ops.sample(logits, temp, torch.ones(4, device=DEV), torch.tensor([1, 2, 3, 4], dtype=torch.int64, device=DEV), out)
     assert out[0].item() == int(logits[0].argmax()) and out[2].item() == int(logits[2].argmax())
     assert 0 <= out[1].item() < 1000 and 0 <= out[3].item() < 1000
+
+
+@pytest.mark.parametrize("new,ctx_len,window", [(512, 30000, None), (300, 20000, 4096), (2048, 16384, None)])
+def test_portions_attention_over_very_long_walks(new, ctx_len, window):
+    """Hundreds of key steps per CTA (every barrier of the tensor-core kernel changes its parity
+    hundreds of times, the page ids come in dozens of chunks, the rule splits the keys where query
+    tiles are few) against the float32 kernel on the same bfloat16 inputs; that kernel is itself
+    checked against float64 at the smaller sizes above."""
+    heads, kv_heads, dim, page = 28, 4, 128, 16
+    g = torch.Generator(device=DEV).manual_seed(new)
+    blocks = -(-ctx_len // page)
+    pages = blocks + 8
+    order = torch.randperm(pages, device=DEV, generator=g)[:blocks].to(torch.int32)
+    keys = torch.randn(pages, page, kv_heads, dim, device=DEV, dtype=torch.bfloat16, generator=g)
+    values = torch.randn(pages, page, kv_heads, dim, device=DEV, dtype=torch.bfloat16, generator=g)
+    q = torch.randn(new, heads * dim, device=DEV, dtype=torch.bfloat16, generator=g)
+    table = torch.full((1, blocks + 3), -1, dtype=torch.int32, device=DEV)
+    table[0, :blocks] = order
+    q_start = torch.tensor([0, new], dtype=torch.int32, device=DEV)
+    ctx = torch.tensor([ctx_len], dtype=torch.int32, device=DEV)
+    seq_of = torch.zeros(new, dtype=torch.int32, device=DEV)
+    ops = cuda_ops(torch.bfloat16)
+    assert ops._attention_lib(dim).shrike_attention_tc_available()
+    got = torch.empty_like(q)
+    ops.paged_attention(q, keys, values, table, q_start, ctx, seq_of, heads, kv_heads, dim, dim ** -0.5, window, got,
+                        max_q_len=new, min_q_len=new, q_lens=[new])
+    ops.check_status()
+    exact = cuda_ops(torch.float32)
+    want = torch.empty(new, heads * dim, device=DEV)
+    exact.paged_attention(q.float(), keys.float(), values.float(), table, q_start, ctx, seq_of, heads, kv_heads, dim,
+                          dim ** -0.5, window, want, max_q_len=new, min_q_len=new)
+    close(got, want, 2e-3, 0, f"{new} new tokens over {ctx_len}")
