@@ -169,7 +169,7 @@ constexpr unsigned O_COL = 128;               // the output accumulator (head si
 constexpr unsigned PAIR_TMEM_COLS = 512;
 
 struct PairShared {
-  unsigned long long q_full, s_full[2], s_read[2], p_full[2][2], pv_done[2][2], pv_last[2];   // [chain]([P buffer])
+  unsigned long long q_full, s_full[2], s_read[2], p_full[2][2], pv_done[2][2], pv_last[2], stagger;   // [chain]([P buffer])
   unsigned long long k_full[PSTAGES], k_free[PSTAGES], v_full[PSTAGES], v_free[PSTAGES];
   unsigned tmem_base;
   volatile int abort;
@@ -267,6 +267,7 @@ portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       mbar_init(&sh->v_full[s], 1);
       mbar_init(&sh->v_free[s], users > 0 ? users : 1u);
     }
+    mbar_init(&sh->stagger, 1);
     sh->abort = 0;
     mbar_init_fence();
   }
@@ -377,6 +378,10 @@ portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         umma_commit(&sh->s_full[c]);
         if ((h & 1) || h + 1 == steps) umma_commit(&sh->k_free[st]);
       };
+      // The two chains' softmax warps share the sub-partitions; started together they stay in step and
+      // do their arithmetic at the same time and their waiting at the same time.  The later chain
+      // starts when the earlier one has written its first probabilities: most of a step behind.
+      if (ok && c == 1 && steps_0 > 0) ok = mbar_wait(&sh->stagger, 0, &sh->abort, args.status, ERR_MMA);
       if (ok) issue_scores(0);
       for (int h = 0; h < steps && ok; ++h) {
         if (h + 1 < steps) {
@@ -392,6 +397,7 @@ portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         }
         if (ok) ok = mbar_wait(&sh->p_full[c][h & 1], (h >> 1) & 1, &sh->abort, args.status, ERR_MMA);
         if (!ok) break;
+        if (c == 0 && h == 0) mbar_arrive(&sh->stagger);   // on every path: the other issuer waits for it
         fence_after_sync();
         const unsigned long long v_base = v_desc0 + static_cast<unsigned>((st * KV_TILE + (h & 1) * HALF_KEYS * 128) >> 4);
         const unsigned tmem_p = tmem_chain + P_COL + (h & 1) * 32;
